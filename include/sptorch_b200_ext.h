@@ -1,0 +1,143 @@
+/*
+ * sptorch_b200_ext.h -- additive entry points of libsptorch_b200.so.
+ *
+ * The 20 symbols of sptorch_b200_hal.h are what sptorch's loader binds today.  They cover
+ * only 11 of the kernels that the forward pass of nn::GPT needs, and every one of them is
+ * reached through host slices.  The functions below make a device-resident forward possible
+ * behind the same library: the remaining KernelProvider kernels (crates/hal/src/lib.rs:374-458),
+ * the nn-level ops that the reference computes inline on the host (LayerNorm, Linear, causal
+ * attention, the embedding sum) and the whole GPT forward.  Same conventions as the base ABI:
+ * int 0 = success, device handles are device addresses, sizes count elements, all work is
+ * enqueued on the library's stream, no function allocates behind the caller's back unless it
+ * says so.
+ */
+#ifndef SPTORCH_B200_EXT_H
+#define SPTORCH_B200_EXT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* storage types of activations / weights */
+#define SPT_F32  0
+#define SPT_BF16 1
+
+/* arithmetic of a contraction (accumulation is always f32) */
+#define SPT_MM_TF32 0   /* f32 operands, tensor cores read them as TF32          */
+#define SPT_MM_BF16 1   /* bf16 operands                                          */
+#define SPT_MM_F32  2   /* f32 operands, f32 FMA on the CUDA cores (exact-order)  */
+
+/* epilogue of sptorch_ext_linear: out = act(alpha * x W^T + bias) + residual */
+#define SPT_EPI_NONE 0
+#define SPT_EPI_GELU 1
+
+/* ---- runtime ---- */
+const char* sptorch_ext_last_error(void);              /* text of the calling thread's last failure */
+int   sptorch_ext_device(void);                        /* CUDA ordinal in use, -1 before init */
+int   sptorch_ext_sm_count(void);
+int   sptorch_ext_set_stream(void* cuda_stream);       /* adopt a caller's stream; NULL = library's own */
+void* sptorch_ext_alloc_bytes(size_t bytes);           /* stream-ordered pool, 256-byte aligned */
+void* sptorch_ext_alloc_pinned(size_t bytes);          /* page-locked host memory */
+void  sptorch_ext_free_pinned(void* p);
+int   sptorch_ext_copy_h2d_bytes(const void* host, void* device, size_t bytes);   /* async if host is pinned */
+int   sptorch_ext_copy_d2h_bytes(const void* device, void* host, size_t bytes);   /* returns with host valid */
+int   sptorch_ext_memset(void* device, int byte, size_t bytes);
+int   sptorch_ext_set_alloc_budget(size_t bytes);      /* tests: allocations beyond this many live bytes fail; 0 = off */
+int   sptorch_ext_timer_begin(void);                   /* CUDA event on the library stream */
+int   sptorch_ext_timer_end(float* ms);                /* second event, waits for it, elapsed ms */
+int   sptorch_ext_flush_l2(void);                      /* overwrites a 256 MiB scratch (allocated on first use) */
+uint32_t sptorch_ext_device_status(void);              /* non-zero if a kernel's bounded wait ran out (sticky until sync) */
+
+/* ---- dtype conversion ---- */
+int sptorch_ext_f32_to_bf16(const void* in, void* out, size_t n);   /* round to nearest even */
+int sptorch_ext_bf16_to_f32(const void* in, void* out, size_t n);
+
+/* ---- rest of KernelProvider (crates/hal/src/lib.rs:430-457; reference kernels :578-646) ---- */
+int sptorch_ext_sum_f32(const void* a, size_t n, float* host_result);
+int sptorch_ext_masked_fill_f32(const void* a, const void* mask_u8, float fill, void* out, size_t n); /* mask!=0 -> fill */
+int sptorch_ext_broadcast_add_f32(const void* a, const void* b, void* out, size_t a_len, size_t b_len); /* b[i % b_len] */
+int sptorch_ext_embedding_lookup_f32(const void* weight, const void* idx_i64, void* out,
+                                     size_t n_idx, size_t vocab, size_t dim);  /* ids validated on device: bad id -> error at sync, row zeroed */
+int sptorch_ext_sgd_update_f32(void* params, const void* grad, float lr, size_t n);
+int sptorch_ext_adam_update_f32(void* params, const void* grad, void* m, void* v, size_t n, float lr,
+                                float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2);
+
+/* ---- core-ops / nn row kernels; dtype = SPT_F32 | SPT_BF16 for input and output alike ---- */
+int sptorch_ext_add(const void* a, const void* b, void* out, size_t n, int dtype);          /* core-ops/src/lib.rs:299 */
+int sptorch_ext_gelu(const void* a, void* out, size_t n, int dtype);                        /* core-ops/src/lib.rs:1331 */
+int sptorch_ext_transpose_f32(const void* a, void* out, size_t rows, size_t cols);          /* core-ops/src/lib.rs:825 */
+int sptorch_ext_layernorm(const void* x, const void* gamma_f32, const void* beta_f32, void* out,
+                          size_t rows, size_t dim, float eps, int dtype);                   /* nn/src/lib.rs:397-418 */
+/* scale -> masked_fill(j>i, -inf) -> row softmax over scores [batch, T, T]  (nn/src/lib.rs:612-632) */
+int sptorch_ext_causal_softmax(const void* scores, void* out, size_t batch, size_t T, float scale, int dtype);
+/* core-ops masked_softmax (core-ops/src/lib.rs:1601-1645): keep!=0 takes part, others give exactly 0 */
+int sptorch_ext_masked_softmax_f32(const void* a, const void* keep_u8, void* out, size_t rows, size_t cols, int rank1);
+/* out[t,:] = tok[ids[t],:] + pos[t % T,:]   (nn/src/lib.rs:1351-1356); ids are int32 on the device */
+int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* ids_i32, void* out,
+                              size_t n_tokens, size_t T, size_t vocab, size_t dim, int dtype);
+
+/* ---- Linear (nn/src/lib.rs:121-133): out[M,N] = act(alpha * x[M,K] W[N,K]^T + bias[N]) + residual[M,N] ----
+ * W is consumed in its native [out,in] layout; the reference's transpose() copy does not exist here.
+ * mode SPT_MM_BF16: x, W, residual, out are bf16 (out may be f32 with out_dtype); SPT_MM_TF32 / SPT_MM_F32: f32.
+ * bias is always f32; bias and residual may be NULL.  ldo = row stride of out/residual in elements (0 = N). */
+/* arithmetic of the f32 C-ABI contractions sptorch_matmul_f32 / sptorch_batch_matmul_f32:
+ * SPT_MM_TF32 (default, tensor cores) or SPT_MM_F32 (CUDA cores, f32 FMA in k order) */
+int sptorch_ext_set_matmul_mode(int mode);
+
+int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const void* residual, void* out,
+                       size_t M, size_t K, size_t N, size_t ldo, float alpha, int epilogue, int mode, int out_dtype);
+
+/* ---- causal multi-head attention core (nn/src/lib.rs:600-637 without the four projections) ----
+ * q, k, v: [B*T, ld] with head h at columns h*hd..; out [B*T, H*hd].  dtype BF16 runs the fused
+ * kernel; F32 runs scores -> causal softmax -> PV through the TF32 GEMM with a caller-visible
+ * workspace of sptorch_ext_attention_workspace() bytes. */
+size_t sptorch_ext_attention_workspace(size_t B, size_t T, size_t H, size_t hd, int dtype);
+int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, void* out, void* workspace,
+                                 size_t B, size_t T, size_t H, size_t hd, size_t ld_qkv, int dtype);
+
+/* ---- GPT forward (nn/src/lib.rs:1332-1364) ---- */
+typedef struct {
+    int32_t vocab, d_model, n_layer, n_head, d_ff, seq_len;
+    int32_t dtype;        /* SPT_F32 (TF32 contractions) or SPT_BF16 */
+    int32_t max_batch;    /* activations are sized for max_batch * seq_len tokens */
+    float   eps;          /* 1e-5 in the reference (nn/src/lib.rs:383) */
+    int32_t tp_rank, tp_size;   /* tensor parallel shard of this process; 0,1 = none */
+} sptorch_gpt_config;
+
+void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg);       /* allocates weights + activations; NULL on failure */
+void  sptorch_ext_gpt_destroy(void* gpt);
+/* name as in GPT::named_parameters (nn/src/lib.rs:1382-1392); host f32 values of the FULL
+ * (unsharded) tensor; converted to the model dtype and sliced for this tp_rank on upload. */
+int   sptorch_ext_gpt_set_param(void* gpt, const char* name, const float* host, size_t n);
+size_t sptorch_ext_gpt_logits_ld(void* gpt);                       /* row stride of device logits (vocab padded to 64) */
+/* ids_i32 [batch*T] on the device -> logits [batch*T, ld] on the device in the model dtype */
+int   sptorch_ext_gpt_forward(void* gpt, const void* ids_i32, int batch, int T, void* logits);
+/* residual stream after embedding (i=0), after block i (1..L), and ln_f output (L+1): [batch*T, d] model dtype */
+int   sptorch_ext_gpt_enable_taps(void* gpt, int on);
+const void* sptorch_ext_gpt_tap(void* gpt, int i);
+/* Host-buffer call, the shape of nn::GPT::forward_ids: ids on the host in, dense [batch*T, vocab]
+ * logits on the host out (model dtype), copies included.  Processes micro-batches of `chunk`
+ * sequences and overlaps the device->host copy of one chunk with the compute of the next. */
+int   sptorch_ext_gpt_forward_host(void* gpt, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk);
+/* number of kernels one sptorch_ext_gpt_forward call of this shape enqueues */
+int   sptorch_ext_gpt_launches(void* gpt, int batch, int T);
+/* tensor-parallel all-reduce hook: called on the library stream's behalf after the row-split
+ * projections; the callee must enqueue a sum-all-reduce of n elements at buf onto cuda_stream. */
+typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_stream, void* user);
+int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
+
+/* ---- NCCL over NVLink (replaces the gRPC star all-reduce of crates/distributed/src/coordinator.rs:73-116) ---- */
+int sptorch_ext_nccl_unique_id(const char* libnccl_path, void* id128);                      /* rank 0: 128-byte id */
+int sptorch_ext_nccl_init(const char* libnccl_path, const void* id128, int rank, int world);
+int sptorch_ext_nccl_allreduce_sum(void* buf, size_t n, int dtype);                         /* in place, library stream */
+int sptorch_ext_nccl_allreduce_avg_f32(void* buf, size_t n);                                /* sum then * 1/world: average_gradients semantics */
+int sptorch_ext_nccl_shutdown(void);
+int sptorch_ext_gpt_use_nccl(void* gpt);      /* install the NCCL all-reduce as the tensor-parallel hook */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPTORCH_B200_EXT_H */

@@ -1,0 +1,79 @@
+"""In-tree build of libsptorch_b200.so (sm_100a only) with nvcc.
+
+Objects are rebuilt when a source or header is newer; the library lands in sptorch_b200/lib/.
+Run as ``python -m sptorch_b200.build`` or through ``__graft_entry__.build()``.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
+LIBDIR = os.path.join(HERE, "lib")
+LIB = os.path.join(LIBDIR, "libsptorch_b200.so")
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+# HBM-bound kernels keep a*b+c as two roundings so that results track the CPU oracle bit for bit where possible
+NO_FMA = {"elementwise.cu", "rowops.cu"}
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", shutil.which("nvcc")):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; the CUDA library cannot be built")
+
+
+def _headers():
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    inc = os.path.join(os.path.dirname(HERE), "include")
+    hs += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
+    return hs
+
+
+def build(verbose: bool = False, force: bool = False) -> str:
+    os.makedirs(OBJ, exist_ok=True)
+    os.makedirs(LIBDIR, exist_ok=True)
+    nvcc = _nvcc()
+    sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    hdr_time = max(os.path.getmtime(h) for h in _headers())
+    logs = {}
+
+    def compile_one(src: str):
+        obj = os.path.join(OBJ, src[:-3] + ".o")
+        spath = os.path.join(CSRC, src)
+        if (not force) and os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(spath), hdr_time):
+            return obj, False
+        cmd = [nvcc, *ARCH, *COMMON, *(["-fmad=false"] if src in NO_FMA else []), "-c", spath, "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        logs[src] = r.stderr
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
+        return obj, True
+
+    with ThreadPoolExecutor(max_workers=min(8, len(sources))) as ex:
+        results = list(ex.map(compile_one, sources))
+    objs = [o for o, _ in results]
+    if force or any(changed for _, changed in results) or not os.path.exists(LIB):
+        cmd = [nvcc, *ARCH, "-shared", "-o", LIB, *objs, "-lcudart_static", "-ldl", "-lpthread", "-lrt"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        for src, log in logs.items():
+            sys.stdout.write(f"==== {src}\n{log}\n")
+    with open(os.path.join(OBJ, "ptxas.log"), "a") as f:
+        for src, log in logs.items():
+            f.write(f"==== {src}\n{log}\n")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))

@@ -1,0 +1,59 @@
+// common.h -- process-global runtime state shared by every translation unit of libsptorch_b200.so.
+//
+// The reference's C-ABI has no context argument (crates/hal-ffi/include/sptorch_hal.h:21-85), so the
+// state is process-global: one device, one stream, one stream-ordered memory pool.  This replaces
+// runtime-cuda's CudaBackend/GpuTensor layer (crates/runtime-cuda/src/lib.rs:26-81), which copies
+// synchronously around every op and zero-fills every output.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <atomic>
+#include <mutex>
+
+namespace spt {
+
+enum DType : int { F32 = 0, BF16 = 1 };
+
+struct Runtime {
+    std::mutex mu;
+    int refcount = 0;
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;      // the stream every op is enqueued on
+    cudaStream_t own_stream = nullptr;  // created at init; `stream` may be swapped for a caller's
+    cudaStream_t copy_stream = nullptr; // second stream for overlapped device->host copies
+    cudaMemPool_t pool = nullptr;
+    std::atomic<int> sticky{0};         // first failure since the last sync; reported again by sync
+    std::atomic<uint64_t> submitted{0}, retired{0};
+    size_t budget = 0;                  // 0 = unlimited; otherwise sptorch_alloc fails past it (tests)
+    std::atomic<size_t> in_use{0};
+    uint32_t* dev_status = nullptr;     // device word written by kernels whose bounded waits ran out
+    cudaEvent_t t0 = nullptr, t1 = nullptr;
+};
+
+Runtime& rt();
+
+// Records msg as the thread's and the process's last error, marks the sticky flag, returns 1.
+int fail(const char* fmt, ...);
+// Makes the runtime's device current for the calling thread; non-zero if the library is not initialised.
+int enter();
+inline void note_submit() { rt().submitted.fetch_add(1, std::memory_order_relaxed); }
+
+#define SPT_CUDA(expr)                                                                     \
+    do {                                                                                   \
+        cudaError_t _e = (expr);                                                           \
+        if (_e != cudaSuccess) return ::spt::fail("%s failed: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+#define SPT_LAUNCH_CHECK(name)                                                             \
+    do {                                                                                   \
+        cudaError_t _e = cudaGetLastError();                                               \
+        if (_e != cudaSuccess) return ::spt::fail("launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+        ::spt::note_submit();                                                              \
+    } while (0)
+
+inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+}  // namespace spt

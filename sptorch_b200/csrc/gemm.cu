@@ -1,0 +1,551 @@
+// gemm.cu -- persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[m,n] = act(alpha * sum_k A[m,k] * B[n,k] + bias[n]) + R[m,n]        (both operands K-major)
+//
+// This is the Linear of the reference (crates/nn/src/lib.rs:121-133): W is consumed in its native
+// [out,in] layout as the K-major B operand, so the transpose() copy the reference makes on every call
+// (crates/core-ops/src/lib.rs:825-836) does not exist, and the bias add / GELU / residual add that the
+// reference runs as separate passes (core-ops/src/lib.rs:1804, 1331, 299) are the epilogue.  It also
+// serves the per-head products of attention (core-ops/src/lib.rs:1763-1799) through two batch dims.
+//
+// Structure of one CTA (192 threads, one CTA per SM, static round-robin over output tiles):
+//   warp 0      TMA producer: 128 x BK tile of A and BN x BK tile of B per stage, 128-byte swizzle,
+//               4-stage ring, completion on mbarriers (no multicast: every CTA loads its own tiles)
+//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=BN, K=32 bytes) from one lane; a stage is
+//               handed back to the producer by tcgen05.commit; the accumulator (f32, BN columns of
+//               TMEM) is double buffered so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue: tcgen05.ld of the warp's 32 TMEM lanes, 32 columns at a time, then
+//               alpha/bias/GELU/residual in registers and 128-bit stores
+// Bound: tensor pipe.  Algorithmic work 2*M*N*K FLOP; bytes (M*K + N*K)*s_in + M*N*s_out.
+#include "gemm.h"
+#include "sm100.cuh"
+#include "../../include/sptorch_b200_hal.h"
+#include "../../include/sptorch_b200_ext.h"
+#include <math.h>
+
+namespace spt {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int kStageRowBytes = 128;          // one swizzle row: 64 bf16 or 32 f32 along K
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 8;                   // m-tiles per rasterisation band (L2 reuse of the B tiles)
+
+struct GemmParams {
+    void* C; const float* bias; const void* R;
+    int M, N, K;
+    long long ldc;
+    int nb1, nb2;
+    long long sC1, sC2;
+    float alpha;
+    int epilogue;
+    int tiles_m, tiles_n;
+    int num_kb;
+    int causal_lower;
+    int causal_k;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float gelu_exact(float x) {
+    const float k = 0.7978845608028654f;
+    float x3 = (x * x) * x;
+    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x3)));
+}
+// bf16 outputs: tanh.approx (max rel. error 2^-11, far below one bf16 ulp of the result)
+__device__ __forceinline__ float gelu_fast(float x) {
+    const float k = 0.7978845608028654f;
+    float u = k * (x + 0.044715f * x * x * x);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    return 0.5f * x * (1.0f + t);
+}
+
+// tile index -> (batch z, m-tile, n-tile): bands of kGroupM m-tiles, n outer / m inner inside a band
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& z, int& tm, int& tn) {
+    int per_batch = tiles_m * tiles_n;
+    z = t / per_batch;
+    int r = t - z * per_batch;
+    int band = r / (kGroupM * tiles_n);
+    int first_m = band * kGroupM;
+    int rows_in_band = min(kGroupM, tiles_m - first_m);
+    int q = r - band * (kGroupM * tiles_n);
+    tn = q / rows_in_band;
+    tm = first_m + (q - tn * rows_in_band);
+}
+
+template <bool TF32, typename TOut, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+    constexpr int A_BYTES = BM * kStageRowBytes;
+    constexpr int B_BYTES = BN * kStageRowBytes;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int BK = TF32 ? 32 : 64;                 // elements of K per stage
+    constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators; power of two >= 32
+    constexpr uint32_t IDESC = make_idesc(TF32, BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw_addr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+    const uint32_t bar_full = base + kStages * STAGE_BYTES;
+    const uint32_t bar_empty = bar_full + 8 * kStages;
+    const uint32_t bar_tfull = bar_empty + 8 * kStages;
+    const uint32_t bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 128); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_tiles = p.tiles_m * p.tiles_n * p.nb1 * p.nb2;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+        int stage = 0; uint32_t phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int z, tm, tn;
+            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
+            if (p.causal_lower && n0 > m0 + BM - 1) continue;
+            const int z1 = z % p.nb1, z2 = z / p.nb1;
+            const int kb_end = p.causal_k ? min(p.num_kb, (m0 + BM + BK - 1) / BK) : p.num_kb;
+            for (int kb = 0; kb < kb_end; kb++) {
+                ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducerWait);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                    tma_load_4d(sa, &tmA, bar_full + 8 * stage, kb * BK, m0, z1, z2);
+                    tma_load_4d(sa + A_BYTES, &tmB, bar_full + 8 * stage, kb * BK, n0, z1, z2);
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int stage = 0; uint32_t phase = 0;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int z, tm, tn;
+            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            if (p.causal_lower && tn * BN > tm * BM + BM - 1) continue;
+            ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaWait);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            const int kb_end = p.causal_k ? min(p.num_kb, (tm * BM + BM + BK - 1) / BK) : p.num_kb;
+            for (int kb = 0; kb < kb_end; kb++) {
+                ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMmaWait);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    const uint64_t adesc = make_kmajor_sw128_desc(sa);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < kStageRowBytes / 32; k++)
+                        mma_ss<TF32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    mma_commit(bar_empty + 8 * stage);            // stage reusable once these MMAs have read it
+                    if (kb == kb_end - 1) mma_commit(bar_tfull + 8 * acc);   // accumulator complete
+                }
+                __syncwarp();
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+            }
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp % 4) ----------------
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        constexpr int kOutVec = 16 / (int)sizeof(TOut);      // elements per 128-bit store
+        const bool vec_ok = (p.ldc % kOutVec == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
+                            (p.sC1 % kOutVec == 0) && (p.sC2 % kOutVec == 0) &&
+                            (p.R == nullptr || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            int z, tm, tn;
+            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
+            if (p.causal_lower && n0 > m0 + BM - 1) continue;
+            const int z1 = z % p.nb1, z2 = z / p.nb1;
+            ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogueWait);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + row_in_tile;
+            const bool row_ok = row < p.M;
+            const long long zoff = (long long)z1 * p.sC1 + (long long)z2 * p.sC2;
+            TOut* crow = reinterpret_cast<TOut*>(p.C) + zoff + (long long)row * p.ldc;
+            const TOut* rrow = p.R ? reinterpret_cast<const TOut*>(p.R) + zoff + (long long)row * p.ldc : nullptr;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= p.N) break;                        // uniform over the warp
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + c * 32, v);
+                tmem_ld_wait();
+                float f[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++) f[j] = __uint_as_float(v[j]) * p.alpha;
+                const bool full = col0 + 32 <= p.N;
+                if (p.bias) {
+                    if (full) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
+                            f[j] += b.x; f[j + 1] += b.y; f[j + 2] += b.z; f[j + 3] += b.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (col0 + j < p.N) f[j] += __ldg(p.bias + col0 + j);
+                    }
+                }
+                if (p.epilogue == EPI_GELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) f[j] = (sizeof(TOut) == 2) ? gelu_fast(f[j]) : gelu_exact(f[j]);
+                }
+                if (row_ok) {
+                    if (full && vec_ok) {
+                        if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                if (rrow) {
+                                    uint4 rv = *reinterpret_cast<const uint4*>(rrow + col0 + j);
+                                    const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                                    for (int q = 0; q < 4; q++) { float2 g = __bfloat1622float2(rh[q]); f[j + 2 * q] += g.x; f[j + 2 * q + 1] += g.y; }
+                                }
+                                uint4 o;
+                                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                                for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(f[j + 2 * q], f[j + 2 * q + 1]);
+                                *reinterpret_cast<uint4*>(crow + col0 + j) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                if (rrow) {
+                                    float4 rv = *reinterpret_cast<const float4*>(rrow + col0 + j);
+                                    f[j] += rv.x; f[j + 1] += rv.y; f[j + 2] += rv.z; f[j + 3] += rv.w;
+                                }
+                                *reinterpret_cast<float4*>(crow + col0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (col0 + j < p.N) {
+                                float o = f[j];
+                                if (rrow) o += (float)rrow[col0 + j];
+                                crow[col0 + j] = (TOut)o;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_tempty + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // teardown: every thread arrives here, also after an aborted wait
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        // give loads that may still be in flight time to land before shared memory is released
+        unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------- host side ----------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// rank-4 map over a K-major operand: dims (K, rows, nb1, nb2), box (128 bytes of K, box_rows, 1, 1)
+static int encode_operand(CUtensorMap* map, const void* ptr, bool tf32, int K, int rows, long long ld, int nb1, int nb2,
+                          long long s1, long long s2, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail("cuTensorMapEncodeTiled is not available from this driver");
+    const size_t es = tf32 ? 4 : 2;
+    cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nb1, (cuuint64_t)nb2};
+    // strides of dims 1..3 in bytes; a dim of extent 1 still needs a legal (multiple of 16) stride
+    cuuint64_t st[3] = {(cuuint64_t)ld * es, (cuuint64_t)(nb1 > 1 ? s1 : ld) * es, (cuuint64_t)(nb2 > 1 ? s2 : ld) * es};
+    cuuint32_t box[4] = {(cuuint32_t)(kStageRowBytes / es), (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, st,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with CUresult %d (K=%d rows=%d ld=%lld)", (int)r, K, rows, ld);
+    return 0;
+}
+
+bool gemm_supported(const GemmDesc& d, const char** why) {
+    static const char* ok = "";
+    const long long es = d.mode == MM_TF32 ? 4 : 2;
+    auto bad = [&](const char* w) { if (why) *why = w; return false; };
+    if (d.mode != MM_TF32 && d.mode != MM_BF16) return bad("mode is not a tensor-core mode");
+    if (d.M <= 0 || d.N <= 0 || d.K <= 0) return bad("empty problem");
+    if ((reinterpret_cast<uintptr_t>(d.A) & 15) || (reinterpret_cast<uintptr_t>(d.B) & 15)) return bad("operand base not 16-byte aligned");
+    if ((d.lda * es) % 16 || (d.ldb * es) % 16) return bad("operand row pitch not a multiple of 16 bytes");
+    if (d.nb1 > 1 && ((d.sA1 * es) % 16 || (d.sB1 * es) % 16)) return bad("batch stride not a multiple of 16 bytes");
+    if (d.nb2 > 1 && ((d.sA2 * es) % 16 || (d.sB2 * es) % 16)) return bad("batch stride not a multiple of 16 bytes");
+    if (d.lda < d.K || d.ldb < d.K) return bad("row pitch smaller than K");
+    if ((long long)d.lda * es >= (1ll << 40) || (long long)d.ldb * es >= (1ll << 40)) return bad("row pitch too large for a tensor map");
+    if (d.mode == MM_TF32 && d.out_dtype != F32) return bad("TF32 mode writes f32 only");
+    if (why) *why = ok;
+    return true;
+}
+
+template <bool TF32, typename TOut, int BN>
+static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
+    auto kern = gemm_tcgen05_kernel<TF32, TOut, BN>;
+    static bool attr_set = false;   // per instantiation
+    if (!attr_set) {
+        SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        attr_set = true;
+    }
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, prm);
+    SPT_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}
+
+static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 1024 /*alignment slack*/ + 256 /*barriers*/; }
+
+int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
+    const char* why = nullptr;
+    if (!gemm_supported(d, &why)) return fail("gemm: %s", why);
+    plan->d = d;
+    int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
+    plan->bn = bn;
+    plan->tiles_m = ceil_div(d.M, BM);
+    plan->tiles_n = ceil_div(d.N, bn);
+    long long total = (long long)plan->tiles_m * plan->tiles_n * d.nb1 * d.nb2;
+    if (total > INT32_MAX) return fail("gemm: too many tiles");
+    plan->grid = (int)(total < rt().sm_count ? total : rt().sm_count);
+    plan->smem = smem_for(bn);
+    const bool tf32 = d.mode == MM_TF32;
+    if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;
+    if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, bn)) return 1;
+    plan->valid = true;
+    return 0;
+}
+
+int gemm_run(const GemmPlan& pl) {
+    if (!pl.valid) return fail("gemm_run: plan not prepared");
+    const GemmDesc& d = pl.d;
+    GemmParams prm;
+    prm.C = d.C; prm.bias = d.bias; prm.R = d.R;
+    prm.M = d.M; prm.N = d.N; prm.K = d.K; prm.ldc = d.ldc;
+    prm.nb1 = d.nb1; prm.nb2 = d.nb2; prm.sC1 = d.sC1; prm.sC2 = d.sC2;
+    prm.alpha = d.alpha; prm.epilogue = d.epilogue;
+    prm.tiles_m = pl.tiles_m; prm.tiles_n = pl.tiles_n;
+    prm.num_kb = ceil_div(d.K, d.mode == MM_TF32 ? 32 : 64);
+    prm.causal_lower = d.causal_lower;
+    prm.causal_k = d.causal_k;
+    prm.status = rt().dev_status;
+    const bool tf32 = d.mode == MM_TF32;
+    const bool out_bf16 = d.out_dtype == BF16;
+#define SPT_GEMM_CASE(BN_)                                                                          \
+    if (pl.bn == BN_) {                                                                             \
+        if (tf32) return launch_t<true, float, BN_>(pl, prm);                                       \
+        if (out_bf16) return launch_t<false, __nv_bfloat16, BN_>(pl, prm);                          \
+        return launch_t<false, float, BN_>(pl, prm);                                                \
+    }
+    SPT_GEMM_CASE(64)
+    SPT_GEMM_CASE(128)
+    SPT_GEMM_CASE(256)
+#undef SPT_GEMM_CASE
+    return fail("gemm_run: no kernel for BN=%d", pl.bn);
+}
+
+// ---------------- CUDA-core f32 matmul (exact-order mode and shapes TMA cannot express) ----------------
+// 64x64 output tile per CTA, 16x16 threads, 4x4 outputs per thread, K consumed in order p = 0..K-1 with
+// one fused multiply-add per product.
+__global__ void __launch_bounds__(256) simt_matmul_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                                                          int M, int N, int K, int b_is_kn, const float* __restrict__ bias,
+                                                          const float* __restrict__ R, float alpha, int epilogue) {
+    __shared__ float As[16][64 + 1];
+    __shared__ float Bs[16][64 + 1];
+    const int z = blockIdx.z;
+    A += (size_t)z * M * K; B += (size_t)z * N * K; C += (size_t)z * M * N;
+    if (R) R += (size_t)z * M * N;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            int r = i / 16, c = i % 16;                 // A tile: 64 rows x 16 k
+            int gm = m0 + r, gk = k0 + c;
+            As[c][r] = (gm < M && gk < K) ? A[(size_t)gm * K + gk] : 0.0f;
+        }
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            int gk, gn, kk, nn;
+            if (b_is_kn) { kk = i / 64; nn = i % 64; } else { nn = i / 16; kk = i % 16; }
+            gk = k0 + kk; gn = n0 + nn;
+            float v = 0.0f;
+            if (gk < K && gn < N) v = b_is_kn ? B[(size_t)gk * N + gn] : B[(size_t)gn * K + gk];
+            Bs[kk][nn] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+            if (gm < M && gn < N) {
+                float v = acc[i][j] * alpha;
+                if (bias) v += bias[gn];
+                if (epilogue == EPI_GELU) v = gelu_exact(v);
+                if (R) v += R[(size_t)gm * N + gn];
+                C[(size_t)gm * N + gn] = v;
+            }
+        }
+}
+
+int simt_matmul_f32(const float* A, const float* B, float* C, int batch, int M, int N, int K, bool b_is_kn, const float* bias,
+                    const float* R, float alpha, int epilogue) {
+    if (batch <= 0 || M <= 0 || N <= 0) return 0;
+    dim3 grid((unsigned)ceil_div(N, 64), (unsigned)ceil_div(M, 64), (unsigned)batch);
+    if (grid.y > 65535 || grid.z > 65535) return fail("simt_matmul: shape exceeds one launch (M tiles %u, batch %u)", grid.y, grid.z);
+    simt_matmul_kernel<<<grid, 256, 0, rt().stream>>>(A, B, C, M, N, K, b_is_kn ? 1 : 0, bias, R, alpha, epilogue);
+    SPT_LAUNCH_CHECK("simt_matmul");
+    return 0;
+}
+
+static std::atomic<int> g_abi_mode{MM_TF32};
+
+// C-ABI matmul: B arrives as [k,n] row-major.  Tensor-core path: transpose B once into a pool scratch
+// (one HBM pass over B) so that both operands are K-major, then the TF32 GEMM.  Shapes whose pitches TMA
+// cannot express, and MM_F32 mode, run on the CUDA cores.
+static int abi_matmul(const void* a, const void* b, void* out, size_t batch, size_t m, size_t k, size_t n) {
+    if (enter()) return 1;
+    if (batch == 0 || m == 0 || n == 0) return 0;
+    if (!a || !b || !out) return fail("matmul_f32: null handle");
+    if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || batch > 65535) return fail("matmul_f32: dimension too large");
+    if (k == 0) return sptorch_ext_memset(out, 0, batch * m * n * sizeof(float));
+    GemmDesc d;
+    d.mode = MM_TF32; d.out_dtype = F32;
+    d.M = (int)m; d.N = (int)n; d.K = (int)k;
+    d.lda = (long long)k; d.ldb = (long long)k; d.ldc = (long long)n;
+    d.nb1 = (int)batch; d.sA1 = (long long)(m * k); d.sB1 = (long long)(n * k); d.sC1 = (long long)(m * n);
+    d.A = a; d.B = b /* placeholder for the support check */; d.C = out;
+    const bool tc = g_abi_mode.load() == MM_TF32 && gemm_supported(d, nullptr) && (m * n * k >= (size_t)64 * 64 * 64);
+    if (!tc) return simt_matmul_f32((const float*)a, (const float*)b, (float*)out, (int)batch, (int)m, (int)n, (int)k, true, nullptr, nullptr, 1.0f, EPI_NONE);
+    float* bt = (float*)sptorch_ext_alloc_bytes(batch * n * k * sizeof(float));
+    if (!bt) return 1;
+    int rc = 0;
+    for (size_t z = 0; z < batch && rc == 0; z++)
+        rc = sptorch_ext_transpose_f32((const float*)b + z * k * n, bt + z * k * n, k, n);
+    if (rc == 0) {
+        d.B = bt;
+        GemmPlan pl;
+        rc = gemm_plan(d, &pl);
+        if (rc == 0) rc = gemm_run(pl);
+    }
+    sptorch_free(bt);
+    return rc;
+}
+
+}  // namespace spt
+
+using namespace spt;
+
+extern "C" {
+
+int sptorch_matmul_f32(const void* a, const void* b, void* out, size_t m, size_t k, size_t n) { return abi_matmul(a, b, out, 1, m, k, n); }
+int sptorch_batch_matmul_f32(const void* a, const void* b, void* out, size_t batch, size_t m, size_t k, size_t n) {
+    return abi_matmul(a, b, out, batch, m, k, n);
+}
+
+int sptorch_ext_set_matmul_mode(int mode) {
+    if (mode != SPT_MM_TF32 && mode != SPT_MM_F32) return fail("set_matmul_mode: the f32 C-ABI accepts SPT_MM_TF32 or SPT_MM_F32");
+    g_abi_mode.store(mode);
+    return 0;
+}
+
+int sptorch_ext_linear(const void* x, const void* w, const void* bias, const void* residual, void* out, size_t M, size_t K, size_t N,
+                       size_t ldo, float alpha, int epilogue, int mode, int out_dtype) {
+    if (enter()) return 1;
+    if (M == 0 || N == 0) return 0;
+    if (!x || !w || !out) return fail("linear: null handle");
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail("linear: dimension too large");
+    if (ldo == 0) ldo = N;
+    if (ldo < N) return fail("linear: ldo < N");
+    if (epilogue != SPT_EPI_NONE && epilogue != SPT_EPI_GELU) return fail("linear: unknown epilogue %d", epilogue);
+    if (mode == SPT_MM_F32 || K == 0) {
+        if (out_dtype != SPT_F32 || ldo != N) return fail("linear: the CUDA-core f32 mode needs f32 output with ldo == N");
+        return simt_matmul_f32((const float*)x, (const float*)w, (float*)out, 1, (int)M, (int)N, (int)K, false, (const float*)bias,
+                               (const float*)residual, alpha, epilogue);
+    }
+    GemmDesc d;
+    d.A = x; d.B = w; d.C = out; d.bias = (const float*)bias; d.R = residual;
+    d.M = (int)M; d.N = (int)N; d.K = (int)K;
+    d.lda = (long long)K; d.ldb = (long long)K; d.ldc = (long long)ldo;
+    d.alpha = alpha; d.epilogue = epilogue; d.mode = mode; d.out_dtype = out_dtype;
+    if (mode == SPT_MM_TF32 && !gemm_supported(d, nullptr) && out_dtype == SPT_F32 && ldo == N)
+        return simt_matmul_f32((const float*)x, (const float*)w, (float*)out, 1, (int)M, (int)N, (int)K, false, (const float*)bias,
+                               (const float*)residual, alpha, epilogue);
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    return gemm_run(pl);
+}
+
+}  // extern "C"

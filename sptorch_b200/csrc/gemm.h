@@ -1,0 +1,51 @@
+// gemm.h -- internal interface of the tcgen05 GEMM (used by the C-ABI entry points, attention and the GPT driver).
+#pragma once
+#include "common.h"
+#include <cuda.h>
+
+namespace spt {
+
+enum MMMode : int { MM_TF32 = 0, MM_BF16 = 1, MM_F32 = 2 };
+enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1 };
+
+// C[z][m,n] = act(alpha * sum_k A[z][m,k] * B[z][n,k] + bias[n]) + R[z][m,n]
+// Both operands are K-major (k contiguous).  z = z1 + nb1*z2 enumerates two batch dimensions with
+// independent element strides per operand (a head index and a sequence index, for attention).
+struct GemmDesc {
+    const void* A = nullptr; const void* B = nullptr; void* C = nullptr;
+    const float* bias = nullptr; const void* R = nullptr;
+    int M = 0, N = 0, K = 0;
+    long long lda = 0, ldb = 0, ldc = 0;          // row strides in elements
+    int nb1 = 1, nb2 = 1;
+    long long sA1 = 0, sA2 = 0, sB1 = 0, sB2 = 0, sC1 = 0, sC2 = 0;   // batch strides in elements (C strides apply to R too)
+    float alpha = 1.0f;
+    int epilogue = EPI_NONE;
+    int mode = MM_BF16;      // MM_BF16: A,B bf16.  MM_TF32: A,B f32.
+    int out_dtype = BF16;    // C and R element type
+    int causal_lower = 0;    // 1: square per-batch output, tiles entirely above the diagonal are skipped (never written)
+    int causal_k = 0;        // 1: A is lower triangular per batch (A[m,k] = 0 for k > m): k-blocks past the tile's last row are skipped
+};
+
+// A prepared launch: tensor maps are encoded once and can be replayed (the GPT driver caches these).
+struct GemmPlan {
+    CUtensorMap tmA, tmB;
+    GemmDesc d;
+    int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0;
+    size_t smem = 0;
+    bool valid = false;
+};
+
+// Returns 0 and fills plan, or non-zero with the reason in last_error (e.g. strides TMA cannot express).
+int gemm_plan(const GemmDesc& d, GemmPlan* plan);
+int gemm_run(const GemmPlan& plan);
+// true when the tcgen05 path can take this problem (alignment / stride rules of TMA)
+bool gemm_supported(const GemmDesc& d, const char** why);
+
+// CUDA-core f32 FMA matmul for shapes the TMA path cannot express and for MM_F32.
+// B is [K,N] row-major when b_is_kn, else [N,K].
+int simt_matmul_f32(const float* A, const float* B, float* C, int batch, int M, int N, int K, bool b_is_kn,
+                    const float* bias, const float* R, float alpha, int epilogue);
+
+int layernorm_launch(const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t dim, float eps, int dtype);
+
+}  // namespace spt

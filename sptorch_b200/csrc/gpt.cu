@@ -1,0 +1,347 @@
+// gpt.cu -- device-resident GPT forward (crates/nn/src/lib.rs:1332-1364, blocks :1174-1214, MHA :574-642).
+//
+// The reference runs one sequence per call and allocates + copies on every op; here a batch of
+// sequences is one [B*T, d] activation matrix (every op of the path is row- or sequence-local, so the
+// per-sequence results are unchanged) and a layer is ten launches:
+//   LN1 | [Wq;Wk] GEMM | V^T GEMM (swapped operands, writes V^T directly) | S=QK^T | causal softmax |
+//   O=PV | Wo GEMM (+residual) | LN2 | W_up GEMM (+bias, GELU) | W_down GEMM (+bias, +residual)
+// Dropout (nn/src/lib.rs:168-182) is the identity in eval mode and is not launched.
+// Weights keep the reference's [out,in] layout; parameter names are GPT::named_parameters' (nn/src/lib.rs:1382-1392).
+// Tensor parallel (tp_size > 1): wq/wk/wv/ffn_up split by output rows (heads / d_ff columns), wo/ffn_down
+// split along K; each produces a partial [M,d] that a caller-supplied all-reduce sums.  Rank 0 alone folds
+// the residual and the ffn_down bias into its partial so that the reduced sum is the new residual stream.
+#include "gemm.h"
+#include "../../include/sptorch_b200_hal.h"
+#include "../../include/sptorch_b200_ext.h"
+#include <string>
+#include <vector>
+#include <cstring>
+#include <cstdio>
+
+namespace spt {
+
+int attention_materialized(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
+                           void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
+
+struct Layer {
+    float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;
+    void *wqk, *wv, *wo, *w1, *w2;
+};
+
+struct Gpt {
+    sptorch_gpt_config c;
+    int es;                 // bytes per activation/weight element
+    int d_loc, H_loc, F_loc;
+    size_t ldl;             // logits row stride
+    void *tok, *pos, *head;
+    float *lnfg, *lnfb;
+    std::vector<Layer> L;
+    // activations for max_batch * seq_len tokens
+    void *x, *y, *h, *qk, *vt, *ao, *f, *scores;
+    size_t scores_elems;
+    std::vector<void*> taps; bool taps_on = false;
+    sptorch_allreduce_fn ar = nullptr; void* ar_user = nullptr;
+    std::vector<void*> owned;
+    // pipelined host call
+    void* logits_dev[2] = {nullptr, nullptr}; int* ids_dev = nullptr; int ids_cap = 0; size_t logits_cap = 0;
+    cudaEvent_t ev_compute[2] = {nullptr, nullptr}, ev_copy[2] = {nullptr, nullptr};
+};
+
+static void* galloc(Gpt* g, size_t bytes) {
+    void* p = sptorch_ext_alloc_bytes(bytes);
+    if (p) g->owned.push_back(p);
+    return p;
+}
+
+static int upload_rows(Gpt* g, void* dst_model_dtype, const float* host, size_t n) {
+    // host f32 -> device in the model dtype (bf16: round to nearest even on the device)
+    if (g->c.dtype == SPT_F32) return sptorch_ext_copy_h2d_bytes(host, dst_model_dtype, n * 4);
+    float* tmp = (float*)sptorch_ext_alloc_bytes(n * 4);
+    if (!tmp) return 1;
+    int rc = sptorch_ext_copy_h2d_bytes(host, tmp, n * 4);
+    if (!rc) rc = sptorch_ext_f32_to_bf16(tmp, dst_model_dtype, n);
+    if (!rc) rc = sptorch_sync();      // host buffer and tmp may be released after return
+    sptorch_free(tmp);
+    return rc;
+}
+
+// rows [r0, r0+nr) of a [R, C] host matrix
+static int upload_row_slice(Gpt* g, void* dst, const float* host, size_t C, size_t r0, size_t nr) {
+    return upload_rows(g, dst, host + r0 * C, nr * C);
+}
+// columns [c0, c0+nc) of a [R, C] host matrix -> dense [R, nc]
+static int upload_col_slice(Gpt* g, void* dst, const float* host, size_t R, size_t C, size_t c0, size_t nc) {
+    if (nc == C) return upload_rows(g, dst, host, R * C);
+    std::vector<float> tmp(R * nc);
+    for (size_t r = 0; r < R; r++) memcpy(&tmp[r * nc], host + r * C + c0, nc * sizeof(float));
+    return upload_rows(g, dst, tmp.data(), R * nc);
+}
+
+static int linear(Gpt* g, const void* x, const void* w, const float* bias, const void* res, void* out, int M, int K, int N,
+                  long long ldo, int epi) {
+    GemmDesc d;
+    d.A = x; d.B = w; d.C = out; d.bias = bias; d.R = res;
+    d.M = M; d.N = N; d.K = K; d.lda = K; d.ldb = K; d.ldc = ldo;
+    d.epilogue = epi;
+    d.mode = g->c.dtype == SPT_BF16 ? MM_BF16 : MM_TF32;
+    d.out_dtype = g->c.dtype;
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    return gemm_run(pl);
+}
+
+static int allreduce(Gpt* g, void* buf, size_t n) {
+    if (g->c.tp_size <= 1) return 0;
+    if (!g->ar) return fail("gpt: tensor parallel forward needs an all-reduce hook (sptorch_ext_gpt_set_allreduce)");
+    if (g->ar(buf, n, g->c.dtype, (void*)rt().stream, g->ar_user)) return fail("gpt: all-reduce hook failed");
+    note_submit();
+    return 0;
+}
+
+static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
+    const sptorch_gpt_config& c = g->c;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head;
+    const int dt = c.dtype;
+    const bool lead = c.tp_rank == 0;
+    if (sptorch_ext_embedding_sum(g->tok, g->pos, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1;
+    void* x = g->x; void* y = g->y;
+    auto tap = [&](int i, const void* src) -> int {
+        if (!g->taps_on) return 0;
+        SPT_CUDA(cudaMemcpyAsync(g->taps[i], src, (size_t)M * d * g->es, cudaMemcpyDeviceToDevice, rt().stream));
+        return 0;
+    };
+    if (tap(0, x)) return 1;
+    for (int l = 0; l < c.n_layer; l++) {
+        const Layer& w = g->L[l];
+        if (layernorm_launch(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
+        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
+        if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
+        if (attention_materialized(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
+                                   /*batch*/ T, g->ao, g->scores, B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
+        if (c.tp_size <= 1) {
+            if (linear(g, g->ao, w.wo, nullptr, x, x, M, dl, d, d, EPI_NONE)) return 1;       // x += attn
+        } else {
+            if (linear(g, g->ao, w.wo, nullptr, lead ? x : nullptr, y, M, dl, d, d, EPI_NONE)) return 1;
+            if (allreduce(g, y, (size_t)M * d)) return 1;
+            std::swap(x, y);
+        }
+        if (layernorm_launch(x, w.ln2g, w.ln2b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, M, d, Fl, Fl, EPI_GELU)) return 1;
+        if (c.tp_size <= 1) {
+            if (linear(g, g->f, w.w2, w.b2, x, x, M, Fl, d, d, EPI_NONE)) return 1;            // x += ffn
+        } else {
+            if (linear(g, g->f, w.w2, lead ? w.b2 : nullptr, lead ? x : nullptr, y, M, Fl, d, d, EPI_NONE)) return 1;
+            if (allreduce(g, y, (size_t)M * d)) return 1;
+            std::swap(x, y);
+        }
+        if (tap(l + 1, x)) return 1;
+    }
+    if (layernorm_launch(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+    if (tap(c.n_layer + 1, g->h)) return 1;
+    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
+    return 0;
+}
+
+}  // namespace spt
+
+using namespace spt;
+
+extern "C" {
+
+void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg) {
+    if (enter()) return nullptr;
+    if (!cfg) { fail("gpt_create: null config"); return nullptr; }
+    sptorch_gpt_config c = *cfg;
+    if (c.tp_size < 1) { c.tp_size = 1; c.tp_rank = 0; }
+    if (c.vocab <= 0 || c.d_model <= 0 || c.n_layer < 0 || c.n_head <= 0 || c.d_ff <= 0 || c.seq_len <= 0 || c.max_batch <= 0) {
+        fail("gpt_create: non-positive dimension"); return nullptr;
+    }
+    if (c.dtype != SPT_F32 && c.dtype != SPT_BF16) { fail("gpt_create: unknown dtype %d", c.dtype); return nullptr; }
+    if (c.d_model % c.n_head) { fail("gpt_create: d_model %% n_head != 0"); return nullptr; }
+    if (c.n_head % c.tp_size || c.d_ff % c.tp_size || c.tp_rank < 0 || c.tp_rank >= c.tp_size) {
+        fail("gpt_create: heads and d_ff must divide by tp_size"); return nullptr;
+    }
+    const int vec = c.dtype == SPT_BF16 ? 8 : 4;
+    const int hd = c.d_model / c.n_head;
+    if (c.d_model % vec || (c.d_ff / c.tp_size) % vec || hd % vec) { fail("gpt_create: d_model, d_ff/tp and head_dim must be multiples of %d", vec); return nullptr; }
+    Gpt* g = new Gpt();
+    g->c = c;
+    g->es = c.dtype == SPT_BF16 ? 2 : 4;
+    g->H_loc = c.n_head / c.tp_size;
+    g->d_loc = g->H_loc * hd;
+    g->F_loc = c.d_ff / c.tp_size;
+    g->ldl = ((size_t)c.vocab + 63) / 64 * 64;
+    const size_t es = g->es, d = c.d_model, V = c.vocab, S = c.seq_len, dl = g->d_loc, Fl = g->F_loc;
+    const size_t Mmax = (size_t)c.max_batch * S;
+    bool ok = true;
+    auto A = [&](size_t bytes) { void* p = galloc(g, bytes); if (!p) ok = false; return p; };
+    g->tok = A(V * d * es); g->pos = A(S * d * es); g->head = A(V * d * es);
+    g->lnfg = (float*)A(d * 4); g->lnfb = (float*)A(d * 4);
+    g->L.resize(c.n_layer);
+    for (auto& w : g->L) {
+        w.ln1g = (float*)A(d * 4); w.ln1b = (float*)A(d * 4); w.ln2g = (float*)A(d * 4); w.ln2b = (float*)A(d * 4);
+        w.b1 = (float*)A(Fl * 4); w.b2 = (float*)A(d * 4);
+        w.wqk = A(2 * dl * d * es); w.wv = A(dl * d * es); w.wo = A(d * dl * es); w.w1 = A(Fl * d * es); w.w2 = A(d * Fl * es);
+    }
+    g->x = A(Mmax * d * es); g->y = A(Mmax * d * es); g->h = A(Mmax * d * es);
+    g->qk = A(Mmax * 2 * dl * es); g->vt = A(dl * Mmax * es); g->ao = A(Mmax * dl * es); g->f = A(Mmax * Fl * es);
+    g->scores_elems = (size_t)c.max_batch * g->H_loc * S * S;
+    g->scores = A(g->scores_elems * es);
+    if (!ok) { sptorch_ext_gpt_destroy(g); return nullptr; }
+    return g;
+}
+
+void sptorch_ext_gpt_destroy(void* gp) {
+    if (!gp) return;
+    Gpt* g = (Gpt*)gp;
+    if (!enter()) {
+        cudaStreamSynchronize(rt().stream);
+        cudaStreamSynchronize(rt().copy_stream);
+        for (void* p : g->owned) sptorch_free(p);
+        for (int i = 0; i < 2; i++) {
+            if (g->ev_compute[i]) cudaEventDestroy(g->ev_compute[i]);
+            if (g->ev_copy[i]) cudaEventDestroy(g->ev_copy[i]);
+        }
+    }
+    delete g;
+}
+
+int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, size_t n) {
+    if (enter()) return 1;
+    if (!gp || !name || !host) return fail("gpt_set_param: null argument");
+    Gpt* g = (Gpt*)gp;
+    const sptorch_gpt_config& c = g->c;
+    const size_t d = c.d_model, V = c.vocab, S = c.seq_len, F = c.d_ff, dl = g->d_loc, Fl = g->F_loc, es = g->es;
+    const size_t r = c.tp_rank;
+    auto need = [&](size_t want) { return n == want ? 0 : fail("gpt_set_param(%s): got %zu values, expected %zu", name, n, want); };
+    auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || sptorch_sync(); };
+    std::string s(name);
+    if (s == "token_emb.weight") return need(V * d) || upload_rows(g, g->tok, host, n);
+    if (s == "pos_emb.weight") return need(S * d) || upload_rows(g, g->pos, host, n);
+    if (s == "lm_head.weight") return need(V * d) || upload_rows(g, g->head, host, n);
+    if (s == "ln_f.gamma") return need(d) || f32(g->lnfg, 0, d);
+    if (s == "ln_f.beta") return need(d) || f32(g->lnfb, 0, d);
+    int li = -1; char rest[64] = "";
+    if (sscanf(name, "blocks.%d.%63s", &li, rest) == 2 && li >= 0 && li < c.n_layer) {
+        Layer& w = g->L[li];
+        std::string t(rest);
+        if (t == "ln1.gamma") return need(d) || f32(w.ln1g, 0, d);
+        if (t == "ln1.beta") return need(d) || f32(w.ln1b, 0, d);
+        if (t == "ln2.gamma") return need(d) || f32(w.ln2g, 0, d);
+        if (t == "ln2.beta") return need(d) || f32(w.ln2b, 0, d);
+        if (t == "attn.wq.weight") return need(d * d) || upload_row_slice(g, w.wqk, host, d, r * dl, dl);
+        if (t == "attn.wk.weight") return need(d * d) || upload_row_slice(g, (uint8_t*)w.wqk + dl * d * es, host, d, r * dl, dl);
+        if (t == "attn.wv.weight") return need(d * d) || upload_row_slice(g, w.wv, host, d, r * dl, dl);
+        if (t == "attn.wo.weight") return need(d * d) || upload_col_slice(g, w.wo, host, d, d, r * dl, dl);
+        if (t == "ffn_up.weight") return need(F * d) || upload_row_slice(g, w.w1, host, d, r * Fl, Fl);
+        if (t == "ffn_up.bias") return need(F) || f32(w.b1, r * Fl, Fl);
+        if (t == "ffn_down.weight") return need(d * F) || upload_col_slice(g, w.w2, host, d, F, r * Fl, Fl);
+        if (t == "ffn_down.bias") return need(d) || f32(w.b2, 0, d);
+    }
+    return fail("gpt_set_param: unknown parameter name '%s'", name);
+}
+
+size_t sptorch_ext_gpt_logits_ld(void* gp) { return gp ? ((Gpt*)gp)->ldl : 0; }
+
+static int check_shape(Gpt* g, int batch, int T) {
+    if (batch <= 0 || T <= 0) return fail("gpt_forward: empty batch or sequence");
+    if (T > g->c.seq_len) return fail("gpt_forward: T=%d exceeds seq_len=%d", T, g->c.seq_len);   // nn/src/lib.rs:1351 asserts the same
+    if ((size_t)batch * T > (size_t)g->c.max_batch * g->c.seq_len) return fail("gpt_forward: batch*T exceeds the activation capacity");
+    if ((size_t)batch * g->H_loc * T * T > g->scores_elems) return fail("gpt_forward: score workspace too small");
+    const int vec = 16 / g->es;
+    if (T % vec) return fail("gpt_forward: T must be a multiple of %d for this dtype", vec);
+    return 0;
+}
+
+int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* logits) {
+    if (enter()) return 1;
+    if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
+    Gpt* g = (Gpt*)gp;
+    if (check_shape(g, batch, T)) return 1;
+    return forward(g, ids, batch, T, logits);
+}
+
+int sptorch_ext_gpt_enable_taps(void* gp, int on) {
+    if (enter()) return 1;
+    if (!gp) return fail("gpt_enable_taps: null model");
+    Gpt* g = (Gpt*)gp;
+    if (on && g->taps.empty()) {
+        size_t bytes = (size_t)g->c.max_batch * g->c.seq_len * g->c.d_model * g->es;
+        for (int i = 0; i < g->c.n_layer + 2; i++) {
+            void* p = galloc(g, bytes);
+            if (!p) return 1;
+            g->taps.push_back(p);
+        }
+    }
+    g->taps_on = on != 0;
+    return 0;
+}
+
+const void* sptorch_ext_gpt_tap(void* gp, int i) {
+    Gpt* g = (Gpt*)gp;
+    if (!g || i < 0 || i >= (int)g->taps.size()) return nullptr;
+    return g->taps[i];
+}
+
+int sptorch_ext_gpt_set_allreduce(void* gp, sptorch_allreduce_fn fn, void* user) {
+    if (!gp) return fail("gpt_set_allreduce: null model");
+    ((Gpt*)gp)->ar = fn; ((Gpt*)gp)->ar_user = user;
+    return 0;
+}
+
+int sptorch_ext_gpt_launches(void* gp, int batch, int T) {
+    (void)batch; (void)T;
+    if (!gp) return 0;
+    Gpt* g = (Gpt*)gp;
+    // embedding + per layer (LN1, QK, V^T, S, softmax, PV, Wo, LN2, up, down) + ln_f + head
+    return 1 + g->c.n_layer * 10 + 2;
+}
+
+int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk) {
+    if (enter()) return 1;
+    if (!gp || !ids_host || !logits_host) return fail("gpt_forward_host: null argument");
+    Gpt* g = (Gpt*)gp;
+    if (chunk <= 0 || chunk > batch) chunk = batch;
+    if (chunk > g->c.max_batch) chunk = g->c.max_batch;
+    if (check_shape(g, chunk, T)) return 1;
+    const size_t es = g->es, V = g->c.vocab, ldl = g->ldl;
+    const size_t need_logits = (size_t)chunk * T * ldl * es;
+    if (g->logits_cap < need_logits) {
+        for (int i = 0; i < 2; i++) {
+            g->logits_dev[i] = galloc(g, need_logits);
+            if (!g->logits_dev[i]) return 1;
+        }
+        g->logits_cap = need_logits;
+    }
+    if (g->ids_cap < batch * T) {
+        g->ids_dev = (int*)galloc(g, (size_t)batch * T * 4);
+        if (!g->ids_dev) return 1;
+        g->ids_cap = batch * T;
+    }
+    for (int i = 0; i < 2; i++) {
+        if (!g->ev_compute[i]) SPT_CUDA(cudaEventCreateWithFlags(&g->ev_compute[i], cudaEventDisableTiming));
+        if (!g->ev_copy[i]) SPT_CUDA(cudaEventCreateWithFlags(&g->ev_copy[i], cudaEventDisableTiming));
+    }
+    cudaStream_t cs = rt().stream, ds = rt().copy_stream;
+    SPT_CUDA(cudaMemcpyAsync(g->ids_dev, ids_host, (size_t)batch * T * 4, cudaMemcpyHostToDevice, cs));
+    int slot = 0, issued = 0;
+    for (int b0 = 0; b0 < batch; b0 += chunk, slot ^= 1, issued++) {
+        int nb = batch - b0 < chunk ? batch - b0 : chunk;
+        if (issued >= 2) SPT_CUDA(cudaStreamWaitEvent(cs, g->ev_copy[slot], 0));      // buffer free again
+        if (forward(g, g->ids_dev + (size_t)b0 * T, nb, T, g->logits_dev[slot])) return 1;
+        SPT_CUDA(cudaEventRecord(g->ev_compute[slot], cs));
+        SPT_CUDA(cudaStreamWaitEvent(ds, g->ev_compute[slot], 0));
+        // dense [rows, V] on the host <- [rows, ldl] on the device
+        SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)logits_host + (size_t)b0 * T * V * es, V * es, g->logits_dev[slot], ldl * es, V * es,
+                                   (size_t)nb * T, cudaMemcpyDeviceToHost, ds));
+        SPT_CUDA(cudaEventRecord(g->ev_copy[slot], ds));
+    }
+    SPT_CUDA(cudaStreamSynchronize(ds));
+    SPT_CUDA(cudaStreamSynchronize(cs));
+    rt().retired.store(rt().submitted.load());
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,564 @@
+// rowops.cu -- HBM-bound row kernels: LayerNorm, row softmax, causal softmax, masked softmax,
+// embedding gather + positional add, 2-D transpose.
+//
+// Common shape: a row (or a pair of rows) lives in the registers of TPR cooperating threads, is read
+// from HBM exactly once with 128-bit loads, reduced with warp shuffles (plus one shared-memory hop when
+// TPR > 32) and written once with 128-bit stores.  The reference computes all of these on the host
+// (crates/nn/src/lib.rs:397-418; crates/core-ops/src/lib.rs:888-935, 1601-1645, 1220-1255, 825-850) and its
+// CUDA backend round-trips through the host for them (crates/runtime-cuda/src/lib.rs:302-490).
+#include "common.h"
+#include "../../include/sptorch_b200_hal.h"
+#include "../../include/sptorch_b200_ext.h"
+#include <math.h>
+
+namespace spt {
+
+constexpr int kRowThreads = 256;
+
+// ---- 128-bit vector access for f32 (4 lanes) and bf16 (8 lanes) ----
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    float v[4];
+    __device__ static Vec load(const float* p) { float4 t = __ldcs(reinterpret_cast<const float4*>(p)); return Vec{{t.x, t.y, t.z, t.w}}; }
+    __device__ static Vec load_keep(const float* p) { float4 t = __ldg(reinterpret_cast<const float4*>(p)); return Vec{{t.x, t.y, t.z, t.w}}; }
+    __device__ void store(float* p) const { __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3])); }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    float v[8];
+    __device__ static Vec unpack(uint4 t) {
+        Vec r;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { float2 f = __bfloat1622float2(h[j]); r.v[2 * j] = f.x; r.v[2 * j + 1] = f.y; }
+        return r;
+    }
+    __device__ static Vec load(const __nv_bfloat16* p) { return unpack(__ldcs(reinterpret_cast<const uint4*>(p))); }
+    __device__ static Vec load_keep(const __nv_bfloat16* p) { return unpack(__ldg(reinterpret_cast<const uint4*>(p))); }
+    __device__ void store(__nv_bfloat16* p) const {
+        uint4 t;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+        for (int j = 0; j < 4; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        __stcs(reinterpret_cast<uint4*>(p), t);
+    }
+};
+
+// reduction over the TPR threads that share a row.  TPR <= 32: shuffles only.  TPR > 32: warp
+// shuffle, then one value per warp through shared memory (sh holds kRowThreads/32 floats).
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float row_reduce(float x, float* sh) {
+    constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+    for (int o = W / 2; o > 0; o >>= 1) {
+        float y = __shfl_xor_sync(0xffffffffu, x, o);
+        x = IS_MAX ? fmaxf(x, y) : x + y;
+    }
+    if (TPR > 32) {
+        constexpr int WPR = TPR / 32;                    // warps per row
+        int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        __syncthreads();                                 // previous use of sh is finished
+        if (lane == 0) sh[warp] = x;
+        __syncthreads();
+        int first = (warp / WPR) * WPR;
+        float r = sh[first];
+#pragma unroll
+        for (int w = 1; w < WPR; w++) r = IS_MAX ? fmaxf(r, sh[first + w]) : r + sh[first + w];
+        x = r;
+    }
+    return x;
+}
+
+// ---------------- LayerNorm (crates/nn/src/lib.rs:397-418) ----------------
+// mean = sum/d; var = sum((x-mean)^2)/d (biased); inv = 1/sqrt(var+eps); y = gamma*((x-mean)*inv)+beta.
+// The two sums are tree reductions here, sequential in the reference: results agree to f32 rounding.
+// Algorithmic bytes per row: 2*dim*sizeof(T) (+ gamma/beta once per CTA, L2 resident).
+template <typename T, int TPR, int V>
+__global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
+                                                                const float* __restrict__ beta, T* __restrict__ out,
+                                                                size_t rows, int dim, float eps) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    constexpr int RPB = kRowThreads / TPR;   // rows per CTA pass
+    __shared__ float sh[kRowThreads / 32];
+    const int t = threadIdx.x % TPR;
+    const int rl = threadIdx.x / TPR;
+    const int nvec = dim / N;
+    const float inv_d = 1.0f / (float)dim;
+    // when TPR > 32 every thread of the CTA must take part in the block-wide barrier of row_reduce,
+    // so the row loop is uniform per CTA and out-of-range rows are predicated, not skipped.
+    for (size_t r0 = (size_t)blockIdx.x * RPB; r0 < rows; r0 += (size_t)gridDim.x * RPB) {
+        size_t r = r0 + rl;
+        bool live = r < rows;
+        const T* xr = x + (live ? r : 0) * (size_t)dim;
+        VT d[V];
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                d[i] = VT::load(xr + c * N);
+#pragma unroll
+                for (int j = 0; j < N; j++) s += d[i].v[j];
+            }
+        }
+        float mean = row_reduce<TPR, false>(s, sh) / (float)dim;
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+#pragma unroll
+                for (int j = 0; j < N; j++) { float e = d[i].v[j] - mean; q += e * e; }
+            }
+        }
+        (void)inv_d;
+        float var = row_reduce<TPR, false>(q, sh) / (float)dim;
+        float inv = 1.0f / sqrtf(var + eps);
+        T* yr = out + (live ? r : 0) * (size_t)dim;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT y;
+#pragma unroll
+                for (int j4 = 0; j4 < N; j4 += 4) {
+                    float4 g = __ldg(reinterpret_cast<const float4*>(gamma + c * N + j4));
+                    float4 b = __ldg(reinterpret_cast<const float4*>(beta + c * N + j4));
+                    y.v[j4 + 0] = g.x * ((d[i].v[j4 + 0] - mean) * inv) + b.x;
+                    y.v[j4 + 1] = g.y * ((d[i].v[j4 + 1] - mean) * inv) + b.y;
+                    y.v[j4 + 2] = g.z * ((d[i].v[j4 + 2] - mean) * inv) + b.z;
+                    y.v[j4 + 3] = g.w * ((d[i].v[j4 + 3] - mean) * inv) + b.w;
+                }
+                y.store(yr + c * N);
+            }
+        }
+    }
+}
+
+// any dim (unaligned, or longer than the register path holds): one CTA per row, three passes that hit L1/L2
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) layernorm_generic_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
+                                                                        const float* __restrict__ beta, T* __restrict__ out,
+                                                                        size_t rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + r * (size_t)dim;
+        float s = 0.0f;
+        for (int c = threadIdx.x; c < dim; c += kRowThreads) s += (float)xr[c];
+        float mean = row_reduce<kRowThreads, false>(s, sh) / (float)dim;
+        float q = 0.0f;
+        for (int c = threadIdx.x; c < dim; c += kRowThreads) { float e = (float)xr[c] - mean; q += e * e; }
+        float var = row_reduce<kRowThreads, false>(q, sh) / (float)dim;
+        float inv = 1.0f / sqrtf(var + eps);
+        T* yr = out + r * (size_t)dim;
+        for (int c = threadIdx.x; c < dim; c += kRowThreads) yr[c] = (T)(gamma[c] * (((float)xr[c] - mean) * inv) + beta[c]);
+    }
+}
+
+// ---------------- row softmax (crates/core-ops/src/lib.rs:903-920; crates/hal/src/lib.rs:582-596) ----------------
+template <typename T, int TPR, int V>
+__global__ void __launch_bounds__(kRowThreads) softmax_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int cols) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    constexpr int RPB = kRowThreads / TPR;
+    __shared__ float sh[kRowThreads / 32];
+    const int t = threadIdx.x % TPR;
+    const int rl = threadIdx.x / TPR;
+    const int nvec = cols / N;
+    for (size_t r0 = (size_t)blockIdx.x * RPB; r0 < rows; r0 += (size_t)gridDim.x * RPB) {
+        size_t r = r0 + rl;
+        bool live = r < rows;
+        const T* xr = x + (live ? r : 0) * (size_t)cols;
+        VT d[V];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                d[i] = VT::load(xr + c * N);
+#pragma unroll
+                for (int j = 0; j < N; j++) mx = fmaxf(mx, d[i].v[j]);
+            }
+        }
+        mx = row_reduce<TPR, true>(mx, sh);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+#pragma unroll
+                for (int j = 0; j < N; j++) { d[i].v[j] = expf(d[i].v[j] - mx); s += d[i].v[j]; }
+            }
+        }
+        s = row_reduce<TPR, false>(s, sh);
+        T* yr = out + (live ? r : 0) * (size_t)cols;
+        const float uniform = 1.0f / (float)cols;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+#pragma unroll
+                for (int j = 0; j < N; j++) d[i].v[j] = (s == 0.0f) ? uniform : d[i].v[j] / s;
+                d[i].store(yr + c * N);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) softmax_generic_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int cols) {
+    __shared__ float sh[kRowThreads / 32];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + r * (size_t)cols;
+        float mx = -INFINITY;
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) mx = fmaxf(mx, (float)xr[c]);
+        mx = row_reduce<kRowThreads, true>(mx, sh);
+        float s = 0.0f;
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) s += expf((float)xr[c] - mx);
+        s = row_reduce<kRowThreads, false>(s, sh);
+        T* yr = out + r * (size_t)cols;
+        const float uniform = 1.0f / (float)cols;
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) yr[c] = (T)((s == 0.0f) ? uniform : expf((float)xr[c] - mx) / s);
+    }
+}
+
+// ---------------- causal softmax over scores [batch, T, T] (crates/nn/src/lib.rs:612-632) ----------------
+// y[i,j] = softmax_j( scale*x[i,j] for j <= i ; -inf for j > i ).  Only the lower triangle is read;
+// the strict upper triangle is written as exact zeros (exp(-inf)/S = 0).  One warp takes the row
+// pair (p, T-1-p) so that every warp moves the same number of bytes.
+// Algorithmic bytes per [T,T] matrix: (T(T+1)/2 + T^2) * sizeof(T).
+template <typename T, int V>
+__device__ __forceinline__ void causal_row(const T* __restrict__ xr, T* __restrict__ yr, int i, int Tn, float scale, int lane) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    const int nvec = Tn / N;
+    const int live_vec = i / N + 1;      // vectors holding at least one j <= i
+    VT d[V];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        int c = k * 32 + lane;
+        if (c < live_vec) {
+            d[k] = VT::load(xr + c * N);
+#pragma unroll
+            for (int j = 0; j < N; j++) {
+                float s = d[k].v[j] * scale;
+                s = (c * N + j > i) ? -INFINITY : s;
+                d[k].v[j] = s;
+                mx = fmaxf(mx, s);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        int c = k * 32 + lane;
+        if (c < live_vec) {
+#pragma unroll
+            for (int j = 0; j < N; j++) { float e = expf(d[k].v[j] - mx); d[k].v[j] = e; sum += e; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        int c = k * 32 + lane;
+        if (c < nvec) {
+            VT y;
+            if (c < live_vec) {
+#pragma unroll
+                for (int j = 0; j < N; j++) y.v[j] = d[k].v[j] / sum;
+            } else {
+#pragma unroll
+                for (int j = 0; j < N; j++) y.v[j] = 0.0f;
+            }
+            y.store(yr + c * N);
+        }
+    }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(kRowThreads) causal_softmax_kernel(const T* __restrict__ x, T* __restrict__ out, size_t batch,
+                                                                     int Tn, float scale) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * kRowThreads + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * kRowThreads) >> 5;
+    const int pairs = (Tn + 1) / 2;
+    const size_t tasks = batch * (size_t)pairs;
+    for (size_t task = warp; task < tasks; task += nwarps) {
+        size_t b = task / pairs;
+        int p = (int)(task % pairs);
+        const T* xb = x + b * (size_t)Tn * Tn;
+        T* yb = out + b * (size_t)Tn * Tn;
+        causal_row<T, V>(xb + (size_t)p * Tn, yb + (size_t)p * Tn, p, Tn, scale, lane);
+        int q = Tn - 1 - p;
+        if (q != p) causal_row<T, V>(xb + (size_t)q * Tn, yb + (size_t)q * Tn, q, Tn, scale, lane);
+    }
+}
+
+// any T: CTA per row, scalar accesses
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) causal_softmax_generic_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                                             size_t batch, int Tn, float scale) {
+    __shared__ float sh[kRowThreads / 32];
+    size_t rows = batch * (size_t)Tn;
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        int i = (int)(r % Tn);
+        const T* xr = x + r * (size_t)Tn;
+        T* yr = out + r * (size_t)Tn;
+        float mx = -INFINITY;
+        for (int c = threadIdx.x; c <= i; c += kRowThreads) mx = fmaxf(mx, (float)xr[c] * scale);
+        mx = row_reduce<kRowThreads, true>(mx, sh);
+        float s = 0.0f;
+        for (int c = threadIdx.x; c <= i; c += kRowThreads) s += expf((float)xr[c] * scale - mx);
+        s = row_reduce<kRowThreads, false>(s, sh);
+        for (int c = threadIdx.x; c < Tn; c += kRowThreads) yr[c] = (T)(c <= i ? expf((float)xr[c] * scale - mx) / s : 0.0f);
+    }
+}
+
+// ---------------- masked_softmax, arbitrary byte mask (crates/core-ops/src/lib.rs:1601-1645) ----------------
+// keep != 0: entry takes part.  A row without kept entries stays all zero.  rank1: the 1-D rule (all-zero
+// result -> uniform over kept) applies; with one row it can only trigger when the sum underflows.
+__global__ void __launch_bounds__(kRowThreads) masked_softmax_kernel(const float* __restrict__ x, const uint8_t* __restrict__ keep,
+                                                                     float* __restrict__ out, size_t rows, int cols, int rank1) {
+    __shared__ float sh[kRowThreads / 32];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float* xr = x + r * (size_t)cols;
+        const uint8_t* kr = keep + r * (size_t)cols;
+        float* yr = out + r * (size_t)cols;
+        float mx = -INFINITY, cnt = 0.0f;
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) if (kr[c]) { mx = fmaxf(mx, xr[c]); cnt += 1.0f; }
+        mx = row_reduce<kRowThreads, true>(mx, sh);
+        cnt = row_reduce<kRowThreads, false>(cnt, sh);
+        if (mx == -INFINITY) {   // uniform over the CTA: no kept entry (or all kept are -inf)
+            for (int c = threadIdx.x; c < cols; c += kRowThreads) yr[c] = (rank1 && kr[c]) ? 1.0f / cnt : 0.0f;
+            continue;
+        }
+        float s = 0.0f;
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) if (kr[c]) s += expf(xr[c] - mx);
+        s = row_reduce<kRowThreads, false>(s, sh);
+        for (int c = threadIdx.x; c < cols; c += kRowThreads) {
+            float e = kr[c] ? expf(xr[c] - mx) : 0.0f;
+            yr[c] = (kr[c] && s > 0.0f) ? e / s : e;
+        }
+    }
+}
+
+// ---------------- embedding gather + positional add (crates/nn/src/lib.rs:1351-1356) ----------------
+// out[t,:] = tok[ids[t],:] + pos[t % T,:].  One warp per token row, 128-bit accesses.  An id outside
+// [0, vocab) zeroes the row and raises the device status word (the reference asserts: core-ops/src/lib.rs:1229).
+// Algorithmic bytes per token: 2*dim*sizeof(T) + 4 (pos rows are L2 resident).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) embedding_sum_kernel(const T* __restrict__ tok, const T* __restrict__ pos,
+                                                                    const int* __restrict__ ids, T* __restrict__ out,
+                                                                    size_t n_tokens, int Tn, int vocab, int dim, uint32_t* status) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    const int lane = threadIdx.x & 31;
+    const size_t warp = ((size_t)blockIdx.x * kRowThreads + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * kRowThreads) >> 5;
+    const int nvec = dim / N;
+    for (size_t t = warp; t < n_tokens; t += nwarps) {
+        int id = ids[t];
+        bool ok = id >= 0 && id < vocab;
+        if (!ok && lane == 0) atomicOr(status, 0x100u);
+        const T* a = tok + (size_t)(ok ? id : 0) * dim;
+        const T* b = pos + (size_t)(t % Tn) * dim;
+        T* y = out + t * (size_t)dim;
+        for (int c = lane; c < nvec; c += 32) {
+            VT u = VT::load_keep(a + c * N), w = VT::load_keep(b + c * N), r;
+#pragma unroll
+            for (int j = 0; j < N; j++) r.v[j] = ok ? u.v[j] + w.v[j] : 0.0f;
+            r.store(y + c * N);
+        }
+        for (int c = nvec * N + lane; c < dim; c += 32) y[c] = (T)(ok ? (float)a[c] + (float)b[c] : 0.0f);
+    }
+}
+
+// ---------------- transpose (crates/core-ops/src/lib.rs:825-836) ----------------
+__global__ void transpose_kernel(const float* __restrict__ a, float* __restrict__ out, int rows, int cols) {
+    __shared__ float tile[32][33];
+    int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        int r = by + j, c = bx + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = a[(size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        int c = bx + j, r = by + threadIdx.x;   // out[c, r]
+        if (r < rows && c < cols) out[(size_t)c * rows + r] = tile[threadIdx.x][j];
+    }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static inline int row_grid(size_t row_groups) {
+    size_t cap = (size_t)rt().sm_count * 8;
+    size_t g = row_groups < cap ? row_groups : cap;
+    return (int)(g < 1 ? 1 : g);
+}
+
+// picks (TPR, V) so that TPR*V >= nvec with V <= 8
+#define SPT_ROW_DISPATCH(KERNEL, T, nvec, ...)                                                              \
+    do {                                                                                                   \
+        int _tpr = (nvec) <= 256 ? 32 : (nvec) <= 512 ? 64 : (nvec) <= 1024 ? 128 : 256;                    \
+        int _v = ((nvec) + _tpr - 1) / _tpr;                                                                \
+        int _rpb = kRowThreads / _tpr;                                                                      \
+        int _grid = row_grid((rows + _rpb - 1) / _rpb);                                                     \
+        if (_tpr == 32) {                                                                                   \
+            if (_v <= 1) KERNEL<T, 32, 1><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);             \
+            else if (_v <= 2) KERNEL<T, 32, 2><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
+            else if (_v <= 4) KERNEL<T, 32, 4><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
+            else if (_v <= 6) KERNEL<T, 32, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
+            else KERNEL<T, 32, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                     \
+        } else if (_tpr == 64) {                                                                            \
+            if (_v <= 6) KERNEL<T, 64, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);             \
+            else KERNEL<T, 64, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                     \
+        } else if (_tpr == 128) {                                                                           \
+            if (_v <= 6) KERNEL<T, 128, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);            \
+            else KERNEL<T, 128, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                    \
+        } else {                                                                                            \
+            if (_v <= 6) KERNEL<T, 256, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);            \
+            else KERNEL<T, 256, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                    \
+        }                                                                                                   \
+    } while (0)
+
+template <typename T>
+static int layernorm_t(const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t dim, float eps) {
+    constexpr int N = Vec<T>::N;
+    const T* xp = (const T*)x; T* op = (T*)out;
+    const float* g = (const float*)gamma; const float* b = (const float*)beta;
+    bool fast = dim % N == 0 && dim / N <= 2048 && aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta);
+    if (fast) {
+        int nvec = (int)(dim / N);
+        SPT_ROW_DISPATCH(layernorm_kernel, T, nvec, xp, g, b, op, rows, (int)dim, eps);
+    } else {
+        layernorm_generic_kernel<T><<<row_grid(rows), kRowThreads, 0, rt().stream>>>(xp, g, b, op, rows, (int)dim, eps);
+    }
+    SPT_LAUNCH_CHECK("layernorm");
+    return 0;
+}
+
+template <typename T>
+static int softmax_t(const void* x, void* out, size_t rows, size_t cols) {
+    constexpr int N = Vec<T>::N;
+    const T* xp = (const T*)x; T* op = (T*)out;
+    bool fast = cols % N == 0 && cols / N <= 2048 && aligned16(x) && aligned16(out);
+    if (fast) {
+        int nvec = (int)(cols / N);
+        SPT_ROW_DISPATCH(softmax_kernel, T, nvec, xp, op, rows, (int)cols);
+    } else {
+        softmax_generic_kernel<T><<<row_grid(rows), kRowThreads, 0, rt().stream>>>(xp, op, rows, (int)cols);
+    }
+    SPT_LAUNCH_CHECK("softmax");
+    return 0;
+}
+
+template <typename T>
+static int causal_softmax_t(const void* x, void* out, size_t batch, size_t Tn, float scale) {
+    constexpr int N = Vec<T>::N;
+    const T* xp = (const T*)x; T* op = (T*)out;
+    bool fast = Tn % N == 0 && Tn / N <= 256 && aligned16(x) && aligned16(out);
+    if (fast) {
+        int nvec = (int)(Tn / N);
+        int v = (nvec + 31) / 32;
+        size_t tasks = batch * ((Tn + 1) / 2);
+        int grid = row_grid((tasks + kRowThreads / 32 - 1) / (kRowThreads / 32));
+        if (v <= 1) causal_softmax_kernel<T, 1><<<grid, kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
+        else if (v <= 2) causal_softmax_kernel<T, 2><<<grid, kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
+        else if (v <= 4) causal_softmax_kernel<T, 4><<<grid, kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
+        else causal_softmax_kernel<T, 8><<<grid, kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
+    } else {
+        causal_softmax_generic_kernel<T><<<row_grid(batch * Tn), kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
+    }
+    SPT_LAUNCH_CHECK("causal_softmax");
+    return 0;
+}
+
+// used by the GPT driver (same translation-unit-independent entry points as the C-ABI below)
+int layernorm_launch(const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t dim, float eps, int dtype) {
+    if (rows == 0 || dim == 0) return 0;
+    if (dim > (size_t)INT32_MAX) return fail("layernorm: dim too large");
+    return dtype == BF16 ? layernorm_t<__nv_bfloat16>(x, gamma, beta, out, rows, dim, eps)
+                         : layernorm_t<float>(x, gamma, beta, out, rows, dim, eps);
+}
+
+}  // namespace spt
+
+using namespace spt;
+
+extern "C" {
+
+int sptorch_softmax_f32(const void* a, void* out, size_t rows, size_t cols) {
+    if (enter()) return 1;
+    if (rows == 0 || cols == 0) return 0;
+    if (!a || !out) return fail("softmax_f32: null handle");
+    if (cols > (size_t)INT32_MAX) return fail("softmax_f32: cols too large");
+    return softmax_t<float>(a, out, rows, cols);
+}
+
+int sptorch_ext_layernorm(const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t dim, float eps, int dtype) {
+    if (enter()) return 1;
+    if (rows == 0 || dim == 0) return 0;
+    if (!x || !gamma || !beta || !out) return fail("layernorm: null handle");
+    if (dtype != SPT_F32 && dtype != SPT_BF16) return fail("layernorm: unknown dtype %d", dtype);
+    return layernorm_launch(x, gamma, beta, out, rows, dim, eps, dtype);
+}
+
+int sptorch_ext_causal_softmax(const void* scores, void* out, size_t batch, size_t T, float scale, int dtype) {
+    if (enter()) return 1;
+    if (batch == 0 || T == 0) return 0;
+    if (!scores || !out) return fail("causal_softmax: null handle");
+    if (T > (size_t)1 << 20) return fail("causal_softmax: T too large");
+    if (dtype == SPT_F32) return causal_softmax_t<float>(scores, out, batch, T, scale);
+    if (dtype == SPT_BF16) return causal_softmax_t<__nv_bfloat16>(scores, out, batch, T, scale);
+    return fail("causal_softmax: unknown dtype %d", dtype);
+}
+
+int sptorch_ext_masked_softmax_f32(const void* a, const void* keep, void* out, size_t rows, size_t cols, int rank1) {
+    if (enter()) return 1;
+    if (rows == 0 || cols == 0) return 0;
+    if (!a || !keep || !out) return fail("masked_softmax: null handle");
+    if (cols > (size_t)INT32_MAX) return fail("masked_softmax: cols too large");
+    masked_softmax_kernel<<<row_grid(rows), kRowThreads, 0, rt().stream>>>((const float*)a, (const uint8_t*)keep, (float*)out, rows, (int)cols, rank1);
+    SPT_LAUNCH_CHECK("masked_softmax");
+    return 0;
+}
+
+int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T,
+                              size_t vocab, size_t dim, int dtype) {
+    if (enter()) return 1;
+    if (n_tokens == 0 || dim == 0) return 0;
+    if (!tok_w || !pos_w || !ids || !out) return fail("embedding_sum: null handle");
+    if (T == 0) return fail("embedding_sum: T == 0");
+    int grid = row_grid((n_tokens + kRowThreads / 32 - 1) / (kRowThreads / 32));
+    if (dtype == SPT_F32) {
+        if (dim % 4 || !aligned16(tok_w) || !aligned16(pos_w) || !aligned16(out)) return fail("embedding_sum: dim %% 4 != 0 or unaligned buffers");
+        embedding_sum_kernel<float><<<grid, kRowThreads, 0, rt().stream>>>((const float*)tok_w, (const float*)pos_w, (const int*)ids, (float*)out,
+                                                                          n_tokens, (int)T, (int)vocab, (int)dim, rt().dev_status);
+    } else if (dtype == SPT_BF16) {
+        if (dim % 8 || !aligned16(tok_w) || !aligned16(pos_w) || !aligned16(out)) return fail("embedding_sum: dim %% 8 != 0 or unaligned buffers");
+        embedding_sum_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, rt().stream>>>((const __nv_bfloat16*)tok_w, (const __nv_bfloat16*)pos_w,
+                                                                                  (const int*)ids, (__nv_bfloat16*)out, n_tokens, (int)T,
+                                                                                  (int)vocab, (int)dim, rt().dev_status);
+    } else return fail("embedding_sum: unknown dtype %d", dtype);
+    SPT_LAUNCH_CHECK("embedding_sum");
+    return 0;
+}
+
+int sptorch_ext_transpose_f32(const void* a, void* out, size_t rows, size_t cols) {
+    if (enter()) return 1;
+    if (rows == 0 || cols == 0) return 0;
+    if (!a || !out) return fail("transpose: null handle");
+    dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32));
+    if (grid.y > 65535) return fail("transpose: too many rows for one launch");
+    transpose_kernel<<<grid, dim3(32, 8), 0, rt().stream>>>((const float*)a, (float*)out, (int)rows, (int)cols);
+    SPT_LAUNCH_CHECK("transpose");
+    return 0;
+}
+
+}  // extern "C"

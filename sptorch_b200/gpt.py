@@ -1,0 +1,110 @@
+"""nn::GPT on the device (crates/nn/src/lib.rs:1263-1437): same constructor arguments, same parameter
+names, ``forward_ids`` with the reference's meaning (token ids in, logits [T, V] out), plus a batched
+device-resident ``forward`` that the benchmark uses."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from .backend import BF16, F32, FfiBackend, HalError, bf16_bits_to_f32
+from .synth import gpt_param_layout
+
+
+class GPT:
+    def __init__(self, backend: FfiBackend, vocab_size: int, d_model: int, n_head: int, n_layer: int, d_ff: int,
+                 seq_len: int, dtype: int = F32, max_batch: int = 1, eps: float = 1e-5, tp_rank: int = 0, tp_size: int = 1):
+        # argument order of GPT::new (nn/src/lib.rs:1332)
+        self.b = backend
+        self.cfg = dict(vocab=vocab_size, d_model=d_model, n_layer=n_layer, n_head=n_head, d_ff=d_ff, seq_len=seq_len)
+        self.dtype, self.max_batch = dtype, max_batch
+        c = _lib.GptConfig(vocab_size, d_model, n_layer, n_head, d_ff, seq_len, dtype, max_batch, eps, tp_rank, tp_size)
+        self.h = backend.lib.sptorch_ext_gpt_create(C.byref(c))
+        if not self.h:
+            raise HalError("gpt_create failed: " + _lib.last_error())
+        self.ldl = backend.lib.sptorch_ext_gpt_logits_ld(self.h)
+        self.es = 2 if dtype == BF16 else 4
+        self._logits = None
+        self._ids = None
+
+    def close(self):
+        if self.h:
+            for buf in (self._logits, self._ids):
+                if buf is not None:
+                    buf.free()
+            self.b.lib.sptorch_ext_gpt_destroy(self.h)
+            self.h = None
+
+    def named_parameters(self):
+        return gpt_param_layout(**self.cfg)
+
+    def load_flat(self, flat: np.ndarray, index: dict):
+        """flat f32 block + {name: (offset, shape)} as produced by synth.gpt_params."""
+        for name, (off, shape) in index.items():
+            self.set_param(name, flat[off:off + int(np.prod(shape))])
+
+    def set_param(self, name: str, values):
+        a = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        self.b._check(self.b.lib.sptorch_ext_gpt_set_param(self.h, name.encode(), a.ctypes.data, a.size), f"set_param({name})")
+
+    def enable_taps(self, on=True):
+        self.b._check(self.b.lib.sptorch_ext_gpt_enable_taps(self.h, int(on)), "enable_taps")
+
+    def tap(self, i: int, n_tokens: int) -> np.ndarray:
+        p = self.b.lib.sptorch_ext_gpt_tap(self.h, i)
+        if not p:
+            raise HalError("taps are not enabled")
+        d = self.cfg["d_model"]
+        raw = np.empty(n_tokens * d, dtype=np.uint16 if self.dtype == BF16 else np.float32)
+        self.b._check(self.b.lib.sptorch_ext_copy_d2h_bytes(p, raw.ctypes.data, raw.nbytes), "tap d2h")
+        return (bf16_bits_to_f32(raw) if self.dtype == BF16 else raw).reshape(n_tokens, d)
+
+    # -- device-resident batched forward --
+    def stage_ids(self, ids: np.ndarray):
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        if self._ids is None or self._ids.n < ids.size:
+            if self._ids is not None:
+                self._ids.free()
+            self._ids = self.b.alloc(ids.size)
+        self.b._check(self.b.lib.sptorch_ext_copy_h2d_bytes(ids.ctypes.data, self._ids.handle, ids.nbytes), "ids h2d")
+        return self._ids
+
+    def logits_buffer(self, n_tokens: int):
+        need = n_tokens * self.ldl
+        if self._logits is None or self._logits.n < need:
+            if self._logits is not None:
+                self._logits.free()
+            self._logits = self.b.alloc(need, self.es)
+        return self._logits
+
+    def forward_device(self, ids_dev, batch: int, T: int, logits_dev):
+        self.b._check(self.b.lib.sptorch_ext_gpt_forward(self.h, ids_dev.handle, batch, T, logits_dev.handle), "gpt_forward")
+
+    def forward(self, ids: np.ndarray) -> np.ndarray:
+        """ids [B, T] -> logits [B, T, V] float32 on the host."""
+        ids = np.asarray(ids)
+        B, T = ids.shape
+        V = self.cfg["vocab"]
+        d_ids = self.stage_ids(ids)
+        d_log = self.logits_buffer(B * T)
+        self.forward_device(d_ids, B, T, d_log)
+        raw = np.empty(B * T * self.ldl, dtype=np.uint16 if self.dtype == BF16 else np.float32)
+        self.b._check(self.b.lib.sptorch_ext_copy_d2h_bytes(d_log.handle, raw.ctypes.data, raw.nbytes), "logits d2h")
+        self.b.synchronize()
+        out = bf16_bits_to_f32(raw) if self.dtype == BF16 else raw
+        return out.reshape(B * T, self.ldl)[:, :V].reshape(B, T, V).copy()
+
+    def forward_ids(self, token_ids) -> np.ndarray:
+        """GPT::forward_ids (nn/src/lib.rs:1349-1364): one sequence of ids -> logits [T, V]."""
+        ids = np.asarray(token_ids).reshape(1, -1)
+        if ids.shape[1] > self.cfg["seq_len"]:
+            raise HalError("sequence longer than seq_len")   # the reference asserts (nn/src/lib.rs:1351)
+        return self.forward(ids)[0]
+
+    def forward_host(self, ids_host_ptr: int, batch: int, T: int, logits_host_ptr: int, chunk: int):
+        """Host-buffer call through the C-ABI: pinned ids in, dense logits out, copies included."""
+        self.b._check(self.b.lib.sptorch_ext_gpt_forward_host(self.h, ids_host_ptr, batch, T, logits_host_ptr, chunk), "gpt_forward_host")
+
+    def launches(self, batch: int, T: int) -> int:
+        return self.b.lib.sptorch_ext_gpt_launches(self.h, batch, T)
