@@ -49,6 +49,11 @@ int   sptorch_ext_set_alloc_budget(size_t bytes);      /* tests: allocations bey
 int   sptorch_ext_timer_begin(void);                   /* CUDA event on the library stream */
 int   sptorch_ext_timer_end(float* ms);                /* second event, waits for it, elapsed ms */
 int   sptorch_ext_flush_l2(void);                      /* overwrites a 256 MiB scratch (allocated on first use) */
+/* per-category device timing of the GPT forward (CUDA events around each launch on the library stream).
+ * categories: 0 linear GEMM, 1 attention GEMMs, 2 causal softmax, 3 layernorm, 4 embedding, 5 other, 6 fused attention */
+#define SPT_PROF_NCAT 7
+int   sptorch_ext_prof_enable(int on);
+int   sptorch_ext_prof_read(float* ms, uint32_t* launches, int ncat);  /* syncs, sums since last read, clears */
 uint32_t sptorch_ext_device_status(void);              /* non-zero if a kernel's bounded wait ran out (sticky until sync) */
 
 /* ---- dtype conversion ---- */

@@ -11,6 +11,9 @@
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
+static int omp_in_parallel_(void) { return omp_in_parallel(); }
+#else
+static int omp_in_parallel_(void) { return 1; }
 #endif
 
 /* ---------- elementwise (crates/core-ops/src/lib.rs:299-332, 1331-1358, 1376-1399;
@@ -196,11 +199,20 @@ void orc_linear(const float* x, const float* w, const float* bias, float* y,
         orc_matmul(x, wt, y, M, K, N);
         free(wt);
     } else if (fast == 1) {
-        const size_t JB = 64;
-        for (size_t j0 = 0; j0 < N; j0 += JB) {
-            size_t j1 = j0 + JB < N ? j0 + JB : N;
-            for (size_t i = 0; i < M; i++)
-                for (size_t j = j0; j < j1; j++) y[i * N + j] = dot8(x + i * K, w + j * K, K);
+        /* rows are independent: split them over threads unless the caller already runs one sequence per thread */
+        const long IB = 32, JB = 256, JI = 64;
+        const long nib = ((long)M + IB - 1) / IB, njb = ((long)N + JB - 1) / JB;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1) if (!omp_in_parallel_())
+        for (long ib = 0; ib < nib; ib++) {
+            for (long jb = 0; jb < njb; jb++) {
+                size_t i0 = (size_t)ib * IB, i1 = i0 + IB < M ? i0 + IB : M;
+                size_t jb0 = (size_t)jb * JB, jb1 = jb0 + JB < N ? jb0 + JB : N;
+                for (size_t j0 = jb0; j0 < jb1; j0 += JI) {
+                    size_t j1 = j0 + JI < jb1 ? j0 + JI : jb1;
+                    for (size_t i = i0; i < i1; i++)
+                        for (size_t j = j0; j < j1; j++) y[i * N + j] = dot8(x + i * K, w + j * K, K);
+                }
+            }
         }
     } else {
         for (size_t i = 0; i < M; i++)
@@ -262,15 +274,18 @@ void orc_mha_causal(const float* x, const float* wq, const float* wk, const floa
     orc_reshape_to_heads(v, v3, T, H, hd);
     /* scores = Q K^T: the reference materialises K^T [H,hd,T] and multiplies [T,hd]x[hd,T];
      * the products and their p-order are the same as dotting rows of Q with rows of K. */
-    for (size_t h = 0; h < H; h++) head_matmul_nt(q3 + h * T * hd, k3 + h * T * hd, sc + h * T * T, T, hd, T, fast);
+#pragma omp parallel for schedule(static) if (!omp_in_parallel_())
+    for (long h = 0; h < (long)H; h++) head_matmul_nt(q3 + h * T * hd, k3 + h * T * hd, sc + h * T * T, T, hd, T, fast);
     float scale = 1.0f / sqrtf((float)hd);
     for (size_t i = 0; i < H * T * T; i++) sc[i] = sc[i] * scale;
     for (size_t h = 0; h < H; h++) for (size_t i = 0; i < T; i++) for (size_t j = i + 1; j < T; j++)
         sc[(h * T + i) * T + j] = -INFINITY;
-    orc_softmax(sc, pr, H * T, T);
+#pragma omp parallel for schedule(static) if (!omp_in_parallel_())
+    for (long h = 0; h < (long)H; h++) orc_softmax(sc + h * T * T, pr + h * T * T, T, T);
     /* out = P V: [T,T]x[T,hd]; V^T lets the same row-dot helper run, order of p unchanged for fast==0 */
     orc_batch_transpose(v3, vt, H, T, hd);
-    for (size_t h = 0; h < H; h++) head_matmul_nt(pr + h * T * T, vt + h * hd * T, o3 + h * T * hd, T, T, hd, fast);
+#pragma omp parallel for schedule(static) if (!omp_in_parallel_())
+    for (long h = 0; h < (long)H; h++) head_matmul_nt(pr + h * T * T, vt + h * hd * T, o3 + h * T * hd, T, T, hd, fast);
     orc_reshape_from_heads(o3, o2, T, H, hd);
     orc_linear(o2, wo, NULL, out, T, d, d, fast);
     free(q); free(k); free(v); free(q3); free(k3); free(v3); free(vt); free(sc); free(pr); free(o3); free(o2);
@@ -345,6 +360,17 @@ int orc_gpt_forward_batch(const orc_gpt_config* c, const float* params, const in
     size_t V = c->vocab, d = c->d_model, L = c->n_layer;
     int rc = 0;
     if (threads < 1) threads = 1;
+    if (B < (size_t)threads) {
+        /* fewer sequences than threads: run them one after another and split the rows / heads of each over the threads */
+#ifdef _OPENMP
+        omp_set_num_threads(threads);
+#endif
+        for (size_t b = 0; b < B; b++) {
+            int r = orc_gpt_forward_ids(c, params, ids + b * T, T, logits + b * T * V, taps ? taps + b * (L + 2) * T * d : NULL, fast);
+            if (r != 0) rc = r;
+        }
+        return rc;
+    }
 #pragma omp parallel for schedule(dynamic, 1) num_threads(threads)
     for (long b = 0; b < (long)B; b++) {
         int r = orc_gpt_forward_ids(c, params, ids + (size_t)b * T, T, logits + (size_t)b * T * V,

@@ -59,6 +59,8 @@ EXT_SYMBOLS = {
     "sptorch_ext_timer_end": (_i, [C.POINTER(C.c_float)]),
     "sptorch_ext_flush_l2": (_i, []),
     "sptorch_ext_device_status": (C.c_uint32, []),
+    "sptorch_ext_prof_enable": (_i, [_i]),
+    "sptorch_ext_prof_read": (_i, [C.POINTER(C.c_float), C.POINTER(C.c_uint32), _i]),
     "sptorch_ext_f32_to_bf16": (_i, [_vp, _vp, _sz]),
     "sptorch_ext_bf16_to_f32": (_i, [_vp, _vp, _sz]),
     "sptorch_ext_sum_f32": (_i, [_vp, _sz, C.POINTER(C.c_float)]),

@@ -49,9 +49,10 @@ int attention_materialized(const void* q, const void* k, const void* vt, long lo
     s.sC1 = (long long)Tn * Tn; s.sC2 = (long long)H * Tn * Tn;
     s.mode = mode; s.out_dtype = dtype; s.causal_lower = 1;
     GemmPlan ps;
-    if (gemm_plan(s, &ps) || gemm_run(ps)) return 1;
+    if (gemm_plan(s, &ps)) return 1;
+    { ProfScope pr(PROF_ATTN_GEMM); if (gemm_run(ps)) return 1; }
     // scale -> mask -> softmax exactly in the reference's order (crates/nn/src/lib.rs:614-632)
-    if (sptorch_ext_causal_softmax(scores, scores, (size_t)B * H, (size_t)Tn, 1.0f / sqrtf((float)hd), dtype)) return 1;
+    { ProfScope pr(PROF_SOFTMAX); if (sptorch_ext_causal_softmax(scores, scores, (size_t)B * H, (size_t)Tn, 1.0f / sqrtf((float)hd), dtype)) return 1; }
     GemmDesc o;
     o.A = scores; o.B = vt; o.C = out;
     o.M = Tn; o.N = hd; o.K = Tn;
@@ -62,7 +63,8 @@ int attention_materialized(const void* q, const void* k, const void* vt, long lo
     o.sC1 = hd; o.sC2 = (long long)Tn * ld_out;
     o.mode = mode; o.out_dtype = dtype; o.causal_k = 1;
     GemmPlan po;
-    if (gemm_plan(o, &po) || gemm_run(po)) return 1;
+    if (gemm_plan(o, &po)) return 1;
+    { ProfScope pr(PROF_ATTN_GEMM); if (gemm_run(po)) return 1; }
     return 0;
 }
 

@@ -87,12 +87,19 @@ static int linear(Gpt* g, const void* x, const void* w, const float* bias, const
     d.out_dtype = g->c.dtype;
     GemmPlan pl;
     if (gemm_plan(d, &pl)) return 1;
+    ProfScope ps(PROF_LINEAR);
     return gemm_run(pl);
+}
+
+static int ln(const void* x, const float* g_, const float* b_, void* out, size_t rows, size_t dim, float eps, int dt) {
+    ProfScope ps(PROF_LAYERNORM);
+    return layernorm_launch(x, g_, b_, out, rows, dim, eps, dt);
 }
 
 static int allreduce(Gpt* g, void* buf, size_t n) {
     if (g->c.tp_size <= 1) return 0;
     if (!g->ar) return fail("gpt: tensor parallel forward needs an all-reduce hook (sptorch_ext_gpt_set_allreduce)");
+    ProfScope ps(PROF_OTHER);
     if (g->ar(buf, n, g->c.dtype, (void*)rt().stream, g->ar_user)) return fail("gpt: all-reduce hook failed");
     note_submit();
     return 0;
@@ -103,7 +110,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head;
     const int dt = c.dtype;
     const bool lead = c.tp_rank == 0;
-    if (sptorch_ext_embedding_sum(g->tok, g->pos, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1;
+    { ProfScope ps(PROF_EMBED); if (sptorch_ext_embedding_sum(g->tok, g->pos, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1; }
     void* x = g->x; void* y = g->y;
     auto tap = [&](int i, const void* src) -> int {
         if (!g->taps_on) return 0;
@@ -113,7 +120,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
     if (tap(0, x)) return 1;
     for (int l = 0; l < c.n_layer; l++) {
         const Layer& w = g->L[l];
-        if (layernorm_launch(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
         // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
         if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
         // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
@@ -127,7 +134,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
             if (allreduce(g, y, (size_t)M * d)) return 1;
             std::swap(x, y);
         }
-        if (layernorm_launch(x, w.ln2g, w.ln2b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        if (ln(x, w.ln2g, w.ln2b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
         if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, M, d, Fl, Fl, EPI_GELU)) return 1;
         if (c.tp_size <= 1) {
             if (linear(g, g->f, w.w2, w.b2, x, x, M, Fl, d, d, EPI_NONE)) return 1;            // x += ffn
@@ -138,7 +145,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         }
         if (tap(l + 1, x)) return 1;
     }
-    if (layernorm_launch(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+    if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
     if (tap(c.n_layer + 1, g->h)) return 1;
     if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
     return 0;

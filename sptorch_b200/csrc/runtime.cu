@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <unordered_map>
+#include <vector>
 
 namespace spt {
 
@@ -22,6 +23,35 @@ static void* g_flush = nullptr;
 static const size_t kFlushBytes = 256u << 20;
 
 Runtime& rt() { return g_rt; }
+
+// ---- per-category event timing ----
+struct ProfRec { int cat; cudaEvent_t e0, e1; };
+static bool g_prof_on = false;
+static std::vector<ProfRec> g_prof_recs;
+static std::vector<cudaEvent_t> g_prof_free;
+static std::mutex g_prof_mu;
+static thread_local cudaEvent_t tl_open_e0 = nullptr;
+
+static cudaEvent_t prof_event() {
+    if (!g_prof_free.empty()) { cudaEvent_t e = g_prof_free.back(); g_prof_free.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+void prof_begin(int) {
+    if (!g_prof_on) return;
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    tl_open_e0 = prof_event();
+    cudaEventRecord(tl_open_e0, g_rt.stream);
+}
+void prof_end(int cat) {
+    if (!g_prof_on || !tl_open_e0) return;
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    cudaEvent_t e1 = prof_event();
+    cudaEventRecord(e1, g_rt.stream);
+    g_prof_recs.push_back({cat, tl_open_e0, e1});
+    tl_open_e0 = nullptr;
+}
 
 int fail(const char* fmt, ...) {
     va_list ap;
@@ -267,6 +297,30 @@ int sptorch_ext_flush_l2(void) {
     if (enter()) return 1;
     if (!g_flush) SPT_CUDA(cudaMalloc(&g_flush, kFlushBytes));
     SPT_CUDA(cudaMemsetAsync(g_flush, 0x5a, kFlushBytes, g_rt.stream));
+    return 0;
+}
+
+int sptorch_ext_prof_enable(int on) {
+    if (enter()) return 1;
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof_on = on != 0;
+    return 0;
+}
+
+// Waits for the stream, adds up the elapsed time and launch count of every category since the last
+// read into ms[PROF_NCAT] / launches[PROF_NCAT], and clears the records.
+int sptorch_ext_prof_read(float* ms, uint32_t* launches, int ncat) {
+    if (enter()) return 1;
+    SPT_CUDA(cudaStreamSynchronize(g_rt.stream));
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    for (int i = 0; i < ncat; i++) { if (ms) ms[i] = 0.0f; if (launches) launches[i] = 0; }
+    for (auto& r : g_prof_recs) {
+        float t = 0.0f;
+        cudaEventElapsedTime(&t, r.e0, r.e1);
+        if (r.cat >= 0 && r.cat < ncat) { if (ms) ms[r.cat] += t; if (launches) launches[r.cat] += 1; }
+        g_prof_free.push_back(r.e0); g_prof_free.push_back(r.e1);
+    }
+    g_prof_recs.clear();
     return 0;
 }
 

@@ -1,0 +1,85 @@
+"""GPU parity tests of the tcgen05 GEMM behind nn::Linear and attention, against the CPU oracle."""
+import numpy as np
+import pytest
+
+from conftest import relerr
+from sptorch_b200.backend import BF16, EPI_GELU, F32, MM_BF16, MM_F32, MM_TF32, bf16_bits_to_f32, f32_to_bf16_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(x):
+    return bf16_bits_to_f32(f32_to_bf16_bits(x)).reshape(np.shape(x))
+
+
+SHAPES = [(1, 8, 8), (128, 64, 64), (128, 64, 256), (129, 72, 257), (256, 768, 768), (512, 768, 3072), (300, 136, 200),
+          (512, 3072, 768), (64, 4096, 512), (1000, 40, 50257 // 64)]
+
+
+@pytest.mark.parametrize("M,K,N", SHAPES)
+def test_linear_tf32_and_bf16_vs_oracle(backend, oracle, M, K, N):
+    rng = np.random.default_rng(M + K + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((N, K))).astype(np.float32)
+    b = (0.01 * rng.standard_normal(N)).astype(np.float32)
+    ref = oracle.linear(x, w, b, fast=2)
+    assert relerr(backend.linear(x, w, b, mode=MM_TF32), ref) <= 2e-3          # north star: TF32 within 2e-3
+    assert relerr(backend.linear(x, w, b, mode=MM_BF16), ref) <= 2e-2          # north star: bf16 within 2e-2
+    assert relerr(backend.linear(x, w, b, mode=MM_F32), ref) <= 5e-6           # CUDA-core f32 FMA
+    # bf16 path against the oracle fed the same bf16-rounded operands: only the output rounding remains
+    refb = oracle.linear(_bf16(x), _bf16(w), b, fast=2)
+    assert relerr(backend.linear(x, w, b, mode=MM_BF16), refb) <= 2 ** -8 * 1.1
+    assert relerr(backend.linear(x, w, b, mode=MM_BF16, out_dtype=F32), refb) <= 1e-5
+
+
+def test_linear_fused_epilogues(backend, oracle):
+    rng = np.random.default_rng(1)
+    M, K, N = 200, 128, 328
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (0.05 * rng.standard_normal((N, K))).astype(np.float32)
+    b = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    lin = oracle.linear(x, w, b, fast=2)
+    ref = oracle.unary("gelu", lin) + r
+    assert relerr(backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_TF32), ref) <= 2e-3
+    assert relerr(backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_F32), ref) <= 5e-6
+    assert relerr(backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_BF16), ref) <= 2e-2
+    assert relerr(backend.linear(x, w, None, alpha=0.5, mode=MM_TF32), 0.5 * oracle.linear(x, w, None, fast=2)) <= 2e-3
+
+
+def test_linear_is_linear_at_full_size(backend):
+    """Size-independent property at a BASELINE config 2 shape (M 4096, K 768, N 3072): f(x1 + x2) = f(x1) + f(x2) and
+    integer-valued operands give exact integers."""
+    rng = np.random.default_rng(2)
+    M, K, N = 4096, 768, 3072
+    x = rng.integers(-4, 5, (M, K)).astype(np.float32)
+    w = rng.integers(-2, 3, (N, K)).astype(np.float32)
+    out = backend.linear(x, w, mode=MM_BF16, out_dtype=F32)
+    ref = (x.astype(np.int32) @ w.astype(np.int32).T).astype(np.float32)
+    assert np.array_equal(out, ref)                       # exact: every product and partial sum is a small integer
+    assert np.array_equal(backend.linear(x, w, mode=MM_TF32), ref)
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 64, 4, 32), (1, 256, 2, 64), (2, 128, 2, 128), (1, 1024, 1, 64), (3, 8, 2, 32)])
+def test_attention_vs_oracle(backend, oracle, B, T, H, hd):
+    rng = np.random.default_rng(B * T + hd)
+    d = H * hd
+    q, k, v = (rng.standard_normal((B, T, d)).astype(np.float32) for _ in range(3))
+    eye = np.eye(d, dtype=np.float32)
+    # oracle: the reference's MHA with identity projections is exactly the attention core
+    ref = np.stack([_mha_core(oracle, q[i], k[i], v[i], H) for i in range(B)])
+    assert relerr(backend.attention_causal(q, k, v, H, dtype=F32), ref) <= 2e-3
+    assert relerr(backend.attention_causal(q, k, v, H, dtype=BF16), ref) <= 2e-2
+    del eye
+
+
+def _mha_core(oracle, q, k, v, H):
+    T, d = q.shape
+    hd = d // H
+    out = np.empty_like(q)
+    for h in range(H):
+        sl = slice(h * hd, (h + 1) * hd)
+        s = oracle.matmul(q[:, sl], oracle.transpose(k[:, sl]), f64=True)[None]
+        p = oracle.causal_softmax(s, 1.0 / np.sqrt(np.float32(hd)))[0]
+        out[:, sl] = oracle.matmul(p, v[:, sl], f64=True)
+    return out

@@ -1,0 +1,132 @@
+"""GPU parity tests of the whole GPT forward against the CPU oracle and the committed golden logits
+(BASELINE config 1), per layer and on the logits, in both arithmetic modes."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import relerr
+from sptorch_b200 import synth
+from sptorch_b200.backend import BF16, F32
+from sptorch_b200.gpt import GPT
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+TOL = {F32: 2e-3, BF16: 2e-2}      # north star: max relative error per layer and on the logits
+
+
+def _model(backend, cfg, dtype, max_batch, params, index):
+    m = GPT(backend, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=dtype, max_batch=max_batch)
+    m.load_flat(params, index)
+    return m
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_c1_tiny_forward_vs_oracle_per_layer(backend, oracle, dtype):
+    cfg = synth.CONFIGS["c1_tiny"]
+    params, index = synth.gpt_params(cfg, 0, randomize_affine=True)     # non-trivial gamma/beta/bias
+    ids = synth.randint(1, 8 * 64, 256).reshape(8, 64)
+    ref, taps = oracle.gpt_forward(cfg, params, ids, fast=0, threads=oracle.max_threads(), want_taps=True)
+    m = _model(backend, cfg, dtype, 8, params, index)
+    m.enable_taps()
+    out = m.forward(ids)
+    assert relerr(out, ref) <= TOL[dtype]
+    for i in range(cfg["n_layer"] + 2):
+        assert relerr(m.tap(i, 8 * 64).reshape(8, 64, -1), taps[:, i]) <= TOL[dtype], f"layer tap {i}"
+    # argmax agreement on tokens whose top-1 margin in the oracle exceeds twice the error bound
+    top2 = np.sort(ref, -1)[..., -2:]
+    clear = (top2[..., 1] - top2[..., 0]) > 2 * TOL[dtype] * np.abs(ref).max()
+    assert (out.argmax(-1) == ref.argmax(-1))[clear].all()
+    m.close()
+
+
+def test_c1_tiny_baseline_init_vs_golden(backend):
+    """BASELINE config 1 exactly (biases 0, gamma 1, beta 0) against the committed fixture."""
+    g = np.load(os.path.join(GOLDEN, "c1_tiny.npz"))
+    cfg = synth.CONFIGS["c1_tiny"]
+    params, index = synth.gpt_params(cfg, 0)
+    m = _model(backend, cfg, F32, 2, params, index)
+    m.enable_taps()
+    out = m.forward(g["ids"])
+    scale = np.abs(g["logits_first64"]).max()
+    assert np.abs(out[:, :, :64] - g["logits_first64"]).max() <= 2e-3 * scale
+    taps = g["taps_seq0"]
+    for i in range(taps.shape[0]):
+        assert relerr(m.tap(i, 2 * 64).reshape(2, 64, -1)[0], taps[i]) <= 2e-3
+    m.close()
+
+
+def test_forward_ids_single_sequence_and_prefix_stability(backend, oracle):
+    # GPT::forward_ids semantics + the reference's self-consistency check (crates/nn/src/lib.rs:3749-3766):
+    # logits of a prefix do not depend on later tokens, and batching does not change a sequence's result
+    cfg = dict(vocab=96, d_model=64, n_layer=2, n_head=2, d_ff=128, seq_len=32)
+    params, index = synth.gpt_params(cfg, 3, randomize_affine=True)
+    ids = synth.randint(5, 4 * 32, 96).reshape(4, 32)
+    m = _model(backend, cfg, F32, 4, params, index)
+    full = m.forward(ids)
+    one = m.forward_ids(ids[2])
+    assert np.array_equal(one, full[2])
+    pre = m.forward_ids(ids[2, :16])
+    assert np.abs(pre - full[2, :16]).max() <= 1e-5 * max(1.0, np.abs(full).max())
+    assert relerr(full, oracle.gpt_forward(cfg, params, ids)) <= 2e-3
+    m.close()
+
+
+def test_forward_rejects_bad_shapes_and_ids(backend):
+    from sptorch_b200.backend import HalError
+    cfg = dict(vocab=32, d_model=32, n_layer=1, n_head=2, d_ff=64, seq_len=16)
+    params, index = synth.gpt_params(cfg, 0)
+    m = _model(backend, cfg, F32, 2, params, index)
+    with pytest.raises(HalError):
+        m.forward(np.zeros((1, 32), dtype=np.int64))          # longer than seq_len (the reference asserts)
+    with pytest.raises(HalError):
+        m.forward(np.zeros((3, 16), dtype=np.int64))          # more tokens than the activations hold
+    with pytest.raises(HalError):
+        m.forward(np.full((1, 16), 99, dtype=np.int64))       # id outside the vocabulary
+    backend.synchronize()
+    assert np.isfinite(m.forward(np.zeros((1, 16), dtype=np.int64))).all()
+    with pytest.raises(HalError):
+        m.set_param("blocks.0.attn.wq.weight", np.zeros(5, np.float32))
+    with pytest.raises(HalError):
+        m.set_param("no.such.param", np.zeros(5, np.float32))
+    m.close()
+
+
+def test_host_buffer_call_matches_device_call(backend):
+    import ctypes as C
+    cfg = dict(vocab=1000, d_model=64, n_layer=2, n_head=2, d_ff=128, seq_len=32)
+    params, index = synth.gpt_params(cfg, 1)
+    ids = synth.randint(2, 6 * 32, 1000).reshape(6, 32).astype(np.int32)
+    m = _model(backend, cfg, BF16, 6, params, index)
+    ref = m.forward(ids)
+    lib = backend.lib
+    pin_ids = lib.sptorch_ext_alloc_pinned(ids.nbytes)
+    pin_out = lib.sptorch_ext_alloc_pinned(6 * 32 * 1000 * 2)
+    C.memmove(pin_ids, ids.ctypes.data, ids.nbytes)
+    from sptorch_b200.backend import bf16_bits_to_f32
+    for chunk in (6, 4, 1):
+        C.memset(pin_out, 0, 6 * 32 * 1000 * 2)
+        m.forward_host(pin_ids, 6, 32, pin_out, chunk)
+        raw = np.ctypeslib.as_array(C.cast(pin_out, C.POINTER(C.c_uint16)), shape=(6 * 32 * 1000,)).copy()
+        assert np.array_equal(bf16_bits_to_f32(raw).reshape(6, 32, 1000), ref), f"chunk {chunk}"
+    lib.sptorch_ext_free_pinned(pin_ids)
+    lib.sptorch_ext_free_pinned(pin_out)
+    m.close()
+
+
+def test_gpt2_small_shape_layer_slice_vs_oracle(backend, oracle):
+    """BASELINE config 4 dimensions (d 768, 12 heads, d_ff 3072, ctx 1024, vocab 50257) with 2 layers and 2
+    sequences, bf16, against the oracle (blocked f32) per layer and on the logits."""
+    cfg = dict(synth.CONFIGS["c4_gpt2s"])
+    cfg["n_layer"] = 2
+    params, index = synth.gpt_params(cfg, 0, residual_scale=True)
+    ids = synth.randint(1, 2 * 1024, cfg["vocab"]).reshape(2, 1024)
+    ref, taps = oracle.gpt_forward(cfg, params, ids, fast=1, threads=oracle.max_threads(), want_taps=True)
+    m = _model(backend, cfg, BF16, 2, params, index)
+    m.enable_taps()
+    out = m.forward(ids)
+    assert relerr(out, ref) <= 2e-2
+    for i in range(cfg["n_layer"] + 2):
+        assert relerr(m.tap(i, 2 * 1024).reshape(2, 1024, -1), taps[:, i]) <= 2e-2, f"layer tap {i}"
+    m.close()

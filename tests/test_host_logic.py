@@ -1,0 +1,104 @@
+"""Host-side logic that needs no GPU: seeded inputs, bf16 conversion, parameter layout, batch sharding
+(single process and two gloo ranks)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_synth_is_counter_based_and_deterministic():
+    from sptorch_b200 import synth
+    a = synth.normal(0, 10000, 0.0, 0.02)
+    b = synth.normal(0, 10000, 0.0, 0.02)
+    assert np.array_equal(a, b)
+    assert np.array_equal(synth.normal(0, 100, start=500), synth.normal(0, 1000)[500:600])
+    assert abs(float(a.std()) - 0.02) < 1e-3 and abs(float(a.mean())) < 1e-3
+    ids = synth.randint(1, 100000, 50257)
+    assert ids.min() >= 0 and ids.max() < 50257 and len(np.unique(ids)) > 40000
+    assert not np.array_equal(synth.normal(0, 100), synth.normal(1, 100))
+
+
+def test_param_layout_matches_named_parameters_order():
+    # crates/nn/src/lib.rs:1382-1392
+    from sptorch_b200 import synth
+    names = [n for n, _ in synth.gpt_param_layout(256, 128, 2, 4, 512, 64)]
+    assert names[:2] == ["token_emb.weight", "pos_emb.weight"]
+    assert names[2:14] == ["blocks.0." + s for s in ("ln1.gamma", "ln1.beta", "attn.wq.weight", "attn.wk.weight", "attn.wv.weight",
+                                                     "attn.wo.weight", "ln2.gamma", "ln2.beta", "ffn_up.weight", "ffn_up.bias",
+                                                     "ffn_down.weight", "ffn_down.bias")]
+    assert names[-3:] == ["ln_f.gamma", "ln_f.beta", "lm_head.weight"]
+    cfg = synth.CONFIGS["c4_gpt2s"]
+    total = sum(int(np.prod(s)) for _, s in synth.gpt_param_layout(cfg["vocab"], cfg["d_model"], cfg["n_layer"], cfg["n_head"], cfg["d_ff"], cfg["seq_len"]))
+    assert total == 163_000_320      # untied head
+
+
+def test_bf16_round_to_nearest_even():
+    from sptorch_b200.backend import bf16_bits_to_f32, f32_to_bf16_bits
+    x = np.array([1.0, 1.00390625, 1.01171875, -2.5, 3.0e38, 1e-40], dtype=np.float32)
+    back = bf16_bits_to_f32(f32_to_bf16_bits(x))
+    assert back[0] == 1.0
+    assert back[1] == 1.0            # exactly half way between 1.0 and 1.0078125: ties to even
+    assert back[2] == np.float32(1.015625)
+    assert back[3] == -2.5
+    import torch
+    t = torch.from_numpy(np.random.default_rng(0).standard_normal(10000).astype(np.float32))
+    assert np.array_equal(bf16_bits_to_f32(f32_to_bf16_bits(t.numpy())), t.to(torch.bfloat16).to(torch.float32).numpy())
+
+
+def test_shard_rule_remainder_to_first_ranks():
+    # DataParallel::scatter, crates/distributed/src/data_parallel.rs:21-37
+    sys.path.insert(0, ROOT)
+    import bench
+    assert [bench.shard(64, 8, r) for r in range(8)] == [(8 * r, 8) for r in range(8)]
+    parts = [bench.shard(10, 4, r) for r in range(4)]
+    assert parts == [(0, 3), (3, 3), (6, 2), (8, 2)]
+    assert sum(n for _, n in parts) == 10
+    assert [bench.shard(2, 4, r)[1] for r in range(4)] == [1, 1, 0, 0]
+
+
+def _gloo_worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import torch
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import binding as O
+    from sptorch_b200 import synth
+    cfg = dict(vocab=64, d_model=32, n_layer=1, n_head=2, d_ff=64, seq_len=16)
+    p, _ = synth.gpt_params(cfg, 0)
+    ids = synth.randint(1, 6 * 16, 64).reshape(6, 16)
+    s, n = bench.shard(6, world, rank)
+    mine = O.gpt_forward(cfg, p, ids[s:s + n])           # this rank's sequences only: no collective in the forward
+    # checksum exchange: sum of all ranks' logits equals the unsharded run's
+    t = torch.tensor([float(mine.astype(np.float64).sum()), float(n)], dtype=torch.float64)
+    dist.all_reduce(t)
+    # timing convention of the bench: max over ranks
+    tm = torch.tensor([0.1 * (rank + 1)], dtype=torch.float64)
+    dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        full = O.gpt_forward(cfg, p, ids)
+        q.put((float(t[0]), float(full.astype(np.float64).sum()), float(t[1]), float(tm[0])))
+    dist.destroy_process_group()
+
+
+def test_batch_sharding_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_gloo_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    sharded_sum, full_sum, n, tmax = got
+    assert n == 6
+    assert abs(sharded_sum - full_sum) < 1e-6 * max(1.0, abs(full_sum))
+    assert abs(tmax - 0.2) < 1e-12
