@@ -49,45 +49,50 @@ def read_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons read through NVML every 20 ms on a thread while the timed region runs
+    (read-only queries; nothing is set)."""
 
     def __init__(self, index):
-        self.index, self.p = index, None
+        self.index, self.samples, self._stop, self._t = index, [], None, None
 
     def start(self):
+        import threading
         try:
-            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
-                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.p = None
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self._max = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # noqa: BLE001
+            self._err = repr(e)
+            return
+        self._stop = threading.Event()
+
+        def loop():
+            while not self._stop.is_set():
+                try:
+                    sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                    rs = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h) if hasattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons") \
+                        else pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    pw = pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0
+                    self.samples.append((sm, rs, pw))
+                except Exception:  # noqa: BLE001
+                    pass
+                self._stop.wait(0.02)
+
+        self._t = threading.Thread(target=loop, daemon=True)
+        self._t.start()
 
     def stop(self):
-        if self.p is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.p.terminate()
-        try:
-            out, _ = self.p.communicate(timeout=5)
-        except Exception:
-            self.p.kill()
-            out = ""
-        sm, mx, reasons = [], [], set()
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if self._t is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "_err", "?")]}
+        self._stop.set()
+        self._t.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": float(self._max), "reasons": ["no samples"]}
+        bits = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
+        reasons = sorted(name for name, bit in bits.items() if any(r & bit for _, r, _ in self.samples))
+        return {"sm_mhz": statistics.median(sm for sm, _, _ in self.samples), "sm_max_mhz": float(self._max), "reasons": reasons,
+                "samples": len(self.samples), "power_w_max": max(p for _, _, p in self.samples)}
 
 
 def dist_env():
@@ -226,7 +231,7 @@ def run_ours(args):
     out_bytes = nseq * T * V * 2
     out_pinned = lib.sptorch_ext_alloc_pinned(out_bytes)
     e2e = None
-    if ids_pinned and out_pinned:
+    if ids_pinned and out_pinned and args.e2e_steps > 0:
         C.memmove(ids_pinned, ids.ctypes.data, ids.nbytes)
         e2e_steps = max(1, min(args.steps, args.e2e_steps))
         model.forward_host(ids_pinned, nseq, T, out_pinned, chunk)   # warm-up (allocates the staging buffers)
@@ -282,6 +287,103 @@ def run_ours(args):
     return 0
 
 
+def _fill(b, buf, n_elems, es, seed, mean=0.0, std=1.0):
+    """Fill a device buffer with seeded normals: a 4 Mi-element host block generated once and tiled."""
+    from sptorch_b200.backend import f32_to_bf16_bits
+    block = synth.normal(seed, min(n_elems, 1 << 22), mean, std)
+    host = block if es == 4 else f32_to_bf16_bits(block)
+    off = 0
+    while off < n_elems:
+        m = min(host.size, n_elems - off)
+        b._check(b.lib.sptorch_ext_copy_h2d_bytes(host.ctypes.data, buf.handle + off * es, m * es), "fill")
+        off += m
+    b.synchronize()
+
+
+def _time_op(b, fn, iters, warmup=3):
+    """Median device time of fn() over iters launches, L2 flushed (256 MiB overwrite) before each."""
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        b.flush_l2()
+        b.timer_begin()
+        fn()
+        ts.append(b.timer_end())
+    return statistics.median(ts), min(ts)
+
+
+def run_sweep(args):
+    """BASELINE config 2 (standalone Linear) and config 3 (row ops): one JSON line per case."""
+    os.environ.setdefault("SPTORCH_B200_DEVICE", "0")
+    from sptorch_b200.backend import BF16, F32, MM_BF16, MM_TF32, FfiBackend
+    b = FfiBackend.load()
+    lib = b.lib
+    peaks = read_peaks()
+    out = []
+    if args.sweep in ("linear", "all"):
+        shapes = [(M, K, N) for M in (512, 4096, 16384) for (K, N) in ((768, 768), (768, 3072), (3072, 768), (4096, 4096))]
+        if args.shape:
+            shapes = [tuple(int(v) for v in args.shape.split(","))]
+        for (M, K, N) in shapes:
+            for mode, name, es in ((MM_BF16, "bf16", 2), (MM_TF32, "tf32", 4)):
+                x, w, y = b.alloc(M * K, es), b.alloc(N * K, es), b.alloc(M * N, es)
+                bias = b.alloc(N)
+                _fill(b, x, M * K, es, 1); _fill(b, w, N * K, es, 2, std=0.02); _fill(b, bias, N, 4, 3, std=0.01)
+                fn = lambda: b._check(lib.sptorch_ext_linear(x.handle, w.handle, bias.handle, None, y.handle, M, K, N, 0, C.c_float(1.0), 0, mode,
+                                                             BF16 if mode == MM_BF16 else F32), "linear")
+                med, best = _time_op(b, fn, args.iters)
+                tf = 2.0 * M * K * N / (med * 1e-3) / 1e12
+                peak = peaks["tf"] if mode == MM_BF16 else peaks["tf"] / 2
+                out.append({"op": "linear", "M": M, "K": K, "N": N, "mode": name, "ms": med, "ms_best": best, "tflops": tf,
+                            "frac": tf / peak, "peak": peak, "peak_note": f"{peaks['source']} burst cuBLAS bf16" + ("" if mode == MM_BF16 else " / 2 (TF32 runs at half the bf16 rate)"),
+                            "frac_nominal": tf / (2250.0 if mode == MM_BF16 else 1125.0)})
+                print(json.dumps(out[-1]), flush=True)
+                for buf in (x, w, y, bias):
+                    buf.free()
+    if args.sweep in ("rowops", "all"):
+        for dim in (768, 2048, 4096):
+            for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+                rows = 65536
+                x, y = b.alloc(rows * dim, es), b.alloc(rows * dim, es)
+                g, be = b.upload(np.ones(dim, np.float32)), b.upload(np.zeros(dim, np.float32))
+                _fill(b, x, rows * dim, es, 4, mean=0.5, std=3.0)
+                fn = lambda: b._check(lib.sptorch_ext_layernorm(x.handle, g.handle, be.handle, y.handle, rows, dim, C.c_float(1e-5), dt), "layernorm")
+                med, best = _time_op(b, fn, args.iters)
+                nbytes = 2 * rows * dim * es + 2 * dim * 4
+                out.append({"op": "layernorm", "rows": rows, "dim": dim, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+                            "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
+                print(json.dumps(out[-1]), flush=True)
+                for buf in (x, y, g, be):
+                    buf.free()
+        for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+            B_, H_, T_ = 16, 12, 1024
+            n = B_ * H_ * T_ * T_
+            x, y = b.alloc(n, es), b.alloc(n, es)
+            _fill(b, x, n, es, 5, std=2.0)
+            fn = lambda: b._check(lib.sptorch_ext_causal_softmax(x.handle, y.handle, B_ * H_, T_, C.c_float(1.0), dt), "causal_softmax")
+            med, best = _time_op(b, fn, args.iters)
+            nbytes = (T_ * (T_ + 1) // 2 + T_ * T_) * B_ * H_ * es
+            out.append({"op": "causal_softmax", "shape": [B_, H_, T_, T_], "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+                        "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes,
+                        "full_read_bytes": 2 * n * es})
+            print(json.dumps(out[-1]), flush=True)
+            x.free(); y.free()
+        for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+            n = 64 << 20
+            x, y = b.alloc(n, es), b.alloc(n, es)
+            _fill(b, x, n, es, 6)
+            fn = lambda: b._check(lib.sptorch_ext_gelu(x.handle, y.handle, n, dt), "gelu")
+            med, best = _time_op(b, fn, args.iters)
+            nbytes = 2 * n * es
+            out.append({"op": "gelu", "n": n, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+                        "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
+            print(json.dumps(out[-1]), flush=True)
+            x.free(); y.free()
+    b.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -292,7 +394,12 @@ def main():
     ap.add_argument("--chunk", type=int, default=8, help="sequences per micro-batch of the host-buffer call")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
+    ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
+    ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
+    if args.sweep:
+        return run_sweep(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
