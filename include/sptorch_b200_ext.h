@@ -99,6 +99,8 @@ int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const
  * q, k, v: [B*T, ld] with head h at columns h*hd..; out [B*T, H*hd].  dtype BF16 runs the fused
  * kernel; F32 runs scores -> causal softmax -> PV through the TF32 GEMM with a caller-visible
  * workspace of sptorch_ext_attention_workspace() bytes. */
+/* 0 (default): bf16 with head_dim 64 or 128 runs the fused kernel, everything else the materialised form; 1: always materialised */
+int sptorch_ext_set_attention_mode(int mode);
 size_t sptorch_ext_attention_workspace(size_t B, size_t T, size_t H, size_t hd, int dtype);
 int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, void* out, void* workspace,
                                  size_t B, size_t T, size_t H, size_t hd, size_t ld_qkv, int dtype);

@@ -33,6 +33,20 @@ __global__ void head_transpose_kernel(const T* __restrict__ v, T* __restrict__ v
 
 int attention_materialized(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
                            void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
+bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
+int attention_fused(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch, void* out,
+                    int B, int T, int H, int hd, long long ld_qk, long long ld_out);
+
+static std::atomic<int> g_attn_mode{0};   // 0 = fused kernel whenever it applies, 1 = always the materialised three-launch form
+int attention_mode() { return g_attn_mode.load(); }
+
+// Picks the fused kernel (bf16, head_dim 64/128) or the materialised form.
+int attention_dispatch(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
+                       void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype) {
+    if (dtype == BF16 && g_attn_mode.load() == 0 && attention_fused_supported(Tn, hd, ld_qk, vt_ld, vt_s_head, vt_s_batch))
+        return attention_fused(q, k, vt, vt_ld, vt_s_head, vt_s_batch, out, B, Tn, H, hd, ld_qk, ld_out);
+    return attention_materialized(q, k, vt, vt_ld, vt_s_head, vt_s_batch, out, scores, B, Tn, H, hd, ld_qk, ld_out, dtype);
+}
 
 // q,k: [B*T, ld_qk]; vt: V^T with element (b,h,e,t) at vt[b*vt_s_batch + h*vt_s_head + e*vt_ld + t];
 // scores: workspace of B*H*T*T elements; out: [B*T, ld_out]
@@ -99,8 +113,14 @@ int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, vo
     else
         head_transpose_kernel<float><<<grid, dim3(32, 8), 0, rt().stream>>>((const float*)v, (float*)vt, (int)T, (int)H, (int)hd, (long long)ld_qkv);
     SPT_LAUNCH_CHECK("head_transpose");
-    return attention_materialized(q, k, vt, (long long)T, (long long)(hd * T), (long long)(H * hd * T), out, scores, (int)B, (int)T, (int)H,
-                                  (int)hd, (long long)ld_qkv, (long long)(H * hd), dtype);
+    return attention_dispatch(q, k, vt, (long long)T, (long long)(hd * T), (long long)(H * hd * T), out, scores, (int)B, (int)T, (int)H,
+                              (int)hd, (long long)ld_qkv, (long long)(H * hd), dtype);
+}
+
+int sptorch_ext_set_attention_mode(int mode) {
+    if (mode != 0 && mode != 1) return fail("set_attention_mode: 0 = fused when possible, 1 = materialised");
+    g_attn_mode.store(mode);
+    return 0;
 }
 
 }  // extern "C"

@@ -39,6 +39,8 @@ Runtime& rt();
 int fail(const char* fmt, ...);
 // Makes the runtime's device current for the calling thread; non-zero if the library is not initialised.
 int enter();
+// Waits for the library stream without consuming the sticky error flag (internal uploads use this).
+int stream_wait();
 inline void note_submit() { rt().submitted.fetch_add(1, std::memory_order_relaxed); }
 
 #define SPT_CUDA(expr)                                                                     \

@@ -179,14 +179,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
     } else {
         // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp % 4) ----------------
+        // tcgen05.ld hands thread i the 32 columns of ROW i, so a direct store would scatter every warp
+        // instruction over 32 cache lines.  Each 32x32 f32 chunk is therefore turned through a 4 KB
+        // per-warp staging block (16-byte granules XOR-swizzled by row, conflict free both ways) so that
+        // 8 (f32) or 4 (bf16) neighbouring lanes finish one row segment: bias, GELU and the residual are
+        // applied in that layout, and global loads/stores are whole 32-byte sectors of consecutive addresses.
         const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
+        float* stage = reinterpret_cast<float*>(smem + kStages * STAGE_BYTES + 256) + (warp - 2) * 1024;
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
         constexpr int kOutVec = 16 / (int)sizeof(TOut);      // elements per 128-bit store
+        constexpr int LPR = 32 / kOutVec;                    // lanes per row segment: 8 (f32) or 4 (bf16)
+        constexpr int RPI = 32 / LPR;                        // rows per warp instruction: 4 or 8
         const bool vec_ok = (p.ldc % kOutVec == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                            (p.sC1 % kOutVec == 0) && (p.sC2 % kOutVec == 0) &&
-                            (p.R == nullptr || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0);
+                            (p.sC1 % kOutVec == 0) && (p.sC2 % kOutVec == 0) && (p.N % kOutVec == 0) &&
+                            (p.R == nullptr || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
+                            (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
+        const int sub = lane / LPR;                          // row within the instruction's row group
+        const int cg = (lane % LPR) * kOutVec;               // first of this lane's kOutVec columns inside the chunk
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             int z, tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
@@ -196,80 +206,97 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogueWait);
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + row_in_tile;
-            const bool row_ok = row < p.M;
             const long long zoff = (long long)z1 * p.sC1 + (long long)z2 * p.sC2;
-            TOut* crow = reinterpret_cast<TOut*>(p.C) + zoff + (long long)row * p.ldc;
-            const TOut* rrow = p.R ? reinterpret_cast<const TOut*>(p.R) + zoff + (long long)row * p.ldc : nullptr;
+            TOut* cbase = reinterpret_cast<TOut*>(p.C) + zoff;
+            const TOut* rbase = p.R ? reinterpret_cast<const TOut*>(p.R) + zoff : nullptr;
+            const int row_base = m0 + quarter * 32;          // first row of this warp's 32
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            const int n_chunks = min(BN / 32, (p.N - n0 + 31) / 32);
+            uint32_t v[32];
+            tmem_ld_32x32(t_row, v);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = 0; c < n_chunks; c++) {
                 const int col0 = n0 + c * 32;
-                if (col0 >= p.N) break;                        // uniform over the warp
-                uint32_t v[32];
-                tmem_ld_32x32(t_row + c * 32, v);
                 tmem_ld_wait();
-                float f[32];
+                // stage: thread = row `lane`, granule g (4 floats) lands at position g ^ (lane & 7)
 #pragma unroll
-                for (int j = 0; j < 32; j++) f[j] = __uint_as_float(v[j]) * p.alpha;
-                const bool full = col0 + 32 <= p.N;
-                if (p.bias) {
-                    if (full) {
+                for (int g = 0; g < 8; g++)
+                    *reinterpret_cast<float4*>(stage + lane * 32 + ((g ^ (lane & 7)) << 2)) =
+                        make_float4(__uint_as_float(v[4 * g]) * p.alpha, __uint_as_float(v[4 * g + 1]) * p.alpha,
+                                    __uint_as_float(v[4 * g + 2]) * p.alpha, __uint_as_float(v[4 * g + 3]) * p.alpha);
+                if (c + 1 < n_chunks) tmem_ld_32x32(t_row + (c + 1) * 32, v);     // overlaps the write-out below
+                else { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }    // accumulator drained: MMA may reuse it
+                __syncwarp();
+                if (vec_ok) {
+                    const int col = col0 + cg;
+                    const bool col_ok = col < p.N;                                // N % kOutVec == 0: whole vector in or out
+                    float bv[kOutVec];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 b = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
-                            f[j] += b.x; f[j + 1] += b.y; f[j + 2] += b.z; f[j + 3] += b.w;
+                    for (int j = 0; j < kOutVec; j++) bv[j] = 0.0f;
+                    if (p.bias && col_ok) {
+#pragma unroll
+                        for (int j = 0; j < kOutVec; j += 4) {
+                            float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col + j));
+                            bv[j] = b4.x; bv[j + 1] = b4.y; bv[j + 2] = b4.z; bv[j + 3] = b4.w;
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (col0 + j < p.N) f[j] += __ldg(p.bias + col0 + j);
                     }
-                }
-                if (p.epilogue == EPI_GELU) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) f[j] = (sizeof(TOut) == 2) ? gelu_fast(f[j]) : gelu_exact(f[j]);
-                }
-                if (row_ok) {
-                    if (full && vec_ok) {
-                        if constexpr (sizeof(TOut) == 2) {
+                    for (int i = 0; i < 32 / RPI; i++) {
+                        const int rr = i * RPI + sub;
+                        const int row = row_base + rr;
+                        float f[kOutVec];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                if (rrow) {
-                                    uint4 rv = *reinterpret_cast<const uint4*>(rrow + col0 + j);
+                        for (int j = 0; j < kOutVec; j += 4) {
+                            const int g = (cg + j) >> 2;
+                            float4 x4 = *reinterpret_cast<const float4*>(stage + rr * 32 + ((g ^ (rr & 7)) << 2));
+                            f[j] = x4.x + bv[j]; f[j + 1] = x4.y + bv[j + 1]; f[j + 2] = x4.z + bv[j + 2]; f[j + 3] = x4.w + bv[j + 3];
+                        }
+                        if (p.epilogue == EPI_GELU) {
+#pragma unroll
+                            for (int j = 0; j < kOutVec; j++) f[j] = (sizeof(TOut) == 2) ? gelu_fast(f[j]) : gelu_exact(f[j]);
+                        }
+                        if (row < p.M && col_ok) {
+                            const long long off = (long long)row * p.ldc + col;
+                            if constexpr (sizeof(TOut) == 2) {
+                                if (rbase) {
+                                    uint4 rv = *reinterpret_cast<const uint4*>(rbase + off);
                                     const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
 #pragma unroll
-                                    for (int q = 0; q < 4; q++) { float2 g = __bfloat1622float2(rh[q]); f[j + 2 * q] += g.x; f[j + 2 * q + 1] += g.y; }
+                                    for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[2 * q] += g2.x; f[2 * q + 1] += g2.y; }
                                 }
                                 uint4 o;
                                 __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-                                for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(f[j + 2 * q], f[j + 2 * q + 1]);
-                                *reinterpret_cast<uint4*>(crow + col0 + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                if (rrow) {
-                                    float4 rv = *reinterpret_cast<const float4*>(rrow + col0 + j);
-                                    f[j] += rv.x; f[j + 1] += rv.y; f[j + 2] += rv.z; f[j + 3] += rv.w;
+                                for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                                *reinterpret_cast<uint4*>(cbase + off) = o;
+                            } else {
+                                if (rbase) {
+                                    float4 rv = *reinterpret_cast<const float4*>(rbase + off);
+                                    f[0] += rv.x; f[1] += rv.y; f[2] += rv.z; f[3] += rv.w;
                                 }
-                                *reinterpret_cast<float4*>(crow + col0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (col0 + j < p.N) {
-                                float o = f[j];
-                                if (rrow) o += (float)rrow[col0 + j];
-                                crow[col0 + j] = (TOut)o;
+                                *reinterpret_cast<float4*>(cbase + off) = make_float4(f[0], f[1], f[2], f[3]);
                             }
                         }
                     }
+                } else {
+                    // unaligned output (odd N or ldc): lane = column, one row per iteration, scalar accesses
+                    const int col = col0 + lane;
+                    const float bcol = (p.bias && col < p.N) ? __ldg(p.bias + col) : 0.0f;
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr++) {
+                        const int row = row_base + rr;
+                        float x = stage[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))] + bcol;
+                        if (p.epilogue == EPI_GELU) x = (sizeof(TOut) == 2) ? gelu_fast(x) : gelu_exact(x);
+                        if (row < p.M && col < p.N) {
+                            const long long off = (long long)row * p.ldc + col;
+                            if (rbase) x += (float)rbase[off];
+                            cbase[off] = (TOut)x;
+                        }
+                    }
                 }
+                __syncwarp();                                  // staging block is rewritten by the next chunk
             }
-            tc_fence_before();
-            mbar_arrive(bar_tempty + 8 * acc);
+            if (n_chunks <= 0) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
@@ -357,7 +384,7 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
     return 0;
 }
 
-static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 1024 /*alignment slack*/ + 256 /*barriers*/; }
+static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * 4096 /*epilogue staging*/; }
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;

@@ -20,8 +20,10 @@
 
 namespace spt {
 
-int attention_materialized(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
-                           void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
+int attention_dispatch(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
+                       void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
+bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
+int attention_mode();
 
 struct Layer {
     float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;
@@ -60,7 +62,7 @@ static int upload_rows(Gpt* g, void* dst_model_dtype, const float* host, size_t 
     if (!tmp) return 1;
     int rc = sptorch_ext_copy_h2d_bytes(host, tmp, n * 4);
     if (!rc) rc = sptorch_ext_f32_to_bf16(tmp, dst_model_dtype, n);
-    if (!rc) rc = sptorch_sync();      // host buffer and tmp may be released after return
+    if (!rc) rc = stream_wait();       // host buffer and tmp may be released after return
     sptorch_free(tmp);
     return rc;
 }
@@ -125,7 +127,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
         // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
         if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
-        if (attention_materialized(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
+        if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
                                    /*batch*/ T, g->ao, g->scores, B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
         if (c.tp_size <= 1) {
             if (linear(g, g->ao, w.wo, nullptr, x, x, M, dl, d, d, EPI_NONE)) return 1;       // x += attn
@@ -223,7 +225,7 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
     const size_t d = c.d_model, V = c.vocab, S = c.seq_len, F = c.d_ff, dl = g->d_loc, Fl = g->F_loc, es = g->es;
     const size_t r = c.tp_rank;
     auto need = [&](size_t want) { return n == want ? 0 : fail("gpt_set_param(%s): got %zu values, expected %zu", name, n, want); };
-    auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || sptorch_sync(); };
+    auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || stream_wait(); };
     std::string s(name);
     if (s == "token_emb.weight") return need(V * d) || upload_rows(g, g->tok, host, n);
     if (s == "pos_emb.weight") return need(S * d) || upload_rows(g, g->pos, host, n);
@@ -299,11 +301,13 @@ int sptorch_ext_gpt_set_allreduce(void* gp, sptorch_allreduce_fn fn, void* user)
 }
 
 int sptorch_ext_gpt_launches(void* gp, int batch, int T) {
-    (void)batch; (void)T;
     if (!gp) return 0;
     Gpt* g = (Gpt*)gp;
-    // embedding + per layer (LN1, QK, V^T, S, softmax, PV, Wo, LN2, up, down) + ln_f + head
-    return 1 + g->c.n_layer * 10 + 2;
+    const int hd = g->c.d_model / g->c.n_head;
+    const long long M = (long long)batch * T;
+    const bool fused = g->c.dtype == SPT_BF16 && attention_mode() == 0 && attention_fused_supported(T, hd, 2 * g->d_loc, M, (long long)hd * M, T);
+    // embedding + per layer (LN1, QK, V^T, attention [1 fused | S, softmax, PV], Wo, LN2, up, down) + ln_f + head
+    return 1 + g->c.n_layer * (fused ? 8 : 10) + 2;
 }
 
 int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk) {

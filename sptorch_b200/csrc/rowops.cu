@@ -14,19 +14,26 @@
 namespace spt {
 
 constexpr int kRowThreads = 256;
+constexpr int kRowVecs = 8;        // 128-bit vectors a thread may hold of its row (unused slots are predicated off)
 
 // ---- 128-bit vector access for f32 (4 lanes) and bf16 (8 lanes) ----
 template <typename T> struct Vec;
 template <> struct Vec<float> {
     static constexpr int N = 4;
+    using Raw = float4;
     float v[4];
+    __device__ static Raw load_raw(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+    __device__ static Vec from_raw(Raw t) { return Vec{{t.x, t.y, t.z, t.w}}; }
     __device__ static Vec load(const float* p) { float4 t = __ldcs(reinterpret_cast<const float4*>(p)); return Vec{{t.x, t.y, t.z, t.w}}; }
     __device__ static Vec load_keep(const float* p) { float4 t = __ldg(reinterpret_cast<const float4*>(p)); return Vec{{t.x, t.y, t.z, t.w}}; }
     __device__ void store(float* p) const { __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3])); }
 };
 template <> struct Vec<__nv_bfloat16> {
     static constexpr int N = 8;
+    using Raw = uint4;                  // rows are held packed in registers (half the registers of unpacked f32)
     float v[8];
+    __device__ static Raw load_raw(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+    __device__ static Vec from_raw(Raw t) { return unpack(t); }
     __device__ static Vec unpack(uint4 t) {
         Vec r;
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
@@ -74,33 +81,38 @@ __device__ __forceinline__ float row_reduce(float x, float* sh) {
 // mean = sum/d; var = sum((x-mean)^2)/d (biased); inv = 1/sqrt(var+eps); y = gamma*((x-mean)*inv)+beta.
 // The two sums are tree reductions here, sequential in the reference: results agree to f32 rounding.
 // Algorithmic bytes per row: 2*dim*sizeof(T) (+ gamma/beta once per CTA, L2 resident).
-template <typename T, int TPR, int V>
+template <typename T, int TPR>
 __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                                                                 const float* __restrict__ beta, T* __restrict__ out,
                                                                 size_t rows, int dim, float eps) {
     using VT = Vec<T>;
     constexpr int N = VT::N;
+    constexpr int V = kRowVecs;
     constexpr int RPB = kRowThreads / TPR;   // rows per CTA pass
     __shared__ float sh[kRowThreads / 32];
     const int t = threadIdx.x % TPR;
     const int rl = threadIdx.x / TPR;
     const int nvec = dim / N;
-    const float inv_d = 1.0f / (float)dim;
     // when TPR > 32 every thread of the CTA must take part in the block-wide barrier of row_reduce,
     // so the row loop is uniform per CTA and out-of-range rows are predicated, not skipped.
     for (size_t r0 = (size_t)blockIdx.x * RPB; r0 < rows; r0 += (size_t)gridDim.x * RPB) {
         size_t r = r0 + rl;
         bool live = r < rows;
         const T* xr = x + (live ? r : 0) * (size_t)dim;
-        VT d[V];
+        typename VT::Raw d[V];
         float s = 0.0f;
 #pragma unroll
         for (int i = 0; i < V; i++) {
             int c = i * TPR + t;
-            if (live && c < nvec) {
-                d[i] = VT::load(xr + c * N);
+            if (live && c < nvec) d[i] = VT::load_raw(xr + c * N);
+        }
 #pragma unroll
-                for (int j = 0; j < N; j++) s += d[i].v[j];
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
+#pragma unroll
+                for (int j = 0; j < N; j++) s += u.v[j];
             }
         }
         float mean = row_reduce<TPR, false>(s, sh) / (float)dim;
@@ -109,11 +121,11 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const T* __restr
         for (int i = 0; i < V; i++) {
             int c = i * TPR + t;
             if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
 #pragma unroll
-                for (int j = 0; j < N; j++) { float e = d[i].v[j] - mean; q += e * e; }
+                for (int j = 0; j < N; j++) { float e = u.v[j] - mean; q += e * e; }
             }
         }
-        (void)inv_d;
         float var = row_reduce<TPR, false>(q, sh) / (float)dim;
         float inv = 1.0f / sqrtf(var + eps);
         T* yr = out + (live ? r : 0) * (size_t)dim;
@@ -121,15 +133,16 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const T* __restr
         for (int i = 0; i < V; i++) {
             int c = i * TPR + t;
             if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
                 VT y;
 #pragma unroll
                 for (int j4 = 0; j4 < N; j4 += 4) {
                     float4 g = __ldg(reinterpret_cast<const float4*>(gamma + c * N + j4));
                     float4 b = __ldg(reinterpret_cast<const float4*>(beta + c * N + j4));
-                    y.v[j4 + 0] = g.x * ((d[i].v[j4 + 0] - mean) * inv) + b.x;
-                    y.v[j4 + 1] = g.y * ((d[i].v[j4 + 1] - mean) * inv) + b.y;
-                    y.v[j4 + 2] = g.z * ((d[i].v[j4 + 2] - mean) * inv) + b.z;
-                    y.v[j4 + 3] = g.w * ((d[i].v[j4 + 3] - mean) * inv) + b.w;
+                    y.v[j4 + 0] = g.x * ((u.v[j4 + 0] - mean) * inv) + b.x;
+                    y.v[j4 + 1] = g.y * ((u.v[j4 + 1] - mean) * inv) + b.y;
+                    y.v[j4 + 2] = g.z * ((u.v[j4 + 2] - mean) * inv) + b.z;
+                    y.v[j4 + 3] = g.w * ((u.v[j4 + 3] - mean) * inv) + b.w;
                 }
                 y.store(yr + c * N);
             }
@@ -158,10 +171,11 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_generic_kernel(const T*
 }
 
 // ---------------- row softmax (crates/core-ops/src/lib.rs:903-920; crates/hal/src/lib.rs:582-596) ----------------
-template <typename T, int TPR, int V>
+template <typename T, int TPR>
 __global__ void __launch_bounds__(kRowThreads) softmax_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int cols) {
     using VT = Vec<T>;
     constexpr int N = VT::N;
+    constexpr int V = kRowVecs;
     constexpr int RPB = kRowThreads / TPR;
     __shared__ float sh[kRowThreads / 32];
     const int t = threadIdx.x % TPR;
@@ -402,28 +416,21 @@ static inline int row_grid(size_t row_groups) {
     return (int)(g < 1 ? 1 : g);
 }
 
-// picks (TPR, V) so that TPR*V >= nvec with V <= 8
+// TPR = the fewest cooperating threads (power of two, 8..256) that hold the row in kRowVecs vectors each: few threads
+// per row means many bytes in flight per thread, which is what saturates HBM on short bf16 rows.
 #define SPT_ROW_DISPATCH(KERNEL, T, nvec, ...)                                                              \
     do {                                                                                                   \
-        int _tpr = (nvec) <= 256 ? 32 : (nvec) <= 512 ? 64 : (nvec) <= 1024 ? 128 : 256;                    \
-        int _v = ((nvec) + _tpr - 1) / _tpr;                                                                \
+        int _tpr = 8;                                                                                       \
+        while (_tpr * kRowVecs < (nvec)) _tpr *= 2;                                                         \
         int _rpb = kRowThreads / _tpr;                                                                      \
         int _grid = row_grid((rows + _rpb - 1) / _rpb);                                                     \
-        if (_tpr == 32) {                                                                                   \
-            if (_v <= 1) KERNEL<T, 32, 1><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);             \
-            else if (_v <= 2) KERNEL<T, 32, 2><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
-            else if (_v <= 4) KERNEL<T, 32, 4><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
-            else if (_v <= 6) KERNEL<T, 32, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);        \
-            else KERNEL<T, 32, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                     \
-        } else if (_tpr == 64) {                                                                            \
-            if (_v <= 6) KERNEL<T, 64, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);             \
-            else KERNEL<T, 64, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                     \
-        } else if (_tpr == 128) {                                                                           \
-            if (_v <= 6) KERNEL<T, 128, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);            \
-            else KERNEL<T, 128, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                    \
-        } else {                                                                                            \
-            if (_v <= 6) KERNEL<T, 256, 6><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);            \
-            else KERNEL<T, 256, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__);                    \
+        switch (_tpr) {                                                                                     \
+            case 8: KERNEL<T, 8><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;               \
+            case 16: KERNEL<T, 16><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;             \
+            case 32: KERNEL<T, 32><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;             \
+            case 64: KERNEL<T, 64><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;             \
+            case 128: KERNEL<T, 128><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;           \
+            default: KERNEL<T, 256><<<_grid, kRowThreads, 0, rt().stream>>>(__VA_ARGS__); break;            \
         }                                                                                                   \
     } while (0)
 

@@ -75,6 +75,13 @@ int enter() {
     return 0;
 }
 
+int stream_wait() {
+    cudaError_t e = cudaStreamSynchronize(g_rt.stream);
+    g_rt.retired.store(g_rt.submitted.load());
+    if (e != cudaSuccess) return fail("stream synchronize failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 static int pick_device() {
     const char* e = getenv("SPTORCH_B200_DEVICE");
     if (!e) e = getenv("LOCAL_RANK");
