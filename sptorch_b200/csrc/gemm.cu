@@ -8,20 +8,22 @@
 // reference runs as separate passes (core-ops/src/lib.rs:1804, 1331, 299) are the epilogue.  It also
 // serves the per-head products of attention (core-ops/src/lib.rs:1763-1799) through two batch dims.
 //
-// Structure of one CTA (192 threads, one CTA per SM, static round-robin over output tiles):
+// Structure of one CTA (320 threads, one CTA per SM, static round-robin over output tiles):
 //   warp 0      TMA producer: 128 x BK tile of A and BN x BK tile of B per stage, 128-byte swizzle,
 //               4-stage ring, completion on mbarriers (no multicast: every CTA loads its own tiles)
 //   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=BN, K=32 bytes) from one lane; a stage is
 //               handed back to the producer by tcgen05.commit; the accumulator (f32, BN columns of
 //               TMEM) is double buffered so the epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2..5  epilogue: tcgen05.ld of the warp's 32 TMEM lanes, 32 columns at a time, then
-//               alpha/bias/GELU/residual in registers and 128-bit stores
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, each taking half of the tile's 32-column chunks:
+//               tcgen05.ld -> alpha/bias/GELU/residual in registers -> packed row into a swizzled 32x32
+//               staging block -> one TMA store per chunk (the store clips at the matrix edge)
 // Bound: tensor pipe.  Algorithmic work 2*M*N*K FLOP; bytes (M*K + N*K)*s_in + M*N*s_out.
 #include "gemm.h"
 #include "sm100.cuh"
 #include "../../include/sptorch_b200_hal.h"
 #include "../../include/sptorch_b200_ext.h"
 #include <math.h>
+#include <cstdlib>
 
 namespace spt {
 
@@ -30,7 +32,8 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 bf16 or 32 f32 along K
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;           // producer warp + MMA warp + 8 epilogue warps
+constexpr int kEpiThreads = 256;
 constexpr int kGroupM = 8;                   // m-tiles per rasterisation band (L2 reuse of the B tiles)
 
 struct GemmParams {
@@ -45,6 +48,9 @@ struct GemmParams {
     int num_kb;
     int causal_lower;
     int causal_k;
+    int tma_store;      // 1: C is written through the tensor map tmC; 0: element-wise stores
+    int r_vec;          // 1: residual rows can be read with 16-byte loads
+    int debug;          // experiments only: bit0 = skip the global write-out, bit1 = skip the whole epilogue body
     uint32_t* status;
 };
 
@@ -77,7 +83,8 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
 
 template <bool TF32, typename TOut, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
     constexpr int A_BYTES = BM * kStageRowBytes;
     constexpr int B_BYTES = BN * kStageRowBytes;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -85,18 +92,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators; power of two >= 32
     constexpr uint32_t IDESC = make_idesc(TF32, BM, BN);
 
-    extern __shared__ uint8_t smem_raw[];
-    // tiles need 1024-byte alignment for the 128-byte swizzle pattern to start at row 0
-    const uint32_t raw_addr = smem_u32(smem_raw);
-    const uint32_t base = (raw_addr + 1023u) & ~1023u;
-    uint8_t* smem = smem_raw + (base - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * STAGE_BYTES);
+    // layout: [kStages x (A tile | B tile)] [8 x 4 KB epilogue staging] [2 x 1 KB bias tiles] [barriers, 256 B]
+    // (operand tiles and staging blocks sit on 1024-byte boundaries: the TMA swizzle is a function of the address bits)
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t base = smem_u32(smem);
+    if ((base & 1023u) != 0) {           // the 128-byte swizzle pattern must start at row 0 of every tile
+        if (threadIdx.x == 0) atomicOr(p.status, 0x200u);
+        return;
+    }
+    constexpr int OFF_STAGING = kStages * STAGE_BYTES;
+    constexpr int OFF_BIAS = OFF_STAGING + 8 * 4096;
+    constexpr int OFF_BARS = OFF_BIAS + 2 * 1024;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
-    const uint32_t bar_full = base + kStages * STAGE_BYTES;
+    const uint32_t bar_full = base + OFF_BARS;
     const uint32_t bar_empty = bar_full + 8 * kStages;
     const uint32_t bar_tfull = bar_empty + 8 * kStages;
     const uint32_t bar_tempty = bar_tfull + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+    const uint32_t bar_bias = bar_tempty + 16;           // two barriers: bias tile of even / odd tiles is in place
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -104,7 +118,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 128); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads); mbar_init(bar_bias + 8 * a, kEpiThreads); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -121,7 +135,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+        if (lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmC); }
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -178,127 +192,165 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     } else {
-        // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp % 4) ----------------
-        // tcgen05.ld hands thread i the 32 columns of ROW i, so a direct store would scatter every warp
-        // instruction over 32 cache lines.  Each 32x32 f32 chunk is therefore turned through a 4 KB
-        // per-warp staging block (16-byte granules XOR-swizzled by row, conflict free both ways) so that
-        // 8 (f32) or 4 (bf16) neighbouring lanes finish one row segment: bias, GELU and the residual are
-        // applied in that layout, and global loads/stores are whole 32-byte sectors of consecutive addresses.
+        // ---------------- epilogue (warps 2..9; TMEM lane quarter = warp % 4, two warps per quarter) ----------------
+        // Only the epilogue's own instruction stream limits it (one warp per scheduler cannot hide a dependent-issue
+        // latency), so the work per element is kept small: thread i keeps ROW i of a 32x32 chunk, applies
+        // alpha/bias/GELU/residual in place, packs the row and writes it once to a swizzled staging block; one lane
+        // then hands the block to the TMA unit, which writes whole rows to HBM and clips at the matrix edge.
+        // Loads the epilogue depends on are issued early: the bias slice before the accumulator is waited for, the
+        // residual vectors of the next chunk before the current chunk is computed.
+        const int ew = warp - 2;                             // 0..7
         const int quarter = warp & 3;
-        float* stage = reinterpret_cast<float*>(smem + kStages * STAGE_BYTES + 256) + (warp - 2) * 1024;
+        const int half = ew >> 2;                            // which half of the tile's chunks this warp takes
+        const int eidx = threadIdx.x - 64;                   // 0..255 over the epilogue threads
+        constexpr int CPW = (BN / 32 + 1) / 2;               // chunks per warp
+        constexpr int kOutVec = 16 / (int)sizeof(TOut);      // elements per 16-byte piece
+        constexpr int NV = 32 / kOutVec;                     // 16-byte pieces per 32-column row: 4 (bf16) or 8 (f32)
+        constexpr int STG_BYTES = 32 * 32 * (int)sizeof(TOut);
+        constexpr int NBUF = 4096 / STG_BYTES;               // staging buffers per warp: 2 (bf16) or 1 (f32)
+        uint8_t* stg = smem + OFF_STAGING + ew * 4096;
+        float* bias_s = reinterpret_cast<float*>(smem + OFF_BIAS);
+        const bool use_tma = p.tma_store != 0;
         int acc = 0; uint32_t acc_phase = 0;
+        uint32_t chunk_seq = 0;                              // chunks this warp has staged so far (buffer parity)
+        uint32_t tile_par = 0, tile_seq = 0;
         bool ok = true;
-        constexpr int kOutVec = 16 / (int)sizeof(TOut);      // elements per 128-bit store
-        constexpr int LPR = 32 / kOutVec;                    // lanes per row segment: 8 (f32) or 4 (bf16)
-        constexpr int RPI = 32 / LPR;                        // rows per warp instruction: 4 or 8
-        const bool vec_ok = (p.ldc % kOutVec == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) &&
-                            (p.sC1 % kOutVec == 0) && (p.sC2 % kOutVec == 0) && (p.N % kOutVec == 0) &&
-                            (p.R == nullptr || (reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
-                            (p.bias == nullptr || (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0);
-        const int sub = lane / LPR;                          // row within the instruction's row group
-        const int cg = (lane % LPR) * kOutVec;               // first of this lane's kOutVec columns inside the chunk
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             int z, tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
             const int m0 = tm * BM, n0 = tn * BN;
             if (p.causal_lower && n0 > m0 + BM - 1) continue;
             const int z1 = z % p.nb1, z2 = z / p.nb1;
-            ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogueWait);
-            if (!ok) break;
-            tc_fence_after();
             const long long zoff = (long long)z1 * p.sC1 + (long long)z2 * p.sC2;
             TOut* cbase = reinterpret_cast<TOut*>(p.C) + zoff;
             const TOut* rbase = p.R ? reinterpret_cast<const TOut*>(p.R) + zoff : nullptr;
-            const int row_base = m0 + quarter * 32;          // first row of this warp's 32
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-            const int n_chunks = min(BN / 32, (p.N - n0 + 31) / 32);
-            uint32_t v[32];
-            tmem_ld_32x32(t_row, v);
-#pragma unroll 1
-            for (int c = 0; c < n_chunks; c++) {
+            const int row = m0 + quarter * 32 + lane;        // this thread's output row
+            const bool row_ok = row < p.M;
+            const int n_chunks = (p.debug & 2) ? 0 : min(BN / 32, (p.N - n0 + 31) / 32);
+            const int c_begin = min(half * CPW, n_chunks), c_end = min(c_begin + CPW, n_chunks);
+            // bias slice of the tile: one value per epilogue thread, parked in shared memory after the barrier wait
+            float bval = 0.0f;
+            if (p.bias && eidx < BN && n0 + eidx < p.N) bval = __ldg(p.bias + n0 + eidx);
+            // residual row segment of one chunk (row-per-thread layout)
+            uint4 rnext[NV];
+            auto fetch_residual = [&](int c) {
                 const int col0 = n0 + c * 32;
+#pragma unroll
+                for (int k = 0; k < NV; k++) rnext[k] = make_uint4(0u, 0u, 0u, 0u);
+                if (rbase && row_ok) {
+                    const TOut* rp = rbase + (long long)row * p.ldc + col0;
+                    if (p.r_vec && col0 + 32 <= p.N) {
+#pragma unroll
+                        for (int k = 0; k < NV; k++) rnext[k] = *reinterpret_cast<const uint4*>(rp + k * kOutVec);
+                    } else {
+                        TOut tmp[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) tmp[j] = (col0 + j < p.N) ? rp[j] : (TOut)0.0f;
+#pragma unroll
+                        for (int k = 0; k < NV; k++) rnext[k] = *reinterpret_cast<const uint4*>(&tmp[k * kOutVec]);
+                    }
+                }
+            };
+            if (c_begin < c_end) fetch_residual(c_begin);
+            ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogueWait);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            uint32_t v[32];
+            if (c_begin < c_end) tmem_ld_32x32(t_row + c_begin * 32, v);
+            // publish the bias tile to the 8 epilogue warps (an mbarrier, not bar.sync: its wait is bounded)
+            bias_s[tile_par * 256 + eidx] = bval;
+            mbar_arrive(bar_bias + 8 * tile_par);
+            ok = mbar_wait(bar_bias + 8 * tile_par, (tile_seq >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
+            if (!ok) break;
+            tile_seq++;
+            const float* bt = bias_s + tile_par * 256;
+#pragma unroll 1
+            for (int c = c_begin; c < c_end; c++) {
+                const int col0 = n0 + c * 32;
+                uint4 rcur[NV];
+#pragma unroll
+                for (int k = 0; k < NV; k++) rcur[k] = rnext[k];
                 tmem_ld_wait();
-                // stage: thread = row `lane`, granule g (4 floats) lands at position g ^ (lane & 7)
+                float f[32];
 #pragma unroll
-                for (int g = 0; g < 8; g++)
-                    *reinterpret_cast<float4*>(stage + lane * 32 + ((g ^ (lane & 7)) << 2)) =
-                        make_float4(__uint_as_float(v[4 * g]) * p.alpha, __uint_as_float(v[4 * g + 1]) * p.alpha,
-                                    __uint_as_float(v[4 * g + 2]) * p.alpha, __uint_as_float(v[4 * g + 3]) * p.alpha);
-                if (c + 1 < n_chunks) tmem_ld_32x32(t_row + (c + 1) * 32, v);     // overlaps the write-out below
-                else { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }    // accumulator drained: MMA may reuse it
-                __syncwarp();
-                if (vec_ok) {
-                    const int col = col0 + cg;
-                    const bool col_ok = col < p.N;                                // N % kOutVec == 0: whole vector in or out
-                    float bv[kOutVec];
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bt + c * 32 + j);      // same address in every lane: broadcast
+                    f[j] = fmaf(__uint_as_float(v[j]), p.alpha, b4.x);         f[j + 1] = fmaf(__uint_as_float(v[j + 1]), p.alpha, b4.y);
+                    f[j + 2] = fmaf(__uint_as_float(v[j + 2]), p.alpha, b4.z); f[j + 3] = fmaf(__uint_as_float(v[j + 3]), p.alpha, b4.w);
+                }
+                if (c + 1 < c_end) { tmem_ld_32x32(t_row + (c + 1) * 32, v); fetch_residual(c + 1); }
+                else { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }    // this warp has drained its part of the accumulator
+                if (p.epilogue == EPI_GELU) {
 #pragma unroll
-                    for (int j = 0; j < kOutVec; j++) bv[j] = 0.0f;
-                    if (p.bias && col_ok) {
+                    for (int j = 0; j < 32; j++) f[j] = (sizeof(TOut) == 2) ? gelu_fast(f[j]) : gelu_exact(f[j]);
+                }
+                if (rbase) {
+                    if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
-                        for (int j = 0; j < kOutVec; j += 4) {
-                            float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col + j));
-                            bv[j] = b4.x; bv[j + 1] = b4.y; bv[j + 2] = b4.z; bv[j + 3] = b4.w;
+                        for (int k = 0; k < NV; k++) {
+                            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rcur[k]);
+#pragma unroll
+                            for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[8 * k + 2 * q] += g2.x; f[8 * k + 2 * q + 1] += g2.y; }
                         }
-                    }
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 32 / RPI; i++) {
-                        const int rr = i * RPI + sub;
-                        const int row = row_base + rr;
-                        float f[kOutVec];
-#pragma unroll
-                        for (int j = 0; j < kOutVec; j += 4) {
-                            const int g = (cg + j) >> 2;
-                            float4 x4 = *reinterpret_cast<const float4*>(stage + rr * 32 + ((g ^ (rr & 7)) << 2));
-                            f[j] = x4.x + bv[j]; f[j + 1] = x4.y + bv[j + 1]; f[j + 2] = x4.z + bv[j + 2]; f[j + 3] = x4.w + bv[j + 3];
-                        }
-                        if (p.epilogue == EPI_GELU) {
-#pragma unroll
-                            for (int j = 0; j < kOutVec; j++) f[j] = (sizeof(TOut) == 2) ? gelu_fast(f[j]) : gelu_exact(f[j]);
-                        }
-                        if (row < p.M && col_ok) {
-                            const long long off = (long long)row * p.ldc + col;
-                            if constexpr (sizeof(TOut) == 2) {
-                                if (rbase) {
-                                    uint4 rv = *reinterpret_cast<const uint4*>(rbase + off);
-                                    const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                                    for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[2 * q] += g2.x; f[2 * q + 1] += g2.y; }
-                                }
-                                uint4 o;
-                                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                                for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
-                                *reinterpret_cast<uint4*>(cbase + off) = o;
-                            } else {
-                                if (rbase) {
-                                    float4 rv = *reinterpret_cast<const float4*>(rbase + off);
-                                    f[0] += rv.x; f[1] += rv.y; f[2] += rv.z; f[3] += rv.w;
-                                }
-                                *reinterpret_cast<float4*>(cbase + off) = make_float4(f[0], f[1], f[2], f[3]);
-                            }
-                        }
-                    }
-                } else {
-                    // unaligned output (odd N or ldc): lane = column, one row per iteration, scalar accesses
-                    const int col = col0 + lane;
-                    const float bcol = (p.bias && col < p.N) ? __ldg(p.bias + col) : 0.0f;
-#pragma unroll 4
-                    for (int rr = 0; rr < 32; rr++) {
-                        const int row = row_base + rr;
-                        float x = stage[rr * 32 + ((((lane >> 2) ^ (rr & 7)) << 2) | (lane & 3))] + bcol;
-                        if (p.epilogue == EPI_GELU) x = (sizeof(TOut) == 2) ? gelu_fast(x) : gelu_exact(x);
-                        if (row < p.M && col < p.N) {
-                            const long long off = (long long)row * p.ldc + col;
-                            if (rbase) x += (float)rbase[off];
-                            cbase[off] = (TOut)x;
+                        for (int k = 0; k < NV; k++) {
+                            f[4 * k] += __uint_as_float(rcur[k].x); f[4 * k + 1] += __uint_as_float(rcur[k].y);
+                            f[4 * k + 2] += __uint_as_float(rcur[k].z); f[4 * k + 3] += __uint_as_float(rcur[k].w);
                         }
                     }
                 }
-                __syncwarp();                                  // staging block is rewritten by the next chunk
+                if (p.debug & 1) continue;
+                if (use_tma) {
+                    uint8_t* buf = stg + (chunk_seq % NBUF) * STG_BYTES;
+                    // the store that last read this buffer must have finished reading it
+                    if (lane == 0) {
+                        if (NBUF == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
+                    __syncwarp();
+                    // row `lane` of the block; 16-byte piece k goes to the position the tensor map's swizzle expects
+                    if constexpr (sizeof(TOut) == 2) {
+                        uint8_t* rowp = buf + lane * 64;
+                        const int sw = (lane >> 1) & 3;                        // 64-byte swizzle: piece ^= (row / 2) % 4
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            uint4 o;
+                            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                            for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(f[8 * k + 2 * q], f[8 * k + 2 * q + 1]);
+                            *reinterpret_cast<uint4*>(rowp + ((k ^ sw) << 4)) = o;
+                        }
+                    } else {
+                        uint8_t* rowp = buf + lane * 128;
+                        const int sw = lane & 7;                               // 128-byte swizzle: piece ^= row % 8
+#pragma unroll
+                        for (int k = 0; k < 8; k++)
+                            *reinterpret_cast<float4*>(rowp + ((k ^ sw) << 4)) = make_float4(f[4 * k], f[4 * k + 1], f[4 * k + 2], f[4 * k + 3]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the TMA unit
+                    __syncwarp();
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                                     ::"l"(reinterpret_cast<uint64_t>(&tmC)), "r"(smem_u32(buf)), "r"(col0), "r"(m0 + quarter * 32), "r"(z1), "r"(z2)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    chunk_seq++;
+                } else if (row_ok) {
+                    // output pitch or base that a tensor map cannot express: element-wise stores of this thread's row
+                    TOut* cp = cbase + (long long)row * p.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) if (col0 + j < p.N) cp[j] = (TOut)f[j];
+                }
             }
-            if (n_chunks <= 0) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }
+            if (c_begin >= c_end) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }
+            tile_par ^= 1;
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // staging must outlive its readers
+        __syncwarp();
     }
 
     // teardown: every thread arrives here, also after an aborted wait
@@ -354,6 +406,22 @@ static int encode_operand(CUtensorMap* map, const void* ptr, bool tf32, int K, i
     return 0;
 }
 
+// rank-4 map over the output: dims (N, M, nb1, nb2), box (32 columns, 32 rows, 1, 1)
+static int encode_output(CUtensorMap* map, void* ptr, bool bf16, int N, int M, long long ld, int nb1, int nb2, long long s1, long long s2) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return fail("cuTensorMapEncodeTiled is not available from this driver");
+    const size_t es = bf16 ? 2 : 4;
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)nb1, (cuuint64_t)nb2};
+    cuuint64_t st[3] = {(cuuint64_t)ld * es, (cuuint64_t)(nb1 > 1 ? s1 : ld) * es, (cuuint64_t)(nb2 > 1 ? s2 : ld) * es};
+    cuuint32_t box[4] = {32, 32, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ptr, dims, st, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed with CUresult %d (N=%d M=%d ld=%lld)", (int)r, N, M, ld);
+    return 0;
+}
+
 bool gemm_supported(const GemmDesc& d, const char** why) {
     static const char* ok = "";
     const long long es = d.mode == MM_TF32 ? 4 : 2;
@@ -379,18 +447,20 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, prm);
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm);
     SPT_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
 
-static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 4 * 4096 /*epilogue staging*/; }
+static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 256 /*barriers*/ + 8 * 4096 /*epilogue staging*/ + 2 * 1024 /*bias tiles*/; }
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;
     if (!gemm_supported(d, &why)) return fail("gemm: %s", why);
     plan->d = d;
     int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
+    static const int force_bn = getenv("SPTORCH_B200_GEMM_BN") ? atoi(getenv("SPTORCH_B200_GEMM_BN")) : 0;
+    if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
     plan->bn = bn;
     plan->tiles_m = ceil_div(d.M, BM);
     plan->tiles_n = ceil_div(d.N, bn);
@@ -401,6 +471,15 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const bool tf32 = d.mode == MM_TF32;
     if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;
     if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, bn)) return 1;
+    // output map: 32x32 boxes, swizzled to match the conflict-free staging layout of the epilogue
+    const long long oes = d.out_dtype == BF16 ? 2 : 4;
+    plan->tma_store = ((reinterpret_cast<uintptr_t>(d.C) & 15) == 0) && (d.ldc * oes) % 16 == 0 && d.ldc >= d.N &&
+                      (d.nb1 <= 1 || (d.sC1 * oes) % 16 == 0) && (d.nb2 <= 1 || (d.sC2 * oes) % 16 == 0);
+    if (plan->tma_store) {
+        if (encode_output(&plan->tmC, d.C, d.out_dtype == BF16, d.N, d.M, d.ldc, d.nb1, d.nb2, d.sC1, d.sC2)) return 1;
+    } else {
+        plan->tmC = plan->tmA;   // never dereferenced by the kernel in this mode
+    }
     plan->valid = true;
     return 0;
 }
@@ -417,7 +496,15 @@ int gemm_run(const GemmPlan& pl) {
     prm.num_kb = ceil_div(d.K, d.mode == MM_TF32 ? 32 : 64);
     prm.causal_lower = d.causal_lower;
     prm.causal_k = d.causal_k;
+    prm.tma_store = pl.tma_store ? 1 : 0;
+    {
+        const long long oes = d.out_dtype == BF16 ? 2 : 4;
+        prm.r_vec = d.R != nullptr && (reinterpret_cast<uintptr_t>(d.R) & 15) == 0 && (d.ldc * oes) % 16 == 0 &&
+                    (d.nb1 <= 1 || (d.sC1 * oes) % 16 == 0) && (d.nb2 <= 1 || (d.sC2 * oes) % 16 == 0);
+    }
     prm.status = rt().dev_status;
+    static const int dbg = getenv("SPTORCH_B200_GEMM_DEBUG") ? atoi(getenv("SPTORCH_B200_GEMM_DEBUG")) : 0;
+    prm.debug = dbg;
     const bool tf32 = d.mode == MM_TF32;
     const bool out_bf16 = d.out_dtype == BF16;
 #define SPT_GEMM_CASE(BN_)                                                                          \

@@ -28,7 +28,8 @@ struct GemmDesc {
 
 // A prepared launch: tensor maps are encoded once and can be replayed (the GPT driver caches these).
 struct GemmPlan {
-    CUtensorMap tmA, tmB;
+    CUtensorMap tmA, tmB, tmC;
+    bool tma_store = false;
     GemmDesc d;
     int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0;
     size_t smem = 0;

@@ -48,7 +48,7 @@ def test_layernorm_mean_zero_property_full_size(backend):
 def test_softmax_vs_oracle(backend, oracle, rows, cols):
     s = (np.random.default_rng(cols).standard_normal((rows, cols)) * 2).astype(np.float32)
     out = backend.softmax_f32(s, rows, cols)
-    assert relerr(out, oracle.softmax(s)) <= 2e-6
+    assert relerr(out, oracle.softmax(s)) <= 4e-6       # tree sum vs sequential sum of up to 10^4 terms, 2-ulp expf
     assert np.abs(out.sum(-1) - 1).max() < 1e-5
 
 
@@ -107,7 +107,8 @@ def test_embedding_sum_vs_oracle(backend, oracle):
     ref = oracle.binary("add", oracle.embedding(tok, ids), oracle.embedding(pos, np.arange(48) % 16))
     assert np.array_equal(backend.embedding_sum(tok, pos, ids, 16).ravel(), ref.ravel())
     out = backend.embedding_sum(_bf16(tok), _bf16(pos), ids, 16, dtype=BF16)
-    assert np.abs(out - (_bf16(tok)[ids] + _bf16(pos)[np.arange(48) % 16])).max() <= 2 ** -7
+    refb = _bf16(tok)[ids] + _bf16(pos)[np.arange(48) % 16]
+    assert np.abs(out - refb).max() <= 2 ** -8 * np.abs(refb).max()      # one bf16 rounding of the sum
 
 
 def test_gelu_bf16_and_f32(backend, oracle):
