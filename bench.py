@@ -106,11 +106,19 @@ def shard(n_items, world, rank):
     return start, base + (1 if rank < rem else 0)
 
 
+def host_threads():
+    """Cores this process may run on (torchrun exports OMP_NUM_THREADS=1, which must not shrink the CPU arm)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(cfg, T, seconds_hint=20.0):
     """The reference's CPU arithmetic (oracle port) on a bounded sample of the same workload."""
     from oracle import binding as O
     O.build()
-    threads = O.max_threads()
+    threads = host_threads()
     params, _ = synth.gpt_params(cfg, 0, residual_scale=True)
     ids = synth.randint(1, T, cfg["vocab"]).reshape(1, T)
     t0 = time.perf_counter()
@@ -128,7 +136,7 @@ def run_reference(args):
     O.build()
     cfg = dict(synth.CONFIGS[WORKLOAD])
     T = cfg["ctx"]
-    threads = O.max_threads()
+    threads = host_threads()
     params, _ = synth.gpt_params(cfg, 0, residual_scale=True)
     # one step = a bounded sample of the global batch: n_seq sequences of the full context length
     n_seq = 1
