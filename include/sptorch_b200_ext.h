@@ -92,6 +92,14 @@ int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* 
  * SPT_MM_TF32 (default, tensor cores) or SPT_MM_F32 (CUDA cores, f32 FMA in k order) */
 int sptorch_ext_set_matmul_mode(int mode);
 
+/* No counterpart in the reference.  sptorch_matmul_f32 for callers that must not allocate device memory (fixed,
+ * audited memory budgets; loops that may not touch the allocator; an exhausted pool): the transposed-B scratch is a
+ * static 8 MiB array inside the library, so k * n is limited to 2,097,152 elements and larger products are rejected.
+ * No cudaMalloc/cudaFree/pool call is made.  The first call on a device resolves the array's address and should come
+ * before any stream capture.  All calls share the array (it keeps the last call's contents; none of it needs
+ * clearing) -- calls that overlap on the GPU race. */
+int sptorch_ext_matmul_f32_static(const void* a, const void* b, void* out, size_t m, size_t k, size_t n);
+
 int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const void* residual, void* out,
                        size_t M, size_t K, size_t N, size_t ldo, float alpha, int epilogue, int mode, int out_dtype);
 

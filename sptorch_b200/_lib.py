@@ -77,6 +77,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_masked_softmax_f32": (_i, [_vp, _vp, _vp, _sz, _sz, _i]),
     "sptorch_ext_embedding_sum": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_set_matmul_mode": (_i, [_i]),
+    "sptorch_ext_matmul_f32_static": (_i, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "sptorch_ext_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _f, _i, _i, _i]),
     "sptorch_ext_set_attention_mode": (_i, [_i]),
     "sptorch_ext_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _i]),

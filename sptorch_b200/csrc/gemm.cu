@@ -620,11 +620,71 @@ static int abi_matmul(const void* a, const void* b, void* out, size_t batch, siz
     return rc;
 }
 
+// ---- matmul for callers that must not allocate ----
+// Scratch for the transposed B operand lives in the library image instead of coming from the pool.
+constexpr size_t kStaticScratchFloats = size_t(1) << 21;                 // 8 MiB: k * n <= 2,097,152
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static float* g_static_scratch_addr[64] = {};                            // device address per CUDA ordinal, filled on first use
+static std::mutex g_static_scratch_mu;
+
 }  // namespace spt
 
 using namespace spt;
 
 extern "C" {
+
+// sptorch_ext_matmul_f32_static: same result as sptorch_matmul_f32 (C = A[m,k] * B[k,n], row-major f32), for callers
+// that cannot let the library allocate device memory while they run: a program whose memory budget is fixed up
+// front and audited, a latency-critical loop that must not touch the allocator (an allocation can synchronise or
+// fail at an arbitrary moment), or code running while the pool is deliberately exhausted.  The only scratch the
+// tensor-core path needs -- B transposed to K-major -- is a fixed 8 MiB array inside the library image, so this
+// call performs no cudaMalloc / cudaFree / pool allocation of any kind.
+//   * limit: k * n <= 2,097,152 elements (for example 1024 x 2048); larger products are rejected with an error.
+//     Every GPU that loads the library carries the 8 MiB until the process exits.
+//   * the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+//     before starting any stream capture.
+//   * all calls share the one array and it keeps the previous call's contents; nothing in it has to start at zero
+//     (each call overwrites the k * n elements it then reads).  Two calls whose kernels overlap on the GPU -- from
+//     different streams or threads -- would race on it: issue them on the library's stream, one after the other.
+// a, b, out are device handles as for sptorch_matmul_f32; returns 0 on success.
+int sptorch_ext_matmul_f32_static(const void* a, const void* b, void* out, size_t m, size_t k, size_t n) {
+    if (enter()) return 1;
+    if (m == 0 || n == 0) return 0;
+    if (!a || !b || !out) return fail("matmul_f32_static: null handle");
+    if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("matmul_f32_static: dimension too large");
+    if (k * n > kStaticScratchFloats)
+        return fail("matmul_f32_static: k*n = %zu exceeds the static scratch of %zu elements; use sptorch_matmul_f32", k * n, (size_t)kStaticScratchFloats);
+    if (k == 0) {
+        SPT_CUDA(cudaMemsetAsync(out, 0, m * n * sizeof(float), rt().stream));
+        note_submit();
+        return 0;
+    }
+    const int dev = rt().device;
+    if (dev < 0 || dev >= 64) return fail("matmul_f32_static: device ordinal %d out of range", dev);
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+        if (!g_static_scratch_addr[dev]) {
+            // in host code the array's name is only a stand-in: the kernel needs the address the runtime reports
+            void* p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess || !p) return fail("matmul_f32_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            g_static_scratch_addr[dev] = (float*)p;
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+    GemmDesc d;
+    d.mode = MM_TF32; d.out_dtype = F32;
+    d.M = (int)m; d.N = (int)n; d.K = (int)k;
+    d.lda = (long long)k; d.ldb = (long long)k; d.ldc = (long long)n;
+    d.A = a; d.B = scratch; d.C = out;
+    const bool tc = g_abi_mode.load() == MM_TF32 && gemm_supported(d, nullptr) && (m * n * k >= (size_t)64 * 64 * 64);
+    if (!tc) return simt_matmul_f32((const float*)a, (const float*)b, (float*)out, 1, (int)m, (int)n, (int)k, true, nullptr, nullptr, 1.0f, EPI_NONE);
+    if (sptorch_ext_transpose_f32(b, scratch, k, n)) return 1;
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    return gemm_run(pl);
+}
 
 int sptorch_matmul_f32(const void* a, const void* b, void* out, size_t m, size_t k, size_t n) { return abi_matmul(a, b, out, 1, m, k, n); }
 int sptorch_batch_matmul_f32(const void* a, const void* b, void* out, size_t batch, size_t m, size_t k, size_t n) {
