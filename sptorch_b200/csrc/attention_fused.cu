@@ -34,6 +34,13 @@ struct AttnParams {
     uint32_t* status;
 };
 
+// 2^x on the special-function unit: one instruction, relative error 2^-22 (P is rounded to bf16 right after)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int HD>
 struct AttnSmem {
     static constexpr int kQBytes = kQTile * HD * 2;
@@ -188,7 +195,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             }
             const float m_new = fmaxf(m, mx);
-            const float alpha = exp2f((m - m_new) * p.scale_log2);       // 0 on the first tile (m = -inf)
+            const float alpha = ex2_approx((m - m_new) * p.scale_log2);       // 0 on the first tile (m = -inf)
             const float mb = m_new * p.scale_log2;
             // pass 2: p = exp2(s*c - m*c), row sum, bf16 P into shared memory
             float sum = 0.0f;
@@ -201,7 +208,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float a0 = __uint_as_float(v[i]), a1 = __uint_as_float(v[i + 1]);
-                    float e0 = exp2f(fmaf(a0, p.scale_log2, -mb)), e1 = exp2f(fmaf(a1, p.scale_log2, -mb));
+                    float e0 = ex2_approx(fmaf(a0, p.scale_log2, -mb)), e1 = ex2_approx(fmaf(a1, p.scale_log2, -mb));
                     if (diag) {
                         if (k0 + c * 32 + i > qrow) e0 = 0.0f;
                         if (k0 + c * 32 + i + 1 > qrow) e1 = 0.0f;

@@ -249,43 +249,64 @@ __device__ __forceinline__ void causal_row(const T* __restrict__ xr, T* __restri
     constexpr int N = VT::N;
     const int nvec = Tn / N;
     const int live_vec = i / N + 1;      // vectors holding at least one j <= i
-    VT d[V];
+    typename VT::Raw raw[V];             // the row stays packed in registers
+#pragma unroll
+    for (int k = 0; k < V; k++) {
+        int c = k * 32 + lane;
+        if (c < live_vec) raw[k] = VT::load_raw(xr + c * N);
+    }
     float mx = -INFINITY;
 #pragma unroll
     for (int k = 0; k < V; k++) {
         int c = k * 32 + lane;
         if (c < live_vec) {
-            d[k] = VT::load(xr + c * N);
+            VT u = VT::from_raw(raw[k]);
 #pragma unroll
             for (int j = 0; j < N; j++) {
-                float s = d[k].v[j] * scale;
-                s = (c * N + j > i) ? -INFINITY : s;
-                d[k].v[j] = s;
-                mx = fmaxf(mx, s);
+                float s = u.v[j] * scale;
+                mx = fmaxf(mx, (c * N + j > i) ? -INFINITY : s);
             }
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float sum = 0.0f;
+    // exponentials are evaluated once; f32 rows put them back into the registers that held the input,
+    // bf16 rows (half as many vectors for the same T) keep them unpacked
+    constexpr bool kInPlace = sizeof(T) == 4;
+    VT e[kInPlace ? 1 : V];
 #pragma unroll
     for (int k = 0; k < V; k++) {
         int c = k * 32 + lane;
         if (c < live_vec) {
+            VT u = VT::from_raw(raw[k]);
 #pragma unroll
-            for (int j = 0; j < N; j++) { float e = expf(d[k].v[j] - mx); d[k].v[j] = e; sum += e; }
+            for (int j = 0; j < N; j++) {
+                float s = u.v[j] * scale;
+                // bf16 storage: 2^x on the special-function unit (relative error 2^-22, far below a bf16 ulp) keeps the
+                // kernel memory bound; f32 storage keeps the precise expf
+                float ex;
+                if constexpr (sizeof(T) == 2) { asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"((s - mx) * 1.4426950408889634f)); }
+                else ex = expf(s - mx);
+                ex = (c * N + j > i) ? 0.0f : ex;
+                u.v[j] = ex; sum += ex;
+            }
+            if constexpr (kInPlace) raw[k] = *reinterpret_cast<typename VT::Raw*>(&u); else e[k] = u;
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv_sum = 1.0f / sum;
 #pragma unroll
     for (int k = 0; k < V; k++) {
         int c = k * 32 + lane;
         if (c < nvec) {
             VT y;
             if (c < live_vec) {
+                VT u;
+                if constexpr (kInPlace) u = VT::from_raw(raw[k]); else u = e[k];
 #pragma unroll
-                for (int j = 0; j < N; j++) y.v[j] = d[k].v[j] / sum;
+                for (int j = 0; j < N; j++) y.v[j] = (sizeof(T) == 2) ? u.v[j] * inv_sum : u.v[j] / sum;
             } else {
 #pragma unroll
                 for (int j = 0; j < N; j++) y.v[j] = 0.0f;
@@ -296,7 +317,7 @@ __device__ __forceinline__ void causal_row(const T* __restrict__ xr, T* __restri
 }
 
 template <typename T, int V>
-__global__ void __launch_bounds__(kRowThreads) causal_softmax_kernel(const T* __restrict__ x, T* __restrict__ out, size_t batch,
+__global__ void __launch_bounds__(kRowThreads, sizeof(T) == 4 ? 4 : 3) causal_softmax_kernel(const T* __restrict__ x, T* __restrict__ out, size_t batch,
                                                                      int Tn, float scale) {
     const int lane = threadIdx.x & 31;
     const size_t warp = ((size_t)blockIdx.x * kRowThreads + threadIdx.x) >> 5;
@@ -308,9 +329,13 @@ __global__ void __launch_bounds__(kRowThreads) causal_softmax_kernel(const T* __
         int p = (int)(task % pairs);
         const T* xb = x + b * (size_t)Tn * Tn;
         T* yb = out + b * (size_t)Tn * Tn;
-        causal_row<T, V>(xb + (size_t)p * Tn, yb + (size_t)p * Tn, p, Tn, scale, lane);
-        int q = Tn - 1 - p;
-        if (q != p) causal_row<T, V>(xb + (size_t)q * Tn, yb + (size_t)q * Tn, q, Tn, scale, lane);
+        // rows p and T-1-p: together T+1 live entries, so every warp moves the same number of bytes
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+            int r = half == 0 ? p : Tn - 1 - p;
+            if (half == 1 && r == p) break;
+            causal_row<T, V>(xb + (size_t)r * Tn, yb + (size_t)r * Tn, r, Tn, scale, lane);
+        }
     }
 }
 
