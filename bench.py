@@ -349,6 +349,26 @@ def run_sweep(args):
                 print(json.dumps(out[-1]), flush=True)
                 for buf in (x, w, y, bias):
                     buf.free()
+    if args.sweep in ("attention", "all"):
+        # causal attention core of one layer: BASELINE config 4 (12 heads x 64) and config 5 (16 heads x 128) shapes, bf16
+        shapes = [(64, 1024, 12, 64), (16, 2048, 16, 128)]
+        if args.shape:
+            shapes = [tuple(int(v) for v in args.shape.split(","))]
+        for (B_, T_, H_, hd_) in shapes:
+            d_ = H_ * hd_
+            q, k, v, o = (b.alloc(B_ * T_ * d_, 2) for _ in range(4))
+            for i, buf in enumerate((q, k, v)):
+                _fill(b, buf, B_ * T_ * d_, 2, 20 + i)
+            ws = b.alloc(lib.sptorch_ext_attention_workspace(B_, T_, H_, hd_, BF16), 1)
+            fn = lambda: b._check(lib.sptorch_ext_attention_causal(q.handle, k.handle, v.handle, o.handle, ws.handle, B_, T_, H_, hd_, d_, BF16), "attention")
+            med, best = _time_op(b, fn, args.iters)
+            flop = 2.0 * B_ * H_ * T_ * (T_ + 1) * hd_
+            out.append({"op": "attention_causal", "B": B_, "T": T_, "H": H_, "hd": hd_, "dtype": "bf16", "ms": med, "ms_best": best,
+                        "tflops": flop / (med * 1e-3) / 1e12, "frac": flop / (med * 1e-3) / 1e12 / peaks["tf"], "peak": peaks["tf"],
+                        "note": "includes the V transpose kernel; FLOP counted on the causal-necessary half"})
+            print(json.dumps(out[-1]), flush=True)
+            for buf in (q, k, v, o, ws):
+                buf.free()
     if args.sweep in ("rowops", "all"):
         for dim in (768, 2048, 4096):
             for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
@@ -392,6 +412,83 @@ def run_sweep(args):
     return 0
 
 
+def run_tp(args):
+    """Tensor-parallel forward (BASELINE config 5 shape, or a small model checked against the oracle with --workload tp_check):
+    wq/wk/wv/ffn_up split by rows, wo/ffn_down along K, one NCCL all-reduce per attention and per MLP block."""
+    rank, local_rank, world = dist_env()
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("SPTORCH_B200_DEVICE", str(local_rank))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from sptorch_b200.backend import BF16, FfiBackend
+    from sptorch_b200.gpt import GPT
+    b = FfiBackend.load()
+    lib = b.lib
+    check = args.workload == "tp_check"
+    if check:
+        cfg = dict(vocab=1000, d_model=256, n_layer=2, n_head=4, d_ff=1024, seq_len=256, batch=2, ctx=256)
+    else:
+        cfg = dict(synth.CONFIGS["c5_1p3b"])
+        if args.layers:
+            cfg["n_layer"] = args.layers
+    T, B = cfg["ctx"], args.batch or cfg["batch"]
+    model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16,
+                max_batch=B, tp_rank=rank, tp_size=world)
+    params, index = synth.gpt_params(cfg, 0, residual_scale=True, randomize_affine=check)
+    model.load_flat(params, index)
+    if world > 1:
+        uid = C.create_string_buffer(128)
+        if rank == 0:
+            b._check(lib.sptorch_ext_nccl_unique_id(None, uid), "nccl_unique_id")
+        box = [uid.raw]
+        dist.broadcast_object_list(box, src=0)
+        uid = C.create_string_buffer(box[0], 128)
+        b._check(lib.sptorch_ext_nccl_init(None, uid, rank, world), "nccl_init")
+        b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
+    ids = synth.randint(1, B * T, cfg["vocab"]).reshape(B, T).astype(np.int32)
+    if check:
+        out = model.forward(ids)
+        if rank == 0:
+            from oracle import binding as O
+            ref = O.gpt_forward(cfg, params, ids, fast=1, threads=host_threads())
+            err = float(np.abs(out - ref).max() / np.abs(ref).max())
+            print(json.dumps({"workload": "tp_check", "tp_size": world, "max_rel_err_vs_oracle": err, "tolerance": 2e-2, "ok": err <= 2e-2}), flush=True)
+    else:
+        del params
+        d_ids, d_logits = model.stage_ids(ids), model.logits_buffer(B * T)
+        sync = lambda: (b.synchronize(), torch.cuda.synchronize(), dist.barrier() if world > 1 else None, torch.cuda.synchronize())
+        for _ in range(max(args.warmup, 3)):
+            model.forward_device(d_ids, B, T, d_logits)
+        sync()
+        lib.sptorch_ext_prof_enable(1); lib.sptorch_ext_prof_read(None, None, 0)
+        b.timer_begin()
+        for _ in range(args.steps):
+            model.forward_device(d_ids, B, T, d_logits)
+        ms = b.timer_end()
+        sync()
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        pm, pn = (C.c_float * 7)(), (C.c_uint32 * 7)()
+        lib.sptorch_ext_prof_read(pm, pn, 7); lib.sptorch_ext_prof_enable(0)
+        if rank == 0:
+            cats = ["linear_gemm", "attention_gemm", "causal_softmax", "layernorm", "embedding", "allreduce", "attention_fused"]
+            lin, attn = flops_per_forward(cfg, B, T)
+            print(json.dumps({"metric": "gpt_forward_tokens_per_s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+                              "steps": args.steps, "ms_per_step": ms / args.steps, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}"},
+                              "achieved_tflops_whole_job": (lin + attn) / (ms / args.steps * 1e-3) / 1e12,
+                              "breakdown_rank0": {c: float(pm[i]) / args.steps for i, c in enumerate(cats) if pn[i]}}), flush=True)
+    model.close()
+    if world > 1:
+        lib.sptorch_ext_nccl_shutdown()
+    b.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,14 +499,19 @@ def main():
     ap.add_argument("--chunk", type=int, default=8, help="sequences per micro-batch of the host-buffer call")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
+    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
     ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
+                    help="c4_gpt2s: the bench line (batch sharding); c5_1p3b / tp_check: tensor parallel over the launched ranks")
+    ap.add_argument("--layers", type=int, default=0, help="with --workload c5_1p3b: run fewer layers")
     args = ap.parse_args()
     if args.sweep:
         return run_sweep(args)
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload != WORKLOAD:
+        return run_tp(args)
     return run_ours(args)
 
 

@@ -109,6 +109,9 @@ int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const
  * workspace of sptorch_ext_attention_workspace() bytes. */
 /* 0 (default): bf16 with head_dim 64 or 128 runs the fused kernel, everything else the materialised form; 1: always materialised */
 int sptorch_ext_set_attention_mode(int mode);
+/* diagnostics: with SPTORCH_B200_ATTN_PROF set in the environment, the last fused-attention launch's cycle counters of CTA 0
+ * (8 phases of one softmax thread, 8 of the MMA-issuing thread) */
+int sptorch_ext_debug_attn_prof(unsigned long long* host16);
 size_t sptorch_ext_attention_workspace(size_t B, size_t T, size_t H, size_t hd, int dtype);
 int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, void* out, void* workspace,
                                  size_t B, size_t T, size_t H, size_t hd, size_t ld_qkv, int dtype);

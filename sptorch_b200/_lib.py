@@ -80,6 +80,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_matmul_f32_static": (_i, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "sptorch_ext_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _f, _i, _i, _i]),
     "sptorch_ext_set_attention_mode": (_i, [_i]),
+    "sptorch_ext_debug_attn_prof": (_i, [C.POINTER(C.c_uint64)]),
     "sptorch_ext_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_attention_causal": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_create": (_vp, [C.POINTER(GptConfig)]),

@@ -2,28 +2,33 @@
 //
 // Same function as crates/nn/src/lib.rs:600-637 (scores = Q K^T * 1/sqrt(hd); entries j > i set to -inf; row
 // softmax; P V; heads merged back) but the [T,T] score and probability matrices never reach HBM: one CTA owns
-// one 128-row query tile of one (sequence, head) and walks the key/value tiles 0..diagonal with a running
-// row maximum and row sum (the softmax is computed exactly; only the order of the sums differs).
+// one 128-row query tile of one (sequence, head) and walks the key/value tiles (64 keys each) up to the diagonal
+// with a running row maximum and row sum (the softmax is exact; only the order of the sums differs).
 //
-//   warp 0      TMA: Q tile once, then K tile [128 keys, hd] and V^T tile [hd, 128 keys] per step, 2-stage ring
-//   warp 1      tcgen05.mma: S = Q K^T (M128 N128) into TMEM, later O_j = P V (M128 N=hd) into TMEM
-//   warps 2..5  one thread per query row: tcgen05.ld S twice (row max, then exp2), causal mask on the diagonal
-//               tile, P written to shared memory as bf16 in the 128-byte-swizzled K-major layout that the P V
-//               MMA reads, O_j read back from TMEM and folded into a register accumulator with the rescale factor
-// Two CTAs are resident per SM for hd = 64 (112 KB of shared memory and 256 TMEM columns each), so one CTA's
-// softmax overlaps the other's MMAs.  Heavy (late) query tiles are scheduled first.
-// Algorithmic work per (sequence, head): 2 * T(T+1) * hd FLOP; HBM traffic Q, K, V read once per query tile pass
+//   warp 0      TMA: Q tile once, then K tile [64 keys, hd] and V^T tile [hd, 64 keys] per step, 3-stage ring
+//   warp 1      tcgen05.mma: S_j = Q K_j^T (M128 N64) into one of two TMEM buffers, issued one step AHEAD of the
+//               softmax; O_j = P_j V_j (M128 N=hd) into one of two TMEM buffers when P_j is ready
+//   warps 2..9  two threads per query row (32 of the 64 key columns each): S_j from TMEM into registers, causal
+//               mask on the diagonal tiles, running maximum agreed with the partner thread, exp2, P_j as bf16 into
+//               one of two shared-memory buffers in the 128-byte-swizzled K-major layout the P V MMA reads; the
+//               product O_{j-1} of the PREVIOUS step is folded into the register accumulator afterwards, so no
+//               thread ever waits for the MMA it has just enabled
+// Two CTAs are resident per SM for hd = 64 (97 KB of shared memory and 256 TMEM columns each).  Heavy (late)
+// query tiles are scheduled first.
+// Algorithmic work per (sequence, head): 2 * T(T+1) * hd FLOP; HBM traffic: Q, K, V read once per query tile
 // (K/V re-reads hit L2), O written once.
 #include "gemm.h"
 #include "sm100.cuh"
 #include "../../include/sptorch_b200_ext.h"
+#include <cstdlib>
 
 namespace spt {
 
 using namespace sm100;
 
-constexpr int kAttnThreads = 192;
-constexpr int kQTile = 128, kKvTile = 128;
+constexpr int kAttnThreads = 320;           // TMA warp + MMA warp + 8 softmax warps
+constexpr int kQTile = 128, kKvTile = 64;
+constexpr int kKvStages = 3;
 
 struct AttnParams {
     __nv_bfloat16* out;
@@ -31,6 +36,7 @@ struct AttnParams {
     int T, H, B;
     int n_qtiles;
     float scale_log2;       // 1/sqrt(hd) * log2(e)
+    unsigned long long* prof;   // diagnostics: cycle counters of CTA 0 (softmax warp 2 lane 0: [0..7], MMA warp lane 0: [8..15]); may be null
     uint32_t* status;
 };
 
@@ -41,56 +47,76 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <int HD>
 struct AttnSmem {
     static constexpr int kQBytes = kQTile * HD * 2;
-    static constexpr int kKBytes = kKvTile * HD * 2;
-    static constexpr int kVBytes = HD * kKvTile * 2;
-    static constexpr int kPBytes = kQTile * kKvTile * 2;
+    static constexpr int kKBytes = kKvTile * HD * 2;          // HD/64 k-blocks of [64 keys x 128 B]
+    static constexpr int kVBytes = HD * kKvTile * 2;          // [HD rows x 128 B]
+    static constexpr int kStageBytes = kKBytes + kVBytes;
+    static constexpr int kPBytes = kQTile * kKvTile * 2;      // [128 rows x 128 B]
     static constexpr int kQ = 0;
-    static constexpr int kK = kQ + kQBytes;
-    static constexpr int kV = kK + 2 * kKBytes;
-    static constexpr int kP = kV + 2 * kVBytes;
-    static constexpr int kBars = kP + kPBytes;
-    static constexpr int kTotal = kBars + 128;
+    static constexpr int kKV = kQ + kQBytes;
+    static constexpr int kP = kKV + kKvStages * kStageBytes;
+    static constexpr int kBars = kP + 2 * kPBytes;            // mbarriers + TMEM slot + abort flag (256 B)
+    static constexpr int kX = kBars + 256;                    // running-maximum exchange: [parity][half][128] floats
+    static constexpr int kTotal = kX + 2048;
 };
 
+// Persistent kernel: CTA c takes work items c, c + gridDim.x, ... of the list (query tile, sequence*head) sorted by
+// decreasing length, and all three roles run straight through item boundaries (barrier phases are driven by running
+// counters), so the loads and the first Q K^T of the next item are in flight while the current one drains.
 template <int HD>
 __global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
     using L = AttnSmem<HD>;
-    constexpr uint32_t TMEM_COLS = 256;                     // S: columns [0,128), O_j: [128, 128+HD)
+    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;    // S: 2 x 64 columns at 0; O: 2 x HD columns at 128
     constexpr uint32_t IDESC_S = make_idesc(false, 128, kKvTile);
     constexpr uint32_t IDESC_O = make_idesc(false, 128, HD);
     constexpr int KB_Q = HD / 64;                           // 128-byte k-blocks along head_dim
-    constexpr int KB_P = kKvTile / 64;                      // 128-byte k-blocks along the keys
+    constexpr int NS = kKvStages;
 
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = smem_u32(smem);
     // barrier slots (8 bytes each)
     const uint32_t bar = base + L::kBars;
-    const uint32_t q_full = bar, k_full = bar + 8, v_full = bar + 24, kv_empty = bar + 40, s_full = bar + 56, s_free = bar + 64,
-                   p_full = bar + 72, o_full = bar + 80, o_free = bar + 88;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBars + 96);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBars + 100);
+    const uint32_t q_full = bar;                    // 2
+    const uint32_t q_free = q_full + 16;            // 2
+    const uint32_t kv_full = q_free + 16;           // NS
+    const uint32_t kv_empty = kv_full + 8 * NS;     // NS
+    const uint32_t s_full = kv_empty + 8 * NS;      // 2
+    const uint32_t s_free = s_full + 16;            // 2
+    const uint32_t p_full = s_free + 16;            // 2
+    const uint32_t o_full = p_full + 16;            // 2
+    const uint32_t o_free = o_full + 16;            // 2
+    const uint32_t mx_bar = o_free + 16;            // 4, one per TMEM lane quarter
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBars + 240);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBars + 244);
+    static_assert(8 * (4 + 2 * NS + 10 + 4) <= 240, "barrier block overflows");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = p.B * p.H;
-    const int qt = p.n_qtiles - 1 - (int)(blockIdx.x / BH);   // heavy tiles first
-    const int bh = (int)(blockIdx.x % BH);
-    const int b = bh / p.H, h = bh % p.H;
-    const int q0 = qt * kQTile;
-    const int n_kv = qt + 1;                                  // causal: key tiles 0..qt
+    const int n_items = BH * p.n_qtiles;
+    const int n_kv_seq = (p.T + kKvTile - 1) / kKvTile;
 
     if ((base & 1023u) != 0) {                                // swizzled tiles need 1024-byte alignment
         if (threadIdx.x == 0) atomicOr(p.status, 0x200u);
         return;
     }
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < 2; s++) { mbar_init(k_full + 8 * s, 1); mbar_init(v_full + 8 * s, 1); mbar_init(kv_empty + 8 * s, 1); }
-        mbar_init(s_full, 1); mbar_init(s_free, 128); mbar_init(p_full, 128); mbar_init(o_full, 1); mbar_init(o_free, 128);
+        for (int s = 0; s < NS; s++) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_empty + 8 * s, 1); }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(q_full + 8 * i, 1); mbar_init(q_free + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(s_free + 8 * i, 256); mbar_init(p_full + 8 * i, 256);
+            mbar_init(o_full + 8 * i, 1); mbar_init(o_free + 8 * i, 256);
+        }
+        for (int q = 0; q < 4; q++) mbar_init(mx_bar + 8 * q, 64);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -101,162 +127,255 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
+    // work item -> (query tile, sequence, head, number of key tiles); heavy (late) query tiles come first
+    auto decode = [&](int item, int& q0, int& bb, int& hh, int& n_kv) {
+        const int qt = p.n_qtiles - 1 - item / BH;
+        const int bh = item % BH;
+        bb = bh / p.H; hh = bh % p.H;
+        q0 = qt * kQTile;
+        n_kv = min((q0 + kQTile + kKvTile - 1) / kKvTile, n_kv_seq);       // causal: keys 0 .. q0+127, clipped to the sequence
+    };
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-            mbar_expect_tx(q_full, L::kQBytes);
-            for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(base + L::kQ + kb * (kQTile * 128), &tmQ, q_full, kb * 64, q0, h, b);
-        }
+        if (lane == 0) { tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
         bool ok = true;
-        for (int j = 0; j < n_kv && ok; j++) {
-            const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-            ok = mbar_wait(kv_empty + 8 * s, ph ^ 1, abort_flag, p.status, kErrProducerWait);
+        uint32_t g = 0, it = 0;
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, it++) {
+            int q0, bb, hh, n_kv;
+            decode(item, q0, bb, hh, n_kv);
+            const uint32_t qb = 0;       // one Q buffer: reloaded as soon as the last Q K^T of the previous item has read it
+            ok = mbar_wait(q_free + 8 * qb, (it & 1) ^ 1, abort_flag, p.status, kErrProducerWait);
             if (!ok) break;
             if (lane == 0) {
-                const int k0 = j * kKvTile;
-                mbar_expect_tx(k_full + 8 * s, L::kKBytes);
-                for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(base + L::kK + s * L::kKBytes + kb * (kKvTile * 128), &tmK, k_full + 8 * s, kb * 64, k0, h, b);
-                mbar_expect_tx(v_full + 8 * s, L::kVBytes);
-                for (int kb = 0; kb < KB_P; kb++) tma_load_4d(base + L::kV + s * L::kVBytes + kb * (HD * 128), &tmV, v_full + 8 * s, k0 + kb * 64, 0, h, b);
+                mbar_expect_tx(q_full + 8 * qb, L::kQBytes);
+                for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(base + L::kQ + qb * L::kQBytes + kb * (kQTile * 128), &tmQ, q_full + 8 * qb, kb * 64, q0, hh, bb);
             }
-            __syncwarp();
+            for (int j = 0; j < n_kv && ok; j++, g++) {
+                const uint32_t s = g % NS, u = (g / NS) & 1;
+                ok = mbar_wait(kv_empty + 8 * s, u ^ 1, abort_flag, p.status, kErrProducerWait);
+                if (!ok) break;
+                if (lane == 0) {
+                    const int k0 = j * kKvTile;
+                    const uint32_t dst = base + L::kKV + s * L::kStageBytes;
+                    mbar_expect_tx(kv_full + 8 * s, L::kStageBytes);
+                    for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(dst + kb * (kKvTile * 128), &tmK, kv_full + 8 * s, kb * 64, k0, hh, bb);
+                    tma_load_4d(dst + L::kKBytes, &tmV, kv_full + 8 * s, k0, 0, hh, bb);
+                }
+                __syncwarp();
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kErrMmaWait);
-        for (int j = 0; j < n_kv && ok; j++) {
-            const int s = j & 1; const uint32_t ph = (j >> 1) & 1, it = j & 1;
-            ok = mbar_wait(k_full + 8 * s, ph, abort_flag, p.status, kErrMmaWait) &&
-                 mbar_wait(s_free, it ^ 1, abort_flag, p.status, kErrMmaWait);
+        bool ok = true;
+        uint32_t g = 0, it = 0;
+        const bool pr = p.prof != nullptr && blockIdx.x == 0 && lane == 0;
+        unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long tprev = clock64();
+#define SPT_TICK(i) do { if (pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
+        auto issue_s = [&](uint32_t gg, uint32_t qb) {        // S = Q K^T of global step gg into S buffer gg & 1
+            const uint32_t kaddr = base + L::kKV + (gg % NS) * L::kStageBytes;
+#pragma unroll
+            for (int kb = 0; kb < KB_Q; kb++) {
+                const uint64_t adesc = make_kmajor_sw128_desc(base + L::kQ + qb * L::kQBytes + kb * (kQTile * 128));
+                const uint64_t bdesc = make_kmajor_sw128_desc(kaddr + kb * (kKvTile * 128));
+#pragma unroll
+                for (int k = 0; k < 4; k++) mma_ss<false>(tmem_s + (gg & 1) * kKvTile, adesc + 2 * k, bdesc + 2 * k, IDESC_S, (kb | k) != 0 ? 1u : 0u);
+            }
+            mma_commit(s_full + 8 * (gg & 1));
+        };
+        // waits until the operands of global step gg are loaded and its S buffer has been drained
+        auto s_ready = [&](uint32_t gg) -> bool {
+            return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait) &&
+                   mbar_wait(s_free + 8 * (gg & 1), ((gg >> 1) & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
+        };
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, it++) {
+            int q0, bb, hh, n_kv;
+            decode(item, q0, bb, hh, n_kv);
+            const uint32_t qb = 0;
+            SPT_TICK(7);
+            ok = mbar_wait(q_full + 8 * qb, it & 1, abort_flag, p.status, kErrMmaWait) && s_ready(g);
             if (!ok) break;
+            SPT_TICK(0);
             tc_fence_after();
             if (lane == 0) {
-#pragma unroll
-                for (int kb = 0; kb < KB_Q; kb++) {
-                    const uint64_t adesc = make_kmajor_sw128_desc(base + L::kQ + kb * (kQTile * 128));
-                    const uint64_t bdesc = make_kmajor_sw128_desc(base + L::kK + s * L::kKBytes + kb * (kKvTile * 128));
-#pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_s, adesc + 2 * k, bdesc + 2 * k, IDESC_S, (kb | k) != 0 ? 1u : 0u);
-                }
-                mma_commit(s_full);
+                issue_s(g, qb);
+                if (n_kv == 1) mma_commit(q_free + 8 * qb);
             }
             __syncwarp();
-            ok = mbar_wait(p_full, it, abort_flag, p.status, kErrMmaWait) &&
-                 mbar_wait(v_full + 8 * s, ph, abort_flag, p.status, kErrMmaWait) &&
-                 mbar_wait(o_free, it ^ 1, abort_flag, p.status, kErrMmaWait);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-#pragma unroll
-                for (int kb = 0; kb < KB_P; kb++) {
-                    const uint64_t adesc = make_kmajor_sw128_desc(base + L::kP + kb * (kQTile * 128));
-                    const uint64_t bdesc = make_kmajor_sw128_desc(base + L::kV + s * L::kVBytes + kb * (HD * 128));
-#pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_o, adesc + 2 * k, bdesc + 2 * k, IDESC_O, (kb | k) != 0 ? 1u : 0u);
+            for (int j = 0; j < n_kv && ok; j++, g++) {
+                const uint32_t u2 = (g >> 1) & 1;
+                if (j + 1 < n_kv) {
+                    // next scores while the softmax warps work on this step
+                    SPT_TICK(7);
+                    ok = s_ready(g + 1);
+                    if (!ok) break;
+                    SPT_TICK(1);
+                    tc_fence_after();
+                    if (lane == 0) {
+                        issue_s(g + 1, qb);
+                        if (j + 2 == n_kv) mma_commit(q_free + 8 * qb);   // last read of this item's Q
+                    }
+                    __syncwarp();
                 }
-                mma_commit(o_full);
-                mma_commit(kv_empty + 8 * s);
+                SPT_TICK(7);
+                ok = mbar_wait(p_full + 8 * (g & 1), u2, abort_flag, p.status, kErrMmaWait);
+                SPT_TICK(2);
+                ok = ok && mbar_wait(o_free + 8 * (g & 1), u2 ^ 1, abort_flag, p.status, kErrMmaWait);
+                if (!ok) break;
+                SPT_TICK(3);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint64_t adesc = make_kmajor_sw128_desc(base + L::kP + (g & 1) * L::kPBytes);
+                    const uint64_t bdesc = make_kmajor_sw128_desc(base + L::kKV + (g % NS) * L::kStageBytes + L::kKBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_o + (g & 1) * HD, adesc + 2 * k, bdesc + 2 * k, IDESC_O, k != 0 ? 1u : 0u);
+                    mma_commit(o_full + 8 * (g & 1));
+                    mma_commit(kv_empty + 8 * (g % NS));
+                }
+                __syncwarp();
             }
-            __syncwarp();
         }
+        if (pr) { for (int i = 0; i < 8; i++) p.prof[8 + i] = pc[i]; }
+#undef SPT_TICK
     } else {
-        // ---------------- softmax + accumulate: thread owns one query row ----------------
+        // ---------------- softmax + accumulate: two threads per query row ----------------
+        // Warps w and w+4 share a TMEM lane quarter.  Of query row r the thread in the lower warp owns key columns
+        // 0..31 of every tile and the first half of the output columns, its partner the other halves.  The two only
+        // have to agree on the running maximum (exchanged through shared memory); row sums stay per thread and are
+        // added once at the end.
         const int quarter = warp & 3;
+        const int ch = (warp - 2) >> 2;                          // column half
         const int r = quarter * 32 + lane;                       // row inside the tile = TMEM lane
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        const int qrow = q0 + r;
-        float m = -INFINITY, l = 0.0f;
-        float O[HD];
-#pragma unroll
-        for (int i = 0; i < HD; i++) O[i] = 0.0f;
-        uint8_t* prow = smem + L::kP + (r >> 3) * 1024 + (r & 7) * 128;   // row r of a 128-row, 128-byte-pitch swizzled block
+        constexpr int OC = HD / 2;                               // output columns per thread
+        const int prow_off = (r >> 3) * 1024 + (r & 7) * 128;    // row r of a [128 x 128 B] swizzled block
         const int rx = r & 7;
+        float* xmax = reinterpret_cast<float*>(smem + L::kX);
+        const uint32_t pair_bar = mx_bar + 8 * quarter;
         bool ok = true;
-        for (int j = 0; j < n_kv && ok; j++) {
-            const uint32_t it = j & 1;
-            const bool diag = (j == qt);
-            const int k0 = j * kKvTile;
-            ok = mbar_wait(s_full, it, abort_flag, p.status, kErrEpilogueWait);
-            if (!ok) break;
+        uint32_t g = 0, px = 0;                                  // global step; pair exchanges done so far
+        float O[OC];
+        const bool pr = p.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+        unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long tprev = clock64();
+#define SPT_TICK(i) do { if (pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
+        // O = a * O + (P V) of global step gg
+        auto fold = [&](uint32_t gg, float a) -> bool {
+            if (!mbar_wait(o_full + 8 * (gg & 1), (gg >> 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
             tc_fence_after();
-            // pass 1: row maximum of the unmasked entries
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kKvTile / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
-                tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float sv = __uint_as_float(v[i]);
-                    if (diag && (k0 + c * 32 + i > qrow)) sv = -INFINITY;
-                    mx = fmaxf(mx, sv);
+            for (int c = 0; c < OC / 32; c++) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_o + lane_off + (gg & 1) * HD + ch * OC + c * 32, v);
+                tmem_ld_wait();
+                const float2 a2 = make_float2(a, a);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float2 o2 = __ffma2_rn(make_float2(O[c * 32 + i], O[c * 32 + i + 1]), a2, make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+                    O[c * 32 + i] = o2.x; O[c * 32 + i + 1] = o2.y;
                 }
             }
-            const float m_new = fmaxf(m, mx);
-            const float alpha = ex2_approx((m - m_new) * p.scale_log2);       // 0 on the first tile (m = -inf)
-            const float mb = m_new * p.scale_log2;
-            // pass 2: p = exp2(s*c - m*c), row sum, bf16 P into shared memory
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < kKvTile / 32; c++) {
+            tc_fence_before();
+            mbar_arrive(o_free + 8 * (gg & 1));
+            return true;
+        };
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            int q0, bb, hh, n_kv;
+            decode(item, q0, bb, hh, n_kv);
+            const int qrow = q0 + r;
+            float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
+#pragma unroll
+            for (int i = 0; i < OC; i++) O[i] = 0.0f;
+            for (int j = 0; j < n_kv && ok; j++, g++) {
+                const uint32_t sb = g & 1;
+                const int kcol0 = j * kKvTile + ch * 32;             // key index of this thread's first column
+                const bool diag = (j * kKvTile + kKvTile - 1 > q0);  // tile reaches past the first row of the query tile
+                SPT_TICK(7);
+                ok = mbar_wait(s_full + 8 * sb, (g >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
+                if (!ok) break;
+                SPT_TICK(0);
+                tc_fence_after();
                 uint32_t v[32];
-                tmem_ld_32x32(tmem_s + lane_off + c * 32, v);
+                tmem_ld_32x32(tmem_s + lane_off + sb * kKvTile + ch * 32, v);
                 tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(s_free + 8 * sb);                        // scores are in registers: the buffer can take the S after next
+                SPT_TICK(1);
+                float mx = -INFINITY;
+                if (diag) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) if (kcol0 + i > qrow) v[i] = 0xff800000u;     // -inf
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                // double buffered by exchange parity: the partner may still be reading the previous value
+                float* xm = xmax + (px & 1) * 256;
+                xm[ch * 128 + r] = mx;
+                mbar_arrive(pair_bar);
+                ok = mbar_wait(pair_bar, px & 1, abort_flag, p.status, kErrEpilogueWait);
+                if (!ok) break;
+                px++;
+                SPT_TICK(2);
+                const float m_new = fmaxf(m, fmaxf(mx, xm[(ch ^ 1) * 128 + r]));
+                const float alpha = ex2_approx((m - m_new) * p.scale_log2);       // 0 on the first tile (m = -inf)
+                const float mb = m_new * p.scale_log2;
+                // the softmax warps are bound by instruction issue: scale/subtract, the row sum and the accumulator
+                // update run on pairs of floats (fma.rn.f32x2 / add.rn.f32x2), the maximum on three inputs at a time
+                float2 sum2 = make_float2(0.0f, 0.0f);
+                const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nmb2 = make_float2(-mb, -mb);
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float a0 = __uint_as_float(v[i]), a1 = __uint_as_float(v[i + 1]);
-                    float e0 = ex2_approx(fmaf(a0, p.scale_log2, -mb)), e1 = ex2_approx(fmaf(a1, p.scale_log2, -mb));
-                    if (diag) {
-                        if (k0 + c * 32 + i > qrow) e0 = 0.0f;
-                        if (k0 + c * 32 + i + 1 > qrow) e1 = 0.0f;
-                    }
-                    sum += e0 + e1;
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
+                    float2 t = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nmb2);
+                    float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));                   // exp2(-inf) = 0 for masked entries
+                    sum2 = __fadd2_rn(sum2, e);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h2);
                 }
-                // columns c*32 .. c*32+31 = 64 bytes = four 16-byte chunks of k-block (c/2), chunk index (c%2)*4 + q
-                uint8_t* blk = prow + (c >> 1) * (kQTile * 128);
+                const float sum = sum2.x + sum2.y;
+                // P buffer sb was last read by the P V two steps back, whose completion this thread's fold already waited for
+                uint8_t* prow = smem + L::kP + sb * L::kPBytes + prow_off;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    const int chunk = ((c & 1) * 4 + q) ^ rx;
-                    *reinterpret_cast<uint4*>(blk + chunk * 16) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    const int chunk = (ch * 4 + q) ^ rx;               // 32 columns = 64 bytes = 16-byte chunks ch*4 .. ch*4+3
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the MMA's async-proxy reads
+                SPT_TICK(3);
+                mbar_arrive(p_full + 8 * sb);
+                l = l * alpha + sum;
+                m = m_new;
+                if (j > 0) ok = fold(g - 1, alpha_prev);              // the previous step's product, long finished
+                SPT_TICK(4);
+                alpha_prev = alpha;
+            }
+            if (ok && n_kv > 0) ok = fold(g - 1, alpha_prev);
+            if (!ok) break;
+            SPT_TICK(5);
+            // total row sum = own half + partner's half
+            float* xm = xmax + (px & 1) * 256;
+            xm[ch * 128 + r] = l;
+            mbar_arrive(pair_bar);
+            ok = mbar_wait(pair_bar, px & 1, abort_flag, p.status, kErrEpilogueWait);
+            if (!ok) break;
+            px++;
+            if (qrow < p.T) {
+                const float inv = 1.0f / (l + xm[(ch ^ 1) * 128 + r]);
+                __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD + ch * OC;
+#pragma unroll
+                for (int i = 0; i < OC; i += 8) {
+                    uint4 o;
+                    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(O[i + 2 * q] * inv, O[i + 2 * q + 1] * inv);
+                    *reinterpret_cast<uint4*>(orow + i) = o;
                 }
             }
-            tc_fence_before();
-            mbar_arrive(s_free);                                   // S may be overwritten by the next Q K^T
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the MMA's async-proxy reads
-            mbar_arrive(p_full);
-            l = l * alpha + sum;
-            m = m_new;
-            ok = mbar_wait(o_full, it, abort_flag, p.status, kErrEpilogueWait);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_o + lane_off + c * 32, v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i++) O[c * 32 + i] = fmaf(O[c * 32 + i], alpha, __uint_as_float(v[i]));
-            }
-            tc_fence_before();
-            mbar_arrive(o_free);
+            SPT_TICK(6);
         }
-        if (ok && qrow < p.T) {
-            const float inv = 1.0f / l;
-            __nv_bfloat16* orow = p.out + ((long long)b * p.T + qrow) * p.ld_out + (long long)h * HD;
-#pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                uint4 o;
-                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-                for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(O[i + 2 * q] * inv, O[i + 2 * q + 1] * inv);
-                *reinterpret_cast<uint4*>(orow + i) = o;
-            }
-        }
+        if (pr) { for (int i = 0; i < 8; i++) p.prof[i] = pc[i]; }
+#undef SPT_TICK
     }
 
     tc_fence_before();
@@ -298,6 +417,21 @@ static int encode4(CUtensorMap* map, const void* ptr, long long d0, long long d1
     return 0;
 }
 
+// diagnostics: when SPTORCH_B200_ATTN_PROF is set, CTA 0 of every fused-attention launch records where one softmax
+// thread and the MMA thread spend their cycles (read back with sptorch_ext_debug_attn_prof)
+static unsigned long long* g_attn_prof = nullptr;
+static unsigned long long* attn_prof_buffer() {
+    static const bool on = getenv("SPTORCH_B200_ATTN_PROF") != nullptr;
+    if (!on) return nullptr;
+    if (!g_attn_prof) { if (cudaMalloc(&g_attn_prof, 16 * sizeof(unsigned long long)) != cudaSuccess) g_attn_prof = nullptr; }
+    return g_attn_prof;
+}
+extern "C" int sptorch_ext_debug_attn_prof(unsigned long long* host16) {
+    if (enter() || !g_attn_prof || !host16) return 1;
+    cudaStreamSynchronize(rt().stream);
+    return cudaMemcpy(host16, g_attn_prof, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
+}
+
 bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch) {
     return (hd == 64 || hd == 128) && T % 8 == 0 && ld_qk % 8 == 0 && vt_ld % 8 == 0 && vt_s_head % 8 == 0 && vt_s_batch % 8 == 0;
 }
@@ -319,8 +453,11 @@ int attention_fused(const void* q, const void* k, const void* vt, long long vt_l
     prm.n_qtiles = ceil_div(T, kQTile);
     prm.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
     prm.status = rt().dev_status;
-    long long grid = (long long)B * H * prm.n_qtiles;
-    if (grid > INT32_MAX) return fail("attention_fused: grid too large");
+    prm.prof = attn_prof_buffer();
+    long long items = (long long)B * H * prm.n_qtiles;
+    if (items > INT32_MAX) return fail("attention_fused: too many work items");
+    const long long slots = (long long)rt().sm_count * (hd == 64 ? 2 : 1);      // resident CTAs
+    long long grid = items < slots ? items : slots;
     ProfScope ps(PROF_ATTN_FUSED);
     if (hd == 64) {
         static bool set = false;

@@ -50,7 +50,6 @@ struct GemmParams {
     int causal_k;
     int tma_store;      // 1: C is written through the tensor map tmC; 0: element-wise stores
     int r_vec;          // 1: residual rows can be read with 16-byte loads
-    int debug;          // experiments only: bit0 = skip the global write-out, bit1 = skip the whole epilogue body
     uint32_t* status;
 };
 
@@ -226,7 +225,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const TOut* rbase = p.R ? reinterpret_cast<const TOut*>(p.R) + zoff : nullptr;
             const int row = m0 + quarter * 32 + lane;        // this thread's output row
             const bool row_ok = row < p.M;
-            const int n_chunks = (p.debug & 2) ? 0 : min(BN / 32, (p.N - n0 + 31) / 32);
+            const int n_chunks = min(BN / 32, (p.N - n0 + 31) / 32);
             const int c_begin = min(half * CPW, n_chunks), c_end = min(c_begin + CPW, n_chunks);
             // bias slice of the tile: one value per epilogue thread, parked in shared memory after the barrier wait
             float bval = 0.0f;
@@ -301,7 +300,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         }
                     }
                 }
-                if (p.debug & 1) continue;
                 if (use_tma) {
                     uint8_t* buf = stg + (chunk_seq % NBUF) * STG_BYTES;
                     // the store that last read this buffer must have finished reading it
@@ -459,8 +457,6 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     if (!gemm_supported(d, &why)) return fail("gemm: %s", why);
     plan->d = d;
     int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
-    static const int force_bn = getenv("SPTORCH_B200_GEMM_BN") ? atoi(getenv("SPTORCH_B200_GEMM_BN")) : 0;
-    if (force_bn == 64 || force_bn == 128 || force_bn == 256) bn = force_bn;
     plan->bn = bn;
     plan->tiles_m = ceil_div(d.M, BM);
     plan->tiles_n = ceil_div(d.N, bn);
@@ -503,8 +499,6 @@ int gemm_run(const GemmPlan& pl) {
                     (d.nb1 <= 1 || (d.sC1 * oes) % 16 == 0) && (d.nb2 <= 1 || (d.sC2 * oes) % 16 == 0);
     }
     prm.status = rt().dev_status;
-    static const int dbg = getenv("SPTORCH_B200_GEMM_DEBUG") ? atoi(getenv("SPTORCH_B200_GEMM_DEBUG")) : 0;
-    prm.debug = dbg;
     const bool tf32 = d.mode == MM_TF32;
     const bool out_bf16 = d.out_dtype == BF16;
 #define SPT_GEMM_CASE(BN_)                                                                          \
