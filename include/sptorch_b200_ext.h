@@ -134,6 +134,8 @@ size_t sptorch_ext_gpt_logits_ld(void* gpt);                       /* row stride
 /* ids_i32 [batch*T] on the device -> logits [batch*T, ld] on the device in the model dtype */
 int   sptorch_ext_gpt_forward(void* gpt, const void* ids_i32, int batch, int T, void* logits);
 /* residual stream after embedding (i=0), after block i (1..L), and ln_f output (L+1): [batch*T, d] model dtype */
+/* CUDA-graph replay of sptorch_ext_gpt_forward (on by default; the third call with unchanged arguments is the first replay) */
+int   sptorch_ext_gpt_enable_graphs(void* gpt, int on);
 int   sptorch_ext_gpt_enable_taps(void* gpt, int on);
 const void* sptorch_ext_gpt_tap(void* gpt, int i);
 /* Host-buffer call, the shape of nn::GPT::forward_ids: ids on the host in, dense [batch*T, vocab]

@@ -88,6 +88,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_set_param": (_i, [_vp, C.c_char_p, _vp, _sz]),
     "sptorch_ext_gpt_logits_ld": (_sz, [_vp]),
     "sptorch_ext_gpt_forward": (_i, [_vp, _vp, _i, _i, _vp]),
+    "sptorch_ext_gpt_enable_graphs": (_i, [_vp, _i]),
     "sptorch_ext_gpt_enable_taps": (_i, [_vp, _i]),
     "sptorch_ext_gpt_tap": (_vp, [_vp, _i]),
     "sptorch_ext_gpt_forward_host": (_i, [_vp, _vp, _i, _i, _vp, _i]),

@@ -58,6 +58,7 @@ inline void note_submit() { rt().submitted.fetch_add(1, std::memory_order_relaxe
 
 // Per-category device timing (CUDA events around launches on the library stream); off by default.
 enum ProfCat : int { PROF_LINEAR = 0, PROF_ATTN_GEMM = 1, PROF_SOFTMAX = 2, PROF_LAYERNORM = 3, PROF_EMBED = 4, PROF_OTHER = 5, PROF_ATTN_FUSED = 6, PROF_NCAT = 7 };
+bool prof_enabled();
 void prof_begin(int cat);
 void prof_end(int cat);
 struct ProfScope { int c; explicit ProfScope(int cat) : c(cat) { prof_begin(c); } ~ProfScope() { prof_end(c); } };

@@ -47,6 +47,12 @@ struct Gpt {
     // pipelined host call
     void* logits_dev[2] = {nullptr, nullptr}; int* ids_dev = nullptr; int ids_cap = 0; size_t logits_cap = 0;
     cudaEvent_t ev_compute[2] = {nullptr, nullptr}, ev_copy[2] = {nullptr, nullptr};
+    // CUDA graph of one forward, keyed by everything that is baked into its kernel arguments
+    struct GraphKey { const void* ids; void* logits; int batch, T; bool taps; cudaStream_t stream; };
+    GraphKey gkey = {nullptr, nullptr, 0, 0, false, nullptr};
+    cudaGraphExec_t gexec = nullptr;
+    int eager_runs = 0;        // forwards of the current key run eagerly so far (the first one sets function attributes)
+    bool graphs = true;
 };
 
 static void* galloc(Gpt* g, size_t bytes) {
@@ -208,6 +214,7 @@ void sptorch_ext_gpt_destroy(void* gp) {
     if (!enter()) {
         cudaStreamSynchronize(rt().stream);
         cudaStreamSynchronize(rt().copy_stream);
+        if (g->gexec) cudaGraphExecDestroy(g->gexec);
         for (void* p : g->owned) sptorch_free(p);
         for (int i = 0; i < 2; i++) {
             if (g->ev_compute[i]) cudaEventDestroy(g->ev_compute[i]);
@@ -269,7 +276,49 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
     if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
     Gpt* g = (Gpt*)gp;
     if (check_shape(g, batch, T)) return 1;
-    return forward(g, ids, batch, T, logits);
+    // The launch-bound inner loop (about 100 kernels, each a few microseconds when the batch is sharded 8 ways) is
+    // replayed as one CUDA graph: the first forward of a given (ids, logits, batch, T) runs eagerly, the second is
+    // captured, later ones are a single cudaGraphLaunch.  Per-kernel timing and tensor-parallel hooks run eagerly.
+    const bool graph_ok = g->graphs && !prof_enabled() && g->c.tp_size <= 1;
+    if (!graph_ok) return forward(g, ids, batch, T, logits);
+    Gpt::GraphKey key = {ids, logits, batch, T, g->taps_on, rt().stream};
+    const bool same = key.ids == g->gkey.ids && key.logits == g->gkey.logits && key.batch == g->gkey.batch && key.T == g->gkey.T &&
+                      key.taps == g->gkey.taps && key.stream == g->gkey.stream;
+    if (!same) {
+        if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
+        g->gkey = key; g->eager_runs = 0;
+    }
+    if (g->gexec) {
+        SPT_CUDA(cudaGraphLaunch(g->gexec, rt().stream));
+        note_submit();
+        return 0;
+    }
+    if (g->eager_runs++ == 0) return forward(g, ids, batch, T, logits);
+    cudaGraph_t graph = nullptr;
+    SPT_CUDA(cudaStreamBeginCapture(rt().stream, cudaStreamCaptureModeThreadLocal));
+    int rc = forward(g, ids, batch, T, logits);
+    cudaError_t e = cudaStreamEndCapture(rt().stream, &graph);
+    if (rc != 0 || e != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        g->graphs = false;                                   // capture is not possible here: stay eager from now on
+        if (rc != 0) return rc;
+        return forward(g, ids, batch, T, logits);
+    }
+    e = cudaGraphInstantiate(&g->gexec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { g->gexec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits); }
+    SPT_CUDA(cudaGraphLaunch(g->gexec, rt().stream));
+    note_submit();
+    return 0;
+}
+
+int sptorch_ext_gpt_enable_graphs(void* gp, int on) {
+    if (!gp) return fail("gpt_enable_graphs: null model");
+    Gpt* g = (Gpt*)gp;
+    g->graphs = on != 0;
+    if (!on && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; g->eager_runs = 0; }
+    return 0;
 }
 
 int sptorch_ext_gpt_enable_taps(void* gp, int on) {

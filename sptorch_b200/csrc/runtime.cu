@@ -38,6 +38,7 @@ static cudaEvent_t prof_event() {
     cudaEventCreate(&e);
     return e;
 }
+bool prof_enabled() { return g_prof_on; }
 void prof_begin(int) {
     if (!g_prof_on) return;
     std::lock_guard<std::mutex> lk(g_prof_mu);

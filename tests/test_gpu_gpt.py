@@ -134,3 +134,22 @@ def test_gpt2_small_shape_layer_slice_vs_oracle(backend, oracle):
     for i in range(cfg["n_layer"] + 2):
         assert relerr(m.tap(i, 2 * 1024).reshape(2, 1024, -1), taps[:, i]) <= 2e-2, f"layer tap {i}"
     m.close()
+
+
+def test_graph_replay_matches_eager(backend):
+    """The third forward with unchanged arguments is a CUDA-graph replay; it must give the eager result bit for bit,
+    and new ids in the same buffer must be picked up (the graph bakes in addresses, not contents)."""
+    cfg = dict(vocab=512, d_model=128, n_layer=2, n_head=2, d_ff=256, seq_len=64)
+    params, index = synth.gpt_params(cfg, 2)
+    m = _model(backend, cfg, BF16, 4, params, index)
+    ids_a = synth.randint(7, 4 * 64, 512).reshape(4, 64)
+    ids_b = synth.randint(8, 4 * 64, 512).reshape(4, 64)
+    backend.lib.sptorch_ext_gpt_enable_graphs(m.h, 0)
+    ref_a, ref_b = m.forward(ids_a), m.forward(ids_b)
+    backend.lib.sptorch_ext_gpt_enable_graphs(m.h, 1)
+    outs = [m.forward(ids_a) for _ in range(4)]          # eager, capture, replay, replay
+    for o in outs:
+        assert np.array_equal(o, ref_a)
+    assert np.array_equal(m.forward(ids_b), ref_b)       # same device buffers, new contents
+    assert not np.array_equal(ref_a, ref_b)
+    m.close()
