@@ -71,7 +71,7 @@ struct AttnSmem {
 // Persistent kernel: CTA c takes work items c, c + gridDim.x, ... of the list (query tile, sequence*head) sorted by
 // decreasing length, and all three roles run straight through item boundaries (barrier phases are driven by running
 // counters), so the loads and the first Q K^T of the next item are in flight while the current one drains.
-template <int HD>
+template <int HD, bool PROF>
 __global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -169,10 +169,10 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // ---------------- MMA issuer ----------------
         bool ok = true;
         uint32_t g = 0, it = 0;
-        const bool pr = p.prof != nullptr && blockIdx.x == 0 && lane == 0;
+        const bool pr = PROF && p.prof != nullptr && blockIdx.x == 0 && lane == 0;
         unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tprev = clock64();
-#define SPT_TICK(i) do { if (pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
+#define SPT_TICK(i) do { if (PROF && pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
         auto issue_s = [&](uint32_t gg, uint32_t qb) {        // S = Q K^T of global step gg into S buffer gg & 1
             const uint32_t kaddr = base + L::kKV + (gg % NS) * L::kStageBytes;
 #pragma unroll
@@ -256,10 +256,10 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         bool ok = true;
         uint32_t g = 0, px = 0;                                  // global step; pair exchanges done so far
         float O[OC];
-        const bool pr = p.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+        const bool pr = PROF && p.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
         unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tprev = clock64();
-#define SPT_TICK(i) do { if (pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
+#define SPT_TICK(i) do { if (PROF && pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
         // O = a * O + (P V) of global step gg
         auto fold = [&](uint32_t gg, float a) -> bool {
             if (!mbar_wait(o_full + 8 * (gg & 1), (gg >> 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
@@ -459,15 +459,15 @@ int attention_fused(const void* q, const void* k, const void* vt, long long vt_l
     const long long slots = (long long)rt().sm_count * (hd == 64 ? 2 : 1);      // resident CTAs
     long long grid = items < slots ? items : slots;
     ProfScope ps(PROF_ATTN_FUSED);
-    if (hd == 64) {
-        static bool set = false;
-        if (!set) { SPT_CUDA(cudaFuncSetAttribute(attn_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<64>::kTotal)); set = true; }
-        attn_fused_kernel<64><<<(unsigned)grid, kAttnThreads, AttnSmem<64>::kTotal, rt().stream>>>(tq, tk, tv, prm);
-    } else {
-        static bool set = false;
-        if (!set) { SPT_CUDA(cudaFuncSetAttribute(attn_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<128>::kTotal)); set = true; }
-        attn_fused_kernel<128><<<(unsigned)grid, kAttnThreads, AttnSmem<128>::kTotal, rt().stream>>>(tq, tk, tv, prm);
-    }
+    auto launch = [&](auto kern, int smem_bytes) -> int {
+        SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        kern<<<(unsigned)grid, kAttnThreads, smem_bytes, rt().stream>>>(tq, tk, tv, prm);
+        return 0;
+    };
+    int lrc;
+    if (hd == 64) lrc = prm.prof ? launch(attn_fused_kernel<64, true>, AttnSmem<64>::kTotal) : launch(attn_fused_kernel<64, false>, AttnSmem<64>::kTotal);
+    else lrc = prm.prof ? launch(attn_fused_kernel<128, true>, AttnSmem<128>::kTotal) : launch(attn_fused_kernel<128, false>, AttnSmem<128>::kTotal);
+    if (lrc) return lrc;
     SPT_LAUNCH_CHECK("attn_fused");
     return 0;
 }

@@ -88,7 +88,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     constexpr int B_BYTES = BN * kStageRowBytes;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int BK = TF32 ? 32 : 64;                 // elements of K per stage
-    constexpr uint32_t TMEM_COLS = 2 * BN;             // two accumulators; power of two >= 32
+    constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : BN <= 128 ? 256 : 512;   // two accumulators of BN columns; a power of two >= 32
     constexpr uint32_t IDESC = make_idesc(TF32, BM, BN);
 
     // layout: [kStages x (A tile | B tile)] [8 x 4 KB epilogue staging] [2 x 1 KB bias tiles] [barriers, 256 B]
