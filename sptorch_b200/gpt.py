@@ -84,8 +84,19 @@ class GPT:
     def forward(self, ids: np.ndarray) -> np.ndarray:
         """ids [B, T] -> logits [B, T, V] float32 on the host."""
         ids = np.asarray(ids)
-        B, T = ids.shape
+        B, T0 = ids.shape
         V = self.cfg["vocab"]
+        if T0 > self.cfg["seq_len"]:
+            raise HalError("sequence longer than seq_len")   # the reference asserts (nn/src/lib.rs:1351)
+        # The kernels want T to be a multiple of one 16-byte vector.  A ragged length is padded at the END with token 0:
+        # under the causal mask no earlier position can see the padding, so rows 0..T0-1 are unchanged; the padded
+        # rows are dropped here.
+        vec = 8 if self.dtype == BF16 else 4
+        T = min(-(-T0 // vec) * vec, max(self.cfg["seq_len"] // vec * vec, T0))
+        if T != T0:
+            if T % vec:
+                raise HalError(f"T={T0} cannot be padded to a multiple of {vec} within seq_len={self.cfg['seq_len']}")
+            ids = np.concatenate([ids, np.zeros((B, T - T0), dtype=ids.dtype)], axis=1)
         d_ids = self.stage_ids(ids)
         d_log = self.logits_buffer(B * T)
         self.forward_device(d_ids, B, T, d_log)
@@ -93,13 +104,11 @@ class GPT:
         self.b._check(self.b.lib.sptorch_ext_copy_d2h_bytes(d_log.handle, raw.ctypes.data, raw.nbytes), "logits d2h")
         self.b.synchronize()
         out = bf16_bits_to_f32(raw) if self.dtype == BF16 else raw
-        return out.reshape(B * T, self.ldl)[:, :V].reshape(B, T, V).copy()
+        return out.reshape(B, T, self.ldl)[:, :T0, :V].copy()
 
     def forward_ids(self, token_ids) -> np.ndarray:
         """GPT::forward_ids (nn/src/lib.rs:1349-1364): one sequence of ids -> logits [T, V]."""
         ids = np.asarray(token_ids).reshape(1, -1)
-        if ids.shape[1] > self.cfg["seq_len"]:
-            raise HalError("sequence longer than seq_len")   # the reference asserts (nn/src/lib.rs:1351)
         return self.forward(ids)[0]
 
     def forward_host(self, ids_host_ptr: int, batch: int, T: int, logits_host_ptr: int, chunk: int):

@@ -153,3 +153,18 @@ def test_graph_replay_matches_eager(backend):
     assert np.array_equal(m.forward(ids_b), ref_b)       # same device buffers, new contents
     assert not np.array_equal(ref_a, ref_b)
     m.close()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("T", [1, 5, 13, 30])
+def test_ragged_sequence_lengths_vs_oracle(backend, oracle, dtype, T):
+    """Any T <= seq_len is legal in the reference (crates/nn/src/lib.rs:1349-1351); lengths that are not a multiple of
+    the vector width are padded behind the causal mask and must still match the oracle."""
+    cfg = dict(vocab=200, d_model=64, n_layer=2, n_head=2, d_ff=128, seq_len=32)
+    params, index = synth.gpt_params(cfg, 4, randomize_affine=True)
+    ids = synth.randint(9, 3 * T, 200).reshape(3, T)
+    m = _model(backend, cfg, dtype, 3, params, index)
+    out = m.forward(ids)
+    assert out.shape == (3, T, 200)
+    assert relerr(out, oracle.gpt_forward(cfg, params, ids)) <= TOL[dtype]
+    m.close()
