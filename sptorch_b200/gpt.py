@@ -92,9 +92,9 @@ class GPT:
         # under the causal mask no earlier position can see the padding, so rows 0..T0-1 are unchanged; the padded
         # rows are dropped here.
         vec = 8 if self.dtype == BF16 else 4
-        T = min(-(-T0 // vec) * vec, max(self.cfg["seq_len"] // vec * vec, T0))
+        T = -(-T0 // vec) * vec
         if T != T0:
-            if T % vec:
+            if T > self.cfg["seq_len"]:
                 raise HalError(f"T={T0} cannot be padded to a multiple of {vec} within seq_len={self.cfg['seq_len']}")
             ids = np.concatenate([ids, np.zeros((B, T - T0), dtype=ids.dtype)], axis=1)
         d_ids = self.stage_ids(ids)
