@@ -84,6 +84,16 @@ int sptorch_ext_masked_softmax_f32(const void* a, const void* keep_u8, void* out
 int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* ids_i32, void* out,
                               size_t n_tokens, size_t T, size_t vocab, size_t dim, int dtype);
 
+/* ---- neighbours of the path (the Qwen-like blocks and the step after the forward) ---- */
+int sptorch_ext_rms_norm(const void* x, const void* weight_f32, void* out, size_t rows, size_t dim, float eps, int dtype);   /* core-ops/src/lib.rs:1453 */
+int sptorch_ext_swiglu(const void* x, const void* gate, void* out, size_t n, int dtype);                                    /* core-ops/src/lib.rs:1529 */
+/* cross_entropy_loss / cross_entropy_loss_ignore_index over logits [rows, ld] (core-ops/src/lib.rs:1079-1194): mean of
+ * -(x[target] - logsumexp(x)) over the rows whose target differs from ignore_index (has_ignore = 0: every row).
+ * row_loss_f32: device scratch of rows + 1 floats (per-row losses, then the mean); the mean is also copied to *host_mean.
+ * A target outside [0, classes) is reported at the next sync (the reference panics). */
+int sptorch_ext_cross_entropy(const void* logits, size_t ld, const void* targets_i64, size_t rows, size_t classes, int has_ignore,
+                              long long ignore_index, void* row_loss_f32, float* host_mean, int dtype);
+
 /* ---- Linear (nn/src/lib.rs:121-133): out[M,N] = act(alpha * x[M,K] W[N,K]^T + bias[N]) + residual[M,N] ----
  * W is consumed in its native [out,in] layout; the reference's transpose() copy does not exist here.
  * mode SPT_MM_BF16: x, W, residual, out are bf16 (out may be f32 with out_dtype); SPT_MM_TF32 / SPT_MM_F32: f32.

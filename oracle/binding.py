@@ -43,6 +43,7 @@ def lib():
         _lib = C.CDLL(so)
         L = _lib
         L.orc_sum.restype = C.c_float
+        L.orc_cross_entropy.restype = C.c_float
         L.orc_gpt_param_count.restype = _sz
         L.orc_gpt_param_count.argtypes = [C.POINTER(GptConfig)]
     return _lib
@@ -164,6 +165,29 @@ def layernorm(x, gamma, beta, eps=1e-5):
     x2 = x.reshape(-1, x.shape[-1]); out = np.empty_like(x2)
     lib().orc_layernorm(_p(x2), _p(g), _p(b), _p(out), _sz(x2.shape[0]), _sz(x2.shape[1]), C.c_float(eps))
     return out.reshape(x.shape)
+
+
+def rms_norm(x, w, eps=1e-6):
+    x = _f32(x); w = _f32(w)
+    x2 = x.reshape(-1, x.shape[-1]); out = np.empty_like(x2)
+    lib().orc_rms_norm(_p(x2), _p(w), _p(out), _sz(x2.shape[0]), _sz(x2.shape[1]), C.c_float(eps))
+    return out.reshape(x.shape)
+
+
+def swiglu(x, gate):
+    x = _f32(x); g = _f32(gate); out = np.empty_like(x)
+    lib().orc_swiglu(_p(x), _p(g), _p(out), _sz(x.size))
+    return out
+
+
+def cross_entropy(logits, targets, ignore_index=None):
+    x = _f32(logits); t = np.ascontiguousarray(targets, dtype=np.int64)
+    bad = C.c_int(0)
+    r = lib().orc_cross_entropy(_p(x), t.ctypes.data_as(_i64), _sz(x.shape[0]), _sz(x.shape[1]), C.c_int(ignore_index is not None),
+                                C.c_int64(ignore_index if ignore_index is not None else 0), C.byref(bad))
+    if bad.value:
+        raise IndexError("cross_entropy target out of range")
+    return float(r)
 
 
 def linear(x, w, bias=None, fast=0):

@@ -145,6 +145,44 @@ void orc_masked_softmax(const float* a, const uint8_t* keep, float* out, size_t 
     }
 }
 
+/* rms_norm: crates/core-ops/src/lib.rs:1453-1475 (sequential sum of squares, inv = 1/sqrt(mean_sq+eps), x*inv*w). */
+void orc_rms_norm(const float* x, const float* w, float* out, size_t rows, size_t dim, float eps) {
+    for (size_t r = 0; r < rows; r++) {
+        const float* xr = x + r * dim; float* yr = out + r * dim;
+        float ms = 0.0f;
+        for (size_t i = 0; i < dim; i++) ms += xr[i] * xr[i];
+        ms /= (float)dim;
+        float inv = 1.0f / sqrtf(ms + eps);
+        for (size_t i = 0; i < dim; i++) yr[i] = xr[i] * inv * w[i];
+    }
+}
+
+/* swiglu: crates/core-ops/src/lib.rs:1529-1540 (s = 1/(1+exp(-g)); x*g*s). */
+void orc_swiglu(const float* x, const float* gate, float* out, size_t n) {
+    for (size_t i = 0; i < n; i++) { float s = 1.0f / (1.0f + expf(-gate[i])); out[i] = x[i] * gate[i] * s; }
+}
+
+/* cross_entropy_loss(_ignore_index), batched path: crates/core-ops/src/lib.rs:1131-1168.  Mean over the rows whose
+ * target is not the ignore index (0 if none); returns -1 through *bad for an out-of-range target (the reference panics). */
+float orc_cross_entropy(const float* logits, const int64_t* targets, size_t rows, size_t classes, int has_ignore,
+                        int64_t ignore_index, int* bad) {
+    float total = 0.0f; size_t active = 0;
+    if (bad) *bad = 0;
+    for (size_t r = 0; r < rows; r++) {
+        const float* x = logits + r * classes;
+        if (has_ignore && targets[r] == ignore_index) continue;
+        if (targets[r] < 0 || (size_t)targets[r] >= classes) { if (bad) *bad = 1; return 0.0f; }
+        float mx = -INFINITY;
+        for (size_t c = 0; c < classes; c++) mx = fmaxf(mx, x[c]);
+        float s = 0.0f;
+        for (size_t c = 0; c < classes; c++) s += expf(x[c] - mx);
+        float ls = logf(s);
+        total += -(x[targets[r]] - mx - ls);
+        active++;
+    }
+    return active == 0 ? 0.0f : total / (float)active;
+}
+
 /* optimizer kernels of the KernelProvider trait: crates/hal/src/lib.rs:616-646. */
 void orc_sgd_update(float* p, const float* g, float lr, size_t n) { for (size_t i = 0; i < n; i++) p[i] -= lr * g[i]; }
 void orc_adam_update(float* p, const float* g, float* m, float* v, size_t n, float lr, float beta1,

@@ -48,6 +48,10 @@ void orc_batch_matmul(const float* a, const float* b, float* out, size_t batch, 
 void orc_softmax(const float* a, float* out, size_t rows, size_t cols);
 void orc_softmax_hal(const float* a, float* out, size_t rows, size_t cols);
 void orc_masked_softmax(const float* a, const uint8_t* keep, float* out, size_t rows, size_t cols, int rank1);
+void orc_rms_norm(const float* x, const float* w, float* out, size_t rows, size_t dim, float eps);
+void orc_swiglu(const float* x, const float* gate, float* out, size_t n);
+float orc_cross_entropy(const float* logits, const int64_t* targets, size_t rows, size_t classes, int has_ignore,
+                        int64_t ignore_index, int* bad);
 void orc_sgd_update(float* p, const float* g, float lr, size_t n);
 void orc_adam_update(float* p, const float* g, float* m, float* v, size_t n, float lr, float beta1,
                      float beta2, float eps, float weight_decay, float bc1, float bc2);

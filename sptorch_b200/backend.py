@@ -335,6 +335,54 @@ class FfiBackend:
         finally:
             dx.free(); do.free()
 
+    def rms_norm(self, x, weight, eps=1e-6, dtype=F32):
+        """core-ops rms_norm (crates/core-ops/src/lib.rs:1453-1491)."""
+        x = _f32(x)
+        rows, dim = int(np.prod(x.shape[:-1])), x.shape[-1]
+        dw = self.upload(weight)
+        dx = self.upload(x) if dtype == F32 else self.upload_bf16(x)
+        do = self.alloc(x.size, 4 if dtype == F32 else 2)
+        try:
+            self._check(self.lib.sptorch_ext_rms_norm(dx.handle, dw.handle, do.handle, rows, dim, C.c_float(eps), dtype), "rms_norm")
+            out = do.to_host()
+            return (out if dtype == F32 else bf16_bits_to_f32(out)).reshape(x.shape)
+        finally:
+            for b in (dw, dx, do):
+                b.free()
+
+    def swiglu(self, x, gate, dtype=F32):
+        """core-ops swiglu (crates/core-ops/src/lib.rs:1529-1556)."""
+        x, g = _f32(x), _f32(gate)
+        up = self.upload if dtype == F32 else self.upload_bf16
+        dx, dg = up(x), up(g)
+        do = self.alloc(x.size, 4 if dtype == F32 else 2)
+        try:
+            self._check(self.lib.sptorch_ext_swiglu(dx.handle, dg.handle, do.handle, x.size, dtype), "swiglu")
+            out = do.to_host()
+            return (out if dtype == F32 else bf16_bits_to_f32(out)).reshape(x.shape)
+        finally:
+            for b in (dx, dg, do):
+                b.free()
+
+    def cross_entropy_loss(self, logits, targets, ignore_index=None, dtype=F32):
+        """core-ops cross_entropy_loss / cross_entropy_loss_ignore_index (crates/core-ops/src/lib.rs:1079-1194)."""
+        x = _f32(logits)
+        if x.ndim == 1:
+            x = x.reshape(1, -1)
+        rows, classes = x.shape
+        t = np.ascontiguousarray(targets, dtype=np.int64).reshape(-1)
+        dx = self.upload(x) if dtype == F32 else self.upload_bf16(x)
+        dt, dl = self.upload_bytes(t), self.alloc(rows + 1)
+        try:
+            mean = C.c_float(0)
+            self._check(self.lib.sptorch_ext_cross_entropy(dx.handle, classes, dt.handle, rows, classes, int(ignore_index is not None),
+                                                           int(ignore_index) if ignore_index is not None else 0, dl.handle, C.byref(mean), dtype), "cross_entropy")
+            self.synchronize()        # an out-of-range target surfaces here (the reference asserts)
+            return mean.value
+        finally:
+            for b in (dx, dt, dl):
+                b.free()
+
     def transpose(self, a):
         a = _f32(a)
         da, do = self.upload(a), self.alloc(a.size)

@@ -38,6 +38,9 @@ struct OpGeluBf16 {
     }
 };
 
+// swiglu: crates/core-ops/src/lib.rs:1529-1540: s = 1/(1+exp(-g)); x*g*s
+struct OpSwiglu { __device__ float operator()(float x, float g) const { float s = 1.0f / (1.0f + expf(-g)); return x * g * s; } };
+
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
@@ -345,6 +348,12 @@ int sptorch_ext_gelu(const void* a, void* out, size_t n, int dtype) {
     if (dtype == SPT_F32) return run_unary_f32(a, out, n, OpGelu{}, "gelu");
     if (dtype == SPT_BF16) return run_unary_bf16(a, out, n, OpGeluBf16{}, "gelu_bf16");
     return fail("gelu: unknown dtype %d", dtype);
+}
+
+int sptorch_ext_swiglu(const void* x, const void* gate, void* out, size_t n, int dtype) {
+    if (dtype == SPT_F32) return run_binary_f32(x, gate, out, n, OpSwiglu{}, "swiglu");
+    if (dtype == SPT_BF16) return run_binary_bf16(x, gate, out, n, OpSwiglu{}, "swiglu_bf16");
+    return fail("swiglu: unknown dtype %d", dtype);
 }
 
 int sptorch_ext_masked_fill_f32(const void* a, const void* mask, float fill, void* out, size_t n) {

@@ -418,6 +418,116 @@ __global__ void __launch_bounds__(kRowThreads) embedding_sum_kernel(const T* __r
     }
 }
 
+// ---------------- rms_norm (crates/core-ops/src/lib.rs:1453-1475) ----------------
+// y = x * (1/sqrt(mean(x^2) + eps)) * w.  Same register-resident row scheme as LayerNorm; one reduction.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kRowThreads) rms_norm_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                                                               size_t rows, int dim, float eps) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    constexpr int V = kRowVecs;
+    constexpr int RPB = kRowThreads / TPR;
+    __shared__ float sh[kRowThreads / 32];
+    const int t = threadIdx.x % TPR;
+    const int rl = threadIdx.x / TPR;
+    const int nvec = dim / N;
+    for (size_t r0 = (size_t)blockIdx.x * RPB; r0 < rows; r0 += (size_t)gridDim.x * RPB) {
+        size_t r = r0 + rl;
+        bool live = r < rows;
+        const T* xr = x + (live ? r : 0) * (size_t)dim;
+        typename VT::Raw d[V];
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) d[i] = VT::load_raw(xr + c * N);
+        }
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
+#pragma unroll
+                for (int j = 0; j < N; j++) q += u.v[j] * u.v[j];
+            }
+        }
+        float ms = row_reduce<TPR, false>(q, sh) / (float)dim;
+        float inv = 1.0f / sqrtf(ms + eps);
+        T* yr = out + (live ? r : 0) * (size_t)dim;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
+                VT y;
+#pragma unroll
+                for (int j4 = 0; j4 < N; j4 += 4) {
+                    float4 g = __ldg(reinterpret_cast<const float4*>(w + c * N + j4));
+                    y.v[j4 + 0] = u.v[j4 + 0] * inv * g.x; y.v[j4 + 1] = u.v[j4 + 1] * inv * g.y;
+                    y.v[j4 + 2] = u.v[j4 + 2] * inv * g.z; y.v[j4 + 3] = u.v[j4 + 3] * inv * g.w;
+                }
+                y.store(yr + c * N);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) rms_norm_generic_kernel(const T* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                                                                       size_t rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + r * (size_t)dim;
+        float q = 0.0f;
+        for (int c = threadIdx.x; c < dim; c += kRowThreads) { float v = (float)xr[c]; q += v * v; }
+        float ms = row_reduce<kRowThreads, false>(q, sh) / (float)dim;
+        float inv = 1.0f / sqrtf(ms + eps);
+        T* yr = out + r * (size_t)dim;
+        for (int c = threadIdx.x; c < dim; c += kRowThreads) yr[c] = (T)((float)xr[c] * inv * w[c]);
+    }
+}
+
+// ---------------- cross_entropy_loss (crates/core-ops/src/lib.rs:1131-1168) ----------------
+// Per row: loss = -(x[target] - max - ln(sum exp(x - max))), one pass over the logits with a running (max, sum) pair
+// per thread, merged across the CTA.  A row whose target equals the ignore index contributes nothing; a target outside
+// [0, classes) raises the device status word (the reference asserts).  Algorithmic bytes: rows * classes * sizeof(T).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) cross_entropy_rows_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                                                                         size_t rows, int classes, int has_ignore, long long ignore_index,
+                                                                         float* __restrict__ row_loss, uint32_t* status) {
+    __shared__ float sh[kRowThreads / 32];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const long long tgt = targets[r];
+        if (has_ignore && tgt == ignore_index) { if (threadIdx.x == 0) row_loss[r] = -1.0f; continue; }   // marker: not counted
+        const bool bad = tgt < 0 || tgt >= classes;
+        if (bad) { if (threadIdx.x == 0) { atomicOr(status, 0x100u); row_loss[r] = -1.0f; } continue; }
+        const T* x = logits + r * (size_t)ld;
+        float m = -INFINITY, s = 0.0f;
+        for (int c = threadIdx.x; c < classes; c += kRowThreads) {
+            float v = (float)x[c];
+            if (v > m) { s = s * expf(m - v) + 1.0f; m = v; } else s += expf(v - m);
+        }
+        float gm = row_reduce<kRowThreads, true>(m, sh);
+        float part = (m == -INFINITY) ? 0.0f : s * expf(m - gm);
+        float gs = row_reduce<kRowThreads, false>(part, sh);
+        if (threadIdx.x == 0) row_loss[r] = -((float)x[tgt] - gm - logf(gs));
+    }
+}
+
+__global__ void __launch_bounds__(kRowThreads) cross_entropy_mean_kernel(const float* __restrict__ row_loss, size_t rows, float* __restrict__ out) {
+    __shared__ double sd[kRowThreads];
+    __shared__ unsigned long long sc[kRowThreads];
+    double t = 0.0; unsigned long long n = 0;
+    for (size_t r = threadIdx.x; r < rows; r += kRowThreads) { float v = row_loss[r]; if (v >= 0.0f || v != -1.0f) { t += (double)v; n++; } }
+    sd[threadIdx.x] = t; sc[threadIdx.x] = n;
+    __syncthreads();
+    for (int o = kRowThreads / 2; o > 0; o >>= 1) {
+        if (threadIdx.x < o) { sd[threadIdx.x] += sd[threadIdx.x + o]; sc[threadIdx.x] += sc[threadIdx.x + o]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[0] = sc[0] ? (float)(sd[0] / (double)sc[0]) : 0.0f;
+}
+
 // ---------------- transpose (crates/core-ops/src/lib.rs:825-836) ----------------
 __global__ void transpose_kernel(const float* __restrict__ a, float* __restrict__ out, int rows, int cols) {
     __shared__ float tile[32][33];
@@ -580,6 +690,51 @@ int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* 
     } else return fail("embedding_sum: unknown dtype %d", dtype);
     SPT_LAUNCH_CHECK("embedding_sum");
     return 0;
+}
+
+int sptorch_ext_rms_norm(const void* x, const void* w, void* out, size_t rows, size_t dim, float eps, int dtype) {
+    if (enter()) return 1;
+    if (rows == 0 || dim == 0) return 0;
+    if (!x || !w || !out) return fail("rms_norm: null handle");
+    if (dim > (size_t)INT32_MAX) return fail("rms_norm: dim too large");
+    if (dtype != SPT_F32 && dtype != SPT_BF16) return fail("rms_norm: unknown dtype %d", dtype);
+    const int N = dtype == SPT_BF16 ? 8 : 4;
+    const bool fast = dim % N == 0 && dim / N <= 2048 && aligned16(x) && aligned16(out) && aligned16(w);
+    const float* wp = (const float*)w;
+    if (dtype == SPT_BF16) {
+        const __nv_bfloat16* xp = (const __nv_bfloat16*)x; __nv_bfloat16* op = (__nv_bfloat16*)out;
+        if (fast) { int nvec = (int)(dim / N); SPT_ROW_DISPATCH(rms_norm_kernel, __nv_bfloat16, nvec, xp, wp, op, rows, (int)dim, eps); }
+        else rms_norm_generic_kernel<__nv_bfloat16><<<row_grid(rows), kRowThreads, 0, rt().stream>>>(xp, wp, op, rows, (int)dim, eps);
+    } else {
+        const float* xp = (const float*)x; float* op = (float*)out;
+        if (fast) { int nvec = (int)(dim / N); SPT_ROW_DISPATCH(rms_norm_kernel, float, nvec, xp, wp, op, rows, (int)dim, eps); }
+        else rms_norm_generic_kernel<float><<<row_grid(rows), kRowThreads, 0, rt().stream>>>(xp, wp, op, rows, (int)dim, eps);
+    }
+    SPT_LAUNCH_CHECK("rms_norm");
+    return 0;
+}
+
+int sptorch_ext_cross_entropy(const void* logits, size_t ld, const void* targets_i64, size_t rows, size_t classes, int has_ignore,
+                              long long ignore_index, void* row_loss_f32, float* host_mean, int dtype) {
+    if (enter()) return 1;
+    if (!host_mean) return fail("cross_entropy: null result pointer");
+    *host_mean = 0.0f;
+    if (rows == 0 || classes == 0) return 0;
+    if (!logits || !targets_i64 || !row_loss_f32) return fail("cross_entropy: null handle");
+    if (ld == 0) ld = classes;
+    if (ld < classes || classes > (size_t)INT32_MAX) return fail("cross_entropy: bad row stride or class count");
+    if (dtype != SPT_F32 && dtype != SPT_BF16) return fail("cross_entropy: unknown dtype %d", dtype);
+    float* rl = (float*)row_loss_f32;                      // rows floats + 1 for the mean
+    if (dtype == SPT_BF16)
+        cross_entropy_rows_kernel<__nv_bfloat16><<<row_grid(rows), kRowThreads, 0, rt().stream>>>((const __nv_bfloat16*)logits, (long long)ld, (const long long*)targets_i64,
+                                                                                                 rows, (int)classes, has_ignore, ignore_index, rl, rt().dev_status);
+    else
+        cross_entropy_rows_kernel<float><<<row_grid(rows), kRowThreads, 0, rt().stream>>>((const float*)logits, (long long)ld, (const long long*)targets_i64, rows,
+                                                                                         (int)classes, has_ignore, ignore_index, rl, rt().dev_status);
+    SPT_LAUNCH_CHECK("cross_entropy_rows");
+    cross_entropy_mean_kernel<<<1, kRowThreads, 0, rt().stream>>>(rl, rows, rl + rows);
+    SPT_LAUNCH_CHECK("cross_entropy_mean");
+    return sptorch_ext_copy_d2h_bytes(rl + rows, host_mean, sizeof(float));
 }
 
 int sptorch_ext_transpose_f32(const void* a, void* out, size_t rows, size_t cols) {

@@ -86,6 +86,21 @@ def test_masked_softmax_kat(oracle):
     assert r1.tolist() == [0.5, 0.5, 0.0]
 
 
+def test_rms_norm_swiglu_cross_entropy_kat(oracle):
+    # crates/core-ops/src/lib.rs:2482-2490, 2505-2511, 2366-2380, 2394-2397
+    d = oracle.rms_norm(np.array([[3, 4], [1, 2]], np.float32), [1, 2], 1e-6).ravel()
+    assert abs(d[0] - 0.8485) < 1e-3 and abs(d[1] - 2.2627) < 1e-3
+    s = oracle.swiglu([1.0, 2.0], [0.0, 1.0])
+    assert abs(s[0]) < 1e-6 and abs(s[1] - 1.4621) < 1e-3
+    assert abs(oracle.cross_entropy(np.zeros((1, 3), np.float32), [0]) - np.log(3)) < 1e-5
+    assert abs(oracle.cross_entropy(np.zeros((2, 3), np.float32), [0, 1]) - np.log(3)) < 1e-5
+    big = np.iinfo(np.int64).max
+    assert abs(oracle.cross_entropy(np.zeros((2, 3), np.float32), [big, 1], ignore_index=big) - np.log(3)) < 1e-5
+    assert oracle.cross_entropy(np.zeros((2, 3), np.float32), [big, big], ignore_index=big) == 0.0
+    with pytest.raises(IndexError):
+        oracle.cross_entropy(np.zeros((2, 3), np.float32), [0, 3])
+
+
 def test_broadcast_add_kat(oracle):
     # crates/core-ops/src/lib.rs:2621-2626; crates/hal/src/lib.rs:884-891
     assert oracle.broadcast_add([1, 2, 3, 4, 5, 6], [10, 20, 30]).tolist() == [11, 22, 33, 14, 25, 36]
