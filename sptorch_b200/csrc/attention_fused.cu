@@ -307,8 +307,17 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < 32; i++) if (kcol0 + i > qrow) v[i] = 0xff800000u;     // -inf
                 }
+                {   // four independent chains instead of one 16-deep dependent chain
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                    for (int i = 0; i < 32; i += 8) {
+                        m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                        m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                        m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                        m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                    }
+                    mx = fmaxf(max3(m0, m1, m2), m3);
+                }
                 // double buffered by exchange parity: the partner may still be reading the previous value
                 float* xm = xmax + (px & 1) * 256;
                 xm[ch * 128 + r] = mx;
@@ -322,18 +331,18 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const float mb = m_new * p.scale_log2;
                 // the softmax warps are bound by instruction issue: scale/subtract, the row sum and the accumulator
                 // update run on pairs of floats (fma.rn.f32x2 / add.rn.f32x2), the maximum on three inputs at a time
-                float2 sum2 = make_float2(0.0f, 0.0f);
+                float2 sum2 = make_float2(0.0f, 0.0f), sum2b = make_float2(0.0f, 0.0f);
                 const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nmb2 = make_float2(-mb, -mb);
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float2 t = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nmb2);
                     float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));                   // exp2(-inf) = 0 for masked entries
-                    sum2 = __fadd2_rn(sum2, e);
+                    if (i & 2) sum2b = __fadd2_rn(sum2b, e); else sum2 = __fadd2_rn(sum2, e);     // two chains
                     __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h2);
                 }
-                const float sum = sum2.x + sum2.y;
+                const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
                 // P buffer sb was last read by the P V two steps back, whose completion this thread's fold already waited for
                 uint8_t* prow = smem + L::kP + sb * L::kPBytes + prow_off;
 #pragma unroll
