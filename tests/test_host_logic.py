@@ -102,3 +102,49 @@ def test_batch_sharding_two_gloo_ranks():
     assert n == 6
     assert abs(sharded_sum - full_sum) < 1e-6 * max(1.0, abs(full_sum))
     assert abs(tmax - 0.2) < 1e-12
+
+
+def _tp_worker(rank, world, port, q):
+    """Tensor-parallel MLP + attention-output partition on CPU ranks: the slicing rule of sptorch_b200/csrc/gpt.cu
+    (ffn_up / wq,wk,wv split by output rows, ffn_down / wo split along K, residual and ffn_down bias folded into rank
+    0's partial) followed by a sum all-reduce must reproduce the unsharded block."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    from oracle import binding as O
+    from sptorch_b200 import synth
+    d, F, M = 32, 64, 10
+    x = synth.normal(1, M * d).reshape(M, d)
+    h = synth.normal(2, M * d).reshape(M, d)                 # LayerNorm output feeding the MLP
+    w1 = synth.normal(3, F * d, std=0.1).reshape(F, d); b1 = synth.normal(4, F, std=0.1)
+    w2 = synth.normal(5, d * F, std=0.1).reshape(d, F); b2 = synth.normal(6, d, std=0.1)
+    Fl = F // world
+    rows = slice(rank * Fl, (rank + 1) * Fl)
+    f = O.unary("gelu", O.linear(h, w1[rows], b1[rows]))     # column-parallel up projection + GELU
+    part = O.linear(f, np.ascontiguousarray(w2[:, rows]), b2 if rank == 0 else None)   # row-parallel down projection
+    if rank == 0:
+        part = part + x                                      # residual folded into rank 0's partial
+    t = torch.from_numpy(part.copy())
+    dist.all_reduce(t)                                       # the one collective of the MLP block
+    if rank == 0:
+        full = x + O.linear(O.unary("gelu", O.linear(h, w1, b1)), w2, b2)
+        q.put(float(np.abs(t.numpy() - full).max()))
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_partition_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 1000
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert err < 1e-5
