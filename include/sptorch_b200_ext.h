@@ -152,6 +152,20 @@ const void* sptorch_ext_gpt_tap(void* gpt, int i);
  * logits on the host out (model dtype), copies included.  Processes micro-batches of `chunk`
  * sequences and overlaps the device->host copy of one chunk with the compute of the next. */
 int   sptorch_ext_gpt_forward_host(void* gpt, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk);
+/* ---- incremental decode with a key/value cache (nn/src/lib.rs:1540-1573, 1619-1646, 706-760) ----
+ * enable_kv_cache allocates [layer][sequence][position][d_model] K and V caches for max_context positions (<= seq_len).
+ * prefill = forward over ids [batch, T] that also fills the cache.  decode runs one token per sequence through the
+ * blocks against the cache: append = 1 takes NEW tokens (their K,V are appended, logits of the new position);
+ * append = 0 recomputes the logits of the last cached token (decode_logits_from_cache right after a prefill).
+ * logits of decode: [batch, ld]. */
+int   sptorch_ext_gpt_enable_kv_cache(void* gpt, int max_context);
+int   sptorch_ext_gpt_cached_len(void* gpt);
+int   sptorch_ext_gpt_prefill(void* gpt, const void* ids_i32, int batch, int T, void* logits);
+int   sptorch_ext_gpt_decode(void* gpt, const void* last_ids_i32, int batch, int append, void* logits);
+/* the attention of one new token over a cache (nn/src/lib.rs:706-760 without the projections): q [B, H*hd];
+ * k_cache, v_cache [B, cache_positions, H*hd] of which the first n positions are valid; out [B, H*hd] */
+int   sptorch_ext_attention_last_token(const void* q, const void* k_cache, const void* v_cache, void* out, size_t B, size_t H, size_t hd,
+                                       size_t n, size_t cache_positions, int dtype);
 /* number of kernels one sptorch_ext_gpt_forward call of this shape enqueues */
 int   sptorch_ext_gpt_launches(void* gpt, int batch, int T);
 /* tensor-parallel all-reduce hook: called on the library stream's behalf after the row-split

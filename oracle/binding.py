@@ -207,6 +207,15 @@ def mha_causal(x, wq, wk, wv, wo, n_head, fast=0):
     return out
 
 
+def attention_last_token(q, k, v):
+    """q [H*hd]; k, v [H, n, hd] -> [H*hd]  (crates/nn/src/lib.rs:727-755)."""
+    k = _f32(k); v = _f32(v); q = _f32(q)
+    H, n, hd = k.shape
+    out = np.empty(H * hd, dtype=np.float32)
+    lib().orc_attention_last_token(_p(q), _p(k), _p(v), _p(out), _sz(H), _sz(n), _sz(hd))
+    return out
+
+
 def _cfg(cfg: dict) -> GptConfig:
     return GptConfig(cfg["vocab"], cfg["d_model"], cfg["n_layer"], cfg["n_head"], cfg["d_ff"], cfg["seq_len"],
                      float(cfg.get("eps", 1e-5)))

@@ -329,6 +329,30 @@ void orc_mha_causal(const float* x, const float* wq, const float* wk, const floa
     free(q); free(k); free(v); free(q3); free(k3); free(v3); free(vt); free(sc); free(pr); free(o3); free(o2);
 }
 
+/* causal_attention_last_token, the cache part: crates/nn/src/lib.rs:727-755.  q[H*hd]; k, v cached as [H, n, hd];
+ * out[H*hd].  Sequential dots, scale, max, exp, denominator, then out += (exp/denom) * v over positions. */
+void orc_attention_last_token(const float* q, const float* k, const float* v, float* out, size_t H, size_t n, size_t hd) {
+    float scale = 1.0f / sqrtf((float)hd);
+    float* sc = (float*)malloc(n * sizeof(float));
+    for (size_t h = 0; h < H; h++) {
+        for (size_t p = 0; p < n; p++) {
+            float dot = 0.0f;
+            for (size_t d = 0; d < hd; d++) dot += q[h * hd + d] * k[(h * n + p) * hd + d];
+            sc[p] = dot * scale;
+        }
+        float mx = -INFINITY;
+        for (size_t p = 0; p < n; p++) mx = fmaxf(mx, sc[p]);
+        float den = 0.0f;
+        for (size_t p = 0; p < n; p++) { sc[p] = expf(sc[p] - mx); den += sc[p]; }
+        for (size_t d = 0; d < hd; d++) out[h * hd + d] = 0.0f;
+        for (size_t p = 0; p < n; p++) {
+            float w = sc[p] / den;
+            for (size_t d = 0; d < hd; d++) out[h * hd + d] += w * v[(h * n + p) * hd + d];
+        }
+    }
+    free(sc);
+}
+
 size_t orc_gpt_param_count(const orc_gpt_config* c) {
     size_t V = c->vocab, d = c->d_model, F = c->d_ff, S = c->seq_len, L = c->n_layer;
     size_t per_block = 2 * d + 4 * d * d + 2 * d + F * d + F + d * F + d;

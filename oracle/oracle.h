@@ -70,6 +70,8 @@ void orc_batch_transpose(const float* x, float* out, size_t H, size_t T, size_t 
 void orc_mha_causal(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
                     float* out, size_t T, size_t d, size_t H, int fast);
 
+void orc_attention_last_token(const float* q, const float* k, const float* v, float* out, size_t H, size_t n, size_t hd);
+
 typedef struct {
     int vocab, d_model, n_layer, n_head, d_ff, seq_len;
     float eps;

@@ -95,6 +95,11 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_enable_taps": (_i, [_vp, _i]),
     "sptorch_ext_gpt_tap": (_vp, [_vp, _i]),
     "sptorch_ext_gpt_forward_host": (_i, [_vp, _vp, _i, _i, _vp, _i]),
+    "sptorch_ext_gpt_enable_kv_cache": (_i, [_vp, _i]),
+    "sptorch_ext_gpt_cached_len": (_i, [_vp]),
+    "sptorch_ext_gpt_prefill": (_i, [_vp, _vp, _i, _i, _vp]),
+    "sptorch_ext_gpt_decode": (_i, [_vp, _vp, _i, _i, _vp]),
+    "sptorch_ext_attention_last_token": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_launches": (_i, [_vp, _i, _i]),
     "sptorch_ext_gpt_set_allreduce": (_i, [_vp, ALLREDUCE_FN, _vp]),
     "sptorch_ext_nccl_unique_id": (_i, [C.c_char_p, _vp]),

@@ -106,7 +106,11 @@ class FfiBackend:
 
     def _check(self, rc: int, what: str):
         if rc != 0:
-            raise HalError(f"{what} failed: " + self.lib.sptorch_ext_last_error().decode(errors="replace"))
+            msg = self.lib.sptorch_ext_last_error().decode(errors="replace")
+            # The library keeps a failure sticky until the next sync for callers that ignore return codes (the Rust
+            # wrapper does: hal-ffi/src/lib.rs:242-248).  This wrapper has seen it, so it consumes the flag.
+            self.lib.sptorch_sync()
+            raise HalError(f"{what} failed: " + msg)
 
     # -- Backend trait (crates/hal/src/lib.rs:337-367) --
     def name(self) -> str:
@@ -453,6 +457,22 @@ class FfiBackend:
         finally:
             for b in (dq, dk, dv, do, dws):
                 b.free()
+
+    def attention_last_token(self, q, k_cache, v_cache, n_head: int, n: int, dtype=F32):
+        """q [B, d]; k_cache, v_cache [B, positions, d] with the first n valid -> [B, d] (crates/nn/src/lib.rs:727-755)."""
+        q, k, v = _f32(q), _f32(k_cache), _f32(v_cache)
+        B, P, d = k.shape
+        up = self.upload if dtype == F32 else self.upload_bf16
+        dq, dk, dv = up(q), up(k), up(v)
+        do = self.alloc(B * d, 4 if dtype == F32 else 2)
+        try:
+            self._check(self.lib.sptorch_ext_attention_last_token(dq.handle, dk.handle, dv.handle, do.handle, B, n_head, d // n_head, n, P, dtype), "attention_last_token")
+            out = do.to_host()
+            self.synchronize()
+            return (out if dtype == F32 else bf16_bits_to_f32(out)).reshape(B, d)
+        finally:
+            for x in (dq, dk, dv, do):
+                x.free()
 
     # -- timing on the library's stream --
     def timer_begin(self):

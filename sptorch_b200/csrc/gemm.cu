@@ -48,6 +48,7 @@ struct GemmParams {
     int num_kb;
     int causal_lower;
     int causal_k;
+    int b_broadcast;
     int tma_store;      // 1: C is written through the tensor map tmC; 0: element-wise stores
     int r_vec;          // 1: residual rows can be read with 16-byte loads
     uint32_t* status;
@@ -157,7 +158,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint32_t sa = base + stage * STAGE_BYTES;
                     mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
                     tma_load_4d(sa, &tmA, bar_full + 8 * stage, kb * BK, m0, z1, z2);
-                    tma_load_4d(sa + A_BYTES, &tmB, bar_full + 8 * stage, kb * BK, n0, z1, z2);
+                    tma_load_4d(sa + A_BYTES, &tmB, bar_full + 8 * stage, kb * BK, n0, p.b_broadcast ? 0 : z1, p.b_broadcast ? 0 : z2);
                 }
                 __syncwarp();
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -441,8 +442,8 @@ bool gemm_supported(const GemmDesc& d, const char** why) {
     if (d.M <= 0 || d.N <= 0 || d.K <= 0) return bad("empty problem");
     if ((reinterpret_cast<uintptr_t>(d.A) & 15) || (reinterpret_cast<uintptr_t>(d.B) & 15)) return bad("operand base not 16-byte aligned");
     if ((d.lda * es) % 16 || (d.ldb * es) % 16) return bad("operand row pitch not a multiple of 16 bytes");
-    if (d.nb1 > 1 && ((d.sA1 * es) % 16 || (d.sB1 * es) % 16)) return bad("batch stride not a multiple of 16 bytes");
-    if (d.nb2 > 1 && ((d.sA2 * es) % 16 || (d.sB2 * es) % 16)) return bad("batch stride not a multiple of 16 bytes");
+    if (d.nb1 > 1 && ((d.sA1 * es) % 16 || (!d.b_broadcast && (d.sB1 * es) % 16))) return bad("batch stride not a multiple of 16 bytes");
+    if (d.nb2 > 1 && ((d.sA2 * es) % 16 || (!d.b_broadcast && (d.sB2 * es) % 16))) return bad("batch stride not a multiple of 16 bytes");
     if (d.lda < d.K || d.ldb < d.K) return bad("row pitch smaller than K");
     if ((long long)d.lda * es >= (1ll << 40) || (long long)d.ldb * es >= (1ll << 40)) return bad("row pitch too large for a tensor map");
     if (d.mode == MM_TF32 && d.out_dtype != F32) return bad("TF32 mode writes f32 only");
@@ -479,7 +480,8 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     plan->smem = smem_for(bn);
     const bool tf32 = d.mode == MM_TF32;
     if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;
-    if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, bn)) return 1;
+    if (d.b_broadcast) { if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, 1, 1, 0, 0, bn)) return 1; }
+    else if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, bn)) return 1;
     // output map: 32x32 boxes, swizzled to match the conflict-free staging layout of the epilogue
     const long long oes = d.out_dtype == BF16 ? 2 : 4;
     plan->tma_store = ((reinterpret_cast<uintptr_t>(d.C) & 15) == 0) && (d.ldc * oes) % 16 == 0 && d.ldc >= d.N &&
@@ -505,6 +507,7 @@ int gemm_run(const GemmPlan& pl) {
     prm.num_kb = ceil_div(d.K, d.mode == MM_TF32 ? 32 : 64);
     prm.causal_lower = d.causal_lower;
     prm.causal_k = d.causal_k;
+    prm.b_broadcast = d.b_broadcast;
     prm.tma_store = pl.tma_store ? 1 : 0;
     {
         const long long oes = d.out_dtype == BF16 ? 2 : 4;

@@ -23,6 +23,7 @@ struct GemmDesc {
     int mode = MM_BF16;      // MM_BF16: A,B bf16.  MM_TF32: A,B f32.
     int out_dtype = BF16;    // C and R element type
     int causal_lower = 0;    // 1: square per-batch output, tiles entirely above the diagonal are skipped (never written)
+    int b_broadcast = 0;     // 1: B has no batch dims (one weight matrix for every batch entry)
     int causal_k = 0;        // 1: A is lower triangular per batch (A[m,k] = 0 for k > m): k-blocks past the tile's last row are skipped
 };
 

@@ -24,6 +24,8 @@ int attention_dispatch(const void* q, const void* k, const void* vt, long long v
                        void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
 bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
 int attention_mode();
+int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
+                         int n, long long seq_stride, long long row_stride, int dtype);
 
 struct Layer {
     float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;
@@ -47,6 +49,11 @@ struct Gpt {
     // pipelined host call
     void* logits_dev[2] = {nullptr, nullptr}; int* ids_dev = nullptr; int ids_cap = 0; size_t logits_cap = 0;
     cudaEvent_t ev_compute[2] = {nullptr, nullptr}, ev_copy[2] = {nullptr, nullptr};
+    // key/value cache for incremental decode: [layer][sequence][position][d_loc], allocated by gpt_enable_kv_cache
+    void *kcache = nullptr, *vcache = nullptr;
+    int cache_ctx = 0, cached_len = 0, cache_batch = 0;
+    bool fill_cache = false;      // set while a prefill runs
+    void *dq = nullptr, *dv = nullptr;   // decode scratch: [max_batch, 2*d_loc] and [max_batch, d_loc]
     // CUDA graph of one forward, keyed by everything that is baked into its kernel arguments
     struct GraphKey { const void* ids; void* logits; int batch, T; bool taps; cudaStream_t stream; };
     GraphKey gkey = {nullptr, nullptr, 0, 0, false, nullptr};
@@ -131,6 +138,23 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
         // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
         if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        if (g->fill_cache) {
+            // prefill: K and V of every position go to the cache rows [sequence][position][dl] (two more projections of h;
+            // the attention below keeps reading the [q|k] and V^T buffers)
+            const size_t lay = (size_t)l * g->c.max_batch * g->cache_ctx * dl * g->es;
+            GemmDesc kd;
+            kd.A = g->h; kd.C = (uint8_t*)g->kcache + lay;
+            kd.B = (const uint8_t*)w.wqk + (size_t)dl * d * g->es;          // the Wk half of [Wq;Wk]
+            kd.M = T; kd.N = dl; kd.K = d; kd.lda = d; kd.ldb = d; kd.ldc = dl;
+            kd.nb1 = 1; kd.nb2 = B; kd.sA2 = (long long)T * d; kd.b_broadcast = 1; kd.sC2 = (long long)g->cache_ctx * dl;
+            kd.mode = dt == SPT_BF16 ? MM_BF16 : MM_TF32; kd.out_dtype = dt;
+            GemmDesc vd = kd;
+            vd.B = w.wv; vd.C = (uint8_t*)g->vcache + lay;
+            GemmPlan pk, pv;
+            if (gemm_plan(kd, &pk) || gemm_plan(vd, &pv)) return 1;
+            { ProfScope ps(PROF_LINEAR); if (gemm_run(pk)) return 1; }
+            { ProfScope ps(PROF_LINEAR); if (gemm_run(pv)) return 1; }
+        }
         // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
         if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
         if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
@@ -310,6 +334,94 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
     if (e != cudaSuccess) { g->gexec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits); }
     SPT_CUDA(cudaGraphLaunch(g->gexec, rt().stream));
     note_submit();
+    return 0;
+}
+
+// ---- incremental decode (crates/nn/src/lib.rs:1540-1573 prefill_kv_cache / append_last_token_kv_cache,
+// :1619-1646 decode_logits_from_cache, :706-760 causal_attention_last_token, :1205-1214 forward_last_token_incremental) ----
+int sptorch_ext_gpt_enable_kv_cache(void* gp, int max_context) {
+    if (enter()) return 1;
+    if (!gp) return fail("gpt_enable_kv_cache: null model");
+    Gpt* g = (Gpt*)gp;
+    if (g->c.tp_size > 1) return fail("gpt_enable_kv_cache: not available with tensor parallel shards");
+    if (max_context <= 0 || max_context > g->c.seq_len) max_context = g->c.seq_len;     // learned positions end at seq_len
+    if (g->kcache) return max_context == g->cache_ctx ? 0 : fail("gpt_enable_kv_cache: cache already allocated with %d positions", g->cache_ctx);
+    const size_t bytes = (size_t)g->c.n_layer * g->c.max_batch * max_context * g->d_loc * g->es;
+    g->kcache = galloc(g, bytes); g->vcache = galloc(g, bytes);
+    g->dq = galloc(g, (size_t)g->c.max_batch * 2 * g->d_loc * g->es);
+    g->dv = galloc(g, (size_t)g->c.max_batch * g->d_loc * g->es);
+    if (!g->kcache || !g->vcache || !g->dq || !g->dv) return 1;
+    g->cache_ctx = max_context; g->cached_len = 0; g->cache_batch = 0;
+    return 0;
+}
+
+int sptorch_ext_gpt_cached_len(void* gp) { return gp ? ((Gpt*)gp)->cached_len : 0; }
+
+// prefill: the ordinary forward over ids [batch, T], which also fills the cache with K and V of all T positions.
+// logits may be NULL (then an internal scratch of the activations is NOT available: pass a buffer if logits are wanted).
+int sptorch_ext_gpt_prefill(void* gp, const void* ids, int batch, int T, void* logits) {
+    if (enter()) return 1;
+    if (!gp || !ids || !logits) return fail("gpt_prefill: null argument");
+    Gpt* g = (Gpt*)gp;
+    if (!g->kcache) return fail("gpt_prefill: call sptorch_ext_gpt_enable_kv_cache first");
+    if (check_shape(g, batch, T)) return 1;
+    if (T > g->cache_ctx) return fail("gpt_prefill: T=%d exceeds the cache of %d positions", T, g->cache_ctx);
+    g->fill_cache = true;
+    int rc = forward(g, ids, batch, T, logits);
+    g->fill_cache = false;
+    if (rc) return rc;
+    g->cached_len = T; g->cache_batch = batch;
+    return 0;
+}
+
+// One incremental step for `batch` sequences that share a cached length.
+//   append = 1: last_ids are NEW tokens: their K,V are appended at position cached_len, the logits are those of the new token
+//               (append_last_token_kv_cache followed by decode_logits_from_cache);
+//   append = 0: last_ids are the tokens already at position cached_len-1: nothing is written, the logits of that last
+//               cached token are recomputed from the cache (decode_logits_from_cache right after a prefill).
+// logits: [batch, ld] in the model dtype, ld = sptorch_ext_gpt_logits_ld.
+int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append, void* logits) {
+    if (enter()) return 1;
+    if (!gp || !last_ids || !logits) return fail("gpt_decode: null argument");
+    Gpt* g = (Gpt*)gp;
+    const sptorch_gpt_config& c = g->c;
+    if (!g->kcache || g->cached_len <= 0) return fail("gpt_decode: the cache is empty (prefill first)");
+    if (batch != g->cache_batch) return fail("gpt_decode: batch %d differs from the cached batch %d", batch, g->cache_batch);
+    if (append && g->cached_len >= g->cache_ctx) return fail("gpt_decode: the cache of %d positions is full", g->cache_ctx);
+    const int d = c.d_model, dl = g->d_loc, Fl = g->F_loc, hd = d / c.n_head, dt = c.dtype, B = batch;
+    const int pos = append ? g->cached_len : g->cached_len - 1;
+    const int n = pos + 1;
+    const int pos_row = pos < c.seq_len - 1 ? pos : c.seq_len - 1;            // last_pos.min(seq_len - 1), nn/src/lib.rs:1631
+    const size_t es = g->es;
+    { ProfScope ps(PROF_EMBED);
+      if (sptorch_ext_embedding_sum(g->tok, (const uint8_t*)g->pos + (size_t)pos_row * d * es, last_ids, g->x, (size_t)B, 1, (size_t)c.vocab, (size_t)d, dt)) return 1; }
+    void* x = g->x;
+    const long long row = dl, seq = (long long)g->cache_ctx * dl;
+    for (int l = 0; l < c.n_layer; l++) {
+        const Layer& w = g->L[l];
+        const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es;
+        uint8_t* kc = (uint8_t*)g->kcache + lay;
+        uint8_t* vc = (uint8_t*)g->vcache + lay;
+        if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
+        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->dq, B, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;     // [q | k] of the token
+        if (append) {
+            if (linear(g, g->h, w.wv, nullptr, nullptr, g->dv, B, d, dl, dl, EPI_NONE)) return 1;
+            // one cache row per sequence and layer
+            SPT_CUDA(cudaMemcpy2DAsync(kc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)dl * es, (size_t)2 * dl * es,
+                                       (size_t)dl * es, (size_t)B, cudaMemcpyDeviceToDevice, rt().stream));
+            SPT_CUDA(cudaMemcpy2DAsync(vc + (size_t)pos * dl * es, (size_t)seq * es, g->dv, (size_t)dl * es, (size_t)dl * es, (size_t)B,
+                                       cudaMemcpyDeviceToDevice, rt().stream));
+        }
+        { ProfScope ps(PROF_ATTN_FUSED);
+          if (attention_last_token(g->dq, 2 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, n, seq, row, dt)) return 1; }
+        if (linear(g, g->ao, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
+        if (ln(x, w.ln2g, w.ln2b, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
+        if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_GELU)) return 1;
+        if (linear(g, g->f, w.w2, w.b2, x, x, B, Fl, d, d, EPI_NONE)) return 1;
+    }
+    if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
+    if (linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
+    if (append) g->cached_len++;
     return 0;
 }
 

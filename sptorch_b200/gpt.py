@@ -111,6 +111,42 @@ class GPT:
         ids = np.asarray(token_ids).reshape(1, -1)
         return self.forward(ids)[0]
 
+    # -- incremental decode (PrefillCache / IncrementalDecode of the reference: nn/src/lib.rs:1540-1573, 1619-1646) --
+    def enable_kv_cache(self, max_context: int = 0):
+        self.b._check(self.b.lib.sptorch_ext_gpt_enable_kv_cache(self.h, max_context), "enable_kv_cache")
+
+    def cached_len(self) -> int:
+        return self.b.lib.sptorch_ext_gpt_cached_len(self.h)
+
+    def _read_logits(self, d_log, rows: int) -> np.ndarray:
+        raw = np.empty(rows * self.ldl, dtype=np.uint16 if self.dtype == BF16 else np.float32)
+        self.b._check(self.b.lib.sptorch_ext_copy_d2h_bytes(d_log.handle, raw.ctypes.data, raw.nbytes), "logits d2h")
+        self.b.synchronize()
+        out = bf16_bits_to_f32(raw) if self.dtype == BF16 else raw
+        return out.reshape(rows, self.ldl)[:, :self.cfg["vocab"]].copy()
+
+    def prefill_kv_cache(self, ids: np.ndarray) -> np.ndarray:
+        """ids [B, T] (T a multiple of the vector width): fills the cache, returns the logits [B, T, V] of the prefix."""
+        ids = np.asarray(ids)
+        B, T = ids.shape
+        d_ids, d_log = self.stage_ids(ids), self.logits_buffer(B * T)
+        self.b._check(self.b.lib.sptorch_ext_gpt_prefill(self.h, d_ids.handle, B, T, d_log.handle), "gpt_prefill")
+        return self._read_logits(d_log, B * T).reshape(B, T, -1)
+
+    def decode_logits_from_cache(self, last_ids) -> np.ndarray:
+        """Logits [B, V] of the last cached token, recomputed from the cache (no append)."""
+        return self._decode(last_ids, 0)
+
+    def append_and_decode(self, new_ids) -> np.ndarray:
+        """Appends one new token per sequence to the cache and returns its logits [B, V]."""
+        return self._decode(new_ids, 1)
+
+    def _decode(self, ids, append: int) -> np.ndarray:
+        ids = np.asarray(ids).reshape(-1)
+        d_ids, d_log = self.stage_ids(ids), self.logits_buffer(ids.size)
+        self.b._check(self.b.lib.sptorch_ext_gpt_decode(self.h, d_ids.handle, ids.size, append, d_log.handle), "gpt_decode")
+        return self._read_logits(d_log, ids.size)
+
     def forward_host(self, ids_host_ptr: int, batch: int, T: int, logits_host_ptr: int, chunk: int):
         """Host-buffer call through the C-ABI: pinned ids in, dense logits out, copies included."""
         self.b._check(self.b.lib.sptorch_ext_gpt_forward_host(self.h, ids_host_ptr, batch, T, logits_host_ptr, chunk), "gpt_forward_host")

@@ -90,8 +90,10 @@ def test_forward_rejects_bad_shapes_and_ids(backend):
         m.set_param("blocks.0.attn.wq.weight", np.zeros(5, np.float32))
     with pytest.raises(HalError):
         m.set_param("no.such.param", np.zeros(5, np.float32))
-    # failures are sticky until the next sync reports them (the reference's wrapper ignores op return codes:
-    # crates/hal-ffi/src/lib.rs:242-248), then the backend is clean again
+    # through the raw C-ABI a failure is sticky until the next sync reports it (the reference's wrapper ignores op return
+    # codes: crates/hal-ffi/src/lib.rs:242-248), then the backend is clean again
+    z = np.zeros(5, np.float32)
+    assert backend.lib.sptorch_ext_gpt_set_param(m.h, b"no.such.param", z.ctypes.data, 5) != 0
     assert backend.lib.sptorch_sync() != 0
     assert backend.lib.sptorch_sync() == 0
     m.close()
