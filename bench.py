@@ -457,6 +457,9 @@ def run_tp(args):
         uid = C.create_string_buffer(box[0], 128)
         b._check(lib.sptorch_ext_nccl_init(None, uid, rank, world), "nccl_init")
         b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
+        b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, int(args.tp_overlap)), "tp_overlap")
+        if args.tp_overlap:
+            b._check(lib.sptorch_ext_set_sm_reserve(args.sm_reserve), "sm_reserve")
     ids = synth.randint(1, B * T, cfg["vocab"]).reshape(B, T).astype(np.int32)
     if check:
         out = model.forward(ids)
@@ -487,7 +490,7 @@ def run_tp(args):
             lin, attn = flops_per_forward(cfg, B, T)
             print(json.dumps({"metric": "gpt_forward_tokens_per_s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
                               "steps": args.steps, "ms_per_step": ms / args.steps, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-                              "config": {"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}"},
+                              "config": {"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}", "tp_overlap": bool(args.tp_overlap), "sm_reserve": args.sm_reserve if args.tp_overlap else 0},
                               "achieved_tflops_whole_job": (lin + attn) / (ms / args.steps * 1e-3) / 1e12,
                               "breakdown_rank0": {c: float(pm[i]) / args.steps for i, c in enumerate(cats) if pn[i]}}), flush=True)
     model.close()
@@ -514,6 +517,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
                     help="c4_gpt2s: the bench line (batch sharding); c5_1p3b / tp_check: tensor parallel over the launched ranks")
+    ap.add_argument("--tp-overlap", type=int, default=0, help="tensor parallel: overlap the all-reduces with the other half of the batch")
+    ap.add_argument("--sm-reserve", type=int, default=16, help="SMs left free for NCCL when --tp-overlap is on")
     ap.add_argument("--layers", type=int, default=0, help="with --workload c5_1p3b: run fewer layers")
     args = ap.parse_args()
     if args.sweep:

@@ -46,6 +46,8 @@ int   sptorch_ext_copy_h2d_bytes(const void* host, void* device, size_t bytes); 
 int   sptorch_ext_copy_d2h_bytes(const void* device, void* host, size_t bytes);   /* returns with host valid */
 int   sptorch_ext_memset(void* device, int byte, size_t bytes);
 int   sptorch_ext_set_alloc_budget(size_t bytes);      /* tests: allocations beyond this many live bytes fail; 0 = off */
+/* persistent GEMM / attention kernels launch on (SM count - n) SMs, leaving room for a collective on another stream */
+int   sptorch_ext_set_sm_reserve(int n);
 int   sptorch_ext_timer_begin(void);                   /* CUDA event on the library stream */
 int   sptorch_ext_timer_end(float* ms);                /* second event, waits for it, elapsed ms */
 int   sptorch_ext_flush_l2(void);                      /* overwrites a 256 MiB scratch (allocated on first use) */
@@ -171,6 +173,10 @@ int   sptorch_ext_gpt_launches(void* gpt, int batch, int T);
 /* tensor-parallel all-reduce hook: called on the library stream's behalf after the row-split
  * projections; the callee must enqueue a sum-all-reduce of n elements at buf onto cuda_stream. */
 typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_stream, void* user);
+/* tensor parallel: reduce one half of the batch on a second stream while the other half computes (default off: with
+ * the statically scheduled persistent GEMM the SMs given up cost as much as the overlap gains; needs an even batch;
+ * combine with sptorch_ext_set_sm_reserve so that the collective finds free SMs) */
+int   sptorch_ext_gpt_enable_tp_overlap(void* gpt, int on);
 int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
 
 /* ---- NCCL over NVLink (replaces the gRPC star all-reduce of crates/distributed/src/coordinator.rs:73-116) ---- */

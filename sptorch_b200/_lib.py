@@ -55,6 +55,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_copy_d2h_bytes": (_i, [_vp, _vp, _sz]),
     "sptorch_ext_memset": (_i, [_vp, _i, _sz]),
     "sptorch_ext_set_alloc_budget": (_i, [_sz]),
+    "sptorch_ext_set_sm_reserve": (_i, [_i]),
     "sptorch_ext_timer_begin": (_i, []),
     "sptorch_ext_timer_end": (_i, [C.POINTER(C.c_float)]),
     "sptorch_ext_flush_l2": (_i, []),
@@ -101,6 +102,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_decode": (_i, [_vp, _vp, _i, _i, _vp]),
     "sptorch_ext_attention_last_token": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_launches": (_i, [_vp, _i, _i]),
+    "sptorch_ext_gpt_enable_tp_overlap": (_i, [_vp, _i]),
     "sptorch_ext_gpt_set_allreduce": (_i, [_vp, ALLREDUCE_FN, _vp]),
     "sptorch_ext_nccl_unique_id": (_i, [C.c_char_p, _vp]),
     "sptorch_ext_nccl_init": (_i, [C.c_char_p, _vp, _i, _i]),

@@ -465,7 +465,7 @@ int attention_fused(const void* q, const void* k, const void* vt, long long vt_l
     prm.prof = attn_prof_buffer();
     long long items = (long long)B * H * prm.n_qtiles;
     if (items > INT32_MAX) return fail("attention_fused: too many work items");
-    const long long slots = (long long)rt().sm_count * (hd == 64 ? 2 : 1);      // resident CTAs
+    const long long slots = (long long)compute_sms() * (hd == 64 ? 2 : 1);      // resident CTAs
     long long grid = items < slots ? items : slots;
     ProfScope ps(PROF_ATTN_FUSED);
     auto launch = [&](auto kern, int smem_bytes) -> int {

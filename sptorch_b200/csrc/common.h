@@ -21,6 +21,7 @@ struct Runtime {
     int refcount = 0;
     int device = -1;
     int sm_count = 0;
+    int sm_reserve = 0;                 // SMs the persistent kernels leave free (for a collective running beside them)
     cudaStream_t stream = nullptr;      // the stream every op is enqueued on
     cudaStream_t own_stream = nullptr;  // created at init; `stream` may be swapped for a caller's
     cudaStream_t copy_stream = nullptr; // second stream for overlapped device->host copies
@@ -62,6 +63,9 @@ bool prof_enabled();
 void prof_begin(int cat);
 void prof_end(int cat);
 struct ProfScope { int c; explicit ProfScope(int cat) : c(cat) { prof_begin(c); } ~ProfScope() { prof_end(c); } };
+
+// SMs the persistent GEMM / attention kernels may fill
+inline int compute_sms() { int n = rt().sm_count - rt().sm_reserve; return n < 1 ? 1 : n; }
 
 inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 

@@ -476,7 +476,7 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     plan->tiles_n = ceil_div(d.N, bn);
     long long total = (long long)plan->tiles_m * plan->tiles_n * d.nb1 * d.nb2;
     if (total > INT32_MAX) return fail("gemm: too many tiles");
-    plan->grid = (int)(total < rt().sm_count ? total : rt().sm_count);
+    plan->grid = (int)(total < compute_sms() ? total : compute_sms());
     plan->smem = smem_for(bn);
     const bool tf32 = d.mode == MM_TF32;
     if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;

@@ -49,6 +49,7 @@ struct Gpt {
     // pipelined host call
     void* logits_dev[2] = {nullptr, nullptr}; int* ids_dev = nullptr; int ids_cap = 0; size_t logits_cap = 0;
     cudaEvent_t ev_compute[2] = {nullptr, nullptr}, ev_copy[2] = {nullptr, nullptr};
+    cudaEvent_t ev_partial[2] = {nullptr, nullptr}, ev_reduced[2] = {nullptr, nullptr};     // tensor-parallel pipeline
     // key/value cache for incremental decode: [layer][sequence][position][d_loc], allocated by gpt_enable_kv_cache
     void *kcache = nullptr, *vcache = nullptr;
     int cache_ctx = 0, cached_len = 0, cache_batch = 0;
@@ -60,6 +61,7 @@ struct Gpt {
     cudaGraphExec_t gexec = nullptr;
     int eager_runs = 0;        // forwards of the current key run eagerly so far (the first one sets function attributes)
     bool graphs = true;
+    bool tp_overlap = false;   // tensor parallel: reduce one half of the batch while the other half computes (opt-in)
 };
 
 static void* galloc(Gpt* g, size_t bytes) {
@@ -120,7 +122,73 @@ static int allreduce(Gpt* g, void* buf, size_t n) {
     return 0;
 }
 
+// Tensor-parallel forward with the all-reduces taken off the critical path: the batch is cut into two halves that go
+// through each half-block alternately, the partial sums of one half are reduced on a second stream while the other
+// half computes.  (The persistent kernels must leave a few SMs free for the collective: sptorch_ext_set_sm_reserve.)
+static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits) {
+    const sptorch_gpt_config& c = g->c;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head, dt = c.dtype;
+    const bool lead = c.tp_rank == 0;
+    const size_t es = g->es;
+    const int Bc = B / 2, Mc = Bc * T;
+    cudaStream_t cs = rt().stream, ms = rt().copy_stream;
+    for (int i = 0; i < 2; i++) {
+        if (!g->ev_partial[i]) SPT_CUDA(cudaEventCreateWithFlags(&g->ev_partial[i], cudaEventDisableTiming));
+        if (!g->ev_reduced[i]) SPT_CUDA(cudaEventCreateWithFlags(&g->ev_reduced[i], cudaEventDisableTiming));
+    }
+    { ProfScope ps(PROF_EMBED); if (sptorch_ext_embedding_sum(g->tok, g->pos, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1; }
+    auto rows = [&](void* base, int ch, size_t width) { return (void*)((uint8_t*)base + (size_t)ch * Mc * width * es); };
+    void* xb[2] = {rows(g->x, 0, d), rows(g->x, 1, d)};
+    void* yb[2] = {rows(g->y, 0, d), rows(g->y, 1, d)};
+    bool pending[2] = {false, false};             // a reduction of this half is in flight on the second stream
+    auto reduce_async = [&](int ch) -> int {
+        SPT_CUDA(cudaEventRecord(g->ev_partial[ch], cs));
+        SPT_CUDA(cudaStreamWaitEvent(ms, g->ev_partial[ch], 0));
+        if (g->ar(yb[ch], (size_t)Mc * d, dt, (void*)ms, g->ar_user)) return fail("gpt: all-reduce hook failed");
+        SPT_CUDA(cudaEventRecord(g->ev_reduced[ch], ms));
+        std::swap(xb[ch], yb[ch]);
+        pending[ch] = true;
+        return 0;
+    };
+    auto wait_reduced = [&](int ch) -> int {
+        if (pending[ch]) { SPT_CUDA(cudaStreamWaitEvent(cs, g->ev_reduced[ch], 0)); pending[ch] = false; }
+        return 0;
+    };
+    for (int l = 0; l < c.n_layer; l++) {
+        const Layer& w = g->L[l];
+        for (int ch = 0; ch < 2; ch++) {
+            if (wait_reduced(ch)) return 1;
+            void* h = rows(g->h, ch, d); void* qk = rows(g->qk, ch, 2 * dl); void* ao = rows(g->ao, ch, dl);
+            void* vt = (uint8_t*)g->vt + (size_t)ch * Mc * es;                      // columns of V^T [dl, M]
+            if (ln(xb[ch], w.ln1g, w.ln1b, h, (size_t)Mc, (size_t)d, c.eps, dt)) return 1;
+            if (linear(g, h, w.wqk, nullptr, nullptr, qk, Mc, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+            if (linear(g, w.wv, h, nullptr, nullptr, vt, dl, d, Mc, M, EPI_NONE)) return 1;
+            if (attention_dispatch(qk, (const uint8_t*)qk + (size_t)dl * es, vt, M, (long long)hd * M, T, ao,
+                                   (uint8_t*)g->scores + (size_t)ch * Bc * Hl * T * T * es, Bc, T, Hl, hd, 2 * dl, dl, dt)) return 1;
+            if (linear(g, ao, w.wo, nullptr, lead ? xb[ch] : nullptr, yb[ch], Mc, dl, d, d, EPI_NONE)) return 1;
+            if (reduce_async(ch)) return 1;
+        }
+        for (int ch = 0; ch < 2; ch++) {
+            if (wait_reduced(ch)) return 1;
+            void* h = rows(g->h, ch, d); void* f = rows(g->f, ch, Fl);
+            if (ln(xb[ch], w.ln2g, w.ln2b, h, (size_t)Mc, (size_t)d, c.eps, dt)) return 1;
+            if (linear(g, h, w.w1, w.b1, nullptr, f, Mc, d, Fl, Fl, EPI_GELU)) return 1;
+            if (linear(g, f, w.w2, lead ? w.b2 : nullptr, lead ? xb[ch] : nullptr, yb[ch], Mc, Fl, d, d, EPI_NONE)) return 1;
+            if (reduce_async(ch)) return 1;
+        }
+    }
+    if (wait_reduced(0) || wait_reduced(1)) return 1;
+    // two swaps per layer and half: both halves are back in the same base buffer, contiguous
+    void* x = xb[0];
+    if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
+    note_submit();
+    return 0;
+}
+
 static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
+    if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0)
+        return forward_tp_pipelined(g, ids, B, T, logits);
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head;
     const int dt = c.dtype;
@@ -243,6 +311,8 @@ void sptorch_ext_gpt_destroy(void* gp) {
         for (int i = 0; i < 2; i++) {
             if (g->ev_compute[i]) cudaEventDestroy(g->ev_compute[i]);
             if (g->ev_copy[i]) cudaEventDestroy(g->ev_copy[i]);
+            if (g->ev_partial[i]) cudaEventDestroy(g->ev_partial[i]);
+            if (g->ev_reduced[i]) cudaEventDestroy(g->ev_reduced[i]);
         }
     }
     delete g;
@@ -422,6 +492,12 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
     if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
     if (linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
     if (append) g->cached_len++;
+    return 0;
+}
+
+int sptorch_ext_gpt_enable_tp_overlap(void* gp, int on) {
+    if (!gp) return fail("gpt_enable_tp_overlap: null model");
+    ((Gpt*)gp)->tp_overlap = on != 0;
     return 0;
 }
 

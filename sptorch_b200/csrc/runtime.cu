@@ -285,6 +285,12 @@ void sptorch_ext_free_pinned(void* p) { if (p && !enter()) cudaFreeHost(p); }
 
 int sptorch_ext_set_alloc_budget(size_t bytes) { g_rt.budget = bytes; return 0; }
 
+int sptorch_ext_set_sm_reserve(int n) {
+    if (n < 0 || (g_rt.sm_count > 0 && n >= g_rt.sm_count)) return fail("set_sm_reserve: %d is outside 0..%d", n, g_rt.sm_count - 1);
+    g_rt.sm_reserve = n;
+    return 0;
+}
+
 int sptorch_ext_timer_begin(void) {
     if (enter()) return 1;
     SPT_CUDA(cudaEventRecord(g_rt.t0, g_rt.stream));
