@@ -20,7 +20,13 @@
 #include "gemm.h"
 #include "sm100.cuh"
 #include "../../include/sptorch_b200_ext.h"
+#include <algorithm>
+#include <array>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <vector>
 
 namespace spt {
 
@@ -38,6 +44,8 @@ struct AttnParams {
     float scale_log2;       // 1/sqrt(hd) * log2(e)
     unsigned long long* prof;   // diagnostics: cycle counters of CTA 0 (softmax warp 2 lane 0: [0..7], MMA warp lane 0: [8..15]); may be null
     uint32_t* status;
+    const int* sched;       // work schedule [sched_len][gridDim.x]: item of CTA c at step k, -1 past the end of its list
+    int sched_len;
 };
 
 // 2^x on the special-function unit: one instruction, relative error 2^-22 (P is rounded to bf16 right after)
@@ -68,9 +76,9 @@ struct AttnSmem {
     static constexpr int kTotal = kX + 2048;
 };
 
-// Persistent kernel: CTA c takes work items c, c + gridDim.x, ... of the list (query tile, sequence*head) sorted by
-// decreasing length, and all three roles run straight through item boundaries (barrier phases are driven by running
-// counters), so the loads and the first Q K^T of the next item are in flight while the current one drains.
+// Persistent kernel: CTA c works through column c of a schedule built on the host (attention_schedule below), and all
+// three roles run straight through item boundaries (barrier phases are driven by running counters), so the loads and
+// the first Q K^T of the next item are in flight while the current one drains.
 template <int HD, bool PROF>
 __global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -102,7 +110,6 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = p.B * p.H;
-    const int n_items = BH * p.n_qtiles;
     const int n_kv_seq = (p.T + kKvTile - 1) / kKvTile;
 
     if ((base & 1023u) != 0) {                                // swizzled tiles need 1024-byte alignment
@@ -127,7 +134,9 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
-    // work item -> (query tile, sequence, head, number of key tiles); heavy (late) query tiles come first
+    // step k of this CTA's list; the entry of the next step is fetched while the current item runs
+    auto fetch = [&](int k) -> int { return k < p.sched_len ? __ldg(p.sched + (size_t)k * gridDim.x + blockIdx.x) : -1; };
+    // work item -> (query tile, sequence, head, number of key tiles)
     auto decode = [&](int item, int& q0, int& bb, int& hh, int& n_kv) {
         const int qt = p.n_qtiles - 1 - item / BH;
         const int bh = item % BH;
@@ -141,9 +150,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) { tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
         bool ok = true;
         uint32_t g = 0, it = 0;
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, it++) {
+        for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
+            const int item_next = fetch(k + 1);
             int q0, bb, hh, n_kv;
             decode(item, q0, bb, hh, n_kv);
+            item = item_next;
             const uint32_t qb = 0;       // one Q buffer: reloaded as soon as the last Q K^T of the previous item has read it
             ok = mbar_wait(q_free + 8 * qb, (it & 1) ^ 1, abort_flag, p.status, kErrProducerWait);
             if (!ok) break;
@@ -189,9 +200,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait) &&
                    mbar_wait(s_free + 8 * (gg & 1), ((gg >> 1) & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
         };
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, it++) {
+        for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
+            const int item_next = fetch(k + 1);
             int q0, bb, hh, n_kv;
             decode(item, q0, bb, hh, n_kv);
+            item = item_next;
             const uint32_t qb = 0;
             SPT_TICK(7);
             ok = mbar_wait(q_full + 8 * qb, it & 1, abort_flag, p.status, kErrMmaWait) && s_ready(g);
@@ -280,9 +293,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_arrive(o_free + 8 * (gg & 1));
             return true;
         };
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        for (int k = 0, item = fetch(0); item >= 0 && ok; k++) {
+            const int item_next = fetch(k + 1);
             int q0, bb, hh, n_kv;
             decode(item, q0, bb, hh, n_kv);
+            item = item_next;
             const int qrow = q0 + r;
             float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
 #pragma unroll
@@ -441,6 +456,54 @@ extern "C" int sptorch_ext_debug_attn_prof(unsigned long long* host16) {
     return cudaMemcpy(host16, g_attn_prof, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
 }
 
+// Work schedule of the persistent kernel.  Items are (query tile, sequence*head); a query tile q reads the keys and values
+// 0 .. 128 q + 127 of its pair, so the eight tiles of one pair re-read the same K/V.  The list is cut into groups of pairs
+// whose K/V fit in L2 together, each group ordered longest tile first, and the items are dealt out in that order to the CTA
+// that has the least work so far (list scheduling with cost = key tiles + 1): the tiles of a pair then run close together
+// in time and their K/V come from L2 instead of DRAM, while the CTAs still finish together.
+struct AttnSchedule { std::vector<int> host; int* dev = nullptr; int len = 0; };
+static std::mutex g_sched_mu;
+static std::map<std::array<int, 6>, AttnSchedule> g_sched;
+
+static int attention_schedule(int B, int H, int T, int hd, int nq, int grid, const int** dev, int* len) {
+    static const int l2_mb = getenv("SPTORCH_B200_ATTN_L2_MB") ? atoi(getenv("SPTORCH_B200_ATTN_L2_MB")) : 32;
+    const int BH = B * H;
+    const long long pair_bytes = 2LL * T * hd * 2;                       // K and V of one (sequence, head)
+    long long group = l2_mb > 0 ? ((long long)l2_mb << 20) / pair_bytes : BH;
+    group = group < 1 ? 1 : (group > BH ? BH : group);
+    std::lock_guard<std::mutex> lk(g_sched_mu);
+    AttnSchedule& s = g_sched[{B, H, T, hd, grid, (int)group}];
+    if (!s.dev) {
+        const int n_kv_seq = ceil_div(T, kKvTile);
+        std::vector<std::vector<int>> lists(grid);
+        using Slot = std::pair<long long, int>;                          // (work so far, CTA)
+        std::priority_queue<Slot, std::vector<Slot>, std::greater<Slot>> heap;
+        for (int c = 0; c < grid; c++) heap.push({0, c});
+        for (int g0 = 0; g0 < BH; g0 += (int)group) {
+            const int g1 = std::min<long long>(BH, g0 + group);
+            for (int qt = nq - 1; qt >= 0; qt--) {
+                const int n_kv = std::min(ceil_div(qt * kQTile + kQTile, kKvTile), n_kv_seq);
+                for (int bh = g0; bh < g1; bh++) {
+                    Slot t = heap.top(); heap.pop();
+                    lists[t.second].push_back((nq - 1 - qt) * BH + bh);
+                    heap.push({t.first + n_kv + 1, t.second});
+                }
+            }
+        }
+        size_t len_max = 0;
+        for (auto& l : lists) len_max = std::max(len_max, l.size());
+        s.len = (int)len_max;
+        s.host.assign(len_max * grid, -1);
+        for (int c = 0; c < grid; c++)
+            for (size_t k = 0; k < lists[c].size(); k++) s.host[k * grid + c] = lists[c][k];
+        SPT_CUDA(cudaMalloc(&s.dev, s.host.size() * sizeof(int)));
+        // the host copy lives as long as the cache entry, so the copy may stay asynchronous
+        SPT_CUDA(cudaMemcpyAsync(s.dev, s.host.data(), s.host.size() * sizeof(int), cudaMemcpyHostToDevice, rt().stream));
+    }
+    *dev = s.dev; *len = s.len;
+    return 0;
+}
+
 bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch) {
     return (hd == 64 || hd == 128) && T % 8 == 0 && ld_qk % 8 == 0 && vt_ld % 8 == 0 && vt_s_head % 8 == 0 && vt_s_batch % 8 == 0;
 }
@@ -467,6 +530,7 @@ int attention_fused(const void* q, const void* k, const void* vt, long long vt_l
     if (items > INT32_MAX) return fail("attention_fused: too many work items");
     const long long slots = (long long)compute_sms() * (hd == 64 ? 2 : 1);      // resident CTAs
     long long grid = items < slots ? items : slots;
+    if (attention_schedule(B, H, T, hd, prm.n_qtiles, (int)grid, &prm.sched, &prm.sched_len)) return 1;
     ProfScope ps(PROF_ATTN_FUSED);
     auto launch = [&](auto kern, int smem_bytes) -> int {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
