@@ -80,6 +80,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_rms_norm": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i]),
     "sptorch_ext_swiglu": (_i, [_vp, _vp, _vp, _sz, _i]),
     "sptorch_ext_cross_entropy": (_i, [_vp, _sz, _vp, _sz, _sz, _i, C.c_longlong, _vp, C.POINTER(C.c_float), _i]),
+    "sptorch_ext_set_gemm_pair": (_i, [_i]),
     "sptorch_ext_set_matmul_mode": (_i, [_i]),
     "sptorch_ext_matmul_f32_static": (_i, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "sptorch_ext_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _f, _i, _i, _i]),

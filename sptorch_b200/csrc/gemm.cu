@@ -32,6 +32,7 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;          // one swizzle row: 64 bf16 or 32 f32 along K
 constexpr int kStages = 4;
+constexpr int kStagesPair = 6;               // pair kernel: a stage is 32 KB per CTA instead of 48 KB
 constexpr int kGemmThreads = 320;           // producer warp + MMA warp + 8 epilogue warps
 constexpr int kEpiThreads = 256;
 constexpr int kGroupM = 8;                   // m-tiles per rasterisation band (L2 reuse of the B tiles)
@@ -87,16 +88,25 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
     tm = first_m + (q - tn * rows_in_band);
 }
 
-template <bool TF32, typename TOut, int BN>
+// PAIR: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs issued by the even CTA.  Each CTA loads its
+// own 128 rows of A and its own half (BN/2 rows) of the B tile, keeps its 128 rows of the accumulator in its own TMEM and
+// runs its own epilogue; per SM the operand traffic from L2 falls from (128 + BN) to (128 + BN/2) rows per k-block.
+// Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' loads; `empty` and `tmem_full` exist in both
+// CTAs and are signalled by two commits of the issuing thread; `tmem_empty` lives in the even CTA and collects the
+// epilogue threads of both.
+template <bool TF32, typename TOut, int BN, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+    constexpr int NSTG = PAIR ? kStagesPair : kStages;
+    constexpr int TM = PAIR ? 2 * BM : BM;             // rows of one scheduled tile
+    constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of B this CTA loads
     constexpr int A_BYTES = BM * kStageRowBytes;
-    constexpr int B_BYTES = BN * kStageRowBytes;
+    constexpr int B_BYTES = B_ROWS * kStageRowBytes;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int BK = TF32 ? 32 : 64;                 // elements of K per stage
     constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : BN <= 128 ? 256 : 512;   // two accumulators of BN columns; a power of two >= 32
-    constexpr uint32_t IDESC = make_idesc(TF32, BM, BN);
+    constexpr uint32_t IDESC = make_idesc(TF32, TM, BN);
 
     // layout: [kStages x (A tile | B tile)] [8 x 4 KB epilogue staging] [2 x 1 KB bias tiles] [barriers, 256 B]
     // (operand tiles and staging blocks sit on 1024-byte boundaries: the TMA swizzle is a function of the address bits)
@@ -106,34 +116,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (threadIdx.x == 0) atomicOr(p.status, 0x200u);
         return;
     }
-    constexpr int OFF_STAGING = kStages * STAGE_BYTES;
+    constexpr int OFF_STAGING = NSTG * STAGE_BYTES;
     constexpr int OFF_BIAS = OFF_STAGING + 8 * 4096;
     constexpr int OFF_BARS = OFF_BIAS + 2 * 1024;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BARS);
     // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
     const uint32_t bar_full = base + OFF_BARS;
-    const uint32_t bar_empty = bar_full + 8 * kStages;
-    const uint32_t bar_tfull = bar_empty + 8 * kStages;
+    const uint32_t bar_empty = bar_full + 8 * NSTG;
+    const uint32_t bar_tfull = bar_empty + 8 * NSTG;
     const uint32_t bar_tempty = bar_tfull + 16;
     const uint32_t bar_bias = bar_tempty + 16;           // two barriers: bias tile of even / odd tiles is in place
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 6);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTG + 6);
+    static_assert(8 * (2 * NSTG + 6) + 8 <= 256, "barrier block overflows");
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;           // 0: the CTA that issues the MMAs
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, kEpiThreads); mbar_init(bar_bias + 8 * a, kEpiThreads); }
+        for (int s = 0; s < NSTG; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, PAIR ? 2 * kEpiThreads : kEpiThreads);
+            mbar_init(bar_bias + 8 * a, kEpiThreads);
+        }
         *abort_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-        tmem_relinquish();
+        if constexpr (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync();        // the peer's barriers are initialised before anything is sent to them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -144,40 +162,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmC); }
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
-            const int m0 = tm * BM, n0 = tn * BN;
-            if (p.causal_lower && n0 > m0 + BM - 1) continue;
+            const int m0 = tm * TM + (int)rank * BM, n0 = tn * BN;
+            if constexpr (!PAIR) { if (p.causal_lower && n0 > m0 + BM - 1) continue; }
             const int z1 = z % p.nb1, z2 = z / p.nb1;
-            const int kb_end = p.causal_k ? min(p.num_kb, (m0 + BM + BK - 1) / BK) : p.num_kb;
+            const int kb_end = (!PAIR && p.causal_k) ? min(p.num_kb, (m0 + BM + BK - 1) / BK) : p.num_kb;
             for (int kb = 0; kb < kb_end; kb++) {
                 ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducerWait);
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t sa = base + stage * STAGE_BYTES;
-                    mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-                    tma_load_4d(sa, &tmA, bar_full + 8 * stage, kb * BK, m0, z1, z2);
-                    tma_load_4d(sa + A_BYTES, &tmB, bar_full + 8 * stage, kb * BK, n0, p.b_broadcast ? 0 : z1, p.b_broadcast ? 0 : z2);
+                    if constexpr (PAIR) {
+                        const uint32_t full0 = mapa(bar_full + 8 * stage, 0);
+                        if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * STAGE_BYTES);
+                        tma_load_4d_pair(sa, &tmA, full0, kb * BK, m0, z1, z2);
+                        tma_load_4d_pair(sa + A_BYTES, &tmB, full0, kb * BK, n0 + (int)rank * B_ROWS, p.b_broadcast ? 0 : z1, p.b_broadcast ? 0 : z2);
+                    } else {
+                        mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                        tma_load_4d(sa, &tmA, bar_full + 8 * stage, kb * BK, m0, z1, z2);
+                        tma_load_4d(sa + A_BYTES, &tmB, bar_full + 8 * stage, kb * BK, n0, p.b_broadcast ? 0 : z1, p.b_broadcast ? 0 : z2);
+                    }
                 }
                 __syncwarp();
-                if (++stage == kStages) { stage = 0; phase ^= 1; }
+                if (++stage == NSTG) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         int stage = 0; uint32_t phase = 0;
         int acc = 0; uint32_t acc_phase = 0;
-        bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        bool ok = rank == 0;                 // the odd CTA of a pair issues nothing: its tiles are driven from the even CTA
+        for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
-            if (p.causal_lower && tn * BN > tm * BM + BM - 1) continue;
+            if constexpr (!PAIR) { if (p.causal_lower && tn * BN > tm * BM + BM - 1) continue; }
             ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaWait);
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
-            const int kb_end = p.causal_k ? min(p.num_kb, (tm * BM + BM + BK - 1) / BK) : p.num_kb;
+            const int kb_end = (!PAIR && p.causal_k) ? min(p.num_kb, (tm * BM + BM + BK - 1) / BK) : p.num_kb;
             for (int kb = 0; kb < kb_end; kb++) {
                 ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMmaWait);
                 if (!ok) break;
@@ -186,14 +211,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const uint32_t sa = base + stage * STAGE_BYTES;
                     const uint64_t adesc = make_kmajor_sw128_desc(sa);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sa + A_BYTES);
+                    if constexpr (PAIR) {
 #pragma unroll
-                    for (int k = 0; k < kStageRowBytes / 32; k++)
-                        mma_ss<TF32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
-                    mma_commit(bar_empty + 8 * stage);            // stage reusable once these MMAs have read it
-                    if (kb == kb_end - 1) mma_commit(bar_tfull + 8 * acc);   // accumulator complete
+                        for (int k = 0; k < kStageRowBytes / 32; k++)
+                            mma_ss_pair<TF32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                        // the stage is handed back to the producers of both CTAs, the finished accumulator to both epilogues
+                        mma_commit_pair(mapa(bar_empty + 8 * stage, 0));
+                        mma_commit_pair(mapa(bar_empty + 8 * stage, 1));
+                        if (kb == kb_end - 1) { mma_commit_pair(mapa(bar_tfull + 8 * acc, 0)); mma_commit_pair(mapa(bar_tfull + 8 * acc, 1)); }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < kStageRowBytes / 32; k++)
+                            mma_ss<TF32>(d_tmem, adesc + 2 * k, bdesc + 2 * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                        mma_commit(bar_empty + 8 * stage);            // stage reusable once these MMAs have read it
+                        if (kb == kb_end - 1) mma_commit(bar_tfull + 8 * acc);   // accumulator complete
+                    }
                 }
                 __syncwarp();
-                if (++stage == kStages) { stage = 0; phase ^= 1; }
+                if (++stage == NSTG) { stage = 0; phase ^= 1; }
             }
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -221,11 +256,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t chunk_seq = 0;                              // chunks this warp has staged so far (buffer parity)
         uint32_t tile_par = 0, tile_seq = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const uint32_t tempty0 = PAIR ? mapa(bar_tempty, 0) : bar_tempty;     // where a drained accumulator is reported
+        auto release_acc = [&](int a) {
+            tc_fence_before();
+            if constexpr (PAIR) mbar_arrive_cluster(tempty0 + 8 * a); else mbar_arrive(tempty0 + 8 * a);
+        };
+        for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
             decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
-            const int m0 = tm * BM, n0 = tn * BN;
-            if (p.causal_lower && n0 > m0 + BM - 1) continue;
+            const int m0 = tm * TM + (int)rank * BM, n0 = tn * BN;
+            if constexpr (!PAIR) { if (p.causal_lower && n0 > m0 + BM - 1) continue; }
             const int z1 = z % p.nb1, z2 = z / p.nb1;
             const long long zoff = (long long)z1 * p.sC1 + (long long)z2 * p.sC2;
             TOut* cbase = reinterpret_cast<TOut*>(p.C) + zoff;
@@ -288,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     f[j] = lo.x; f[j + 1] = lo.y; f[j + 2] = hi.x; f[j + 3] = hi.y;
                 }
                 if (c + 1 < c_end) { tmem_ld_32x32(t_row + (c + 1) * 32, v); fetch_residual(c + 1); }
-                else { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }    // this warp has drained its part of the accumulator
+                else release_acc(acc);                                            // this warp has drained its part of the accumulator
                 if (p.epilogue == EPI_GELU) {
                     if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
@@ -357,7 +397,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     for (int j = 0; j < 32; j++) if (col0 + j < p.N) cp[j] = (TOut)f[j];
                 }
             }
-            if (c_begin >= c_end) { tc_fence_before(); mbar_arrive(bar_tempty + 8 * acc); }
+            if (c_begin >= c_end) release_acc(acc);
             tile_par ^= 1;
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -374,9 +414,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         while (globaltimer() - t0 < 200000ull) { }
         __syncthreads();
     }
+    if constexpr (PAIR) cluster_sync();        // neither CTA leaves (or frees TMEM) while the other may still signal it
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -453,7 +494,7 @@ bool gemm_supported(const GemmDesc& d, const char** why) {
 
 template <bool TF32, typename TOut, int BN>
 static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
-    auto kern = gemm_tcgen05_kernel<TF32, TOut, BN>;
+    auto kern = gemm_tcgen05_kernel<TF32, TOut, BN, false>;
     static bool attr_set = false;   // per instantiation
     if (!attr_set) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
@@ -465,6 +506,51 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
 }
 
 static size_t smem_for(int bn) { return (size_t)kStages * (BM + bn) * kStageRowBytes + 256 /*barriers*/ + 8 * 4096 /*epilogue staging*/ + 2 * 1024 /*bias tiles*/; }
+static size_t smem_for_pair() { return (size_t)kStagesPair * (BM + 128) * kStageRowBytes + 256 + 8 * 4096 + 2 * 1024; }
+
+// pair kernel: clusters of two CTAs
+template <bool TF32, typename TOut>
+static int launch_pair_t(const GemmPlan& pl, const GemmParams& prm) {
+    auto kern = gemm_tcgen05_kernel<TF32, TOut, 256, true>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.grid); cfg.blockDim = dim3(kGemmThreads); cfg.dynamicSmemBytes = pl.smem; cfg.stream = rt().stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm));
+    SPT_LAUNCH_CHECK("gemm_tcgen05 (pair)");
+    return 0;
+}
+
+// how many two-CTA clusters of the pair kernel the device holds at once (0: unknown or none -> pair kernel not used)
+static int max_pairs() {
+    static int n = -1;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        auto kern = gemm_tcgen05_kernel<false, __nv_bfloat16, 256, true>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for_pair()) != cudaSuccess) { cudaGetLastError(); n = 0; return; }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 512); cfg.blockDim = dim3(kGemmThreads); cfg.dynamicSmemBytes = smem_for_pair();
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int c = 0;
+        if (cudaOccupancyMaxActiveClusters(&c, kern, &cfg) != cudaSuccess) { cudaGetLastError(); c = 0; }
+        n = c;
+    });
+    return n;
+}
+
+// 0: one-CTA tiles; 1: CTA pairs wherever they apply; 2 (default): CTA pairs for TF32 problems only.  Measured on B200
+// (65536 x 768 -> 3072): TF32 0.512 -> 0.490 ms with pairs, bf16 0.246 -> 0.252 ms: a bf16 stage already arrives fast
+// enough for one SM, a TF32 stage (twice the bytes per FLOP) does not.  SPTORCH_B200_GEMM_PAIR in the environment sets the
+// initial value, sptorch_ext_set_gemm_pair changes it.
+static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GEMM_PAIR"); return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2; }()};
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;
@@ -472,16 +558,27 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     plan->d = d;
     int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
     plan->bn = bn;
-    plan->tiles_m = ceil_div(d.M, BM);
+    // wide problems run on CTA pairs (each SM then loads half of the B tile); the triangular attention products do not
+    int pairs = 0;
+    const int pm = g_pair_mode.load();
+    if ((pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
+    plan->pair = pairs > 0;
+    plan->tiles_m = ceil_div(d.M, plan->pair ? 2 * BM : BM);
     plan->tiles_n = ceil_div(d.N, bn);
     long long total = (long long)plan->tiles_m * plan->tiles_n * d.nb1 * d.nb2;
     if (total > INT32_MAX) return fail("gemm: too many tiles");
-    plan->grid = (int)(total < compute_sms() ? total : compute_sms());
-    plan->smem = smem_for(bn);
+    if (plan->pair) {
+        plan->grid = 2 * (int)(total < pairs ? total : pairs);
+        plan->smem = smem_for_pair();
+    } else {
+        plan->grid = (int)(total < compute_sms() ? total : compute_sms());
+        plan->smem = smem_for(bn);
+    }
     const bool tf32 = d.mode == MM_TF32;
+    const int b_box = plan->pair ? bn / 2 : bn;
     if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;
-    if (d.b_broadcast) { if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, 1, 1, 0, 0, bn)) return 1; }
-    else if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, bn)) return 1;
+    if (d.b_broadcast) { if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, 1, 1, 0, 0, b_box)) return 1; }
+    else if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, b_box)) return 1;
     // output map: 32x32 boxes, swizzled to match the conflict-free staging layout of the epilogue
     const long long oes = d.out_dtype == BF16 ? 2 : 4;
     plan->tma_store = ((reinterpret_cast<uintptr_t>(d.C) & 15) == 0) && (d.ldc * oes) % 16 == 0 && d.ldc >= d.N &&
@@ -517,6 +614,11 @@ int gemm_run(const GemmPlan& pl) {
     prm.status = rt().dev_status;
     const bool tf32 = d.mode == MM_TF32;
     const bool out_bf16 = d.out_dtype == BF16;
+    if (pl.pair) {
+        if (tf32) return launch_pair_t<true, float>(pl, prm);
+        if (out_bf16) return launch_pair_t<false, __nv_bfloat16>(pl, prm);
+        return launch_pair_t<false, float>(pl, prm);
+    }
 #define SPT_GEMM_CASE(BN_)                                                                          \
     if (pl.bn == BN_) {                                                                             \
         if (tf32) return launch_t<true, float, BN_>(pl, prm);                                       \
@@ -597,6 +699,12 @@ int simt_matmul_f32(const float* A, const float* B, float* C, int batch, int M, 
 }
 
 static std::atomic<int> g_abi_mode{MM_TF32};
+
+extern "C" int sptorch_ext_set_gemm_pair(int mode) {
+    if (mode < 0 || mode > 2) return fail("set_gemm_pair: mode %d is not 0, 1 or 2", mode);
+    g_pair_mode.store(mode);
+    return 0;
+}
 
 // C-ABI matmul: B arrives as [k,n] row-major.  Tensor-core path: transpose B once into a pool scratch
 // (one HBM pass over B) so that both operands are K-major, then the TF32 GEMM.  Shapes whose pitches TMA

@@ -34,6 +34,7 @@ struct GemmPlan {
     GemmDesc d;
     int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0;
     size_t smem = 0;
+    bool pair = false;       // two-CTA tiles (256 x 256, cta_group::2); grid counts CTAs, two per tile worker
     bool valid = false;
 };
 

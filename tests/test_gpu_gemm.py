@@ -60,6 +60,32 @@ def test_linear_is_linear_at_full_size(backend):
     assert np.array_equal(backend.linear(x, w, mode=MM_TF32), ref)
 
 
+@pytest.mark.parametrize("M,K,N", [(129, 64, 129), (256, 64, 256), (640, 200, 328), (1000, 768, 1000), (2048, 3072, 768), (4100, 136, 50257 // 16)])
+def test_pair_tiles_equal_single_cta_tiles(backend, oracle, M, K, N):
+    """Wide problems run on CTA pairs (256 x 256 tiles, one MMA over two SMs).  Every output element is still the same
+    k-ordered f32 accumulation, so the result must be bit-identical to the one-CTA kernel's; both are checked against the
+    oracle.  Shapes cover a second row half that is partly or wholly outside the matrix and ragged N."""
+    rng = np.random.default_rng(M * 7 + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (0.05 * rng.standard_normal((N, K))).astype(np.float32)
+    b = (0.1 * rng.standard_normal(N)).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    ref = oracle.unary("gelu", oracle.linear(x, w, b, fast=2)) + r
+    try:
+        outs = {}
+        for pair in (1, 0):
+            backend._check(backend.lib.sptorch_ext_set_gemm_pair(pair), "set_gemm_pair")
+            outs[pair] = [backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_TF32),
+                          backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_BF16),
+                          backend.linear(x, w, b, mode=MM_BF16, out_dtype=F32)]
+    finally:
+        backend.lib.sptorch_ext_set_gemm_pair(2)
+    for a, c in zip(outs[1], outs[0]):
+        assert np.array_equal(a, c)
+    assert relerr(outs[1][0], ref) <= 2e-3
+    assert relerr(outs[1][1], ref) <= 2e-2
+
+
 @pytest.mark.parametrize("B,T,H,hd", [(2, 64, 4, 32), (1, 256, 2, 64), (2, 128, 2, 128), (1, 1024, 1, 64), (3, 8, 2, 32)])
 def test_attention_vs_oracle(backend, oracle, B, T, H, hd):
     rng = np.random.default_rng(B * T + hd)
