@@ -546,11 +546,11 @@ static int max_pairs() {
     return n;
 }
 
-// 0: one-CTA tiles; 1: CTA pairs wherever they apply; 2 (default): CTA pairs for TF32 problems only.  Measured on B200
-// (65536 x 768 -> 3072): TF32 0.512 -> 0.490 ms with pairs, bf16 0.246 -> 0.252 ms: a bf16 stage already arrives fast
-// enough for one SM, a TF32 stage (twice the bytes per FLOP) does not.  SPTORCH_B200_GEMM_PAIR in the environment sets the
-// initial value, sptorch_ext_set_gemm_pair changes it.
-static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GEMM_PAIR"); return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2; }()};
+// 0 (default): one-CTA tiles; 1: CTA pairs wherever they apply; 2: CTA pairs for TF32 problems only.  Measured on B200, bf16:
+// 65536 x 768 -> 3072 0.246 ms (one CTA) vs 0.252 ms (pairs), 16384 x 4096 -> 4096 0.366 vs 0.395 ms; TF32: 0.512 vs 0.490 ms
+// and 0.801 vs 0.814 ms.  With loads and epilogue switched off the pair kernel's MMA stream alone ran 18 % slower than the
+// one-CTA kernel's, so the halved B traffic does not pay.  SPTORCH_B200_GEMM_PAIR in the environment sets the initial value.
+static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GEMM_PAIR"); return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0; }()};
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;

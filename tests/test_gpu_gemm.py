@@ -79,7 +79,7 @@ def test_pair_tiles_equal_single_cta_tiles(backend, oracle, M, K, N):
                           backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_BF16),
                           backend.linear(x, w, b, mode=MM_BF16, out_dtype=F32)]
     finally:
-        backend.lib.sptorch_ext_set_gemm_pair(2)
+        backend.lib.sptorch_ext_set_gemm_pair(0)
     for a, c in zip(outs[1], outs[0]):
         assert np.array_equal(a, c)
     assert relerr(outs[1][0], ref) <= 2e-3
