@@ -33,6 +33,7 @@ extern "C" {
 /* epilogue of sptorch_ext_linear: out = act(alpha * x W^T + bias) + residual */
 #define SPT_EPI_NONE 0
 #define SPT_EPI_GELU 1
+#define SPT_EPI_SWIGLU 2   /* out = residual * g * sigmoid(g), g = alpha x W^T + bias: swiglu(x, gate) of core-ops/src/lib.rs:1529-1541 with the gate projection fused */
 
 /* ---- runtime ---- */
 const char* sptorch_ext_last_error(void);              /* text of the calling thread's last failure */
@@ -82,13 +83,19 @@ int sptorch_ext_layernorm(const void* x, const void* gamma_f32, const void* beta
 int sptorch_ext_causal_softmax(const void* scores, void* out, size_t batch, size_t T, float scale, int dtype);
 /* core-ops masked_softmax (core-ops/src/lib.rs:1601-1645): keep!=0 takes part, others give exactly 0 */
 int sptorch_ext_masked_softmax_f32(const void* a, const void* keep_u8, void* out, size_t rows, size_t cols, int rank1);
-/* out[t,:] = tok[ids[t],:] + pos[t % T,:]   (nn/src/lib.rs:1351-1356); ids are int32 on the device */
+/* out[t,:] = tok[ids[t],:] + pos[t % T,:]   (nn/src/lib.rs:1351-1356); ids are int32 on the device;
+ * pos_w may be NULL: token rows only (QwenLikeGPT::forward_ids, nn/src/lib.rs:1458-1459) */
 int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* ids_i32, void* out,
                               size_t n_tokens, size_t T, size_t vocab, size_t dim, int dtype);
 
 /* ---- neighbours of the path (the Qwen-like blocks and the step after the forward) ---- */
 int sptorch_ext_rms_norm(const void* x, const void* weight_f32, void* out, size_t rows, size_t dim, float eps, int dtype);   /* core-ops/src/lib.rs:1453 */
-int sptorch_ext_swiglu(const void* x, const void* gate, void* out, size_t n, int dtype);                                    /* core-ops/src/lib.rs:1529 */
+int sptorch_ext_swiglu(const void* x, const void* gate, void* out, size_t n, int dtype);
+/* Rotary position embedding, in place (apply_rope_raw, nn/src/lib.rs:930-961, as MultiHeadAttention::forward_causal_impl applies it
+ * to Q and K, :606-609).  x is token-major [rows, ld] with head h at columns h*head_dim (the reference's [n_head, seq_len, head_dim]
+ * permute is not needed); row r has position position_offset + r % seq_len; pairs are (2p, 2p+1), theta = pos / base^(2p/head_dim). */
+int sptorch_ext_rope(void* x, size_t rows, size_t seq_len, size_t n_heads, size_t head_dim, size_t ld, float rope_base,
+                     size_t position_offset, int dtype);                                    /* core-ops/src/lib.rs:1529 */
 /* cross_entropy_loss / cross_entropy_loss_ignore_index over logits [rows, ld] (core-ops/src/lib.rs:1079-1194): mean of
  * -(x[target] - logsumexp(x)) over the rows whose target differs from ignore_index (has_ignore = 0: every row).
  * row_loss_f32: device scratch of rows + 1 floats (per-row losses, then the mean); the mean is also copied to *host_mean.
@@ -139,7 +146,13 @@ typedef struct {
     int32_t max_batch;    /* activations are sized for max_batch * seq_len tokens */
     float   eps;          /* 1e-5 in the reference (nn/src/lib.rs:383) */
     int32_t tp_rank, tp_size;   /* tensor parallel shard of this process; 0,1 = none */
+    int32_t arch;         /* SPT_ARCH_GPT: nn::GPT (learned positions, LayerNorm, GELU MLP);
+                           * SPT_ARCH_QWEN_LIKE: nn::QwenLikeGPT (nn/src/lib.rs:1439-1467: no position table, RMSNorm with eps 1e-6,
+                           * RoPE on Q and K, SwiGLU MLP with up / gate / down projections, all three biased) */
+    float   rope_base;    /* SPT_ARCH_QWEN_LIKE: 10000 in the reference (nn/src/lib.rs:1083); 0 selects that default */
 } sptorch_gpt_config;
+#define SPT_ARCH_GPT 0
+#define SPT_ARCH_QWEN_LIKE 1
 
 void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg);       /* allocates weights + activations; NULL on failure */
 void  sptorch_ext_gpt_destroy(void* gpt);

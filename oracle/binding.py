@@ -46,6 +46,8 @@ def lib():
         L.orc_cross_entropy.restype = C.c_float
         L.orc_gpt_param_count.restype = _sz
         L.orc_gpt_param_count.argtypes = [C.POINTER(GptConfig)]
+        L.orc_qwen_param_count.restype = _sz
+        L.orc_qwen_param_count.argtypes = [C.POINTER(GptConfig)]
     return _lib
 
 
@@ -207,6 +209,23 @@ def mha_causal(x, wq, wk, wv, wo, n_head, fast=0):
     return out
 
 
+def rope(x, rope_base=10000.0, position_offset=0, inverse=False):
+    """x [n_head, seq_len, head_dim] (crates/nn/src/lib.rs:930-961)."""
+    x = _f32(x); H, T, hd = x.shape
+    out = np.empty_like(x)
+    if lib().orc_rope(_p(x), _p(out), _sz(H), _sz(T), _sz(hd), C.c_float(rope_base), _sz(position_offset), C.c_int(int(inverse))) != 0:
+        raise ValueError("rope requires an even head dimension")
+    return out
+
+
+def mha_causal_rope(x, wq, wk, wv, wo, n_head, rope_base=10000.0, position_offset=0, fast=0):
+    x = _f32(x); T, d = x.shape
+    out = np.empty_like(x)
+    lib().orc_mha_causal_rope(_p(x), _p(_f32(wq)), _p(_f32(wk)), _p(_f32(wv)), _p(_f32(wo)), _p(out),
+                              _sz(T), _sz(d), _sz(n_head), C.c_int(fast), C.c_float(rope_base), _sz(position_offset))
+    return out
+
+
 def attention_last_token(q, k, v):
     """q [H*hd]; k, v [H, n, hd] -> [H*hd]  (crates/nn/src/lib.rs:727-755)."""
     k = _f32(k); v = _f32(v); q = _f32(q)
@@ -238,4 +257,21 @@ def gpt_forward(cfg: dict, params: np.ndarray, ids: np.ndarray, fast=0, threads=
                                      _p(taps) if taps is not None else None, C.c_int(fast), C.c_int(threads))
     if rc != 0:
         raise IndexError(f"oracle gpt forward failed rc={rc}")
+    return (logits, taps) if want_taps else logits
+
+
+def qwen_forward(cfg: dict, params: np.ndarray, ids: np.ndarray, fast=0, threads=1, want_taps=False, rope_base=10000.0):
+    """QwenLikeGPT: ids [B,T] int64 -> logits [B,T,V] (and taps [B, L+2, T, d]); cfg["eps"] is the RMSNorm epsilon (1e-6)."""
+    cfg = dict(cfg); cfg.setdefault("eps", 1e-6)
+    c = _cfg(cfg)
+    params = _f32(params)
+    assert params.size == lib().orc_qwen_param_count(C.byref(c)), "parameter block size mismatch"
+    ids = np.ascontiguousarray(ids, dtype=np.int64)
+    B, T = ids.shape
+    logits = np.empty((B, T, cfg["vocab"]), dtype=np.float32)
+    taps = np.empty((B, cfg["n_layer"] + 2, T, cfg["d_model"]), dtype=np.float32) if want_taps else None
+    rc = lib().orc_qwen_forward_batch(C.byref(c), C.c_float(rope_base), _p(params), ids.ctypes.data_as(_i64), _sz(B), _sz(T), _p(logits),
+                                      _p(taps) if taps is not None else None, C.c_int(fast), C.c_int(threads))
+    if rc != 0:
+        raise IndexError(f"oracle qwen forward failed rc={rc}")
     return (logits, taps) if want_taps else logits

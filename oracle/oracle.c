@@ -289,9 +289,45 @@ static void head_matmul_nt(const float* a, const float* bt, float* out, size_t m
         }
 }
 
+/* apply_rope_raw: crates/nn/src/lib.rs:930-961.  data, out: [n_head, seq_len, head_dim]; pairs (2p, 2p+1) of every head
+ * are rotated by theta = absolute_pos / base^(2p/head_dim), all in f32 (powf, sinf, cosf as f32::powf / sin_cos). */
+int orc_rope(const float* data, float* out, size_t n_head, size_t seq_len, size_t head_dim, float rope_base,
+             size_t position_offset, int inverse) {
+    if (head_dim % 2) return -1;                       /* the reference asserts an even head dimension */
+    size_t half = head_dim / 2;
+    for (size_t h = 0; h < n_head; h++)
+        for (size_t pos = 0; pos < seq_len; pos++) {
+            size_t off = h * seq_len * head_dim + pos * head_dim;
+            size_t absolute_pos = position_offset + pos;
+            for (size_t pair = 0; pair < half; pair++) {
+                float theta = (float)absolute_pos / powf(rope_base, (float)(2 * pair) / (float)head_dim);
+                float sn = sinf(theta), cs = cosf(theta);
+                if (inverse) sn = -sn;
+                float even = data[off + 2 * pair], odd = data[off + 2 * pair + 1];
+                out[off + 2 * pair] = even * cs - odd * sn;
+                out[off + 2 * pair + 1] = even * sn + odd * cs;
+            }
+        }
+    return 0;
+}
+
+static void mha_causal_impl(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
+                            float* out, size_t T, size_t d, size_t H, int fast, int use_rope, float rope_base, size_t position_offset);
+
 /* MultiHeadAttention::forward_causal_impl: crates/nn/src/lib.rs:590-642. */
 void orc_mha_causal(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
                     float* out, size_t T, size_t d, size_t H, int fast) {
+    mha_causal_impl(x, wq, wk, wv, wo, out, T, d, H, fast, 0, 0.0f, 0);
+}
+
+/* MultiHeadAttention::forward_causal_rope_with_offset: crates/nn/src/lib.rs:655-661 (Q and K rotated after the head split, :606-609). */
+void orc_mha_causal_rope(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
+                         float* out, size_t T, size_t d, size_t H, int fast, float rope_base, size_t position_offset) {
+    mha_causal_impl(x, wq, wk, wv, wo, out, T, d, H, fast, 1, rope_base, position_offset);
+}
+
+static void mha_causal_impl(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
+                            float* out, size_t T, size_t d, size_t H, int fast, int use_rope, float rope_base, size_t position_offset) {
     size_t hd = d / H;
     float* q = (float*)malloc(T * d * sizeof(float));
     float* k = (float*)malloc(T * d * sizeof(float));
@@ -310,6 +346,13 @@ void orc_mha_causal(const float* x, const float* wq, const float* wk, const floa
     orc_reshape_to_heads(q, q3, T, H, hd);
     orc_reshape_to_heads(k, k3, T, H, hd);
     orc_reshape_to_heads(v, v3, T, H, hd);
+    if (use_rope) {
+        /* q and k are free again after the head split: rotate into them and swap the roles */
+        orc_rope(q3, q, H, T, hd, rope_base, position_offset, 0);
+        orc_rope(k3, k, H, T, hd, rope_base, position_offset, 0);
+        float* t_ = q3; q3 = q; q = t_;
+        t_ = k3; k3 = k; k = t_;
+    }
     /* scores = Q K^T: the reference materialises K^T [H,hd,T] and multiplies [T,hd]x[hd,T];
      * the products and their p-order are the same as dotting rows of Q with rows of K. */
 #pragma omp parallel for schedule(static) if (!omp_in_parallel_())
@@ -406,6 +449,75 @@ int orc_gpt_forward_ids(const orc_gpt_config* c, const float* params, const int6
     }
 done:
     free(x); free(t0); free(t1); free(hbuf); free(gbuf); free(posid);
+    return rc;
+}
+
+/* Flat parameter block of QwenLikeGPT in named_parameters order (crates/nn/src/lib.rs:1483-1492, block :1157-1166):
+ * token_emb.weight[V,d]; per block norm1.weight[d], attn.wq/wk/wv/wo.weight[d,d], norm2.weight[d], ffn_up.weight[F,d], ffn_up.bias[F],
+ * ffn_gate.weight[F,d], ffn_gate.bias[F], ffn_down.weight[d,F], ffn_down.bias[d]; then norm_f.weight[d], lm_head.weight[V,d]. */
+size_t orc_qwen_param_count(const orc_gpt_config* c) {
+    size_t V = c->vocab, d = c->d_model, F = c->d_ff, L = c->n_layer;
+    return V * d + L * (2 * d + 4 * d * d + 2 * (F * d + F) + d * F + d) + d + V * d;
+}
+
+/* QwenLikeGPT::forward_ids (crates/nn/src/lib.rs:1454-1467) with QwenLikeBlock::forward_seq_inference (:1106-1117): dropout is
+ * the identity in evaluation.  c->eps is the RMSNorm epsilon (1e-6, :468); rope_base 10000 (:1083).  taps as in orc_gpt_forward_ids. */
+int orc_qwen_forward_ids(const orc_gpt_config* c, float rope_base, const float* params, const int64_t* ids, size_t T,
+                         float* logits, float* taps, int fast) {
+    size_t V = c->vocab, d = c->d_model, F = c->d_ff, L = c->n_layer, H = c->n_head;
+    if (T > (size_t)c->seq_len) return -2;
+    float* x = (float*)malloc(T * d * sizeof(float));
+    float* t0 = (float*)malloc(T * d * sizeof(float));
+    float* t1 = (float*)malloc(T * d * sizeof(float));
+    float* up = (float*)malloc(T * F * sizeof(float));
+    float* gate = (float*)malloc(T * F * sizeof(float));
+    float* act = (float*)malloc(T * F * sizeof(float));
+    int rc = 0;
+    const float* p = params;
+    const float* tok = p; p += V * d;
+    if (orc_embedding(tok, ids, x, T, V, d) != 0) { rc = -1; goto done; }
+    if (taps) memcpy(taps, x, T * d * sizeof(float));
+    for (size_t l = 0; l < L; l++) {
+        const float* n1 = p;              const float* wq = n1 + d;
+        const float* wk = wq + d * d;     const float* wv = wk + d * d;     const float* wo = wv + d * d;
+        const float* n2 = wo + d * d;     const float* wu = n2 + d;         const float* bu = wu + F * d;
+        const float* wg = bu + F;         const float* bg = wg + F * d;
+        const float* wd = bg + F;         const float* bd = wd + d * F;
+        p = bd + d;
+        orc_rms_norm(x, n1, t0, T, d, c->eps);
+        orc_mha_causal_rope(t0, wq, wk, wv, wo, t1, T, d, H, fast, rope_base, 0);
+        orc_add(x, t1, x, T * d);
+        orc_rms_norm(x, n2, t0, T, d, c->eps);
+        orc_linear(t0, wu, bu, up, T, d, F, fast);
+        orc_linear(t0, wg, bg, gate, T, d, F, fast);
+        orc_swiglu(up, gate, act, T * F);
+        orc_linear(act, wd, bd, t1, T, F, d, fast);
+        orc_add(x, t1, x, T * d);
+        if (taps) memcpy(taps + (l + 1) * T * d, x, T * d * sizeof(float));
+    }
+    {
+        const float* nf = p; const float* head = nf + d;
+        orc_rms_norm(x, nf, t0, T, d, c->eps);
+        if (taps) memcpy(taps + (L + 1) * T * d, t0, T * d * sizeof(float));
+        orc_linear(t0, head, NULL, logits, T, d, V, fast);
+    }
+done:
+    free(x); free(t0); free(t1); free(up); free(gate); free(act);
+    return rc;
+}
+
+int orc_qwen_forward_batch(const orc_gpt_config* c, float rope_base, const float* params, const int64_t* ids, size_t B,
+                           size_t T, float* logits, float* taps, int fast, int threads) {
+    size_t V = c->vocab, d = c->d_model, L = c->n_layer;
+    int rc = 0;
+#ifdef _OPENMP
+    if (threads >= 1) omp_set_num_threads(threads);
+#endif
+    /* sequences one after another; the rows and heads of each are split over the threads */
+    for (size_t b = 0; b < B; b++) {
+        int r = orc_qwen_forward_ids(c, rope_base, params, ids + b * T, T, logits + b * T * V, taps ? taps + b * (L + 2) * T * d : NULL, fast);
+        if (r != 0) rc = r;
+    }
     return rc;
 }
 

@@ -70,6 +70,11 @@ void orc_batch_transpose(const float* x, float* out, size_t H, size_t T, size_t 
 void orc_mha_causal(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
                     float* out, size_t T, size_t d, size_t H, int fast);
 
+int  orc_rope(const float* data, float* out, size_t n_head, size_t seq_len, size_t head_dim, float rope_base,
+              size_t position_offset, int inverse);
+void orc_mha_causal_rope(const float* x, const float* wq, const float* wk, const float* wv, const float* wo,
+                         float* out, size_t T, size_t d, size_t H, int fast, float rope_base, size_t position_offset);
+
 void orc_attention_last_token(const float* q, const float* k, const float* v, float* out, size_t H, size_t n, size_t hd);
 
 typedef struct {
@@ -92,6 +97,12 @@ int orc_gpt_forward_ids(const orc_gpt_config* c, const float* params, const int6
 /* Batch = independent calls (the reference has no batch dimension); OpenMP over sequences. */
 int orc_gpt_forward_batch(const orc_gpt_config* c, const float* params, const int64_t* ids, size_t B,
                           size_t T, float* logits, float* taps, int fast, int threads);
+/* QwenLikeGPT (crates/nn/src/lib.rs:1439-1467): parameter block in named_parameters order, see oracle.c */
+size_t orc_qwen_param_count(const orc_gpt_config* c);
+int orc_qwen_forward_ids(const orc_gpt_config* c, float rope_base, const float* params, const int64_t* ids, size_t T,
+                         float* logits, float* taps, int fast);
+int orc_qwen_forward_batch(const orc_gpt_config* c, float rope_base, const float* params, const int64_t* ids, size_t B,
+                           size_t T, float* logits, float* taps, int fast, int threads);
 int orc_max_threads(void);
 
 #ifdef __cplusplus

@@ -14,7 +14,7 @@ _vp, _sz, _f, _i = C.c_void_p, C.c_size_t, C.c_float, C.c_int
 class GptConfig(C.Structure):
     _fields_ = [("vocab", C.c_int32), ("d_model", C.c_int32), ("n_layer", C.c_int32), ("n_head", C.c_int32),
                 ("d_ff", C.c_int32), ("seq_len", C.c_int32), ("dtype", C.c_int32), ("max_batch", C.c_int32),
-                ("eps", C.c_float), ("tp_rank", C.c_int32), ("tp_size", C.c_int32)]
+                ("eps", C.c_float), ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("arch", C.c_int32), ("rope_base", C.c_float)]
 
 
 ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p)
@@ -79,6 +79,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_embedding_sum": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_rms_norm": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _i]),
     "sptorch_ext_swiglu": (_i, [_vp, _vp, _vp, _sz, _i]),
+    "sptorch_ext_rope": (_i, [_vp, _sz, _sz, _sz, _sz, _sz, _f, _sz, _i]),
     "sptorch_ext_cross_entropy": (_i, [_vp, _sz, _vp, _sz, _sz, _i, C.c_longlong, _vp, C.POINTER(C.c_float), _i]),
     "sptorch_ext_set_gemm_pair": (_i, [_i]),
     "sptorch_ext_set_matmul_mode": (_i, [_i]),

@@ -21,7 +21,7 @@ from . import _lib
 
 F32, BF16 = 0, 1
 MM_TF32, MM_BF16, MM_F32 = 0, 1, 2
-EPI_NONE, EPI_GELU = 0, 1
+EPI_NONE, EPI_GELU, EPI_SWIGLU = 0, 1, 2
 
 
 class HalError(RuntimeError):
@@ -411,6 +411,22 @@ class FfiBackend:
         finally:
             for b in (dt, dp, di, do):
                 b.free()
+
+    def rope(self, x, rope_base=10000.0, position_offset=0, dtype=F32):
+        """rotary_position_embedding_with_offset (crates/nn/src/lib.rs:975-983): x [n_head, seq_len, head_dim] as in the reference;
+        the device kernel works on the token-major layout, so the permutes happen here on the host."""
+        x = _f32(x)
+        H, T, hd = x.shape
+        tm = np.ascontiguousarray(x.transpose(1, 0, 2)).reshape(T, H * hd)
+        d = self.upload_bf16(tm) if dtype == BF16 else self.upload(tm)
+        try:
+            self._check(self.lib.sptorch_ext_rope(d.handle, T, T, H, hd, H * hd, C.c_float(rope_base), position_offset, dtype), "rope")
+            out = d.to_host()
+            self.synchronize()
+            out = bf16_bits_to_f32(out) if dtype == BF16 else out
+            return np.ascontiguousarray(out.reshape(T, H, hd).transpose(1, 0, 2))
+        finally:
+            d.free()
 
     def linear(self, x, w, bias=None, residual=None, alpha=1.0, epilogue=EPI_NONE, mode=MM_TF32, out_dtype=None):
         """nn::Linear::forward (crates/nn/src/lib.rs:121-133) with optional fused epilogue."""

@@ -75,6 +75,16 @@ __device__ __forceinline__ float2 gelu_fast2(float2 x) {
     return __ffma2_rn(hx, t, hx);
 }
 
+// g * sigmoid(g) (core-ops/src/lib.rs:1537-1538: s = 1 / (1 + exp(-g)), the product with x follows in the caller)
+__device__ __forceinline__ float silu_exact(float g) { return g * (1.0f / (1.0f + expf(-g))); }
+// bf16 outputs: ex2.approx + rcp.approx, relative error 2^-21, below one bf16 ulp
+__device__ __forceinline__ float silu_fast(float g) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return g * r;
+}
+
 // tile index -> (batch z, m-tile, n-tile): bands of kGroupM m-tiles, n outer / m inner inside a band
 __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& z, int& tm, int& tn) {
     int per_batch = tiles_m * tiles_n;
@@ -337,8 +347,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 32; j++) f[j] = gelu_exact(f[j]);
                     }
+                } else if (p.epilogue == EPI_SWIGLU) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) f[j] = sizeof(TOut) == 2 ? silu_fast(f[j]) : silu_exact(f[j]);
                 }
-                if (rbase) {
+                if (rbase && p.epilogue == EPI_SWIGLU) {
+                    // the R operand is the other factor: x * (g * sigmoid(g))
+                    if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+                        for (int k = 0; k < NV; k++) {
+                            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rcur[k]);
+#pragma unroll
+                            for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[8 * k + 2 * q] *= g2.x; f[8 * k + 2 * q + 1] *= g2.y; }
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < NV; k++) {
+                            f[4 * k] *= __uint_as_float(rcur[k].x); f[4 * k + 1] *= __uint_as_float(rcur[k].y);
+                            f[4 * k + 2] *= __uint_as_float(rcur[k].z); f[4 * k + 3] *= __uint_as_float(rcur[k].w);
+                        }
+                    }
+                } else if (rbase) {
                     if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
                         for (int k = 0; k < NV; k++) {
@@ -682,7 +711,8 @@ __global__ void __launch_bounds__(256) simt_matmul_kernel(const float* __restric
                 float v = acc[i][j] * alpha;
                 if (bias) v += bias[gn];
                 if (epilogue == EPI_GELU) v = gelu_exact(v);
-                if (R) v += R[(size_t)gm * N + gn];
+                if (epilogue == EPI_SWIGLU) { const float s_ = 1.0f / (1.0f + expf(-v)); v = R ? (R[(size_t)gm * N + gn] * v) * s_ : v * s_; }
+                else if (R) v += R[(size_t)gm * N + gn];
                 C[(size_t)gm * N + gn] = v;
             }
         }
@@ -823,7 +853,8 @@ int sptorch_ext_linear(const void* x, const void* w, const void* bias, const voi
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail("linear: dimension too large");
     if (ldo == 0) ldo = N;
     if (ldo < N) return fail("linear: ldo < N");
-    if (epilogue != SPT_EPI_NONE && epilogue != SPT_EPI_GELU) return fail("linear: unknown epilogue %d", epilogue);
+    if (epilogue != SPT_EPI_NONE && epilogue != SPT_EPI_GELU && epilogue != SPT_EPI_SWIGLU) return fail("linear: unknown epilogue %d", epilogue);
+    if (epilogue == SPT_EPI_SWIGLU && !residual) return fail("linear: the SwiGLU epilogue multiplies by the residual operand, which is null");
     if (mode == SPT_MM_F32 || K == 0) {
         if (out_dtype != SPT_F32 || ldo != N) return fail("linear: the CUDA-core f32 mode needs f32 output with ldo == N");
         return simt_matmul_f32((const float*)x, (const float*)w, (float*)out, 1, (int)M, (int)N, (int)K, false, (const float*)bias,

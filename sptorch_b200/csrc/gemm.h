@@ -6,7 +6,8 @@
 namespace spt {
 
 enum MMMode : int { MM_TF32 = 0, MM_BF16 = 1, MM_F32 = 2 };
-enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1 };
+// EPI_SWIGLU: C = R * g * sigmoid(g) with g = alpha * A B^T + bias (R is the other factor of the reference's swiglu(x, gate), not a residual)
+enum Epilogue : int { EPI_NONE = 0, EPI_GELU = 1, EPI_SWIGLU = 2 };
 
 // C[z][m,n] = act(alpha * sum_k A[z][m,k] * B[z][n,k] + bias[n]) + R[z][m,n]
 // Both operands are K-major (k contiguous).  z = z1 + nb1*z2 enumerates two batch dimensions with

@@ -24,12 +24,14 @@ int attention_dispatch(const void* q, const void* k, const void* vt, long long v
                        void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
 bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
 int attention_mode();
+int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype);
 int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
                          int n, long long seq_stride, long long row_stride, int dtype);
 
 struct Layer {
-    float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;
+    float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;     // Qwen-like: ln1g / ln2g hold the RMSNorm weights, the betas are unused
     void *wqk, *wv, *wo, *w1, *w2;
+    void* wg = nullptr; float* bg = nullptr;         // Qwen-like: gate projection of the SwiGLU MLP
 };
 
 struct Gpt {
@@ -186,7 +188,62 @@ static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* log
     return 0;
 }
 
+int rms_launch(const void* x, const float* w, void* out, size_t rows, size_t dim, float eps, int dt) {
+    ProfScope ps(PROF_LAYERNORM);
+    return sptorch_ext_rms_norm(x, w, out, rows, dim, eps, dt);
+}
+
+// QwenLikeGPT::forward_ids (nn/src/lib.rs:1454-1467) over a batch; block = QwenLikeBlock::forward_seq_inference (:1106-1117):
+//   x += Wo attn(rope(q), rope(k), v) of rms(x);  x += Wdown (up * gate * sigmoid(gate)) + bdown of rms(x)
+// Launches per layer: RMSNorm, [q|k] GEMM, RoPE over both, V^T GEMM, attention, Wo GEMM (+residual), RMSNorm, up GEMM (+bias),
+// gate GEMM (+bias, SwiGLU product with the up output in the epilogue), down GEMM (+bias, +residual).
+static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
+    const sptorch_gpt_config& c = g->c;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head, dt = c.dtype;
+    const bool lead = c.tp_rank == 0;
+    { ProfScope ps(PROF_EMBED); if (sptorch_ext_embedding_sum(g->tok, nullptr, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1; }
+    void* x = g->x; void* y = g->y;
+    auto tap = [&](int i, const void* src) -> int {
+        if (!g->taps_on) return 0;
+        SPT_CUDA(cudaMemcpyAsync(g->taps[i], src, (size_t)M * d * g->es, cudaMemcpyDeviceToDevice, rt().stream));
+        return 0;
+    };
+    if (tap(0, x)) return 1;
+    for (int l = 0; l < c.n_layer; l++) {
+        const Layer& w = g->L[l];
+        if (rms_launch(x, w.ln1g, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        { ProfScope ps(PROF_OTHER); if (rope_launch(g->qk, M, T, 2 * Hl, hd, 2 * dl, c.rope_base, 0, dt)) return 1; }
+        if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
+        if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, M, (long long)hd * M, T, g->ao, g->scores,
+                               B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
+        if (c.tp_size <= 1) {
+            if (linear(g, g->ao, w.wo, nullptr, x, x, M, dl, d, d, EPI_NONE)) return 1;
+        } else {
+            if (linear(g, g->ao, w.wo, nullptr, lead ? x : nullptr, y, M, dl, d, d, EPI_NONE)) return 1;
+            if (allreduce(g, y, (size_t)M * d)) return 1;
+            std::swap(x, y);
+        }
+        if (rms_launch(x, w.ln2g, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+        if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, M, d, Fl, Fl, EPI_NONE)) return 1;                 // up
+        if (linear(g, g->h, w.wg, w.bg, g->f, g->f, M, d, Fl, Fl, EPI_SWIGLU)) return 1;                  // f = up * silu(gate)
+        if (c.tp_size <= 1) {
+            if (linear(g, g->f, w.w2, w.b2, x, x, M, Fl, d, d, EPI_NONE)) return 1;
+        } else {
+            if (linear(g, g->f, w.w2, lead ? w.b2 : nullptr, lead ? x : nullptr, y, M, Fl, d, d, EPI_NONE)) return 1;
+            if (allreduce(g, y, (size_t)M * d)) return 1;
+            std::swap(x, y);
+        }
+        if (tap(l + 1, x)) return 1;
+    }
+    if (rms_launch(x, g->lnfg, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+    if (tap(c.n_layer + 1, g->h)) return 1;
+    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
+    return 0;
+}
+
 static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
+    if (g->c.arch == SPT_ARCH_QWEN_LIKE) return forward_qwen(g, ids, B, T, logits);
     if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0)
         return forward_tp_pipelined(g, ids, B, T, logits);
     const sptorch_gpt_config& c = g->c;
@@ -266,6 +323,8 @@ void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg) {
         fail("gpt_create: non-positive dimension"); return nullptr;
     }
     if (c.dtype != SPT_F32 && c.dtype != SPT_BF16) { fail("gpt_create: unknown dtype %d", c.dtype); return nullptr; }
+    if (c.arch != SPT_ARCH_GPT && c.arch != SPT_ARCH_QWEN_LIKE) { fail("gpt_create: unknown architecture %d", c.arch); return nullptr; }
+    if (c.arch == SPT_ARCH_QWEN_LIKE && !(c.rope_base > 0.0f)) c.rope_base = 10000.0f;
     if (c.d_model % c.n_head) { fail("gpt_create: d_model %% n_head != 0"); return nullptr; }
     if (c.n_head % c.tp_size || c.d_ff % c.tp_size || c.tp_rank < 0 || c.tp_rank >= c.tp_size) {
         fail("gpt_create: heads and d_ff must divide by tp_size"); return nullptr;
@@ -291,6 +350,7 @@ void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg) {
         w.ln1g = (float*)A(d * 4); w.ln1b = (float*)A(d * 4); w.ln2g = (float*)A(d * 4); w.ln2b = (float*)A(d * 4);
         w.b1 = (float*)A(Fl * 4); w.b2 = (float*)A(d * 4);
         w.wqk = A(2 * dl * d * es); w.wv = A(dl * d * es); w.wo = A(d * dl * es); w.w1 = A(Fl * d * es); w.w2 = A(d * Fl * es);
+        if (c.arch == SPT_ARCH_QWEN_LIKE) { w.wg = A(Fl * d * es); w.bg = (float*)A(Fl * 4); }
     }
     g->x = A(Mmax * d * es); g->y = A(Mmax * d * es); g->h = A(Mmax * d * es);
     g->qk = A(Mmax * 2 * dl * es); g->vt = A(dl * Mmax * es); g->ao = A(Mmax * dl * es); g->f = A(Mmax * Fl * es);
@@ -328,6 +388,9 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
     auto need = [&](size_t want) { return n == want ? 0 : fail("gpt_set_param(%s): got %zu values, expected %zu", name, n, want); };
     auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || stream_wait(); };
     std::string s(name);
+    const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;
+    if (qwen && (s == "pos_emb.weight" || s == "ln_f.gamma" || s == "ln_f.beta")) return fail("gpt_set_param: '%s' is not a parameter of the Qwen-like model", name);
+    if (qwen && s == "norm_f.weight") return need(d) || f32(g->lnfg, 0, d);
     if (s == "token_emb.weight") return need(V * d) || upload_rows(g, g->tok, host, n);
     if (s == "pos_emb.weight") return need(S * d) || upload_rows(g, g->pos, host, n);
     if (s == "lm_head.weight") return need(V * d) || upload_rows(g, g->head, host, n);
@@ -337,6 +400,14 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
     if (sscanf(name, "blocks.%d.%63s", &li, rest) == 2 && li >= 0 && li < c.n_layer) {
         Layer& w = g->L[li];
         std::string t(rest);
+        if (qwen) {
+            // QwenLikeBlock::named_parameters (nn/src/lib.rs:1157-1166)
+            if (t == "norm1.weight") return need(d) || f32(w.ln1g, 0, d);
+            if (t == "norm2.weight") return need(d) || f32(w.ln2g, 0, d);
+            if (t == "ffn_gate.weight") return need(F * d) || upload_row_slice(g, w.wg, host, d, r * Fl, Fl);
+            if (t == "ffn_gate.bias") return need(F) || f32(w.bg, r * Fl, Fl);
+            if (t.compare(0, 2, "ln") == 0) return fail("gpt_set_param: '%s' is not a parameter of the Qwen-like model", name);
+        }
         if (t == "ln1.gamma") return need(d) || f32(w.ln1g, 0, d);
         if (t == "ln1.beta") return need(d) || f32(w.ln1b, 0, d);
         if (t == "ln2.gamma") return need(d) || f32(w.ln2g, 0, d);
@@ -414,6 +485,7 @@ int sptorch_ext_gpt_enable_kv_cache(void* gp, int max_context) {
     if (!gp) return fail("gpt_enable_kv_cache: null model");
     Gpt* g = (Gpt*)gp;
     if (g->c.tp_size > 1) return fail("gpt_enable_kv_cache: not available with tensor parallel shards");
+    if (g->c.arch != SPT_ARCH_GPT) return fail("gpt_enable_kv_cache: the key/value cache is implemented for the GPT architecture only");
     if (max_context <= 0 || max_context > g->c.seq_len) max_context = g->c.seq_len;     // learned positions end at seq_len
     if (g->kcache) return max_context == g->cache_ctx ? 0 : fail("gpt_enable_kv_cache: cache already allocated with %d positions", g->cache_ctx);
     const size_t bytes = (size_t)g->c.n_layer * g->c.max_batch * max_context * g->d_loc * g->es;
@@ -543,8 +615,9 @@ int sptorch_ext_gpt_launches(void* gp, int batch, int T) {
     const int hd = g->c.d_model / g->c.n_head;
     const long long M = (long long)batch * T;
     const bool fused = g->c.dtype == SPT_BF16 && attention_mode() == 0 && attention_fused_supported(T, hd, 2 * g->d_loc, M, (long long)hd * M, T);
-    // embedding + per layer (LN1, QK, V^T, attention [1 fused | S, softmax, PV], Wo, LN2, up, down) + ln_f + head
-    return 1 + g->c.n_layer * (fused ? 8 : 10) + 2;
+    // embedding + per layer (LN1, QK, V^T, attention [1 fused | S, softmax, PV], Wo, LN2, up, down) + ln_f + head;
+    // the Qwen-like block adds the RoPE pass and the gate projection
+    return 1 + g->c.n_layer * ((fused ? 8 : 10) + (g->c.arch == SPT_ARCH_QWEN_LIKE ? 2 : 0)) + 2;
 }
 
 int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk) {

@@ -406,15 +406,21 @@ __global__ void __launch_bounds__(kRowThreads) embedding_sum_kernel(const T* __r
         bool ok = id >= 0 && id < vocab;
         if (!ok && lane == 0) atomicOr(status, 0x100u);
         const T* a = tok + (size_t)(ok ? id : 0) * dim;
-        const T* b = pos + (size_t)(t % Tn) * dim;
+        const T* b = pos ? pos + (size_t)(t % Tn) * dim : nullptr;      // no position table: plain gather (RoPE models)
         T* y = out + t * (size_t)dim;
         for (int c = lane; c < nvec; c += 32) {
-            VT u = VT::load_keep(a + c * N), w = VT::load_keep(b + c * N), r;
+            VT u = VT::load_keep(a + c * N), r;
+            if (b) {
+                VT w = VT::load_keep(b + c * N);
 #pragma unroll
-            for (int j = 0; j < N; j++) r.v[j] = ok ? u.v[j] + w.v[j] : 0.0f;
+                for (int j = 0; j < N; j++) r.v[j] = ok ? u.v[j] + w.v[j] : 0.0f;
+            } else {
+#pragma unroll
+                for (int j = 0; j < N; j++) r.v[j] = ok ? u.v[j] : 0.0f;
+            }
             r.store(y + c * N);
         }
-        for (int c = nvec * N + lane; c < dim; c += 32) y[c] = (T)(ok ? (float)a[c] + (float)b[c] : 0.0f);
+        for (int c = nvec * N + lane; c < dim; c += 32) y[c] = (T)(ok ? (float)a[c] + (b ? (float)b[c] : 0.0f) : 0.0f);
     }
 }
 
@@ -675,7 +681,7 @@ int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* 
                               size_t vocab, size_t dim, int dtype) {
     if (enter()) return 1;
     if (n_tokens == 0 || dim == 0) return 0;
-    if (!tok_w || !pos_w || !ids || !out) return fail("embedding_sum: null handle");
+    if (!tok_w || !ids || !out) return fail("embedding_sum: null handle");     // pos_w may be null: token rows only
     if (T == 0) return fail("embedding_sum: T == 0");
     int grid = row_grid((n_tokens + kRowThreads / 32 - 1) / (kRowThreads / 32));
     if (dtype == SPT_F32) {

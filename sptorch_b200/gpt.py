@@ -9,17 +9,20 @@ import numpy as np
 
 from . import _lib
 from .backend import BF16, F32, FfiBackend, HalError, bf16_bits_to_f32
-from .synth import gpt_param_layout
+from .synth import gpt_param_layout, qwen_param_layout
+
+ARCH_GPT, ARCH_QWEN_LIKE = 0, 1
 
 
 class GPT:
     def __init__(self, backend: FfiBackend, vocab_size: int, d_model: int, n_head: int, n_layer: int, d_ff: int,
-                 seq_len: int, dtype: int = F32, max_batch: int = 1, eps: float = 1e-5, tp_rank: int = 0, tp_size: int = 1):
+                 seq_len: int, dtype: int = F32, max_batch: int = 1, eps: float = 1e-5, tp_rank: int = 0, tp_size: int = 1,
+                 arch: int = ARCH_GPT, rope_base: float = 10000.0):
         # argument order of GPT::new (nn/src/lib.rs:1332)
         self.b = backend
         self.cfg = dict(vocab=vocab_size, d_model=d_model, n_layer=n_layer, n_head=n_head, d_ff=d_ff, seq_len=seq_len)
-        self.dtype, self.max_batch = dtype, max_batch
-        c = _lib.GptConfig(vocab_size, d_model, n_layer, n_head, d_ff, seq_len, dtype, max_batch, eps, tp_rank, tp_size)
+        self.dtype, self.max_batch, self.arch = dtype, max_batch, arch
+        c = _lib.GptConfig(vocab_size, d_model, n_layer, n_head, d_ff, seq_len, dtype, max_batch, eps, tp_rank, tp_size, arch, rope_base)
         self.h = backend.lib.sptorch_ext_gpt_create(C.byref(c))
         if not self.h:
             raise HalError("gpt_create failed: " + _lib.last_error())
@@ -37,7 +40,7 @@ class GPT:
             self.h = None
 
     def named_parameters(self):
-        return gpt_param_layout(**self.cfg)
+        return (qwen_param_layout if self.arch == ARCH_QWEN_LIKE else gpt_param_layout)(**self.cfg)
 
     def load_flat(self, flat: np.ndarray, index: dict):
         """flat f32 block + {name: (offset, shape)} as produced by synth.gpt_params."""
@@ -153,3 +156,13 @@ class GPT:
 
     def launches(self, batch: int, T: int) -> int:
         return self.b.lib.sptorch_ext_gpt_launches(self.h, batch, T)
+
+
+class QwenLikeGPT(GPT):
+    """nn::QwenLikeGPT (crates/nn/src/lib.rs:1439-1467): same constructor arguments as the reference's ``new``; RMSNorm
+    (eps 1e-6), RoPE on Q and K (base 10000), SwiGLU MLP.  ``forward_ids`` / ``forward`` as for GPT; no key/value cache."""
+
+    def __init__(self, backend: FfiBackend, vocab_size: int, d_model: int, n_head: int, n_layer: int, d_ff: int, seq_len: int,
+                 dtype: int = F32, max_batch: int = 1, eps: float = 1e-6, rope_base: float = 10000.0, tp_rank: int = 0, tp_size: int = 1):
+        super().__init__(backend, vocab_size, d_model, n_head, n_layer, d_ff, seq_len, dtype=dtype, max_batch=max_batch, eps=eps,
+                         tp_rank=tp_rank, tp_size=tp_size, arch=ARCH_QWEN_LIKE, rope_base=rope_base)

@@ -100,16 +100,35 @@ def gpt_param_layout(vocab, d_model, n_layer, n_head, d_ff, seq_len):
     return names
 
 
-def gpt_params(cfg: dict, seed: int = 0, residual_scale: bool = False, randomize_affine: bool = False):
+def qwen_param_layout(vocab, d_model, n_layer, n_head, d_ff, seq_len):
+    """[(name, shape)] of QwenLikeGPT::named_parameters (crates/nn/src/lib.rs:1483-1492, block :1157-1166)."""
+    d, F = d_model, d_ff
+    names = [("token_emb.weight", (vocab, d))]
+    for i in range(n_layer):
+        p = f"blocks.{i}."
+        names += [
+            (p + "norm1.weight", (d,)),
+            (p + "attn.wq.weight", (d, d)), (p + "attn.wk.weight", (d, d)),
+            (p + "attn.wv.weight", (d, d)), (p + "attn.wo.weight", (d, d)),
+            (p + "norm2.weight", (d,)),
+            (p + "ffn_up.weight", (F, d)), (p + "ffn_up.bias", (F,)),
+            (p + "ffn_gate.weight", (F, d)), (p + "ffn_gate.bias", (F,)),
+            (p + "ffn_down.weight", (d, F)), (p + "ffn_down.bias", (d,)),
+        ]
+    names += [("norm_f.weight", (d,)), ("lm_head.weight", (vocab, d))]
+    return names
+
+
+def gpt_params(cfg: dict, seed: int = 0, residual_scale: bool = False, randomize_affine: bool = False, arch: str = "gpt"):
     """Flat float32 parameter block + {name: (offset, shape)}.
 
     Every ``*.weight`` ~ N(0, 0.02) drawn from one stream in layout order, biases 0,
-    gamma 1, beta 0.  ``residual_scale`` multiplies attn.wo and ffn_down weights by
+    gamma (and RMSNorm weights) 1, beta 0.  ``arch="qwen"`` gives the QwenLikeGPT block instead.  ``residual_scale`` multiplies attn.wo and ffn_down weights by
     1/sqrt(2*n_layer).  ``randomize_affine`` (tests only) draws gamma/beta/biases too so
     that a wrong bias or affine path cannot hide behind zeros.
     """
-    layout = gpt_param_layout(cfg["vocab"], cfg["d_model"], cfg["n_layer"], cfg["n_head"],
-                              cfg["d_ff"], cfg["seq_len"])
+    layout = (qwen_param_layout if arch == "qwen" else gpt_param_layout)(cfg["vocab"], cfg["d_model"], cfg["n_layer"], cfg["n_head"],
+                                                                         cfg["d_ff"], cfg["seq_len"])
     total = sum(int(np.prod(s)) for _, s in layout)
     flat = np.empty(total, dtype=np.float32)
     index = {}
@@ -117,12 +136,13 @@ def gpt_params(cfg: dict, seed: int = 0, residual_scale: bool = False, randomize
     rs = 1.0 / np.sqrt(2.0 * cfg["n_layer"])
     for name, shape in layout:
         n = int(np.prod(shape))
-        if name.endswith(".weight"):
+        is_norm_scale = name.endswith(".gamma") or ".norm" in name or name.startswith("norm")     # LayerNorm gamma / RMSNorm weight: 1
+        if name.endswith(".weight") and not is_norm_scale:
             w = normal(seed, n, 0.0, 0.02, start=off)
             if residual_scale and (name.endswith("attn.wo.weight") or name.endswith("ffn_down.weight")):
                 w = (w * np.float32(rs)).astype(np.float32)
             flat[off:off + n] = w
-        elif name.endswith(".gamma"):
+        elif is_norm_scale:
             flat[off:off + n] = 1.0 + (normal(seed + 101, n, 0.0, 0.1, start=off) if randomize_affine else 0.0)
         else:  # beta / bias
             flat[off:off + n] = normal(seed + 202, n, 0.0, 0.05, start=off) if randomize_affine else 0.0

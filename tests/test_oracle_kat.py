@@ -213,3 +213,70 @@ def test_golden_fixture_matches_oracle(oracle):
     logits = oracle.gpt_forward(cfg, p, ids[:2], fast=0)
     assert np.abs(logits[:, :, :64] - g["logits_first64"]).max() < 1e-5
     assert np.array_equal(logits.argmax(-1), g["argmax"])
+
+
+def test_rope_known_answers_and_numpy_restatement(oracle):
+    # test_rope_keeps_position_zero_and_rotates_later_positions (nn/src/lib.rs:3313-3329)
+    out = oracle.rope(np.array([[[1, 2, 3, 4], [1, 0, 0, 1]]], np.float32))
+    assert np.array_equal(out[0, 0], [1, 2, 3, 4])
+    assert abs(out[0, 1, 0] - 1.0) > 1e-3 or abs(out[0, 1, 1]) > 1e-3
+    # test_rope_offset_matches_sliced_full_sequence_position (:3331-3347)
+    full = np.arange(1, 13, dtype=np.float32).reshape(1, 3, 4)
+    assert np.array_equal(oracle.rope(full)[0, 2], oracle.rope(full[:, 2:3], position_offset=2)[0, 0])
+    # the inverse rotation (the backward of the reference, :1010-1023) undoes the forward one
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, 17, 8)).astype(np.float32)
+    assert np.allclose(oracle.rope(oracle.rope(x, 10000.0, 4), 10000.0, 4, inverse=True), x, atol=1e-5)
+    # independent float64 statement of the same rotation
+    pos = np.arange(17)[None, :, None] + 4
+    theta = pos / (10000.0 ** (2 * np.arange(4)[None, None, :] / 8))
+    ev, od = x[..., 0::2].astype(np.float64), x[..., 1::2].astype(np.float64)
+    ref = np.empty_like(x, dtype=np.float64)
+    ref[..., 0::2] = ev * np.cos(theta) - od * np.sin(theta)
+    ref[..., 1::2] = ev * np.sin(theta) + od * np.cos(theta)
+    assert np.allclose(oracle.rope(x, 10000.0, 4), ref, atol=2e-6)
+    with pytest.raises(ValueError):
+        oracle.rope(np.zeros((1, 2, 3), np.float32))
+
+
+def test_qwen_like_forward_against_numpy_restatement(oracle):
+    """QwenLikeGPT::forward_ids (nn/src/lib.rs:1454-1467) at the size of the reference's own test (:3367-3376), against a float64
+    numpy statement of the same graph written independently of oracle.c."""
+    from sptorch_b200 import synth
+    cfg = dict(vocab=12, d_model=8, n_layer=2, n_head=2, d_ff=16, seq_len=6)
+    params, index = synth.gpt_params(cfg, 0, arch="qwen", randomize_affine=True)
+    P = {k: params[o:o + int(np.prod(s))].reshape(s).astype(np.float64) for k, (o, s) in index.items()}
+    ids = np.array([[0, 1, 2, 3], [11, 5, 5, 7]])
+    out, taps = oracle.qwen_forward(cfg, params, ids, want_taps=True)
+    assert out.shape == (2, 4, 12)
+    d, H, hd, T = 8, 2, 4, 4
+
+    def rms(v, w):
+        return v / np.sqrt((v * v).mean(-1, keepdims=True) + 1e-6) * w
+
+    def rope(v):                      # [T, d] token-major, head h at columns h*hd
+        v = v.reshape(T, H, hd).copy()
+        theta = np.arange(T)[:, None, None] / (10000.0 ** (2 * np.arange(hd // 2)[None, None, :] / hd))
+        ev, od = v[..., 0::2].copy(), v[..., 1::2].copy()
+        v[..., 0::2] = ev * np.cos(theta) - od * np.sin(theta)
+        v[..., 1::2] = ev * np.sin(theta) + od * np.cos(theta)
+        return v
+
+    for b in range(2):
+        x = P["token_emb.weight"][ids[b]]
+        for l in range(2):
+            p = f"blocks.{l}."
+            h = rms(x, P[p + "norm1.weight"])
+            q, k = rope(h @ P[p + "attn.wq.weight"].T), rope(h @ P[p + "attn.wk.weight"].T)
+            v = (h @ P[p + "attn.wv.weight"].T).reshape(T, H, hd)
+            sc = np.einsum("ihe,jhe->hij", q, k) / np.sqrt(hd)
+            sc = np.where(np.triu(np.ones((T, T), bool), 1)[None], -np.inf, sc)
+            pr = np.exp(sc - sc.max(-1, keepdims=True)); pr /= pr.sum(-1, keepdims=True)
+            x = x + np.einsum("hij,jhe->ihe", pr, v).reshape(T, d) @ P[p + "attn.wo.weight"].T
+            h = rms(x, P[p + "norm2.weight"])
+            up = h @ P[p + "ffn_up.weight"].T + P[p + "ffn_up.bias"]
+            g = h @ P[p + "ffn_gate.weight"].T + P[p + "ffn_gate.bias"]
+            x = x + (up * g / (1 + np.exp(-g))) @ P[p + "ffn_down.weight"].T + P[p + "ffn_down.bias"]
+            assert np.allclose(taps[b, l + 1], x, atol=1e-5)
+        logits = rms(x, P["norm_f.weight"]) @ P["lm_head.weight"].T
+        assert np.allclose(out[b], logits, atol=1e-5)
