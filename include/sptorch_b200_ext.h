@@ -196,6 +196,34 @@ typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_s
 int   sptorch_ext_gpt_enable_tp_overlap(void* gpt, int on);
 int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
 
+/* ---- on-disk weight formats of the reference (crates/serialize/src/lib.rs, safetensors.rs; crates/versioning/src/lib.rs:32-66) ----
+ * Readers are host code and work without a GPU: a file is parsed into f32 entries (F16 / BF16 widened exactly as the
+ * reference's f16_to_f32 / bf16_to_f32), then a loader checks it against the model's named parameters with the reference's
+ * strictness (magic, version, schema, count, duplicate / missing names, shape, dtype) and uploads only if every check passed. */
+#define SPT_WEIGHTS_AUTO 0          /* by content */
+#define SPT_WEIGHTS_SPTC 1          /* binary checkpoint "SPTC": save_checkpoint / load_checkpoint, serialize/src/lib.rs:34-131 */
+#define SPT_WEIGHTS_STATE_DICT 2    /* JSON state_dict "sptorch.state_dict.v1": serialize/src/lib.rs:315-328, 446-481 */
+#define SPT_WEIGHTS_SAFETENSORS 3   /* serialize/src/safetensors.rs:25-73 */
+void*        sptorch_ext_weights_open(const char* path, int format);      /* NULL on failure, reason in sptorch_ext_last_error */
+void         sptorch_ext_weights_close(void* w);
+int          sptorch_ext_weights_format(void* w);
+size_t       sptorch_ext_weights_count(void* w);
+const char*  sptorch_ext_weights_name(void* w, size_t i);                 /* "" in a binary checkpoint, which stores no names */
+const char*  sptorch_ext_weights_dtype(void* w, size_t i);                /* dtype as stored: "F32", "F16", "BF16" */
+size_t       sptorch_ext_weights_ndim(void* w, size_t i);
+size_t       sptorch_ext_weights_dim(void* w, size_t i, size_t k);
+size_t       sptorch_ext_weights_numel(void* w, size_t i);
+const float* sptorch_ext_weights_data(void* w, size_t i);
+/* named parameters of the model in the reference's order (GPT::named_parameters nn/src/lib.rs:1382-1392, QwenLikeGPT :1483-1492) */
+size_t       sptorch_ext_gpt_param_count(void* gpt);
+int          sptorch_ext_gpt_param_info(void* gpt, size_t i, char* name, size_t name_cap, size_t* dims, size_t* ndim /* in: capacity, out: rank */);
+/* binary checkpoint: by position (load_checkpoint); state_dict: by name (load_state_dict, serialize/src/lib.rs:237-313);
+ * safetensors: n_map pairs {model parameter name, name in the file} as SafeTensorsFile::load_into (safetensors.rs:85-116),
+ * or mapping NULL / n_map 0: every model parameter under its own name */
+int          sptorch_ext_gpt_load_weights(void* gpt, void* w, const char* const* mapping, size_t n_map);
+/* JSON state_dict plus "<path>.manifest.json" (load_state_dict_bundle, serialize/src/lib.rs:366-441) */
+int          sptorch_ext_gpt_load_bundle(void* gpt, const char* weights_path);
+
 /* ---- NCCL over NVLink (replaces the gRPC star all-reduce of crates/distributed/src/coordinator.rs:73-116) ---- */
 int sptorch_ext_nccl_unique_id(const char* libnccl_path, void* id128);                      /* rank 0: 128-byte id */
 int sptorch_ext_nccl_init(const char* libnccl_path, const void* id128, int rank, int world);

@@ -105,6 +105,20 @@ EXT_SYMBOLS = {
     "sptorch_ext_attention_last_token": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_launches": (_i, [_vp, _i, _i]),
     "sptorch_ext_gpt_enable_tp_overlap": (_i, [_vp, _i]),
+    "sptorch_ext_weights_open": (_vp, [C.c_char_p, _i]),
+    "sptorch_ext_weights_close": (None, [_vp]),
+    "sptorch_ext_weights_format": (_i, [_vp]),
+    "sptorch_ext_weights_count": (_sz, [_vp]),
+    "sptorch_ext_weights_name": (C.c_char_p, [_vp, _sz]),
+    "sptorch_ext_weights_dtype": (C.c_char_p, [_vp, _sz]),
+    "sptorch_ext_weights_ndim": (_sz, [_vp, _sz]),
+    "sptorch_ext_weights_dim": (_sz, [_vp, _sz, _sz]),
+    "sptorch_ext_weights_numel": (_sz, [_vp, _sz]),
+    "sptorch_ext_weights_data": (C.POINTER(C.c_float), [_vp, _sz]),
+    "sptorch_ext_gpt_param_count": (_sz, [_vp]),
+    "sptorch_ext_gpt_param_info": (_i, [_vp, _sz, C.c_char_p, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
+    "sptorch_ext_gpt_load_weights": (_i, [_vp, _vp, C.POINTER(C.c_char_p), _sz]),
+    "sptorch_ext_gpt_load_bundle": (_i, [_vp, C.c_char_p]),
     "sptorch_ext_gpt_set_allreduce": (_i, [_vp, ALLREDUCE_FN, _vp]),
     "sptorch_ext_nccl_unique_id": (_i, [C.c_char_p, _vp]),
     "sptorch_ext_nccl_init": (_i, [C.c_char_p, _vp, _i, _i]),

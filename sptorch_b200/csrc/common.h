@@ -38,6 +38,8 @@ Runtime& rt();
 
 // Records msg as the thread's and the process's last error, marks the sticky flag, returns 1.
 int fail(const char* fmt, ...);
+// Same, for host-only work (file parsing): nothing was submitted to the device, so the sticky flag stays clear.
+int fail_host(const char* fmt, ...);
 // Makes the runtime's device current for the calling thread; non-zero if the library is not initialised.
 int enter();
 // Waits for the library stream without consuming the sticky error flag (internal uploads use this).

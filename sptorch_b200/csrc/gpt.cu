@@ -308,6 +308,32 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
     return 0;
 }
 
+// GPT::named_parameters (nn/src/lib.rs:1382-1392) / QwenLikeGPT::named_parameters (:1483-1492) with the full (unsharded) shapes
+struct ParamInfo { std::string name; std::vector<size_t> shape; };
+std::vector<ParamInfo> gpt_param_table(void* gp) {
+    const sptorch_gpt_config& c = ((Gpt*)gp)->c;
+    const size_t d = c.d_model, V = c.vocab, S = c.seq_len, F = c.d_ff;
+    const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;
+    std::vector<ParamInfo> t;
+    t.push_back({"token_emb.weight", {V, d}});
+    if (!qwen) t.push_back({"pos_emb.weight", {S, d}});
+    for (int l = 0; l < c.n_layer; l++) {
+        const std::string p = "blocks." + std::to_string(l) + ".";
+        if (qwen) t.push_back({p + "norm1.weight", {d}});
+        else { t.push_back({p + "ln1.gamma", {d}}); t.push_back({p + "ln1.beta", {d}}); }
+        for (const char* w : {"attn.wq.weight", "attn.wk.weight", "attn.wv.weight", "attn.wo.weight"}) t.push_back({p + w, {d, d}});
+        if (qwen) t.push_back({p + "norm2.weight", {d}});
+        else { t.push_back({p + "ln2.gamma", {d}}); t.push_back({p + "ln2.beta", {d}}); }
+        t.push_back({p + "ffn_up.weight", {F, d}}); t.push_back({p + "ffn_up.bias", {F}});
+        if (qwen) { t.push_back({p + "ffn_gate.weight", {F, d}}); t.push_back({p + "ffn_gate.bias", {F}}); }
+        t.push_back({p + "ffn_down.weight", {d, F}}); t.push_back({p + "ffn_down.bias", {d}});
+    }
+    if (qwen) t.push_back({"norm_f.weight", {d}});
+    else { t.push_back({"ln_f.gamma", {d}}); t.push_back({"ln_f.beta", {d}}); }
+    t.push_back({"lm_head.weight", {V, d}});
+    return t;
+}
+
 }  // namespace spt
 
 using namespace spt;

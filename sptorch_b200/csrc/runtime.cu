@@ -63,6 +63,14 @@ int fail(const char* fmt, ...) {
     return 1;
 }
 
+int fail_host(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
 int enter() {
     if (g_rt.refcount <= 0 || g_rt.device < 0) {
         snprintf(tl_error, sizeof(tl_error), "sptorch_b200: backend not initialised");
