@@ -35,7 +35,7 @@ constexpr int kStages = 4;
 constexpr int kStagesPair = 6;               // pair kernel: a stage is 32 KB per CTA instead of 48 KB
 constexpr int kGemmThreads = 320;           // producer warp + MMA warp + 8 epilogue warps
 constexpr int kEpiThreads = 256;
-constexpr int kGroupM = 8;                   // m-tiles per rasterisation band (L2 reuse of the B tiles)
+constexpr int kGroupM = 8;                   // default m-tiles per rasterisation band (L2 reuse of the B tiles)
 
 struct GemmParams {
     void* C; const float* bias; const void* R;
@@ -50,6 +50,7 @@ struct GemmParams {
     int causal_lower;
     int causal_k;
     int b_broadcast;
+    int group_m;        // m-tiles per rasterisation band
     int tma_store;      // 1: C is written through the tensor map tmC; 0: element-wise stores
     int r_vec;          // 1: residual rows can be read with 16-byte loads
     uint32_t* status;
@@ -86,14 +87,14 @@ __device__ __forceinline__ float silu_fast(float g) {
 }
 
 // tile index -> (batch z, m-tile, n-tile): bands of kGroupM m-tiles, n outer / m inner inside a band
-__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int& z, int& tm, int& tn) {
+__device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int group_m, int& z, int& tm, int& tn) {
     int per_batch = tiles_m * tiles_n;
     z = t / per_batch;
     int r = t - z * per_batch;
-    int band = r / (kGroupM * tiles_n);
-    int first_m = band * kGroupM;
-    int rows_in_band = min(kGroupM, tiles_m - first_m);
-    int q = r - band * (kGroupM * tiles_n);
+    int band = r / (group_m * tiles_n);
+    int first_m = band * group_m;
+    int rows_in_band = min(group_m, tiles_m - first_m);
+    int q = r - band * (group_m * tiles_n);
     tn = q / rows_in_band;
     tm = first_m + (q - tn * rows_in_band);
 }
@@ -174,7 +175,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         bool ok = true;
         for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
-            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            decode_tile(t, p.tiles_m, p.tiles_n, p.group_m, z, tm, tn);
             const int m0 = tm * TM + (int)rank * BM, n0 = tn * BN;
             if constexpr (!PAIR) { if (p.causal_lower && n0 > m0 + BM - 1) continue; }
             const int z1 = z % p.nb1, z2 = z / p.nb1;
@@ -206,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         bool ok = rank == 0;                 // the odd CTA of a pair issues nothing: its tiles are driven from the even CTA
         for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
-            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            decode_tile(t, p.tiles_m, p.tiles_n, p.group_m, z, tm, tn);
             if constexpr (!PAIR) { if (p.causal_lower && tn * BN > tm * BM + BM - 1) continue; }
             ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaWait);
             if (!ok) break;
@@ -273,7 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         };
         for (int t = worker; t < total_tiles && ok; t += n_workers) {
             int z, tm, tn;
-            decode_tile(t, p.tiles_m, p.tiles_n, z, tm, tn);
+            decode_tile(t, p.tiles_m, p.tiles_n, p.group_m, z, tm, tn);
             const int m0 = tm * TM + (int)rank * BM, n0 = tn * BN;
             if constexpr (!PAIR) { if (p.causal_lower && n0 > m0 + BM - 1) continue; }
             const int z1 = z % p.nb1, z2 = z / p.nb1;
@@ -603,6 +604,14 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
         plan->grid = (int)(total < compute_sms() ? total : compute_sms());
         plan->smem = smem_for(bn);
     }
+    // Rasterisation band: B tiles are re-read once per band of m-tiles.  A B operand that fits L2 beside the streams stays
+    // resident whatever the band; a large one (the LM head: 77 MB of bf16 weights under 6.6 GB of output writes) is evicted
+    // between bands and came from DRAM 64 times with 8-tile bands (ncu: 5.0 GB read for 0.18 GB of operands); 64-tile bands
+    // cut the re-reads eightfold and the head GEMM from 4.85 to 4.26 ms, while small-B shapes measured 1 % slower with them.
+    {
+        const long long b_bytes = (long long)d.N * d.K * (d.mode == MM_TF32 ? 4 : 2);
+        plan->group_m = b_bytes > (48ll << 20) ? 64 : kGroupM;
+    }
     const bool tf32 = d.mode == MM_TF32;
     const int b_box = plan->pair ? bn / 2 : bn;
     if (encode_operand(&plan->tmA, d.A, tf32, d.K, d.M, d.lda, d.nb1, d.nb2, d.sA1, d.sA2, BM)) return 1;
@@ -630,6 +639,7 @@ int gemm_run(const GemmPlan& pl) {
     prm.nb1 = d.nb1; prm.nb2 = d.nb2; prm.sC1 = d.sC1; prm.sC2 = d.sC2;
     prm.alpha = d.alpha; prm.epilogue = d.epilogue;
     prm.tiles_m = pl.tiles_m; prm.tiles_n = pl.tiles_n;
+    prm.group_m = pl.group_m;
     prm.num_kb = ceil_div(d.K, d.mode == MM_TF32 ? 32 : 64);
     prm.causal_lower = d.causal_lower;
     prm.causal_k = d.causal_k;

@@ -33,7 +33,7 @@ struct GemmPlan {
     CUtensorMap tmA, tmB, tmC;
     bool tma_store = false;
     GemmDesc d;
-    int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0;
+    int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0, group_m = 8;
     size_t smem = 0;
     bool pair = false;       // two-CTA tiles (256 x 256, cta_group::2); grid counts CTAs, two per tile worker
     bool valid = false;
