@@ -162,6 +162,17 @@ def run_reference(args):
     return 0
 
 
+GEMM_DRAM_BYTES_PER_LAUNCH = 456.7e6
+
+
+def gemm_bytes(cfg, nseq, T):
+    """Operand, residual and output bytes of the 61 Linear launches of one bf16 forward over nseq sequences."""
+    d, F, V, L, M = cfg["d_model"], cfg["d_ff"], cfg["vocab"], cfg["n_layer"], nseq * T
+    ldl = -(-V // 64) * 64
+    per_layer = (M * d + 2 * d * d + 2 * M * d) + (d * d + M * d + M * d) + (M * d + d * d + 2 * M * d) + (M * d + F * d + M * F) + (M * F + d * F + 2 * M * d)
+    return 2.0 * (L * per_layer + M * d + V * d + M * ldl)
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     if world != args.gpus and world > 1:
@@ -290,7 +301,13 @@ def run_ours(args):
                          "timing": "CUDA events around each launch on the library stream, in a second pass of the same K steps launched eagerly "
                                    "(the first pass, which gives `value`, replays a CUDA graph and cannot be instrumented per kernel)",
                          "eager_pass_ms_per_step": ms_eager / args.steps,
-                         "algorithmic_flop_per_step_this_rank": lin_flop, "traffic": None},
+                         "algorithmic_flop_per_step_this_rank": lin_flop,
+                         # DRAM bytes per GEMM launch (read + write, mean over the 61 launches of one full-size forward at batch 64
+                         # on one GPU) from the single-pass ncu capture summarised in profiles/dram_traffic_gpt_forward_c4.md;
+                         # it scales with the sequences a rank holds, so it is given for the 1-GPU shard only
+                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if nseq == GB else None,
+                         "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
+                         "algorithmic_bytes_per_launch": gemm_bytes(cfg, nseq, T) / max(lin_launches, 1)},
             "breakdown": breakdown,
             "whole_forward": {"algorithmic_tflop_per_step": (lin_flop + attn_flop) * world / 1e12,
                               "achieved_tflops_per_gpu": (lin_flop + attn_flop) / (ms / args.steps * 1e-3) / 1e12},
