@@ -170,3 +170,50 @@ def test_ragged_sequence_lengths_vs_oracle(backend, oracle, dtype, T):
     assert out.shape == (3, T, 200)
     assert relerr(out, oracle.gpt_forward(cfg, params, ids)) <= TOL[dtype]
     m.close()
+
+
+def test_full_size_config4_properties(backend):
+    """BASELINE config 4 at full size (163 M parameters, 64 x 1024 tokens, bf16), where no CPU oracle finishes in seconds:
+    size-independent properties of the reference's forward.  (1) a sequence's logits do not depend on what else is in the
+    batch (the reference has no batch dimension at all); (2) causality: logits before position p do not depend on the token at
+    p (crates/nn/src/lib.rs:3749-3766 checks the same self-consistency on a small model); (3) the logits are finite and the
+    graph-replayed step equals the eager one.  All comparisons are bit for bit."""
+    cfg = synth.CONFIGS["c4_gpt2s"]
+    params, index = synth.gpt_params(cfg, 0, residual_scale=True)
+    B, T, V = cfg["batch"], cfg["ctx"], cfg["vocab"]
+    m = GPT(backend, V, cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16, max_batch=B)
+    m.load_flat(params, index)
+    del params
+    ids = synth.randint(1, B * T, V).reshape(B, T).astype(np.int32)
+    ld = m.ldl
+
+    def rows_of(d_log, seq, n_seq=1):
+        raw = np.empty(n_seq * T * ld, dtype=np.uint16)
+        backend._check(backend.lib.sptorch_ext_copy_d2h_bytes(d_log.handle + seq * T * ld * 2, raw.ctypes.data, raw.nbytes), "d2h")
+        backend.synchronize()
+        return raw.reshape(n_seq * T, ld)[:, :V]
+
+    d_log = m.logits_buffer(B * T)
+    d_ids = m.stage_ids(ids)
+    runs = []
+    for _ in range(3):                                   # eager, captured, replayed
+        m.forward_device(d_ids, B, T, d_log)
+        runs.append(rows_of(d_log, 5).copy())
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    in_batch = {s: rows_of(d_log, s).copy() for s in (0, 5, 63)}
+    from sptorch_b200.backend import bf16_bits_to_f32
+    assert np.isfinite(bf16_bits_to_f32(in_batch[5].ravel())).all()
+    # (1) alone == inside the batch
+    for s in (0, 5, 63):
+        d1 = m.stage_ids(ids[s:s + 1])
+        m.forward_device(d1, 1, T, d_log)
+        assert np.array_equal(rows_of(d_log, 0), in_batch[s]), f"sequence {s}"
+    # (2) causality at full length
+    p = 700
+    changed = ids[5:6].copy()
+    changed[0, p] = (changed[0, p] + 1) % V
+    m.forward_device(m.stage_ids(changed), 1, T, d_log)
+    after = rows_of(d_log, 0)
+    assert np.array_equal(after[:p], in_batch[5][:p])
+    assert not np.array_equal(after[p], in_batch[5][p])
+    m.close()
