@@ -196,6 +196,19 @@ typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_s
 int   sptorch_ext_gpt_enable_tp_overlap(void* gpt, int on);
 int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
 
+/* ---- the step after the forward: sampling candidates (nn/src/lib.rs:2381-2418) ----
+ * One row of logits on the device (f32 or bf16, at least vocab_size values) -> candidates on the host in the reference's
+ * order: repetition penalty (history tokens: negative values multiplied, others divided by max(penalty, 1)) and division by
+ * max(temperature, 1e-8), non-finite values dropped, stable sort by value descending, top_k cut (0 = none), softmax, top_p cut
+ * on the running sum (clamped to [0, 1], at least one candidate stays), softmax over the kept ones.  out_logits are the
+ * scaled values the reference stores in TokenCandidate::logit.  The call synchronises; *count candidates are written
+ * (an error if they exceed capacity; vocab_size always suffices). */
+int       sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
+                                          float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
+                                          int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count);
+/* sample_from_candidates (nn/src/lib.rs:2420-2429) for the caller's uniform draw `threshold` in [0, 1); -1 without candidates */
+long long sptorch_ext_sample_from_candidates(const int32_t* ids, const float* probs, size_t count, float threshold);
+
 /* ---- on-disk weight formats of the reference (crates/serialize/src/lib.rs, safetensors.rs; crates/versioning/src/lib.rs:32-66) ----
  * Readers are host code and work without a GPU: a file is parsed into f32 entries (F16 / BF16 widened exactly as the
  * reference's f16_to_f32 / bf16_to_f32), then a loader checks it against the model's named parameters with the reference's

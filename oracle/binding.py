@@ -46,6 +46,7 @@ def lib():
         L.orc_cross_entropy.restype = C.c_float
         L.orc_gpt_param_count.restype = _sz
         L.orc_gpt_param_count.argtypes = [C.POINTER(GptConfig)]
+        L.orc_sampling_candidates.restype = C.c_long
         L.orc_qwen_param_count.restype = _sz
         L.orc_qwen_param_count.argtypes = [C.POINTER(GptConfig)]
     return _lib
@@ -275,3 +276,17 @@ def qwen_forward(cfg: dict, params: np.ndarray, ids: np.ndarray, fast=0, threads
     if rc != 0:
         raise IndexError(f"oracle qwen forward failed rc={rc}")
     return (logits, taps) if want_taps else logits
+
+
+def sampling_candidates(logits, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, history=()):
+    """sampling_candidates (crates/nn/src/lib.rs:2381-2418) -> (ids int64, scaled logits, probabilities)."""
+    x = _f32(logits).ravel()
+    V = x.size if vocab_size is None else vocab_size
+    h = np.ascontiguousarray(history, dtype=np.int64)
+    ids = np.empty(max(V, 1), np.int64); lg = np.empty(max(V, 1), np.float32); pr = np.empty(max(V, 1), np.float32)
+    n = lib().orc_sampling_candidates(_p(x), _sz(x.size), _sz(V), C.c_float(temperature), _sz(top_k), C.c_float(top_p),
+                                      C.c_float(repetition_penalty), h.ctypes.data_as(_i64), _sz(h.size),
+                                      ids.ctypes.data_as(_i64), _p(lg), _p(pr))
+    if n < 0:
+        raise ValueError("vocab_size must not exceed logits length")
+    return ids[:n].copy(), lg[:n].copy(), pr[:n].copy()

@@ -521,6 +521,63 @@ int orc_qwen_forward_batch(const orc_gpt_config* c, float rope_base, const float
     return rc;
 }
 
+/* sampling_candidates: crates/nn/src/lib.rs:2381-2418 (penalize_repeated_logit :2343-2352, normalize_candidates :2354-2374).
+ * out_* hold up to vocab_size entries; returns the number of candidates, or -1 if vocab_size exceeds n_logits (the
+ * reference asserts).  The sort is a stable merge sort, as Rust's sort_by. */
+typedef struct { int64_t id; float v; } orc_cand;
+static void cand_merge_sort(orc_cand* a, orc_cand* tmp, size_t n) {
+    if (n < 2) return;
+    size_t h = n / 2;
+    cand_merge_sort(a, tmp, h);
+    cand_merge_sort(a + h, tmp, n - h);
+    size_t i = 0, j = h, k = 0;
+    while (i < h && j < n) tmp[k++] = (a[j].v > a[i].v) ? a[j++] : a[i++];      /* descending; equal values keep their order */
+    while (i < h) tmp[k++] = a[i++];
+    while (j < n) tmp[k++] = a[j++];
+    memcpy(a, tmp, n * sizeof(orc_cand));
+}
+static void cand_normalize(const orc_cand* c, size_t n, float* probs) {
+    if (n == 0) return;
+    float mx = -INFINITY;
+    for (size_t i = 0; i < n; i++) mx = fmaxf(mx, c[i].v);
+    float sum = 0.0f;
+    for (size_t i = 0; i < n; i++) { probs[i] = expf(c[i].v - mx); sum += probs[i]; }
+    for (size_t i = 0; i < n; i++) probs[i] = probs[i] / sum;
+}
+long orc_sampling_candidates(const float* logits, size_t n_logits, size_t vocab_size, float temperature, size_t top_k, float top_p,
+                             float repetition_penalty, const int64_t* history, size_t n_history,
+                             int64_t* out_ids, float* out_logits, float* out_probs) {
+    if (vocab_size > n_logits) return -1;
+    float temp = fmaxf(temperature, 1e-8f);
+    float penalty = fmaxf(repetition_penalty, 1.0f);
+    orc_cand* c = (orc_cand*)malloc((vocab_size + 1) * sizeof(orc_cand));
+    orc_cand* tmp = (orc_cand*)malloc((vocab_size + 1) * sizeof(orc_cand));
+    size_t n = 0;
+    for (size_t t = 0; t < vocab_size; t++) {
+        float x = logits[t];
+        int seen = 0;
+        for (size_t h = 0; h < n_history && !seen; h++) seen = history[h] == (int64_t)t;
+        if (penalty != 1.0f && seen) x = signbit(x) ? x * penalty : x / penalty;
+        x = x / temp;
+        if (isfinite(x)) { c[n].id = (int64_t)t; c[n].v = x; n++; }
+    }
+    cand_merge_sort(c, tmp, n);
+    if (top_k > 0 && n > top_k) n = top_k;
+    cand_normalize(c, n, out_probs);
+    float p = top_p < 0.0f ? 0.0f : (top_p > 1.0f ? 1.0f : top_p);
+    if (top_p != top_p) p = 0.0f;        /* clamp of a NaN is not reachable from the reference's configs; treated as 0 */
+    if (!(p >= 1.0f) && n > 1) {
+        float cum = 0.0f;
+        size_t kept = 0;
+        for (size_t i = 0; i < n; i++) { cum += out_probs[i]; kept = i + 1; if (cum >= p) break; }
+        n = kept;
+        cand_normalize(c, n, out_probs);
+    }
+    for (size_t i = 0; i < n; i++) { out_ids[i] = c[i].id; out_logits[i] = c[i].v; }
+    free(c); free(tmp);
+    return (long)n;
+}
+
 int orc_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -412,6 +412,31 @@ class FfiBackend:
             for b in (dt, dp, di, do):
                 b.free()
 
+    def sampling_candidates(self, logits, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, history=(),
+                            dtype=F32):
+        """sampling_candidates (crates/nn/src/lib.rs:2381-2418): one row of logits -> (token ids, scaled logits, probabilities)
+        in the reference's candidate order.  ``logits`` may be a host array (uploaded here) or a DeviceBuffer."""
+        own = not isinstance(logits, DeviceBuffer)
+        d = (self.upload_bf16(_f32(logits).ravel()) if dtype == BF16 else self.upload(_f32(logits).ravel())) if own else logits
+        V = d.n if vocab_size is None else vocab_size
+        h = np.ascontiguousarray(history, dtype=np.int64)
+        cap = max(V, 1)
+        ids, lg, pr = np.empty(cap, np.int32), np.empty(cap, np.float32), np.empty(cap, np.float32)
+        n = C.c_size_t(0)
+        try:
+            self._check(self.lib.sptorch_ext_sampling_candidates(d.handle, d.n, dtype, V, C.c_float(temperature), top_k, C.c_float(top_p),
+                                                                 C.c_float(repetition_penalty), h.ctypes.data, h.size,
+                                                                 ids.ctypes.data, lg.ctypes.data, pr.ctypes.data, cap, C.byref(n)), "sampling_candidates")
+        finally:
+            if own:
+                d.free()
+        return ids[:n.value].copy(), lg[:n.value].copy(), pr[:n.value].copy()
+
+    def sample_from_candidates(self, ids, probs, threshold: float) -> int:
+        """sample_from_candidates (nn/src/lib.rs:2420-2429) for a uniform draw ``threshold`` in [0, 1)."""
+        ids = np.ascontiguousarray(ids, np.int32); probs = np.ascontiguousarray(probs, np.float32)
+        return int(self.lib.sptorch_ext_sample_from_candidates(ids.ctypes.data, probs.ctypes.data, ids.size, C.c_float(threshold)))
+
     def rope(self, x, rope_base=10000.0, position_offset=0, dtype=F32):
         """rotary_position_embedding_with_offset (crates/nn/src/lib.rs:975-983): x [n_head, seq_len, head_dim] as in the reference;
         the device kernel works on the token-major layout, so the permutes happen here on the host."""

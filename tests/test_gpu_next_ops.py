@@ -73,3 +73,44 @@ def test_cross_entropy_bad_target_is_an_error_not_a_fault(backend):
         backend.cross_entropy_loss(np.zeros((2, 3), np.float32), [0, 3])
     backend.synchronize()
     assert abs(backend.cross_entropy_loss(np.zeros((2, 3), np.float32), [0, 1]) - np.log(3)) < 1e-5
+
+
+def test_sampling_candidates_known_answers(backend):
+    # test_sampling_candidates_apply_top_p_after_probability_sort (crates/nn/src/lib.rs:3833-3845)
+    ids, lg, pr = backend.sampling_candidates([3.0, 2.0, 1.0, 0.0], top_p=0.75)
+    assert list(ids) == [0, 1] and abs(pr.sum() - 1.0) < 1e-6
+    # test_sampling_candidates_repetition_penalty_can_suppress_seen_token (:3847-3858)
+    ids, lg, pr = backend.sampling_candidates([3.0, 2.5, 1.0], repetition_penalty=3.0, top_k=1, history=[0])
+    assert len(ids) == 1 and ids[0] == 1
+    ids, lg, pr = backend.sampling_candidates([1.0, 2.0, 2.0, -np.inf, np.nan, 2.0])
+    assert list(ids) == [1, 2, 5, 0]                                  # ties in token order, non-finite values dropped
+    ids, lg, pr = backend.sampling_candidates([-1.0, -1.5], repetition_penalty=2.0, history=[0])
+    assert list(ids) == [1, 0] and list(lg) == [-1.5, -2.0]           # a negative logit is multiplied by the penalty
+    assert len(backend.sampling_candidates([0.3, 0.2, 0.1], top_p=0.0)[0]) == 1
+    assert len(backend.sampling_candidates([np.inf, np.nan])[0]) == 0
+    with pytest.raises(HalError):
+        backend.sampling_candidates([1.0, 2.0], vocab_size=3)         # the reference asserts vocab_size <= logits length
+    # sample_from_candidates (:2420-2429)
+    assert backend.sample_from_candidates([7, 8, 9], [0.5, 0.3, 0.2], 0.49) == 7
+    assert backend.sample_from_candidates([7, 8, 9], [0.5, 0.3, 0.2], 0.51) == 8
+    assert backend.sample_from_candidates([7, 8, 9], [0.5, 0.3, 0.1], 0.99) == 9     # falls off the end: the last candidate
+    assert backend.sample_from_candidates([], [], 0.5) == -1
+
+
+@pytest.mark.parametrize("V,k,p,t,rp", [(50, 0, 1.0, 1.0, 1.0), (300, 40, 0.9, 0.7, 1.3), (1000, 0, 0.5, 1.5, 2.0), (257, 5, 0.3, 0.2, 1.0),
+                                        (50257, 50, 0.95, 0.8, 1.2), (50257, 0, 0.9, 1.0, 1.1), (50257, 0, 1.0, 1.0, 1.0), (50304, 1, 1.0, 1e-9, 1.0)])
+def test_sampling_candidates_vs_oracle(backend, oracle, V, k, p, t, rp):
+    rng = np.random.default_rng(V + k)
+    x = (rng.standard_normal(V) * 3).astype(np.float32)
+    x[rng.integers(0, V, 3)] = -np.inf                               # constraint-masked tokens (filtered_step_logits, :2465-2480)
+    hist = rng.integers(0, V, 64)
+    want = oracle.sampling_candidates(x, temperature=t, top_k=k, top_p=p, repetition_penalty=rp, history=hist)
+    got = backend.sampling_candidates(x, temperature=t, top_k=k, top_p=p, repetition_penalty=rp, history=hist)
+    assert np.array_equal(got[0], want[0])                            # same candidates in the same order
+    assert np.array_equal(got[1], want[1])                            # scaled logits: the same f32 operations
+    assert np.allclose(got[2], want[2], rtol=2e-6, atol=1e-9)         # expf differs by an ulp between host and device
+    # bf16 logits of the LM head: same candidates as the oracle on the widened row
+    xb = _bf16(np.where(np.isfinite(x), x, 0.0)).ravel()
+    want = oracle.sampling_candidates(xb, temperature=t, top_k=k, top_p=1.0, repetition_penalty=rp, history=hist)
+    got = backend.sampling_candidates(xb, temperature=t, top_k=k, top_p=1.0, repetition_penalty=rp, history=hist, dtype=BF16)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])

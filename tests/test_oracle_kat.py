@@ -280,3 +280,43 @@ def test_qwen_like_forward_against_numpy_restatement(oracle):
             assert np.allclose(taps[b, l + 1], x, atol=1e-5)
         logits = rms(x, P["norm_f.weight"]) @ P["lm_head.weight"].T
         assert np.allclose(out[b], logits, atol=1e-5)
+
+
+def test_sampling_candidates_known_answers(oracle):
+    # test_sampling_candidates_apply_top_p_after_probability_sort (nn/src/lib.rs:3833-3845)
+    ids, lg, pr = oracle.sampling_candidates([3.0, 2.0, 1.0, 0.0], top_p=0.75)
+    assert list(ids) == [0, 1] and abs(pr.sum() - 1.0) < 1e-6
+    # test_sampling_candidates_repetition_penalty_can_suppress_seen_token (:3847-3858)
+    ids, lg, pr = oracle.sampling_candidates([3.0, 2.5, 1.0], repetition_penalty=3.0, top_k=1, history=[0])
+    assert len(ids) == 1 and ids[0] == 1
+    # edge cases the function defines: ties keep token order, non-finite logits drop out, a negative logit is multiplied,
+    # temperature is floored, top_p 0 still keeps one candidate, an empty candidate set is possible
+    ids, lg, pr = oracle.sampling_candidates([1.0, 2.0, 2.0, -np.inf, np.nan, 2.0])
+    assert list(ids) == [1, 2, 5, 0]
+    ids, lg, pr = oracle.sampling_candidates([-1.0, -1.5], repetition_penalty=2.0, history=[0])
+    assert list(ids) == [1, 0] and list(lg) == [-1.5, -2.0]
+    ids, lg, pr = oracle.sampling_candidates([1.0, 0.0], temperature=0.0)
+    assert lg[0] == np.float32(1.0) / np.float32(1e-8) and pr[0] == 1.0
+    assert len(oracle.sampling_candidates([0.3, 0.2, 0.1], top_p=0.0)[0]) == 1
+    assert len(oracle.sampling_candidates([np.inf, np.nan])[0]) == 0
+    with pytest.raises(ValueError):
+        oracle.sampling_candidates([1.0, 2.0], vocab_size=3)
+    # independent numpy statement on random rows
+    rng = np.random.default_rng(4)
+    for V, k, p, t, rp in [(50, 0, 1.0, 1.0, 1.0), (300, 40, 0.9, 0.7, 1.3), (1000, 0, 0.5, 1.5, 2.0), (257, 5, 0.3, 0.2, 1.0)]:
+        x = (rng.standard_normal(V) * 3).astype(np.float32)
+        hist = rng.integers(0, V, 20)
+        ids, lg, pr = oracle.sampling_candidates(x, temperature=t, top_k=k, top_p=p, repetition_penalty=rp, history=hist)
+        y = x.copy()
+        seen = np.zeros(V, bool); seen[hist] = True
+        if rp != 1.0:
+            y = np.where(seen, np.where(np.signbit(y), y * np.float32(rp), y / np.float32(rp)), y).astype(np.float32)
+        y = (y / np.float32(t)).astype(np.float32)
+        order = np.argsort(-y, kind="stable")
+        if k:
+            order = order[:k]
+        e = np.exp((y[order] - y[order].max()).astype(np.float64)); q = e / e.sum()
+        if p < 1.0:
+            n = int(np.searchsorted(np.cumsum(q), p - 1e-9) + 1)
+            order = order[:n]; e = e[:n]; q = e / e.sum()
+        assert list(ids) == list(order) and np.array_equal(lg, y[order]) and np.allclose(pr, q, atol=1e-6)
