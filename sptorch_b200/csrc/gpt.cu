@@ -214,6 +214,24 @@ static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
         if (rms_launch(x, w.ln1g, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
         if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
         { ProfScope ps(PROF_OTHER); if (rope_launch(g->qk, M, T, 2 * Hl, hd, 2 * dl, c.rope_base, 0, dt)) return 1; }
+        if (g->fill_cache) {
+            // prefill (project_kv_cache_with_offset, nn/src/lib.rs:672-683): the ROTATED keys and the values of every position go to
+            // the cache rows [sequence][position][dl]; keys are copied out of the [q|k] buffer, values come from one more projection
+            const size_t es_ = g->es;
+            const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es_;
+            for (int b = 0; b < B; b++)
+                SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)g->kcache + lay + (size_t)b * g->cache_ctx * dl * es_, (size_t)dl * es_,
+                                           (const uint8_t*)g->qk + ((size_t)b * T * 2 * dl + dl) * es_, (size_t)2 * dl * es_,
+                                           (size_t)dl * es_, (size_t)T, cudaMemcpyDeviceToDevice, rt().stream));
+            GemmDesc vd;
+            vd.A = g->h; vd.B = w.wv; vd.C = (uint8_t*)g->vcache + lay;
+            vd.M = T; vd.N = dl; vd.K = d; vd.lda = d; vd.ldb = d; vd.ldc = dl;
+            vd.nb1 = 1; vd.nb2 = B; vd.sA2 = (long long)T * d; vd.b_broadcast = 1; vd.sC2 = (long long)g->cache_ctx * dl;
+            vd.mode = dt == SPT_BF16 ? MM_BF16 : MM_TF32; vd.out_dtype = dt;
+            GemmPlan pv;
+            if (gemm_plan(vd, &pv)) return 1;
+            { ProfScope ps(PROF_LINEAR); if (gemm_run(pv)) return 1; }
+        }
         if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
         if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, M, (long long)hd * M, T, g->ao, g->scores,
                                B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
@@ -511,8 +529,7 @@ int sptorch_ext_gpt_enable_kv_cache(void* gp, int max_context) {
     if (!gp) return fail("gpt_enable_kv_cache: null model");
     Gpt* g = (Gpt*)gp;
     if (g->c.tp_size > 1) return fail("gpt_enable_kv_cache: not available with tensor parallel shards");
-    if (g->c.arch != SPT_ARCH_GPT) return fail("gpt_enable_kv_cache: the key/value cache is implemented for the GPT architecture only");
-    if (max_context <= 0 || max_context > g->c.seq_len) max_context = g->c.seq_len;     // learned positions end at seq_len
+    if (max_context <= 0 || max_context > g->c.seq_len) max_context = g->c.seq_len;     // learned positions end at seq_len; forward_ids asserts it for both models
     if (g->kcache) return max_context == g->cache_ctx ? 0 : fail("gpt_enable_kv_cache: cache already allocated with %d positions", g->cache_ctx);
     const size_t bytes = (size_t)g->c.n_layer * g->c.max_batch * max_context * g->d_loc * g->es;
     g->kcache = galloc(g, bytes); g->vcache = galloc(g, bytes);
@@ -561,8 +578,13 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
     const int n = pos + 1;
     const int pos_row = pos < c.seq_len - 1 ? pos : c.seq_len - 1;            // last_pos.min(seq_len - 1), nn/src/lib.rs:1631
     const size_t es = g->es;
+    const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;     // QwenLikeBlock::forward_last_token_incremental, nn/src/lib.rs:1119-1131
+    auto norm = [&](const void* in, const float* gamma, const float* beta, void* out) {
+        return qwen ? rms_launch(in, gamma, out, (size_t)B, (size_t)d, c.eps, dt) : ln(in, gamma, beta, out, (size_t)B, (size_t)d, c.eps, dt);
+    };
     { ProfScope ps(PROF_EMBED);
-      if (sptorch_ext_embedding_sum(g->tok, (const uint8_t*)g->pos + (size_t)pos_row * d * es, last_ids, g->x, (size_t)B, 1, (size_t)c.vocab, (size_t)d, dt)) return 1; }
+      if (sptorch_ext_embedding_sum(g->tok, qwen ? nullptr : (const uint8_t*)g->pos + (size_t)pos_row * d * es, last_ids, g->x, (size_t)B, 1,
+                                    (size_t)c.vocab, (size_t)d, dt)) return 1; }
     void* x = g->x;
     const long long row = dl, seq = (long long)g->cache_ctx * dl;
     for (int l = 0; l < c.n_layer; l++) {
@@ -570,8 +592,10 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
         const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es;
         uint8_t* kc = (uint8_t*)g->kcache + lay;
         uint8_t* vc = (uint8_t*)g->vcache + lay;
-        if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
+        if (norm(x, w.ln1g, w.ln1b, g->h)) return 1;
         if (linear(g, g->h, w.wqk, nullptr, nullptr, g->dq, B, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;     // [q | k] of the token
+        // the query (and the key about to be cached) are rotated to the token's absolute position (nn/src/lib.rs:718-721, 678-680)
+        if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 2 * dl, c.rope_base, pos, dt)) return 1; }
         if (append) {
             if (linear(g, g->h, w.wv, nullptr, nullptr, g->dv, B, d, dl, dl, EPI_NONE)) return 1;
             // one cache row per sequence and layer
@@ -583,11 +607,14 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
         { ProfScope ps(PROF_ATTN_FUSED);
           if (attention_last_token(g->dq, 2 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, n, seq, row, dt)) return 1; }
         if (linear(g, g->ao, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
-        if (ln(x, w.ln2g, w.ln2b, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
-        if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_GELU)) return 1;
+        if (norm(x, w.ln2g, w.ln2b, g->h)) return 1;
+        if (qwen) {
+            if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_NONE)) return 1;
+            if (linear(g, g->h, w.wg, w.bg, g->f, g->f, B, d, Fl, Fl, EPI_SWIGLU)) return 1;
+        } else if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_GELU)) return 1;
         if (linear(g, g->f, w.w2, w.b2, x, x, B, Fl, d, d, EPI_NONE)) return 1;
     }
-    if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)B, (size_t)d, c.eps, dt)) return 1;
+    if (norm(x, g->lnfg, g->lnfb, g->h)) return 1;
     if (linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
     if (append) g->cached_len++;
     return 0;

@@ -160,7 +160,8 @@ class GPT:
 
 class QwenLikeGPT(GPT):
     """nn::QwenLikeGPT (crates/nn/src/lib.rs:1439-1467): same constructor arguments as the reference's ``new``; RMSNorm
-    (eps 1e-6), RoPE on Q and K (base 10000), SwiGLU MLP.  ``forward_ids`` / ``forward`` as for GPT; no key/value cache."""
+    (eps 1e-6), RoPE on Q and K (base 10000), SwiGLU MLP.  ``forward_ids`` / ``forward`` and the key/value cache calls as for GPT
+    (the cache holds the rotated keys, as project_kv_cache_with_offset stores them)."""
 
     def __init__(self, backend: FfiBackend, vocab_size: int, d_model: int, n_head: int, n_layer: int, d_ff: int, seq_len: int,
                  dtype: int = F32, max_batch: int = 1, eps: float = 1e-6, rope_base: float = 10000.0, tp_rank: int = 0, tp_size: int = 1):

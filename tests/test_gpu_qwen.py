@@ -73,8 +73,6 @@ def test_qwen_like_reference_test_shape(backend, oracle):
     assert relerr(out, oracle.qwen_forward(cfg, params, np.array([[0, 1, 2, 3]]))[0]) <= 2e-3
     with pytest.raises(HalError):
         m.set_param("pos_emb.weight", np.zeros(6 * 8, np.float32))       # no position table in this model
-    with pytest.raises(HalError):
-        m.enable_kv_cache()
     m.close()
 
 
@@ -110,4 +108,26 @@ def test_qwen_like_gpt2_small_shape_layer_slice(backend, oracle):
     ref = oracle.qwen_forward(cfg, params, ids, fast=1, threads=oracle.max_threads())
     m = _qwen(backend, cfg, BF16, 2, params, index)
     assert relerr(m.forward(ids), ref) <= 2e-2
+    m.close()
+
+
+@pytest.mark.parametrize("dtype,tol", [(F32, 2e-3), (BF16, 3e-2)])
+def test_qwen_like_incremental_decode_equals_full_forward(backend, dtype, tol):
+    """The reference's self-consistency checks for the cache path (crates/nn/src/lib.rs:3749-3830) on the RoPE model: decoding from
+    the cache equals the last row of the full forward, appending token by token equals the full forward's rows.  The cache
+    holds rotated keys (project_kv_cache_with_offset, :672-683); the query is rotated to its absolute position (:718-721)."""
+    cfg = dict(vocab=64, d_model=64, n_layer=2, n_head=2, d_ff=128, seq_len=32)
+    params, index = synth.gpt_params(cfg, 9, arch="qwen", randomize_affine=True)
+    m = _qwen(backend, cfg, dtype, 2, params, index)
+    m.enable_kv_cache()
+    ids = synth.randint(4, 2 * 24, 64).reshape(2, 24)
+    full = m.forward(ids)
+    scale = np.abs(full).max()
+    pre = m.prefill_kv_cache(ids[:, :8])
+    assert np.array_equal(pre, m.forward(ids[:, :8]))
+    assert np.abs(m.decode_logits_from_cache(ids[:, 7]) - full[:, 7]).max() <= tol * scale
+    for t in range(8, 24):
+        step = m.append_and_decode(ids[:, t])
+        assert m.cached_len() == t + 1
+        assert np.abs(step - full[:, t]).max() <= tol * scale, f"position {t}"
     m.close()
