@@ -14,6 +14,14 @@ from .synth import gpt_param_layout, qwen_param_layout
 ARCH_GPT, ARCH_QWEN_LIKE = 0, 1
 
 
+def _lib_view(backend, buf, offset_elems: int, n: int, itemsize: int):
+    """A DeviceBuffer over part of another one (not owning: freeing it is a no-op)."""
+    from .backend import DeviceBuffer
+    v = DeviceBuffer(backend, buf.handle + offset_elems * itemsize, n, itemsize)
+    v.free = lambda: None
+    return v
+
+
 class GPT:
     def __init__(self, backend: FfiBackend, vocab_size: int, d_model: int, n_head: int, n_layer: int, d_ff: int,
                  seq_len: int, dtype: int = F32, max_batch: int = 1, eps: float = 1e-5, tp_rank: int = 0, tp_size: int = 1,
@@ -30,6 +38,8 @@ class GPT:
         self.es = 2 if dtype == BF16 else 4
         self._logits = None
         self._ids = None
+        self._gen_ctx = None
+        self.kv_cache_enabled = False
 
     def close(self):
         if self.h:
@@ -117,6 +127,7 @@ class GPT:
     # -- incremental decode (PrefillCache / IncrementalDecode of the reference: nn/src/lib.rs:1540-1573, 1619-1646) --
     def enable_kv_cache(self, max_context: int = 0):
         self.b._check(self.b.lib.sptorch_ext_gpt_enable_kv_cache(self.h, max_context), "enable_kv_cache")
+        self.kv_cache_enabled = True
 
     def cached_len(self) -> int:
         return self.b.lib.sptorch_ext_gpt_cached_len(self.h)
@@ -149,6 +160,77 @@ class GPT:
         d_ids, d_log = self.stage_ids(ids), self.logits_buffer(ids.size)
         self.b._check(self.b.lib.sptorch_ext_gpt_decode(self.h, d_ids.handle, ids.size, append, d_log.handle), "gpt_decode")
         return self._read_logits(d_log, ids.size)
+
+    # -- generation (generate_with_config_inner / decode_next_token_inner, nn/src/lib.rs:2431-2464, 2526-2553) --
+    def _last_logits_device(self, context):
+        """Logits of the last token of ``context`` as a device row: from the key/value cache while the context only grew by
+        one token since the last call, otherwise by a fresh prefill (vector-aligned prefix) plus single-token appends."""
+        n = len(context)
+        vec = 8 if self.dtype == BF16 else 4
+        d_log = self.logits_buffer(max(n, 1))
+        grew_by_one = self._gen_ctx is not None and n == len(self._gen_ctx) + 1 and list(context[:-1]) == self._gen_ctx
+        if grew_by_one and self.cached_len() == n - 1:
+            d_ids = self.stage_ids(np.asarray(context[-1:]))
+            self.b._check(self.b.lib.sptorch_ext_gpt_decode(self.h, d_ids.handle, 1, 1, d_log.handle), "gpt_decode")
+        else:
+            t0 = (n // vec) * vec
+            if t0:
+                d_ids = self.stage_ids(np.asarray(context[:t0]).reshape(1, t0))
+                self.b._check(self.b.lib.sptorch_ext_gpt_prefill(self.h, d_ids.handle, 1, t0, d_log.handle), "gpt_prefill")
+                rest = context[t0:]
+                if not len(rest):      # the last row of the prefill is the row wanted: recompute it from the cache as a single row
+                    d_ids = self.stage_ids(np.asarray(context[-1:]))
+                    self.b._check(self.b.lib.sptorch_ext_gpt_decode(self.h, d_ids.handle, 1, 0, d_log.handle), "gpt_decode")
+            else:                      # shorter than one vector: a padded forward, nothing cached
+                self._gen_ctx = None
+                ids = np.zeros((1, vec), dtype=np.int64); ids[0, :n] = context
+                d_ids = self.stage_ids(ids)
+                self.forward_device(d_ids, 1, vec, d_log)
+                return _lib_view(self.b, d_log, (n - 1) * self.ldl, self.ldl, self.es)
+            for tok in context[t0:]:
+                d_ids = self.stage_ids(np.asarray([tok]))
+                self.b._check(self.b.lib.sptorch_ext_gpt_decode(self.h, d_ids.handle, 1, 1, d_log.handle), "gpt_decode")
+        self._gen_ctx = list(context)
+        return _lib_view(self.b, d_log, 0, self.ldl, self.es)
+
+    def decode_next_token(self, tokens: list, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
+                          eos_token_id=None, draw=None):
+        """One step of decode_next_token_inner (nn/src/lib.rs:2431-2464) on ``tokens`` (prompt + generated so far, extended in
+        place).  Returns (token or None, candidates (ids, logits, probs), stop_reason) with the reference's stop reasons.
+        ``draw`` supplies the uniform numbers in [0, 1) of sample_from_candidates; default: numpy's global generator."""
+        V = self.cfg["vocab"] if vocab_size is None else vocab_size
+        if V <= 0:
+            raise HalError("vocab_size must be positive")                        # the reference asserts
+        if eos_token_id is not None and tokens and tokens[-1] == eos_token_id:
+            return None, (np.zeros(0, np.int32),) * 3, "AlreadyEnded"
+        context = tokens[-self.cfg["seq_len"]:]                                  # InferenceState::context (nn/src/lib.rs:2242-2248)
+        row = self._last_logits_device(context)
+        cand = self.b.sampling_candidates(row, vocab_size=V, temperature=temperature, top_k=top_k, top_p=top_p,
+                                          repetition_penalty=repetition_penalty, history=tokens, dtype=self.dtype)
+        if not len(cand[0]):
+            return None, cand, "NoCandidates"
+        u = float(np.random.random() if draw is None else draw())
+        nxt = self.b.sample_from_candidates(cand[0], cand[2], u)
+        tokens.append(nxt)
+        return nxt, cand, ("EosToken" if nxt == eos_token_id else "NotStopped")
+
+    def generate(self, prompt, max_new_tokens: int, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
+                 eos_token_id=None, draw=None) -> list:
+        """generate_with_config (nn/src/lib.rs:2526-2553, 2584-2593): prompt + up to max_new_tokens sampled tokens; stops after an
+        end-of-sequence token or when no candidate is left; a prompt that already ends with it is returned unchanged.
+        ``top_k=1`` is the reference's greedy configuration."""
+        if not self.kv_cache_enabled:
+            self.enable_kv_cache()
+            self.kv_cache_enabled = True
+        self._gen_ctx = None
+        tokens = [int(t) for t in prompt]
+        if eos_token_id is not None and tokens and tokens[-1] == eos_token_id:
+            return tokens
+        for _ in range(max_new_tokens):
+            nxt, _, reason = self.decode_next_token(tokens, vocab_size, temperature, top_k, top_p, repetition_penalty, eos_token_id, draw)
+            if nxt is None or reason != "NotStopped":
+                break
+        return tokens
 
     def forward_host(self, ids_host_ptr: int, batch: int, T: int, logits_host_ptr: int, chunk: int):
         """Host-buffer call through the C-ABI: pinned ids in, dense logits out, copies included."""
