@@ -124,8 +124,16 @@ def cpu_baseline(cfg, T, seconds_hint=20.0):
     t0 = time.perf_counter()
     O.gpt_forward(cfg, params, ids, fast=1, threads=threads)
     dt = time.perf_counter() - t0
+    # the reference itself is single-threaded (matrixmultiply without its threading feature, no rayon): the same port on
+    # one thread, on a shorter sequence so that the leg stays bounded
+    T1 = min(T, 128)
+    t1 = time.perf_counter()
+    O.gpt_forward(cfg, params, ids[:, :T1], fast=1, threads=1)
+    dt1 = time.perf_counter() - t1
     return {"value": T / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"1 sequence of {T} tokens of the same model, rows/heads split over {threads} OpenMP threads, {dt:.1f} s"}
+            "sample": f"1 sequence of {T} tokens of the same model, rows/heads split over {threads} OpenMP threads, {dt:.1f} s",
+            "single_thread": {"value": T1 / dt1, "unit": "tokens/s", "cores": 1,
+                              "sample": f"1 sequence of {T1} tokens on one thread (how the reference itself runs), {dt1:.1f} s"}}
 
 
 def run_reference(args):
@@ -348,6 +356,71 @@ def _time_op(b, fn, iters, warmup=3):
     return statistics.median(ts), min(ts)
 
 
+def sweep_abi(args, b):
+    """The eleven ops of the reference's C-ABI through sptorch_*_f32 with HOST slices (upload, kernel, download: what the
+    reference's FfiBackend wrapper does per op, crates/hal-ffi/src/lib.rs:337-446), device-resident, and the reference's own C
+    implementation (crates/hal-ffi/mock_npu/mock_npu.c compiled in place) on one host thread."""
+    import ctypes as C
+    from oracle import binding as O
+    ref = O.ref_lib()
+    lib = b.lib
+    rng = np.random.default_rng(0)
+    sz = C.c_size_t
+    n = 1 << 24
+    x = rng.standard_normal(n).astype(np.float32); y = rng.standard_normal(n).astype(np.float32); pos = (np.abs(x) + 0.1).astype(np.float32)
+    m_, k_, n_ = 512, 512, 512
+    A = rng.standard_normal((m_, k_)).astype(np.float32); Bm = rng.standard_normal((k_, n_)).astype(np.float32)
+    bt, bm, bk, bn = 12, 256, 64, 256
+    BA = rng.standard_normal((bt, bm, bk)).astype(np.float32); BB = rng.standard_normal((bt, bk, bn)).astype(np.float32)
+    rows, cols = 8192, 1024
+    S = rng.standard_normal((rows, cols)).astype(np.float32)
+    # (symbol, inputs, output elements, argument builder from handles/pointers, algorithmic bytes or flop, unit)
+    cases = [("sptorch_add_f32", [x, y], n, lambda i, o: (i[0], i[1], o, sz(n)), 12 * n, "B"),
+             ("sptorch_mul_f32", [x, y], n, lambda i, o: (i[0], i[1], o, sz(n)), 12 * n, "B")]
+    for op, arr in (("neg", x), ("exp", x), ("log", pos), ("relu", x), ("gelu", x)):
+        cases.append((f"sptorch_{op}_f32", [arr], n, lambda i, o: (i[0], o, sz(n)), 8 * n, "B"))
+    cases += [("sptorch_scale_f32", [x], n, lambda i, o: (i[0], C.c_float(0.5), o, sz(n)), 8 * n, "B"),
+              ("sptorch_softmax_f32", [S], rows * cols, lambda i, o: (i[0], o, sz(rows), sz(cols)), 8 * rows * cols, "B"),
+              ("sptorch_matmul_f32", [A, Bm], m_ * n_, lambda i, o: (i[0], i[1], o, sz(m_), sz(k_), sz(n_)), 2 * m_ * k_ * n_, "FLOP"),
+              ("sptorch_batch_matmul_f32", [BA, BB], bt * bm * bn, lambda i, o: (i[0], i[1], o, sz(bt), sz(bm), sz(bk), sz(bn)), 2 * bt * bm * bk * bn, "FLOP")]
+    out = []
+    for name, ins, out_n, build, work, unit in cases:
+        fn = getattr(lib, name)
+        # host slices in, host slice out
+        ts = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            bufs = [b.upload(a_) for a_ in ins]
+            o = b.alloc(out_n)
+            b._check(fn(*build([u.handle for u in bufs], o.handle)), name)
+            got = o.to_host()
+            b.synchronize()
+            ts.append(time.perf_counter() - t0)
+            for u in bufs + [o]:
+                u.free()
+        host_ms = statistics.median(ts) * 1e3
+        # device-resident
+        bufs = [b.upload(a_) for a_ in ins]
+        o = b.alloc(out_n)
+        dev_ms, _ = _time_op(b, lambda: b._check(fn(*build([u.handle for u in bufs], o.handle)), name), args.iters)
+        for u in bufs + [o]:
+            u.free()
+        line = {"op": name, "elements_out": out_n, "host_slices_ms": host_ms, "device_resident_ms": dev_ms,
+                "device_rate": work / (dev_ms * 1e-3) / 1e9, "device_rate_unit": "GB/s" if unit == "B" else "GFLOP/s"}
+        if ref is not None:
+            ro = np.empty(out_n, np.float32)
+            rf = getattr(ref, name)
+            t0 = time.perf_counter()
+            rf(*build([a_.ctypes.data_as(C.c_void_p) for a_ in ins], ro.ctypes.data_as(C.c_void_p)))
+            line["reference_c_ms"] = (time.perf_counter() - t0) * 1e3
+            line["reference_c"] = "crates/hal-ffi/mock_npu/mock_npu.c, one host thread"
+            scale = max(1.0, float(np.abs(ro).max()))
+            line["max_abs_diff_vs_reference_c"] = float(np.abs(got - ro.ravel()).max() / scale)
+        out.append(line)
+        print(json.dumps(line), flush=True)
+    return out
+
+
 def run_sweep(args):
     """BASELINE config 2 (standalone Linear) and config 3 (row ops): one JSON line per case."""
     os.environ.setdefault("SPTORCH_B200_DEVICE", "0")
@@ -376,6 +449,8 @@ def run_sweep(args):
                 print(json.dumps(out[-1]), flush=True)
                 for buf in (x, w, y, bias):
                     buf.free()
+    if args.sweep == "abi":
+        sweep_abi(args, b)
     if args.sweep in ("attention", "all"):
         # causal attention core of one layer: BASELINE config 4 (12 heads x 64) and config 5 (16 heads x 128) shapes, bf16
         shapes = [(64, 1024, 12, 64), (16, 2048, 16, 128)]
@@ -529,7 +604,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=8, help="sequences per micro-batch of the host-buffer call")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
+    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "abi", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
     ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
