@@ -234,15 +234,19 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 SPT_TICK(7);
                 ok = mbar_wait(p_full + 8 * (g & 1), u2, abort_flag, p.status, kErrMmaWait);
                 SPT_TICK(2);
-                ok = ok && mbar_wait(o_free + 8 * (g & 1), u2 ^ 1, abort_flag, p.status, kErrMmaWait);
+                // the output accumulator of an item (buffer = item parity) is written for the first time: the item two back must
+                // have been read out of it
+                if (j == 0) ok = ok && mbar_wait(o_free + 8 * (it & 1), ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
                 if (!ok) break;
                 SPT_TICK(3);
                 tc_fence_after();
                 if (lane == 0) {
                     const uint64_t adesc = make_kmajor_sw128_desc(base + L::kP + (g & 1) * L::kPBytes);
                     const uint64_t bdesc = make_kmajor_sw128_desc(base + L::kKV + (g % NS) * L::kStageBytes + L::kKBytes);
+                    // O accumulates in TMEM over the key tiles of the item (the softmax warps rescale it in place when a row
+                    // maximum grows enough)
 #pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_o + (g & 1) * HD, adesc + 2 * k, bdesc + 2 * k, IDESC_O, k != 0 ? 1u : 0u);
+                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_o + (it & 1) * HD, adesc + 2 * k, bdesc + 2 * k, IDESC_O, (j | k) != 0 ? 1u : 0u);
                     mma_commit(o_full + 8 * (g & 1));
                     mma_commit(kv_empty + 8 * (g % NS));
                 }
@@ -267,31 +271,15 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         float* xmax = reinterpret_cast<float*>(smem + L::kX);
         const uint32_t pair_bar = mx_bar + 8 * quarter;
         bool ok = true;
-        uint32_t g = 0, px = 0;                                  // global step; pair exchanges done so far
-        float O[OC];
+        uint32_t g = 0, px = 0, it = 0;                          // global step; pair exchanges done so far; items done so far
         const bool pr = PROF && p.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
         unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         long long tprev = clock64();
 #define SPT_TICK(i) do { if (PROF && pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
-        // O = a * O + (P V) of global step gg
-        auto fold = [&](uint32_t gg, float a) -> bool {
-            if (!mbar_wait(o_full + 8 * (gg & 1), (gg >> 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < OC / 32; c++) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_o + lane_off + (gg & 1) * HD + ch * OC + c * 32, v);
-                tmem_ld_wait();
-                const float2 a2 = make_float2(a, a);
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float2 o2 = __ffma2_rn(make_float2(O[c * 32 + i], O[c * 32 + i + 1]), a2, make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
-                    O[c * 32 + i] = o2.x; O[c * 32 + i + 1] = o2.y;
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(o_free + 8 * (gg & 1));
-            return true;
+        // P V of global step gg has completed (its commit arrives on o_full[gg & 1]; a thread never waits for a step whose
+        // successor two steps on could already have been committed, because that commit needs this thread's own P)
+        auto pv_done = [&](uint32_t gg) -> bool {
+            return mbar_wait(o_full + 8 * (gg & 1), (gg >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
         };
         for (int k = 0, item = fetch(0); item >= 0 && ok; k++) {
             const int item_next = fetch(k + 1);
@@ -299,9 +287,8 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             decode(item, q0, bb, hh, n_kv);
             item = item_next;
             const int qrow = q0 + r;
-            float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
-#pragma unroll
-            for (int i = 0; i < OC; i++) O[i] = 0.0f;
+            float m = -INFINITY, l = 0.0f;
+            const uint32_t o_addr = tmem_o + lane_off + (it & 1) * HD + ch * OC;      // this thread's half of its output row
             for (int j = 0; j < n_kv && ok; j++, g++) {
                 const uint32_t sb = g & 1;
                 const int kcol0 = j * kKvTile + ch * 32;             // key index of this thread's first column
@@ -341,9 +328,33 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (!ok) break;
                 px++;
                 SPT_TICK(2);
-                const float m_new = fmaxf(m, fmaxf(mx, xm[(ch ^ 1) * 128 + r]));
-                const float alpha = ex2_approx((m - m_new) * p.scale_log2);       // 0 on the first tile (m = -inf)
-                const float mb = m_new * p.scale_log2;
+                // Lazy rescaling: the reference maximum of a row only moves when the new maximum exceeds it by more than 8 in the
+                // exponent (P then stays below 2^8, exact enough in bf16 and harmless in the f32 sums); the accumulated output
+                // in TMEM and the row sum are multiplied by 2^(old - new) at that moment.  Both threads of a row see the same
+                // maxima and take the same decision; tcgen05.ld / st are warp-wide, so a warp rescales when any of its rows does
+                // (the others multiply by one).
+                const float m_cand = fmaxf(m, fmaxf(mx, xm[(ch ^ 1) * 128 + r]));
+                if (j == 0) m = m_cand;
+                const bool grow = j > 0 && (m_cand - m) * p.scale_log2 > 8.0f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    float alpha = 1.0f;
+                    if (grow) { alpha = ex2_approx((m - m_cand) * p.scale_log2); m = m_cand; l *= alpha; }
+                    ok = pv_done(g - 1);                               // every product accumulated so far is in place
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < OC / 32; c++) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(o_addr + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32(o_addr + c * 32, o);
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
+                const float mb = m * p.scale_log2;
                 // the softmax warps are bound by instruction issue: scale/subtract, the row sum and the accumulator
                 // update run on pairs of floats (fma.rn.f32x2 / add.rn.f32x2), the maximum on three inputs at a time
                 float2 sum2 = make_float2(0.0f, 0.0f), sum2b = make_float2(0.0f, 0.0f);
@@ -358,7 +369,8 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h2);
                 }
                 const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
-                // P buffer sb was last read by the P V two steps back, whose completion this thread's fold already waited for
+                // P buffer sb was last read by the P V two steps back
+                if (g >= 2) { ok = pv_done(g - 2); if (!ok) break; }
                 uint8_t* prow = smem + L::kP + sb * L::kPBytes + prow_off;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
@@ -368,13 +380,9 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the MMA's async-proxy reads
                 SPT_TICK(3);
                 mbar_arrive(p_full + 8 * sb);
-                l = l * alpha + sum;
-                m = m_new;
-                if (j > 0) ok = fold(g - 1, alpha_prev);              // the previous step's product, long finished
+                l += sum;
                 SPT_TICK(4);
-                alpha_prev = alpha;
             }
-            if (ok && n_kv > 0) ok = fold(g - 1, alpha_prev);
             if (!ok) break;
             SPT_TICK(5);
             // total row sum = own half + partner's half
@@ -384,18 +392,30 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             ok = mbar_wait(pair_bar, px & 1, abort_flag, p.status, kErrEpilogueWait);
             if (!ok) break;
             px++;
-            if (qrow < p.T) {
-                const float inv = 1.0f / (l + xm[(ch ^ 1) * 128 + r]);
-                __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD + ch * OC;
+            const float inv = 1.0f / (l + xm[(ch ^ 1) * 128 + r]);
+            ok = pv_done(g - 1);                                       // the item's last product
+            if (!ok) break;
+            tc_fence_after();
+            __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD + ch * OC;
 #pragma unroll
-                for (int i = 0; i < OC; i += 8) {
-                    uint4 o;
-                    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int c = 0; c < OC / 32; c++) {
+                uint32_t o[32];
+                tmem_ld_32x32(o_addr + c * 32, o);
+                tmem_ld_wait();
+                if (qrow < p.T) {
 #pragma unroll
-                    for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(O[i + 2 * q] * inv, O[i + 2 * q + 1] * inv);
-                    *reinterpret_cast<uint4*>(orow + i) = o;
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                        for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * q]) * inv, __uint_as_float(o[i + 2 * q + 1]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                    }
                 }
             }
+            tc_fence_before();
+            mbar_arrive(o_free + 8 * (it & 1));                        // the accumulator may be overwritten by the item after next
+            it++;
             SPT_TICK(6);
         }
         if (pr) { for (int i = 0; i < 8; i++) p.prof[i] = pc[i]; }
