@@ -60,6 +60,19 @@ def test_linear_is_linear_at_full_size(backend):
     assert np.array_equal(backend.linear(x, w, mode=MM_TF32), ref)
 
 
+@pytest.mark.parametrize("M,K,N", [(1100, 512, 50304), (8320, 512, 50304), (300, 64, 1000), (4100, 64, 328)])
+def test_tile_rasterisation_covers_every_tile_exactly_once(backend, M, K, N):
+    """Integer-valued operands make every output exact, so a tile that is skipped, doubled or misplaced by the tile decode shows
+    up as a wrong integer.  Shapes: a B operand above 48 MB (64-tile bands: one ragged band, then a full band plus a ragged
+    one) and small operands (8-tile bands with ragged tails)."""
+    rng = np.random.default_rng(M + N)
+    x = rng.integers(-4, 5, (M, K)).astype(np.float32)
+    w = rng.integers(-2, 3, (N, K)).astype(np.float32)
+    ref = x @ w.T                                            # exact in f32: |sum| <= 8 * 512
+    assert np.array_equal(backend.linear(x, w, mode=MM_BF16, out_dtype=F32), ref)
+    assert np.array_equal(backend.linear(x, w, mode=MM_TF32), ref)
+
+
 @pytest.mark.parametrize("M,K,N", [(129, 64, 129), (256, 64, 256), (640, 200, 328), (1000, 768, 1000), (2048, 3072, 768), (4100, 136, 50257 // 16)])
 def test_pair_tiles_equal_single_cta_tiles(backend, oracle, M, K, N):
     """Wide problems run on CTA pairs (256 x 256 tiles, one MMA over two SMs).  Every output element is still the same
