@@ -178,4 +178,53 @@ inline std::vector<float> RawBuffer::to_host() const {
     return v;
 }
 
+// ---- key/value cache metadata (crates/hal/src/lib.rs:129-239): host-side bookkeeping only ----
+enum class DType { F32, F16, BF16 };
+inline size_t dtype_size_bytes(DType t) { return t == DType::F32 ? 4 : 2; }
+
+// One K or V buffer is [layer, position, head, dim]; `position` is a slot of the window, not an absolute token position.
+// The device model's caches use the same order per sequence ([layer][sequence][position][head * dim]).
+struct KvCacheBufferSpec {
+    DeviceId device; DType dtype; size_t n_layer, max_context, n_head, head_dim;
+    KvCacheBufferSpec(DeviceId dev, DType dt, size_t layers, size_t ctx, size_t heads, size_t hd)
+        : device(std::move(dev)), dtype(dt), n_layer(layers), max_context(ctx), n_head(heads), head_dim(hd) {
+        if (!ctx) throw HalError("max_context must be positive");
+        if (!heads) throw HalError("n_head must be positive");
+        if (!hd) throw HalError("head_dim must be positive");
+    }
+    size_t elements_per_kind() const { return n_layer * max_context * n_head * head_dim; }
+    size_t total_elements() const { return elements_per_kind() * 2; }
+    size_t total_bytes() const { return total_elements() * dtype_size_bytes(dtype); }
+    size_t element_offset(size_t layer, size_t position, size_t head, size_t dim) const {
+        if (layer >= n_layer) throw HalError("layer out of range");
+        if (position >= max_context) throw HalError("position out of range");
+        if (head >= n_head) throw HalError("head out of range");
+        if (dim >= head_dim) throw HalError("dim out of range");
+        return (((layer * max_context + position) * n_head + head) * head_dim) + dim;
+    }
+    bool operator==(const KvCacheBufferSpec& o) const {
+        return device.backend == o.device.backend && device.ordinal == o.device.ordinal && dtype == o.dtype && n_layer == o.n_layer &&
+               max_context == o.max_context && n_head == o.n_head && head_dim == o.head_dim;
+    }
+};
+
+// Which absolute positions the cached window covers (crates/hal/src/lib.rs:186-239).
+struct KvCacheWindowState {
+    size_t window_start = 0, cached_len = 0, max_context;
+    explicit KvCacheWindowState(size_t ctx) : max_context(ctx) { if (!ctx) throw HalError("max_context must be positive"); }
+    size_t next_position() const { return window_start + cached_len; }
+    bool last_position(size_t* pos) const { if (!cached_len) return false; *pos = window_start + cached_len - 1; return true; }
+    void prefill(size_t start_position, size_t len) {
+        if (len > max_context) throw HalError("prefill len cannot exceed max_context");
+        window_start = start_position; cached_len = len;
+    }
+    void append(size_t len) {
+        const size_t total = cached_len + len;
+        const size_t dropped = total > max_context ? total - max_context : 0;
+        window_start += dropped;
+        cached_len = total < max_context ? total : max_context;
+    }
+    bool operator==(const KvCacheWindowState& o) const { return window_start == o.window_start && cached_len == o.cached_len && max_context == o.max_context; }
+};
+
 }  // namespace sptorch_b200

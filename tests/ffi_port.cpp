@@ -11,7 +11,31 @@ static int failures = 0;
 #define CHECK(cond) do { if (!(cond)) { std::printf("FAIL %s:%d %s\n", __FILE__, __LINE__, #cond); failures++; } } while (0)
 static bool eq(const std::vector<float>& a, std::initializer_list<float> b) { return a == std::vector<float>(b); }
 
+// crates/hal/src/lib.rs:674-700: pure host bookkeeping, needs no backend
+static void kv_cache_metadata_tests() {
+    KvCacheBufferSpec spec(DeviceId{"cuda", 0}, DType::BF16, 2, 4, 3, 8);                 // test_kv_cache_buffer_spec_layout_and_capacity
+    CHECK(spec.elements_per_kind() == 2 * 4 * 3 * 8);
+    CHECK(spec.total_elements() == 2 * 2 * 4 * 3 * 8);
+    CHECK(spec.total_bytes() == 2 * 2 * 4 * 3 * 8 * 2);
+    CHECK(spec.element_offset(1, 2, 1, 3) == (((4 + 2) * 3 + 1) * 8) + 3);
+    bool threw = false;
+    try { spec.element_offset(2, 0, 0, 0); } catch (const HalError&) { threw = true; }
+    CHECK(threw);
+    KvCacheWindowState w(3);                                                              // test_kv_cache_window_state_prefill_and_append
+    size_t last = 99;
+    CHECK(w.next_position() == 0 && !w.last_position(&last));
+    w.prefill(5, 2);
+    CHECK(w.window_start == 5 && w.cached_len == 2 && w.last_position(&last) && last == 6 && w.next_position() == 7);
+    w.append(2);
+    CHECK(w.window_start == 6 && w.cached_len == 3 && w.last_position(&last) && last == 8 && w.next_position() == 9);
+    KvCacheWindowState v(3);                                                              // window part of test_cpu_kv_cache_buffer_tracks_capacity_and_window
+    v.prefill(10, 3); v.append(1);
+    KvCacheWindowState want(3); want.window_start = 11; want.cached_len = 3;
+    CHECK(v == want);
+}
+
 int main(int argc, char** argv) {
+    if (argc == 2 && std::string(argv[1]) == "--metadata") { kv_cache_metadata_tests(); std::printf(failures ? "FAILED %d\n" : "OK\n", failures); return failures ? 1 : 0; }
     if (argc < 2) { std::printf("usage: %s lib.so [name]\n", argv[0]); return 2; }
     std::shared_ptr<FfiBackend> be;
     try { be = FfiBackend::load(argv[1]); }

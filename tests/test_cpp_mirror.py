@@ -22,6 +22,12 @@ def _build():
     return EXE
 
 
+def test_cpp_kv_cache_metadata():
+    """KvCacheBufferSpec / KvCacheWindowState of the C++ mirror against the reference's tests (crates/hal/src/lib.rs:674-721)."""
+    r = subprocess.run([_build(), "--metadata"], capture_output=True, text=True)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout + r.stderr
+
+
 @pytest.mark.skipif(not os.path.exists(MOCK), reason="reference C backend not built")
 def test_cpp_port_passes_on_reference_backend():
     r = subprocess.run([_build(), MOCK, "mock_npu"], capture_output=True, text=True)

@@ -148,3 +148,27 @@ def test_tensor_parallel_partition_two_gloo_ranks():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert err < 1e-5
+
+
+def test_kv_cache_metadata_mirrors_the_reference():
+    # crates/hal/src/lib.rs:674-721
+    from sptorch_b200.kv_cache import KvCacheBufferSpec, KvCacheWindowState
+    spec = KvCacheBufferSpec(("cuda", 0), "BF16", 2, 4, 3, 8)
+    assert spec.elements_per_kind() == 2 * 4 * 3 * 8
+    assert spec.total_elements() == 2 * 2 * 4 * 3 * 8
+    assert spec.total_bytes() == 2 * 2 * 4 * 3 * 8 * 2
+    assert spec.element_offset(1, 2, 1, 3) == (((4 + 2) * 3 + 1) * 8) + 3
+    with pytest.raises(IndexError):
+        spec.element_offset(0, 4, 0, 0)
+    with pytest.raises(ValueError):
+        KvCacheBufferSpec(("cpu", 0), "F32", 1, 0, 2, 4)
+    w = KvCacheWindowState(3)
+    assert w.next_position() == 0 and w.last_position() is None
+    w.prefill(5, 2)
+    assert (w.window_start, w.cached_len, w.last_position(), w.next_position()) == (5, 2, 6, 7)
+    w.append(2)
+    assert (w.window_start, w.cached_len, w.last_position(), w.next_position()) == (6, 3, 8, 9)
+    v = KvCacheWindowState(3)
+    v.prefill(10, 3); v.append(1)
+    assert v == KvCacheWindowState(3, 11, 3)
+    assert KvCacheBufferSpec(("cpu", 0), "F32", 1, 3, 2, 4).total_bytes() == 2 * 1 * 3 * 2 * 4 * 4
