@@ -206,6 +206,7 @@ def run_ours(args):
     model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16, max_batch=max(nseq, 1))
     params, index = synth.gpt_params(cfg, 0, residual_scale=True)
     model.load_flat(params, index)
+    b._check(lib.sptorch_ext_gpt_enable_ln_fold(model.h, int(args.ln_fold)), "ln_fold")
     del params
     ids_all = synth.randint(1, GB * T, cfg["vocab"]).reshape(GB, T).astype(np.int32)
     ids = np.ascontiguousarray(ids_all[start:start + nseq])
@@ -609,6 +610,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
                     help="c4_gpt2s: the bench line (batch sharding); c5_1p3b / tp_check: tensor parallel over the launched ranks")
+    ap.add_argument("--ln-fold", type=int, default=0, help="1: LayerNorm folded into the GEMM epilogues instead of separate kernels")
     ap.add_argument("--tp-overlap", type=int, default=0, help="tensor parallel: overlap the all-reduces with the other half of the batch")
     ap.add_argument("--sm-reserve", type=int, default=16, help="SMs left free for NCCL when --tp-overlap is on")
     ap.add_argument("--layers", type=int, default=0, help="with --workload c5_1p3b: run fewer layers")

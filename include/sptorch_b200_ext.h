@@ -190,6 +190,10 @@ int   sptorch_ext_gpt_launches(void* gpt, int batch, int T);
 /* tensor-parallel all-reduce hook: called on the library stream's behalf after the row-split
  * projections; the callee must enqueue a sum-all-reduce of n elements at buf onto cuda_stream. */
 typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_stream, void* user);
+/* 1: bf16 GPT models apply LayerNorm inside the epilogue of the GEMMs that consume it (weights pre-multiplied by gamma, a per-token
+ * statistics pass instead of a normalising pass).  Default 0: on B200 the statistics passes save 0.57 ms per step of BASELINE
+ * config 4 and the heavier epilogues cost 0.5 ms, so the step time does not move (19.2 ms either way). */
+int   sptorch_ext_gpt_enable_ln_fold(void* gpt, int on);
 /* tensor parallel: reduce one half of the batch on a second stream while the other half computes (default off: with
  * the statically scheduled persistent GEMM the SMs given up cost as much as the overlap gains; needs an even batch;
  * combine with sptorch_ext_set_sm_reserve so that the collective finds free SMs) */

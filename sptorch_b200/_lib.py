@@ -104,6 +104,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_decode": (_i, [_vp, _vp, _i, _i, _vp]),
     "sptorch_ext_attention_last_token": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_launches": (_i, [_vp, _i, _i]),
+    "sptorch_ext_gpt_enable_ln_fold": (_i, [_vp, _i]),
     "sptorch_ext_gpt_enable_tp_overlap": (_i, [_vp, _i]),
     "sptorch_ext_sampling_candidates": (_i, [_vp, _sz, _i, _sz, _f, _sz, _f, _f, _vp, _sz, _vp, _vp, _vp, _sz, C.POINTER(_sz)]),
     "sptorch_ext_sample_from_candidates": (C.c_longlong, [_vp, _vp, _sz, _f]),

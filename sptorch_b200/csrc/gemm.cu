@@ -56,6 +56,9 @@ struct GemmParams {
     uint32_t* status;
 };
 
+// LayerNorm folded into the epilogue (see GemmDesc): a kernel argument of its own, read by the NORM variants only
+struct NormArgs { const float2* stats; const float* s; const float* c; };
+
 __device__ __forceinline__ float gelu_exact(float x) {
     const float k = 0.7978845608028654f;
     float x3 = (x * x) * x;
@@ -99,16 +102,21 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
     tm = first_m + (q - tn * rows_in_band);
 }
 
+// what an epilogue thread keeps per tile for its output row when LayerNorm is folded into the product (nothing otherwise)
+template <int NORM> struct NormRow {};
+template <> struct NormRow<1> { float2 stat; };
+template <> struct NormRow<2> { float s, c; };
+
 // PAIR: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs issued by the even CTA.  Each CTA loads its
 // own 128 rows of A and its own half (BN/2 rows) of the B tile, keeps its 128 rows of the accumulator in its own TMEM and
 // runs its own epilogue; per SM the operand traffic from L2 falls from (128 + BN) to (128 + BN/2) rows per k-block.
 // Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' loads; `empty` and `tmem_full` exist in both
 // CTAs and are signalled by two commits of the issuing thread; `tmem_empty` lives in the even CTA and collects the
 // epilogue threads of both.
-template <bool TF32, typename TOut, int BN, bool PAIR>
+template <bool TF32, typename TOut, int BN, bool PAIR, int NORM = 0>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p, const NormArgs na) {
     constexpr int NSTG = PAIR ? kStagesPair : kStages;
     constexpr int TM = PAIR ? 2 * BM : BM;             // rows of one scheduled tile
     constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of B this CTA loads
@@ -288,6 +296,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // bias slice of the tile: one value per epilogue thread, parked in shared memory after the barrier wait
             float bval = 0.0f;
             if (p.bias && eidx < BN && n0 + eidx < p.N) bval = __ldg(p.bias + n0 + eidx);
+            // folded LayerNorm: what this thread's output row needs for the whole tile
+            NormRow<NORM> nr;
+            if constexpr (NORM == 1) { nr.stat = row_ok ? __ldg(na.stats + (long long)z * p.M + row) : make_float2(1.0f, 0.0f); }
+            if constexpr (NORM == 2) { nr.s = row_ok ? __ldg(na.s + row) : 0.0f; nr.c = row_ok ? __ldg(na.c + row) : 0.0f; }
             // residual row segment of one chunk (row-per-thread layout)
             uint4 rnext[NV];
             auto fetch_residual = [&](int c) {
@@ -330,6 +342,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 for (int k = 0; k < NV; k++) rcur[k] = rnext[k];
                 tmem_ld_wait();
                 float f[32];
+                if constexpr (NORM == 1) {
+                    // y = inv[row] * acc + (c[n] - (mean inv)[row] * s[n]); c sits in the bias tile, s is read through L1 (one address per warp)
+                    const float2 inv2 = make_float2(nr.stat.x, nr.stat.x), nmi2 = make_float2(-nr.stat.y, -nr.stat.y);
+                    const float* sp = na.s + n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4*>(bt + c * 32 + j);
+                        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sp + j));       // norm_s is readable up to N rounded up to 32
+                        float2 lo = __ffma2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), inv2, __ffma2_rn(nmi2, make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
+                        float2 hi = __ffma2_rn(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), inv2, __ffma2_rn(nmi2, make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
+                        f[j] = lo.x; f[j + 1] = lo.y; f[j + 2] = hi.x; f[j + 3] = hi.y;
+                    }
+                } else if constexpr (NORM == 2) {
+                    // the normalised operand is B: statistics per output column, s / c per output row (this thread's row)
+                    const float2* stp = na.stats + (long long)z * p.N + n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const bool in = n0 + c * 32 + j + 1 < p.N;
+                        const float4 st2 = in ? __ldg(reinterpret_cast<const float4*>(stp + j)) : make_float4(0.f, 0.f, 0.f, 0.f);   // (inv, mi) of two columns
+                        f[j] = __uint_as_float(v[j]) * st2.x + (nr.c - st2.y * nr.s);
+                        f[j + 1] = __uint_as_float(v[j + 1]) * st2.z + (nr.c - st2.w * nr.s);
+                    }
+                } else {
                 const float2 al2 = make_float2(p.alpha, p.alpha);
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
@@ -337,6 +372,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     float2 lo = __ffma2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), al2, make_float2(b4.x, b4.y));
                     float2 hi = __ffma2_rn(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), al2, make_float2(b4.z, b4.w));
                     f[j] = lo.x; f[j + 1] = lo.y; f[j + 2] = hi.x; f[j + 3] = hi.y;
+                }
                 }
                 if (c + 1 < c_end) { tmem_ld_32x32(t_row + (c + 1) * 32, v); fetch_residual(c + 1); }
                 else release_acc(acc);                                            // this warp has drained its part of the accumulator
@@ -518,6 +554,14 @@ bool gemm_supported(const GemmDesc& d, const char** why) {
     if (d.lda < d.K || d.ldb < d.K) return bad("row pitch smaller than K");
     if ((long long)d.lda * es >= (1ll << 40) || (long long)d.ldb * es >= (1ll << 40)) return bad("row pitch too large for a tensor map");
     if (d.mode == MM_TF32 && d.out_dtype != F32) return bad("TF32 mode writes f32 only");
+    if (d.norm_axis) {
+        if (d.norm_axis != 1 && d.norm_axis != 2) return bad("norm_axis is not 0, 1 or 2");
+        if (!d.norm_stats || !d.norm_s || (d.norm_axis == 2 && !d.norm_c)) return bad("folded LayerNorm needs its statistics and column sums");
+        if (d.norm_axis == 2 && d.bias) return bad("norm_axis 2 takes its constants through norm_c, not bias");
+        if ((reinterpret_cast<uintptr_t>(d.norm_stats) | reinterpret_cast<uintptr_t>(d.norm_s)) & 15) return bad("folded LayerNorm vectors must be 16-byte aligned");
+        if (d.norm_axis == 2 && d.N % 2) return bad("folded LayerNorm along columns needs an even N");
+        if (d.alpha != 1.0f) return bad("folded LayerNorm does not combine with alpha");
+    }
     if (why) *why = ok;
     return true;
 }
@@ -530,8 +574,22 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm);
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr, nullptr});
     SPT_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}
+
+// folded-LayerNorm epilogues exist for the shape class that uses them: bf16 in and out, 256-column tiles, one CTA per tile
+template <int NORM>
+static int launch_norm_t(const GemmPlan& pl, const GemmParams& prm) {
+    auto kern = gemm_tcgen05_kernel<false, __nv_bfloat16, 256, false, NORM>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        attr_set = true;
+    }
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{pl.d.norm_stats, pl.d.norm_s, pl.d.norm_c});
+    SPT_LAUNCH_CHECK("gemm_tcgen05 (folded LayerNorm)");
     return 0;
 }
 
@@ -552,7 +610,7 @@ static int launch_pair_t(const GemmPlan& pl, const GemmParams& prm) {
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm));
+    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr, nullptr}));
     SPT_LAUNCH_CHECK("gemm_tcgen05 (pair)");
     return 0;
 }
@@ -591,7 +649,7 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     // wide problems run on CTA pairs (each SM then loads half of the B tile); the triangular attention products do not
     int pairs = 0;
     const int pm = g_pair_mode.load();
-    if ((pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
+    if (!d.norm_axis && (pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
     plan->pair = pairs > 0;
     plan->tiles_m = ceil_div(d.M, plan->pair ? 2 * BM : BM);
     plan->tiles_n = ceil_div(d.N, bn);
@@ -653,6 +711,10 @@ int gemm_run(const GemmPlan& pl) {
     prm.status = rt().dev_status;
     const bool tf32 = d.mode == MM_TF32;
     const bool out_bf16 = d.out_dtype == BF16;
+    if (d.norm_axis) {
+        if (tf32 || !out_bf16 || pl.bn != 256 || pl.pair) return fail("gemm_run: the folded-LayerNorm epilogue needs bf16 operands and output and N > 128");
+        return d.norm_axis == 1 ? launch_norm_t<1>(pl, prm) : launch_norm_t<2>(pl, prm);
+    }
     if (pl.pair) {
         if (tf32) return launch_pair_t<true, float>(pl, prm);
         if (out_bf16) return launch_pair_t<false, __nv_bfloat16>(pl, prm);

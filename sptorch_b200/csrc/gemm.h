@@ -26,6 +26,16 @@ struct GemmDesc {
     int causal_lower = 0;    // 1: square per-batch output, tiles entirely above the diagonal are skipped (never written)
     int b_broadcast = 0;     // 1: B has no batch dims (one weight matrix for every batch entry)
     int causal_k = 0;        // 1: A is lower triangular per batch (A[m,k] = 0 for k > m): k-blocks past the tile's last row are skipped
+    // LayerNorm folded into the product.  With W' = W * gamma (per input feature), s[n] = sum_k W'[n,k], c[n] = sum_k beta[k] W[n,k] + bias[n]:
+    //   LN(x) W^T + bias = inv[m] * (x W'^T)[m,n] - (mean[m] inv[m]) * s[n] + c[n]
+    // so the GEMM reads the un-normalised rows and the epilogue applies the row statistics.  norm_axis 1: the normalised operand
+    // is A (statistics per output row, s / c per output column, c passed as `bias`); norm_axis 2: it is B (statistics per output
+    // column, norm_s / norm_c per output row) -- the transposed V projection.  stats[i] = (inv_std, mean * inv_std).
+    // norm_s (axis 1) must be readable up to N rounded up to 32 elements, norm_stats (axis 2) likewise.
+    int norm_axis = 0;
+    const float2* norm_stats = nullptr;
+    const float* norm_s = nullptr;
+    const float* norm_c = nullptr;   // norm_axis 2 only
 };
 
 // A prepared launch: tensor maps are encoded once and can be replayed (the GPT driver caches these).
@@ -51,5 +61,10 @@ int simt_matmul_f32(const float* A, const float* B, float* C, int batch, int M, 
                     const float* bias, const float* R, float alpha, int epilogue);
 
 int layernorm_launch(const void* x, const void* gamma, const void* beta, void* out, size_t rows, size_t dim, float eps, int dtype);
+// LayerNorm folded into the following GEMM (GemmDesc::norm_axis): per-row statistics, and the folded weights / vectors
+bool layernorm_stats_supported(size_t dim, int dtype);
+int layernorm_stats_launch(const void* x, float2* stats, size_t rows, size_t dim, float eps, int dtype);
+int layernorm_fold_launch(const void* w, const float* gamma, const float* beta, const float* bias, void* w_folded, float* svec, float* cvec,
+                          size_t N, size_t K, int dtype);
 
 }  // namespace spt

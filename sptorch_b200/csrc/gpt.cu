@@ -32,6 +32,9 @@ struct Layer {
     float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;     // Qwen-like: ln1g / ln2g hold the RMSNorm weights, the betas are unused
     void *wqk, *wv, *wo, *w1, *w2;
     void* wg = nullptr; float* bg = nullptr;         // Qwen-like: gate projection of the SwiGLU MLP
+    // LayerNorm folded into the GEMMs that consume it (bf16 GPT): weights times gamma, their row sums s, and c = W beta (+ bias)
+    void *wqk_f = nullptr, *wv_f = nullptr, *w1_f = nullptr;
+    float *s_qk = nullptr, *c_qk = nullptr, *s_v = nullptr, *c_v = nullptr, *s_1 = nullptr, *c_1 = nullptr;
 };
 
 struct Gpt {
@@ -63,6 +66,9 @@ struct Gpt {
     cudaGraphExec_t gexec = nullptr;
     int eager_runs = 0;        // forwards of the current key run eagerly so far (the first one sets function attributes)
     bool graphs = true;
+    // folded LayerNorm (see forward): per-token statistics, the head's folded copy, and whether the copies are stale
+    float2* ln_stats = nullptr; void* head_f = nullptr; float *s_h = nullptr, *c_h = nullptr;
+    bool ln_fold = false, fold_ready = false, fold_dirty = true;     // opt-in: measured neutral (see sptorch_ext_gpt_enable_ln_fold)
     bool tp_overlap = false;   // tensor parallel: reduce one half of the batch while the other half computes (opt-in)
 };
 
@@ -122,6 +128,77 @@ static int allreduce(Gpt* g, void* buf, size_t n) {
     if (g->ar(buf, n, g->c.dtype, (void*)rt().stream, g->ar_user)) return fail("gpt: all-reduce hook failed");
     note_submit();
     return 0;
+}
+
+// ---- LayerNorm folded into the GEMMs ----
+// LN(x) W^T + b = inv * (x (W gamma)^T) - (mean inv) * s + c with s = rowsum(W gamma), c = W beta + b.  The forward then launches,
+// instead of a LayerNorm pass that reads and writes every activation, a statistics pass that only reads them (8 bytes per token
+// out), and the GEMMs consume the residual stream directly.  Used for bf16 GPT models whose GEMMs all take the 256-column tile.
+static bool fold_applicable(const Gpt* g, int M) {
+    const sptorch_gpt_config& c = g->c;
+    return g->ln_fold && c.arch == SPT_ARCH_GPT && c.dtype == SPT_BF16 && !g->fill_cache && layernorm_stats_supported((size_t)c.d_model, c.dtype) &&
+           2 * g->d_loc > 128 && g->F_loc > 128 && c.vocab > 128 && M > 128 && M % 2 == 0;
+}
+
+static int fold_prepare(Gpt* g) {
+    const sptorch_gpt_config& c = g->c;
+    const size_t d = c.d_model, dl = g->d_loc, Fl = g->F_loc, V = c.vocab, es = g->es;
+    auto pad32 = [](size_t n) { return (n + 31) / 32 * 32; };
+    if (!g->fold_ready) {
+        bool ok = true;
+        auto A = [&](size_t bytes) { void* p = galloc(g, bytes); if (!p) ok = false; return p; };
+        auto Z = [&](size_t n) { float* p = (float*)A(pad32(n) * 4); if (p && sptorch_ext_memset(p, 0, pad32(n) * 4)) ok = false; return p; };
+        for (auto& w : g->L) {
+            w.wqk_f = A(2 * dl * d * es); w.wv_f = A(dl * d * es); w.w1_f = A(Fl * d * es);
+            w.s_qk = Z(2 * dl); w.c_qk = Z(2 * dl); w.s_v = Z(dl); w.c_v = Z(dl); w.s_1 = Z(Fl); w.c_1 = Z(Fl);
+        }
+        g->head_f = A(V * d * es); g->s_h = Z(V); g->c_h = Z(V);
+        g->ln_stats = (float2*)A(((size_t)c.max_batch * c.seq_len + 32) * sizeof(float2));
+        if (ok && sptorch_ext_memset(g->ln_stats, 0, ((size_t)c.max_batch * c.seq_len + 32) * sizeof(float2))) ok = false;
+        if (!ok) return 1;
+        g->fold_ready = true; g->fold_dirty = true;
+    }
+    if (g->fold_dirty) {
+        for (auto& w : g->L) {
+            if (layernorm_fold_launch(w.wqk, w.ln1g, w.ln1b, nullptr, w.wqk_f, w.s_qk, w.c_qk, 2 * dl, d, c.dtype)) return 1;
+            if (layernorm_fold_launch(w.wv, w.ln1g, w.ln1b, nullptr, w.wv_f, w.s_v, w.c_v, dl, d, c.dtype)) return 1;
+            if (layernorm_fold_launch(w.w1, w.ln2g, w.ln2b, w.b1, w.w1_f, w.s_1, w.c_1, Fl, d, c.dtype)) return 1;
+        }
+        if (layernorm_fold_launch(g->head, g->lnfg, g->lnfb, nullptr, g->head_f, g->s_h, g->c_h, V, d, c.dtype)) return 1;
+        g->fold_dirty = false;
+    }
+    return 0;
+}
+
+static int ln_stats(Gpt* g, const void* x, int M) {
+    ProfScope ps(PROF_LAYERNORM);
+    return layernorm_stats_launch(x, g->ln_stats, (size_t)M, (size_t)g->c.d_model, g->c.eps, g->c.dtype);
+}
+
+// y[M,N] = act(LN(x) W^T + b) from the un-normalised x and the folded constants
+static int linear_folded(Gpt* g, const void* x, const void* wf, const float* cvec, const float* svec, void* out, int M, int K, int N, long long ldo, int epi) {
+    GemmDesc d;
+    d.A = x; d.B = wf; d.C = out; d.bias = cvec;
+    d.M = M; d.N = N; d.K = K; d.lda = K; d.ldb = K; d.ldc = ldo;
+    d.epilogue = epi; d.mode = MM_BF16; d.out_dtype = SPT_BF16;
+    d.norm_axis = 1; d.norm_stats = g->ln_stats; d.norm_s = svec;
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    ProfScope ps(PROF_LINEAR);
+    return gemm_run(pl);
+}
+
+// out[N_w, M] = (LN(x) W^T)^T: the weights are the A operand, the tokens the columns (the transposed V projection)
+static int linear_folded_t(Gpt* g, const void* wf, const void* x, const float* svec, const float* cvec, void* out, int Nw, int K, int M) {
+    GemmDesc d;
+    d.A = wf; d.B = x; d.C = out;
+    d.M = Nw; d.N = M; d.K = K; d.lda = K; d.ldb = K; d.ldc = M;
+    d.mode = MM_BF16; d.out_dtype = SPT_BF16;
+    d.norm_axis = 2; d.norm_stats = g->ln_stats; d.norm_s = svec; d.norm_c = cvec;
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    ProfScope ps(PROF_LINEAR);
+    return gemm_run(pl);
 }
 
 // Tensor-parallel forward with the all-reduces taken off the critical path: the batch is cut into two halves that go
@@ -276,11 +353,17 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         return 0;
     };
     if (tap(0, x)) return 1;
+    const bool fold = fold_applicable(g, M) && g->fold_ready && !g->fold_dirty;
     for (int l = 0; l < c.n_layer; l++) {
         const Layer& w = g->L[l];
-        if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
-        // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
-        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        if (fold) {
+            if (ln_stats(g, x, M)) return 1;
+            if (linear_folded(g, x, w.wqk_f, w.c_qk, w.s_qk, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        } else {
+            if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+            // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
+            if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+        }
         if (g->fill_cache) {
             // prefill: K and V of every position go to the cache rows [sequence][position][dl] (two more projections of h;
             // the attention below keeps reading the [q|k] and V^T buffers)
@@ -299,7 +382,8 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
             { ProfScope ps(PROF_LINEAR); if (gemm_run(pv)) return 1; }
         }
         // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
-        if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
+        if (fold) { if (linear_folded_t(g, w.wv_f, x, w.s_v, w.c_v, g->vt, dl, d, M)) return 1; }
+        else if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
         if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
                                    /*batch*/ T, g->ao, g->scores, B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
         if (c.tp_size <= 1) {
@@ -309,8 +393,13 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
             if (allreduce(g, y, (size_t)M * d)) return 1;
             std::swap(x, y);
         }
-        if (ln(x, w.ln2g, w.ln2b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
-        if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, M, d, Fl, Fl, EPI_GELU)) return 1;
+        if (fold) {
+            if (ln_stats(g, x, M)) return 1;
+            if (linear_folded(g, x, w.w1_f, w.c_1, w.s_1, g->f, M, d, Fl, Fl, EPI_GELU)) return 1;
+        } else {
+            if (ln(x, w.ln2g, w.ln2b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+            if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, M, d, Fl, Fl, EPI_GELU)) return 1;
+        }
         if (c.tp_size <= 1) {
             if (linear(g, g->f, w.w2, w.b2, x, x, M, Fl, d, d, EPI_NONE)) return 1;            // x += ffn
         } else {
@@ -319,6 +408,14 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
             std::swap(x, y);
         }
         if (tap(l + 1, x)) return 1;
+    }
+    if (fold) {
+        if (g->taps_on) {          // the tap of ln_f's output is the only reader of the normalised rows
+            if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
+            if (tap(c.n_layer + 1, g->h)) return 1;
+        }
+        if (ln_stats(g, x, M)) return 1;
+        return linear_folded(g, x, g->head_f, g->c_h, g->s_h, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE);
     }
     if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
     if (tap(c.n_layer + 1, g->h)) return 1;
@@ -432,6 +529,7 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
     auto need = [&](size_t want) { return n == want ? 0 : fail("gpt_set_param(%s): got %zu values, expected %zu", name, n, want); };
     auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || stream_wait(); };
     std::string s(name);
+    g->fold_dirty = true;                       // folded copies of the weights follow any parameter change
     const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;
     if (qwen && (s == "pos_emb.weight" || s == "ln_f.gamma" || s == "ln_f.beta")) return fail("gpt_set_param: '%s' is not a parameter of the Qwen-like model", name);
     if (qwen && s == "norm_f.weight") return need(d) || f32(g->lnfg, 0, d);
@@ -485,6 +583,7 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
     if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
     Gpt* g = (Gpt*)gp;
     if (check_shape(g, batch, T)) return 1;
+    if (fold_applicable(g, batch * T) && fold_prepare(g)) return 1;      // outside any graph capture
     // The launch-bound inner loop (about 100 kernels, each a few microseconds when the batch is sharded 8 ways) is
     // replayed as one CUDA graph: the first forward of a given (ids, logits, batch, T) runs eagerly, the second is
     // captured, later ones are a single cudaGraphLaunch.  Per-kernel timing and tensor-parallel hooks run eagerly.
@@ -620,6 +719,16 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
     return 0;
 }
 
+int sptorch_ext_gpt_enable_ln_fold(void* gp, int on) {
+    if (!gp) return fail("gpt_enable_ln_fold: null model");
+    Gpt* g = (Gpt*)gp;
+    if (g->ln_fold != (on != 0)) {
+        g->ln_fold = on != 0;
+        if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; g->eager_runs = 0; }     // the captured launches belong to the other path
+    }
+    return 0;
+}
+
 int sptorch_ext_gpt_enable_tp_overlap(void* gp, int on) {
     if (!gp) return fail("gpt_enable_tp_overlap: null model");
     ((Gpt*)gp)->tp_overlap = on != 0;
@@ -680,6 +789,7 @@ int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, i
     if (chunk <= 0 || chunk > batch) chunk = batch;
     if (chunk > g->c.max_batch) chunk = g->c.max_batch;
     if (check_shape(g, chunk, T)) return 1;
+    if (fold_applicable(g, chunk * T) && fold_prepare(g)) return 1;
     const size_t es = g->es, V = g->c.vocab, ldl = g->ldl;
     const size_t need_logits = (size_t)chunk * T * ldl * es;
     if (g->logits_cap < need_logits) {

@@ -7,6 +7,7 @@
 // (crates/nn/src/lib.rs:397-418; crates/core-ops/src/lib.rs:888-935, 1601-1645, 1220-1255, 825-850) and its
 // CUDA backend round-trips through the host for them (crates/runtime-cuda/src/lib.rs:302-490).
 #include "common.h"
+#include <cstdlib>
 #include "../../include/sptorch_b200_hal.h"
 #include "../../include/sptorch_b200_ext.h"
 #include <math.h>
@@ -147,6 +148,84 @@ __global__ void __launch_bounds__(kRowThreads) layernorm_kernel(const T* __restr
                 y.store(yr + c * N);
             }
         }
+    }
+}
+
+// Row statistics only: stats[row] = (1/sqrt(var + eps), mean/sqrt(var + eps)), the two numbers a GEMM epilogue needs to apply
+// LayerNorm to its un-normalised operand (GemmDesc::norm_axis).  Same mean-then-centred-variance arithmetic as the kernel
+// above; reads the rows once and writes 8 bytes per row.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kRowThreads) layernorm_stats_kernel(const T* __restrict__ x, float2* __restrict__ stats, size_t rows, int dim, float eps) {
+    using VT = Vec<T>;
+    constexpr int N = VT::N;
+    constexpr int V = kRowVecs;
+    constexpr int RPB = kRowThreads / TPR;
+    __shared__ float sh[kRowThreads / 32];
+    const int t = threadIdx.x % TPR;
+    const int rl = threadIdx.x / TPR;
+    const int nvec = dim / N;
+    for (size_t r0 = (size_t)blockIdx.x * RPB; r0 < rows; r0 += (size_t)gridDim.x * RPB) {
+        size_t r = r0 + rl;
+        bool live = r < rows;
+        const T* xr = x + (live ? r : 0) * (size_t)dim;
+        typename VT::Raw d[V];
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) d[i] = VT::load_raw(xr + c * N);
+        }
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
+#pragma unroll
+                for (int j = 0; j < N; j++) s += u.v[j];
+            }
+        }
+        float mean = row_reduce<TPR, false>(s, sh) / (float)dim;
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            int c = i * TPR + t;
+            if (live && c < nvec) {
+                VT u = VT::from_raw(d[i]);
+#pragma unroll
+                for (int j = 0; j < N; j++) { float e = u.v[j] - mean; q += e * e; }
+            }
+        }
+        float var = row_reduce<TPR, false>(q, sh) / (float)dim;
+        float inv = 1.0f / sqrtf(var + eps);
+        if (live && t == 0) stats[r] = make_float2(inv, mean * inv);
+    }
+}
+
+// W'[n,k] = W[n,k] * gamma[k] (rounded to T), s[n] = sum_k W'[n,k], c[n] = sum_k beta[k] W[n,k] (+ bias[n]): the constants of a
+// Linear that follows a LayerNorm when the normalisation is applied in the GEMM epilogue.  One CTA per output feature n.
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_fold_kernel(const T* __restrict__ w, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                             const float* __restrict__ bias, T* __restrict__ wf, float* __restrict__ svec,
+                                                             float* __restrict__ cvec, int K) {
+    __shared__ float red[2][8];
+    const size_t n = blockIdx.x;
+    float s = 0.0f, c = 0.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float wv = (float)w[n * K + k];
+        const T folded = (T)(wv * gamma[k]);
+        wf[n * K + k] = folded;
+        s += (float)folded;                      // the sum of what the tensor cores will actually multiply
+        c += beta[k] * wv;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { s += __shfl_xor_sync(0xffffffffu, s, o); c += __shfl_xor_sync(0xffffffffu, c, o); }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = s; red[1][threadIdx.x >> 5] = c; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float st = 0.0f, ct = 0.0f;
+        for (int i = 0; i < 8; i++) { st += red[0][i]; ct += red[1][i]; }
+        svec[n] = st;
+        cvec[n] = ct + (bias ? bias[n] : 0.0f);
     }
 }
 
@@ -626,6 +705,38 @@ static int causal_softmax_t(const void* x, void* out, size_t batch, size_t Tn, f
         causal_softmax_generic_kernel<T><<<row_grid(batch * Tn), kRowThreads, 0, rt().stream>>>(xp, op, batch, (int)Tn, scale);
     }
     SPT_LAUNCH_CHECK("causal_softmax");
+    return 0;
+}
+
+// bf16 rows whose length the register path holds; the GPT driver checks `layernorm_stats_supported` before it relies on this
+bool layernorm_stats_supported(size_t dim, int dtype) { return dtype == BF16 && dim % 8 == 0 && dim / 8 <= 2048; }
+int layernorm_stats_launch(const void* x, float2* stats, size_t rows, size_t dim, float eps, int dtype) {
+    if (rows == 0) return 0;
+    if (!layernorm_stats_supported(dim, dtype) || !aligned16(x)) return fail("layernorm_stats: unsupported row length, dtype or alignment");
+    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+    const int nvec = (int)(dim / 8);
+    const int per_sm = 8;
+    int tpr = 8;
+    while (tpr * kRowVecs < nvec) tpr *= 2;
+    const int rpb = kRowThreads / tpr;
+    const int grid = row_grid((rows + rpb - 1) / rpb, per_sm);
+    switch (tpr) {
+        case 8: layernorm_stats_kernel<__nv_bfloat16, 8><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+        case 16: layernorm_stats_kernel<__nv_bfloat16, 16><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+        case 32: layernorm_stats_kernel<__nv_bfloat16, 32><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+        case 64: layernorm_stats_kernel<__nv_bfloat16, 64><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+        case 128: layernorm_stats_kernel<__nv_bfloat16, 128><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+        default: layernorm_stats_kernel<__nv_bfloat16, 256><<<grid, kRowThreads, 0, rt().stream>>>(xp, stats, rows, (int)dim, eps); break;
+    }
+    SPT_LAUNCH_CHECK("layernorm_stats");
+    return 0;
+}
+int layernorm_fold_launch(const void* w, const float* gamma, const float* beta, const float* bias, void* wf, float* svec, float* cvec,
+                          size_t N, size_t K, int dtype) {
+    if (N == 0 || K == 0) return 0;
+    if (dtype != BF16) return fail("layernorm_fold: bf16 weights only");
+    layernorm_fold_kernel<__nv_bfloat16><<<(unsigned)N, 256, 0, rt().stream>>>((const __nv_bfloat16*)w, gamma, beta, bias, (__nv_bfloat16*)wf, svec, cvec, (int)K);
+    SPT_LAUNCH_CHECK("layernorm_fold");
     return 0;
 }
 

@@ -61,6 +61,10 @@ class GPT:
         a = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
         self.b._check(self.b.lib.sptorch_ext_gpt_set_param(self.h, name.encode(), a.ctypes.data, a.size), f"set_param({name})")
 
+    def enable_ln_fold(self, on=True):
+        """LayerNorm applied inside the epilogues of the consuming GEMMs (bf16 GPT only; off by default)."""
+        self.b._check(self.b.lib.sptorch_ext_gpt_enable_ln_fold(self.h, int(on)), "enable_ln_fold")
+
     def enable_taps(self, on=True):
         self.b._check(self.b.lib.sptorch_ext_gpt_enable_taps(self.h, int(on)), "enable_taps")
 

@@ -217,3 +217,36 @@ def test_full_size_config4_properties(backend):
     assert np.array_equal(after[:p], in_batch[5][:p])
     assert not np.array_equal(after[p], in_batch[5][p])
     m.close()
+
+
+def test_layernorm_folded_into_the_gemms(backend, oracle):
+    """The opt-in path that applies LayerNorm in the GEMM epilogues (statistics pass + weights pre-multiplied by gamma) against
+    the oracle per layer, and against the default path: both are the same function within the bf16 tolerance, including after
+    a parameter change (the folded copies must follow it) and through CUDA-graph replay."""
+    cfg = synth.CONFIGS["c1_tiny"]
+    params, index = synth.gpt_params(cfg, 0, randomize_affine=True)
+    ids = synth.randint(1, 8 * 64, 256).reshape(8, 64)
+    ref, taps = oracle.gpt_forward(cfg, params, ids, fast=0, threads=oracle.max_threads(), want_taps=True)
+    m = _model(backend, cfg, BF16, 8, params, index)
+    plain = m.forward(ids)
+    m.enable_ln_fold()
+    m.enable_taps()
+    out = m.forward(ids)
+    assert relerr(out, ref) <= TOL[BF16]
+    for i in range(cfg["n_layer"] + 2):
+        assert relerr(m.tap(i, 8 * 64).reshape(8, 64, -1), taps[:, i]) <= TOL[BF16], f"layer tap {i}"
+    assert relerr(out, plain) <= TOL[BF16] and not np.array_equal(out, plain)          # a different evaluation order, the same function
+    m.enable_taps(False)
+    d_ids, d_log = m.stage_ids(ids), m.logits_buffer(8 * 64)
+    runs = []
+    for _ in range(3):
+        m.forward_device(d_ids, 8, 64, d_log)
+        runs.append(d_log.to_host().copy())
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    # new LayerNorm parameters: the next forward must use them
+    off, shape = index["blocks.1.ln2.gamma"]
+    g2 = params[off:off + shape[0]] * 1.5
+    m.set_param("blocks.1.ln2.gamma", g2)
+    p2 = params.copy(); p2[off:off + shape[0]] = g2
+    assert relerr(m.forward(ids), oracle.gpt_forward(cfg, p2, ids, fast=0, threads=oracle.max_threads())) <= TOL[BF16]
+    m.close()
