@@ -591,11 +591,11 @@ int orc_gpt_forward_batch(const orc_gpt_config* c, const float* params, const in
     size_t V = c->vocab, d = c->d_model, L = c->n_layer;
     int rc = 0;
     if (threads < 1) threads = 1;
+#ifdef _OPENMP
+    omp_set_num_threads(threads);       /* also bounds the row / head loops inside one sequence (threads == 1: truly one thread) */
+#endif
     if (B < (size_t)threads) {
         /* fewer sequences than threads: run them one after another and split the rows / heads of each over the threads */
-#ifdef _OPENMP
-        omp_set_num_threads(threads);
-#endif
         for (size_t b = 0; b < B; b++) {
             int r = orc_gpt_forward_ids(c, params, ids + b * T, T, logits + b * T * V, taps ? taps + b * (L + 2) * T * d : NULL, fast);
             if (r != 0) rc = r;
