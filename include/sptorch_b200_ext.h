@@ -210,6 +210,12 @@ int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* us
 int       sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
                                           float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
                                           int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count);
+/* the same with a TokenConstraint's allowed set applied first (filtered_step_logits, nn/src/lib.rs:2465-2480): every token outside
+ * `allowed` counts as -inf; an empty set leaves no candidate */
+int       sptorch_ext_sampling_candidates_constrained(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature,
+                                                      size_t top_k, float top_p, float repetition_penalty, const int64_t* history,
+                                                      size_t n_history, const int64_t* allowed, size_t n_allowed,
+                                                      int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count);
 /* sample_from_candidates (nn/src/lib.rs:2420-2429) for the caller's uniform draw `threshold` in [0, 1); -1 without candidates */
 long long sptorch_ext_sample_from_candidates(const int32_t* ids, const float* probs, size_t count, float threshold);
 

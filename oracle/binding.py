@@ -278,9 +278,15 @@ def qwen_forward(cfg: dict, params: np.ndarray, ids: np.ndarray, fast=0, threads
     return (logits, taps) if want_taps else logits
 
 
-def sampling_candidates(logits, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, history=()):
-    """sampling_candidates (crates/nn/src/lib.rs:2381-2418) -> (ids int64, scaled logits, probabilities)."""
+def sampling_candidates(logits, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, history=(), allowed=None):
+    """sampling_candidates (crates/nn/src/lib.rs:2381-2418) -> (ids int64, scaled logits, probabilities); ``allowed`` applies
+    filtered_step_logits (:2465-2480) first."""
     x = _f32(logits).ravel()
+    if allowed is not None:
+        a = np.ascontiguousarray(sorted(allowed), dtype=np.int64)
+        y = np.empty_like(x)
+        lib().orc_filter_step_logits(_p(x), _sz(x.size), a.ctypes.data_as(_i64), _sz(a.size), _p(y))
+        x = y
     V = x.size if vocab_size is None else vocab_size
     h = np.ascontiguousarray(history, dtype=np.int64)
     ids = np.empty(max(V, 1), np.int64); lg = np.empty(max(V, 1), np.float32); pr = np.empty(max(V, 1), np.float32)

@@ -544,6 +544,15 @@ static void cand_normalize(const orc_cand* c, size_t n, float* probs) {
     for (size_t i = 0; i < n; i++) { probs[i] = expf(c[i].v - mx); sum += probs[i]; }
     for (size_t i = 0; i < n; i++) probs[i] = probs[i] / sum;
 }
+/* filtered_step_logits (crates/nn/src/lib.rs:2465-2480): tokens outside the constraint's allowed set become -inf */
+void orc_filter_step_logits(const float* logits, size_t n, const int64_t* allowed, size_t n_allowed, float* out) {
+    for (size_t t = 0; t < n; t++) {
+        int in = 0;
+        for (size_t a = 0; a < n_allowed && !in; a++) in = allowed[a] == (int64_t)t;
+        out[t] = in ? logits[t] : -INFINITY;
+    }
+}
+
 long orc_sampling_candidates(const float* logits, size_t n_logits, size_t vocab_size, float temperature, size_t top_k, float top_p,
                              float repetition_penalty, const int64_t* history, size_t n_history,
                              int64_t* out_ids, float* out_logits, float* out_probs) {

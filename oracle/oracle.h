@@ -104,6 +104,7 @@ int orc_qwen_forward_ids(const orc_gpt_config* c, float rope_base, const float* 
 int orc_qwen_forward_batch(const orc_gpt_config* c, float rope_base, const float* params, const int64_t* ids, size_t B,
                            size_t T, float* logits, float* taps, int fast, int threads);
 /* ---- sampling (crates/nn/src/lib.rs:2381-2418) ---- */
+void orc_filter_step_logits(const float* logits, size_t n, const int64_t* allowed, size_t n_allowed, float* out);
 long orc_sampling_candidates(const float* logits, size_t n_logits, size_t vocab_size, float temperature, size_t top_k, float top_p,
                              float repetition_penalty, const int64_t* history, size_t n_history,
                              int64_t* out_ids, float* out_logits, float* out_probs);

@@ -107,6 +107,7 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_enable_ln_fold": (_i, [_vp, _i]),
     "sptorch_ext_gpt_enable_tp_overlap": (_i, [_vp, _i]),
     "sptorch_ext_sampling_candidates": (_i, [_vp, _sz, _i, _sz, _f, _sz, _f, _f, _vp, _sz, _vp, _vp, _vp, _sz, C.POINTER(_sz)]),
+    "sptorch_ext_sampling_candidates_constrained": (_i, [_vp, _sz, _i, _sz, _f, _sz, _f, _f, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _sz, C.POINTER(_sz)]),
     "sptorch_ext_sample_from_candidates": (C.c_longlong, [_vp, _vp, _sz, _f]),
     "sptorch_ext_weights_open": (_vp, [C.c_char_p, _i]),
     "sptorch_ext_weights_close": (None, [_vp]),

@@ -413,7 +413,7 @@ class FfiBackend:
                 b.free()
 
     def sampling_candidates(self, logits, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0, history=(),
-                            dtype=F32):
+                            dtype=F32, allowed=None):
         """sampling_candidates (crates/nn/src/lib.rs:2381-2418): one row of logits -> (token ids, scaled logits, probabilities)
         in the reference's candidate order.  ``logits`` may be a host array (uploaded here) or a DeviceBuffer."""
         own = not isinstance(logits, DeviceBuffer)
@@ -424,9 +424,16 @@ class FfiBackend:
         ids, lg, pr = np.empty(cap, np.int32), np.empty(cap, np.float32), np.empty(cap, np.float32)
         n = C.c_size_t(0)
         try:
-            self._check(self.lib.sptorch_ext_sampling_candidates(d.handle, d.n, dtype, V, C.c_float(temperature), top_k, C.c_float(top_p),
-                                                                 C.c_float(repetition_penalty), h.ctypes.data, h.size,
-                                                                 ids.ctypes.data, lg.ctypes.data, pr.ctypes.data, cap, C.byref(n)), "sampling_candidates")
+            if allowed is None:
+                rc = self.lib.sptorch_ext_sampling_candidates(d.handle, d.n, dtype, V, C.c_float(temperature), top_k, C.c_float(top_p),
+                                                              C.c_float(repetition_penalty), h.ctypes.data, h.size,
+                                                              ids.ctypes.data, lg.ctypes.data, pr.ctypes.data, cap, C.byref(n))
+            else:       # a TokenConstraint's allowed_next set (nn/src/lib.rs:2465-2480)
+                a = np.ascontiguousarray(sorted(allowed), dtype=np.int64)
+                rc = self.lib.sptorch_ext_sampling_candidates_constrained(d.handle, d.n, dtype, V, C.c_float(temperature), top_k, C.c_float(top_p),
+                                                                          C.c_float(repetition_penalty), h.ctypes.data, h.size, a.ctypes.data, a.size,
+                                                                          ids.ctypes.data, lg.ctypes.data, pr.ctypes.data, cap, C.byref(n))
+            self._check(rc, "sampling_candidates")
         finally:
             if own:
                 d.free()

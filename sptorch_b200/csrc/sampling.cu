@@ -24,10 +24,12 @@ constexpr int kMaxVocabBitmapWords = 8192;     // shared-memory bitmap: vocabula
 template <typename T>
 __global__ void __launch_bounds__(kSampThreads) sampling_prep_kernel(const T* __restrict__ logits, int vocab, float temperature, float penalty,
                                                                      const int* __restrict__ history, int n_hist,
+                                                                     const int* __restrict__ allowed, int n_allowed,
                                                                      float* __restrict__ keys, int* __restrict__ ids, int* __restrict__ n_valid) {
-    extern __shared__ uint32_t seen[];                     // one bit per token: appears in the history
+    extern __shared__ uint32_t seen[];                     // one bit per token: appears in the history; then one bit per allowed token
     const int words = (vocab + 31) / 32;
-    for (int w = threadIdx.x; w < words; w += blockDim.x) seen[w] = 0u;
+    uint32_t* allow = seen + words;
+    for (int w = threadIdx.x; w < words; w += blockDim.x) { seen[w] = 0u; if (allowed) allow[w] = 0u; }
     __shared__ int count;
     if (threadIdx.x == 0) count = 0;
     __syncthreads();
@@ -35,10 +37,15 @@ __global__ void __launch_bounds__(kSampThreads) sampling_prep_kernel(const T* __
         const int t = history[i];
         if (t >= 0 && t < vocab) atomicOr(&seen[t >> 5], 1u << (t & 31));
     }
+    for (int i = threadIdx.x; i < n_allowed; i += blockDim.x) {
+        const int t = allowed[i];
+        if (t >= 0 && t < vocab) atomicOr(&allow[t >> 5], 1u << (t & 31));
+    }
     __syncthreads();
     int mine = 0;
     for (int t = threadIdx.x; t < vocab; t += blockDim.x) {
         float x = (float)logits[t];
+        if (allowed && !(allow[t >> 5] >> (t & 31) & 1u)) x = -CUDART_INF_F;      // filtered_step_logits: outside the constraint's set
         if (penalty != 1.0f && (seen[t >> 5] >> (t & 31) & 1u)) x = signbit(x) ? x * penalty : x / penalty;
         x = x / temperature;
         const bool ok = isfinite(x);
@@ -105,9 +112,10 @@ using namespace spt;
 
 extern "C" {
 
-int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
-                                    float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
-                                    int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count) {
+static int sampling_impl(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
+                         float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
+                         const int64_t* allowed, size_t n_allowed, bool constrained,
+                         int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count) {
     if (enter()) return 1;
     if (!count) return fail("sampling_candidates: null count");
     *count = 0;
@@ -117,6 +125,8 @@ int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dty
     if (vocab_size == 0) return 0;
     if (vocab_size > (size_t)kMaxVocabBitmapWords * 32) return fail("sampling_candidates: vocabularies above %d tokens are not supported", kMaxVocabBitmapWords * 32);
     if (n_history && !history) return fail("sampling_candidates: null history");
+    if (constrained && n_allowed && !allowed) return fail("sampling_candidates: null constraint set");
+    if (constrained && (size_t)((vocab_size + 31) / 32) * 8 > 48 * 1024) return fail("sampling_candidates: a constraint set needs a vocabulary of at most 196608 tokens");
     const int V = (int)vocab_size;
     const float temp = temperature > 1e-8f ? temperature : 1e-8f;                       // `temperature.max(1e-8)`
     const float pen = repetition_penalty > 1.0f ? repetition_penalty : 1.0f;            // `repetition_penalty.max(1.0)`
@@ -128,6 +138,8 @@ int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dty
     std::vector<int> hist;
     hist.reserve(n_history);
     for (size_t i = 0; i < n_history; i++) if (history[i] >= 0 && history[i] < (int64_t)V) hist.push_back((int)history[i]);
+    const size_t n_hist_kept = hist.size();
+    if (constrained) for (size_t i = 0; i < n_allowed; i++) if (allowed[i] >= 0 && allowed[i] < (int64_t)V) hist.push_back((int)allowed[i]);   // one upload: history, then the set
     cudaStream_t st = rt().stream;
     size_t tmp_bytes = 0;
     SPT_CUDA(cub::DeviceRadixSort::SortPairsDescending(nullptr, tmp_bytes, (const float*)nullptr, (float*)nullptr, (const int*)nullptr, (int*)nullptr, V, 0, 32, st));
@@ -142,11 +154,14 @@ int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dty
     int h_count = 0;
     do {
         if (!hist.empty() && cudaMemcpyAsync(hist_d, hist.data(), hist.size() * 4, cudaMemcpyHostToDevice, st) != cudaSuccess) { rc = fail("sampling_candidates: history upload failed"); break; }
-        const size_t smem = (size_t)((V + 31) / 32) * 4;
+        const size_t smem = (size_t)((V + 31) / 32) * 4 * (constrained ? 2 : 1);
+        // a constraint with an empty set leaves nothing: the pointer is what switches the filter on
+        const int* allow_d = constrained ? hist_d + n_hist_kept : nullptr;
+        const int n_allow = constrained ? (int)(hist.size() - n_hist_kept) : 0;
         if (dtype == SPT_BF16)
-            sampling_prep_kernel<__nv_bfloat16><<<1, kSampThreads, smem, st>>>((const __nv_bfloat16*)logits, V, temp, pen, hist_d, (int)hist.size(), keys, ids, counters);
+            sampling_prep_kernel<__nv_bfloat16><<<1, kSampThreads, smem, st>>>((const __nv_bfloat16*)logits, V, temp, pen, hist_d, (int)n_hist_kept, allow_d, n_allow, keys, ids, counters);
         else
-            sampling_prep_kernel<float><<<1, kSampThreads, smem, st>>>((const float*)logits, V, temp, pen, hist_d, (int)hist.size(), keys, ids, counters);
+            sampling_prep_kernel<float><<<1, kSampThreads, smem, st>>>((const float*)logits, V, temp, pen, hist_d, (int)n_hist_kept, allow_d, n_allow, keys, ids, counters);
         if (cudaGetLastError() != cudaSuccess) { rc = fail("sampling_candidates: prep launch failed"); break; }
         if (cub::DeviceRadixSort::SortPairsDescending(tmp, tmp_bytes, keys, keys_s, ids, ids_s, V, 0, 32, st) != cudaSuccess) { rc = fail("sampling_candidates: sort failed"); break; }
         sampling_finish_kernel<<<1, kSampThreads, 0, st>>>(keys_s, counters, k, tp, probs, counters + 1);
@@ -165,6 +180,21 @@ int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dty
     sptorch_free(ws);
     note_submit();
     return rc;
+}
+
+int sptorch_ext_sampling_candidates(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
+                                    float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
+                                    int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count) {
+    return sampling_impl(logits, n_logits, dtype, vocab_size, temperature, top_k, top_p, repetition_penalty, history, n_history, nullptr, 0, false,
+                         out_ids, out_logits, out_probs, capacity, count);
+}
+
+int sptorch_ext_sampling_candidates_constrained(const void* logits, size_t n_logits, int dtype, size_t vocab_size, float temperature, size_t top_k,
+                                                float top_p, float repetition_penalty, const int64_t* history, size_t n_history,
+                                                const int64_t* allowed, size_t n_allowed,
+                                                int32_t* out_ids, float* out_logits, float* out_probs, size_t capacity, size_t* count) {
+    return sampling_impl(logits, n_logits, dtype, vocab_size, temperature, top_k, top_p, repetition_penalty, history, n_history, allowed, n_allowed, true,
+                         out_ids, out_logits, out_probs, capacity, count);
 }
 
 // sample_from_candidates (nn/src/lib.rs:2420-2429) given the caller's uniform draw in [0, 1): host arithmetic only

@@ -39,6 +39,7 @@ class GPT:
         self._logits = None
         self._ids = None
         self._gen_ctx = None
+        self._prompt_len = 0
         self.kv_cache_enabled = False
 
     def close(self):
@@ -198,10 +199,11 @@ class GPT:
         return _lib_view(self.b, d_log, 0, self.ldl, self.es)
 
     def decode_next_token(self, tokens: list, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
-                          eos_token_id=None, draw=None):
+                          eos_token_id=None, draw=None, constraint=None):
         """One step of decode_next_token_inner (nn/src/lib.rs:2431-2464) on ``tokens`` (prompt + generated so far, extended in
         place).  Returns (token or None, candidates (ids, logits, probs), stop_reason) with the reference's stop reasons.
-        ``draw`` supplies the uniform numbers in [0, 1) of sample_from_candidates; default: numpy's global generator."""
+        ``draw`` supplies the uniform numbers in [0, 1) of sample_from_candidates; default: numpy's global generator.
+        ``constraint``: the reference's TokenConstraint as a callable generated_tokens -> set of allowed ids, or None for no limit."""
         V = self.cfg["vocab"] if vocab_size is None else vocab_size
         if V <= 0:
             raise HalError("vocab_size must be positive")                        # the reference asserts
@@ -209,8 +211,9 @@ class GPT:
             return None, (np.zeros(0, np.int32),) * 3, "AlreadyEnded"
         context = tokens[-self.cfg["seq_len"]:]                                  # InferenceState::context (nn/src/lib.rs:2242-2248)
         row = self._last_logits_device(context)
+        allowed = constraint(tokens[self._prompt_len:]) if constraint is not None else None
         cand = self.b.sampling_candidates(row, vocab_size=V, temperature=temperature, top_k=top_k, top_p=top_p,
-                                          repetition_penalty=repetition_penalty, history=tokens, dtype=self.dtype)
+                                          repetition_penalty=repetition_penalty, history=tokens, dtype=self.dtype, allowed=allowed)
         if not len(cand[0]):
             return None, cand, "NoCandidates"
         u = float(np.random.random() if draw is None else draw())
@@ -219,7 +222,7 @@ class GPT:
         return nxt, cand, ("EosToken" if nxt == eos_token_id else "NotStopped")
 
     def generate(self, prompt, max_new_tokens: int, vocab_size=None, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
-                 eos_token_id=None, draw=None) -> list:
+                 eos_token_id=None, draw=None, constraint=None) -> list:
         """generate_with_config (nn/src/lib.rs:2526-2553, 2584-2593): prompt + up to max_new_tokens sampled tokens; stops after an
         end-of-sequence token or when no candidate is left; a prompt that already ends with it is returned unchanged.
         ``top_k=1`` is the reference's greedy configuration."""
@@ -228,10 +231,12 @@ class GPT:
             self.kv_cache_enabled = True
         self._gen_ctx = None
         tokens = [int(t) for t in prompt]
+        self._prompt_len = len(tokens)
         if eos_token_id is not None and tokens and tokens[-1] == eos_token_id:
             return tokens
         for _ in range(max_new_tokens):
-            nxt, _, reason = self.decode_next_token(tokens, vocab_size, temperature, top_k, top_p, repetition_penalty, eos_token_id, draw)
+            nxt, _, reason = self.decode_next_token(tokens, vocab_size, temperature, top_k, top_p, repetition_penalty, eos_token_id, draw,
+                                                    constraint)
             if nxt is None or reason != "NotStopped":
                 break
         return tokens

@@ -47,6 +47,10 @@ def test_generation_length_eos_and_window(backend, cls):
     # a vocabulary cut that leaves nothing finite: every logit masked by the penalty-free -inf is impossible here, so cut to the
     # sampled distribution instead: with all mass on one candidate any draw returns it
     assert m.generate([0], 3, vocab_size=6, top_p=0.0, draw=lambda: 0.999) == [0, 1, 2, 3]
+    # a constraint (TokenConstraint::allowed_next on the generated tokens, nn/src/lib.rs:2465-2480): only even tokens allowed, then nothing
+    assert m.generate([0], 3, vocab_size=6, top_k=1, constraint=lambda gen: {0, 2, 4}) [1:] != [1, 2, 3]
+    out = m.generate([0], 5, vocab_size=6, top_k=1, constraint=lambda gen: {2, 4} if len(gen) < 2 else set())
+    assert len(out) == 3 and set(out[1:]) <= {2, 4}                   # stops with NoCandidates when the set is empty
     m.close()
 
 

@@ -114,3 +114,18 @@ def test_sampling_candidates_vs_oracle(backend, oracle, V, k, p, t, rp):
     want = oracle.sampling_candidates(xb, temperature=t, top_k=k, top_p=1.0, repetition_penalty=rp, history=hist)
     got = backend.sampling_candidates(xb, temperature=t, top_k=k, top_p=1.0, repetition_penalty=rp, history=hist, dtype=BF16)
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+
+
+def test_constrained_sampling_vs_oracle(backend, oracle):
+    """A TokenConstraint's allowed set (filtered_step_logits, crates/nn/src/lib.rs:2465-2480) applied before the candidates are built."""
+    rng = np.random.default_rng(9)
+    V = 5000
+    x = (rng.standard_normal(V) * 3).astype(np.float32)
+    allowed = set(int(t) for t in rng.integers(0, V, 40))
+    for k, p in ((0, 1.0), (5, 1.0), (0, 0.6)):
+        want = oracle.sampling_candidates(x, top_k=k, top_p=p, temperature=0.9, repetition_penalty=1.2, history=[1, 2, 3], allowed=allowed)
+        got = backend.sampling_candidates(x, top_k=k, top_p=p, temperature=0.9, repetition_penalty=1.2, history=[1, 2, 3], allowed=allowed)
+        assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.allclose(got[2], want[2], rtol=2e-6)
+        assert set(got[0]) <= allowed
+    assert len(backend.sampling_candidates(x, allowed=set())[0]) == 0            # an empty set leaves no candidate (NoCandidates)
+    assert len(backend.sampling_candidates(x, allowed=None)[0]) == V
