@@ -275,6 +275,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t chunk_seq = 0;                              // chunks this warp has staged so far (buffer parity)
         uint32_t tile_par = 0, tile_seq = 0;
         bool ok = true;
+        const bool has_bias = p.bias != nullptr;
+        if (!has_bias) {
+            bias_s[eidx] = 0.0f; bias_s[256 + eidx] = 0.0f;
+            mbar_arrive(bar_bias);
+            ok = mbar_wait(bar_bias, 0, abort_flag, p.status, kErrEpilogueWait);
+        }
         const uint32_t tempty0 = PAIR ? mapa(bar_tempty, 0) : bar_tempty;     // where a drained accumulator is reported
         auto release_acc = [&](int a) {
             tc_fence_before();
@@ -327,12 +333,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
             uint32_t v[32];
             if (c_begin < c_end) tmem_ld_32x32(t_row + c_begin * 32, v);
-            // publish the bias tile to the 8 epilogue warps (an mbarrier, not bar.sync: its wait is bounded)
-            bias_s[tile_par * 256 + eidx] = bval;
-            mbar_arrive(bar_bias + 8 * tile_par);
-            ok = mbar_wait(bar_bias + 8 * tile_par, (tile_seq >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
-            if (!ok) break;
-            tile_seq++;
+            // publish the bias tile to the 8 epilogue warps (an mbarrier, not bar.sync: its wait is bounded).  Without a bias the
+            // tiles were zeroed once before the loop and the eight warps need not meet at every tile.
+            if (has_bias) {
+                bias_s[tile_par * 256 + eidx] = bval;
+                mbar_arrive(bar_bias + 8 * tile_par);
+                ok = mbar_wait(bar_bias + 8 * tile_par, (tile_seq >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
+                if (!ok) break;
+                tile_seq++;
+            }
             const float* bt = bias_s + tile_par * 256;
 #pragma unroll 1
             for (int c = c_begin; c < c_end; c++) {
