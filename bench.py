@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the GPT forward hot path (BASELINE config 4: GPT-2-small shape, global batch 64 x 1024
+"""Benchmark of the GPT forward hot path (workload c4_gpt2s: GPT-2-small shape, global batch 64 x 1024
 tokens, bf16 weights/activations, f32 accumulate), batch-sharded over N GPUs of one node.
 
     python bench.py --gpus N --steps K --warmup W              # this repository's CUDA path
@@ -161,7 +161,9 @@ def run_reference(args):
         "impl": "reference", "metric": "gpt_forward_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": cfg["batch"], "seq_len": T, "note": "CPU port of the reference arithmetic; the Rust reference cannot be built here"},
+        "config": {"workload": WORKLOAD, "global_batch": cfg["batch"], "seq_len": T, "sequences_per_step": n_seq,
+                   "note": "CPU port of the reference arithmetic; the Rust reference cannot be built here; a step is ONE sequence of the "
+                           "global batch (the reference has no batch dimension), tokens/s is comparable"},
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -170,14 +172,18 @@ def run_reference(args):
     return 0
 
 
-GEMM_DRAM_BYTES_PER_LAUNCH = 456.7e6
+# DRAM bytes (read + write) of ONE launch of the dominant GEMM per algorithmic byte, from a small ncu capture of a single
+# Linear launch (the W_up shape at 8192 rows, two launches captured); the bench scales it by the algorithmic bytes of the
+# launches it times.  None until such a capture of the current kernel exists.
+GEMM_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = None
 
 
 def gemm_bytes(cfg, nseq, T):
-    """Operand, residual and output bytes of the 61 Linear launches of one bf16 forward over nseq sequences."""
+    """Operand, residual and output bytes of the Linear launches (QKV, Wo, up, down per layer; LM head) of one bf16 forward over
+    nseq sequences."""
     d, F, V, L, M = cfg["d_model"], cfg["d_ff"], cfg["vocab"], cfg["n_layer"], nseq * T
     ldl = -(-V // 64) * 64
-    per_layer = (M * d + 2 * d * d + 2 * M * d) + (d * d + M * d + M * d) + (M * d + d * d + 2 * M * d) + (M * d + F * d + M * F) + (M * F + d * F + 2 * M * d)
+    per_layer = (M * d + 3 * d * d + 3 * M * d) + (M * d + d * d + 2 * M * d) + (M * d + F * d + M * F) + (M * F + d * F + 2 * M * d)
     return 2.0 * (L * per_layer + M * d + V * d + M * ldl)
 
 
@@ -277,9 +283,20 @@ def run_ours(args):
         b.synchronize()
         dt = time.perf_counter() - t0
         dt = max_over_ranks(dt)
+        # the roof of this call: the same bytes as one plain contiguous device-to-host copy into the same pinned buffer, all ranks at once
+        barrier()
+        t0 = time.perf_counter()
+        b._check(lib.sptorch_ext_copy_d2h_bytes(d_logits.handle, out_pinned, out_bytes), "d2h roof")
+        dt_copy = max_over_ranks(time.perf_counter() - t0)
         e2e = {"value": tokens_per_step * e2e_steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(GB * T * 4),
                "d2h_bytes_per_step": int(GB * T * V * 2), "steps": e2e_steps, "chunk_sequences": chunk,
-               "api": "sptorch_ext_gpt_forward_host (pinned ids in, dense bf16 logits [B*T,V] out)"}
+               "ms_per_step": 1e3 * dt / e2e_steps,
+               "d2h_gbs": GB * T * V * 2 * e2e_steps / dt / 1e9,
+               "d2h_peak_gbs": world * out_bytes / dt_copy / 1e9,
+               "d2h_peak_note": "one contiguous cudaMemcpyAsync of this rank's logits bytes into the same pinned buffer, all ranks at the same time "
+                                "(whole-job GB/s, max time over ranks): the end-to-end call cannot be faster than this copy",
+               "api": "sptorch_ext_gpt_forward_host (pinned ids in, dense bf16 logits [B*T,V] out; the padded logits are compacted on the device "
+                      "and leave as one contiguous copy per micro-batch, overlapped with the next micro-batch's compute)"}
         lib.sptorch_ext_free_pinned(ids_pinned)
         lib.sptorch_ext_free_pinned(out_pinned)
     barrier()
@@ -311,11 +328,11 @@ def run_ours(args):
                                    "(the first pass, which gives `value`, replays a CUDA graph and cannot be instrumented per kernel)",
                          "eager_pass_ms_per_step": ms_eager / args.steps,
                          "algorithmic_flop_per_step_this_rank": lin_flop,
-                         # DRAM bytes per GEMM launch (read + write, mean over the 61 launches of one full-size forward at batch 64
-                         # on one GPU) from the single-pass ncu capture summarised in profiles/dram_traffic_gpt_forward_c4.md;
-                         # it scales with the sequences a rank holds, so it is given for the 1-GPU shard only
-                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH if nseq == GB else None,
+                         "traffic": (GEMM_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE * gemm_bytes(cfg, nseq, T) / max(lin_launches, 1)
+                                     if GEMM_DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE else None),
                          "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)",
+                         "traffic_source": "ratio of DRAM bytes to algorithmic bytes measured by ncu on one small Linear launch of the same kernel, "
+                                           "times the algorithmic bytes per launch of this run (DRAM traffic of this kernel grows with the bytes it streams)",
                          "algorithmic_bytes_per_launch": gemm_bytes(cfg, nseq, T) / max(lin_launches, 1)},
             "breakdown": breakdown,
             "whole_forward": {"algorithmic_tflop_per_step": (lin_flop + attn_flop) * world / 1e12,
@@ -323,8 +340,16 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(cfg, T)
-        print(json.dumps(line), flush=True)
     model.close()
+    # ---- the rest of the record: op sweeps on one GPU, the tensor-parallel split on several ----
+    if world == 1 and args.sweeps:
+        line["sweeps"] = compact_sweeps(b, read_peaks(), args.sweep_iters)
+    if world > 1 and args.tp:
+        rec = tp_measure(b, rank, world, dist, max(2, min(args.steps, 5)), args.warmup, layers=args.layers)
+        if rank == 0:
+            line["c5_tp"] = rec
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     b.close()
     if dist is not None:
         dist.destroy_process_group()
@@ -422,102 +447,261 @@ def sweep_abi(args, b):
     return out
 
 
+LINEAR_SWEEP_SHAPES = [(M, K, N) for M in (512, 4096, 16384) for (K, N) in ((768, 768), (768, 3072), (3072, 768), (4096, 4096))]
+ATTENTION_SWEEP_SHAPES = [(64, 1024, 12, 64), (16, 2048, 16, 128)]       # one layer of c4_gpt2s and of c5_1p3b
+
+
+def sweep_linear(b, peaks, iters, shapes=None, emit=None):
+    """Standalone Linear y = x W^T + b at the sweep's shapes, bf16 and TF32: TFLOP/s and the fraction of the measured burst peak."""
+    from sptorch_b200.backend import BF16, F32, MM_BF16, MM_TF32
+    lib, out = b.lib, []
+    for (M, K, N) in (shapes or LINEAR_SWEEP_SHAPES):
+        for mode, name, es in ((MM_BF16, "bf16", 2), (MM_TF32, "tf32", 4)):
+            x, w, y = b.alloc(M * K, es), b.alloc(N * K, es), b.alloc(M * N, es)
+            bias = b.alloc(N)
+            _fill(b, x, M * K, es, 1); _fill(b, w, N * K, es, 2, std=0.02); _fill(b, bias, N, 4, 3, std=0.01)
+            fn = lambda: b._check(lib.sptorch_ext_linear(x.handle, w.handle, bias.handle, None, y.handle, M, K, N, 0, C.c_float(1.0), 0, mode,
+                                                         BF16 if mode == MM_BF16 else F32), "linear")
+            med, best = _time_op(b, fn, iters)
+            tf = 2.0 * M * K * N / (med * 1e-3) / 1e12
+            peak = peaks["tf"] if mode == MM_BF16 else peaks["tf"] / 2
+            out.append({"op": "linear", "M": M, "K": K, "N": N, "mode": name, "ms": med, "ms_best": best, "tflops": tf,
+                        "frac": tf / peak, "peak": peak, "peak_note": f"{peaks['source']} burst cuBLAS bf16" + ("" if mode == MM_BF16 else " / 2 (TF32 runs at half the bf16 rate)"),
+                        "frac_nominal": tf / (2250.0 if mode == MM_BF16 else 1125.0)})
+            if emit:
+                emit(out[-1])
+            for buf in (x, w, y, bias):
+                buf.free()
+    return out
+
+
+def sweep_attention(b, peaks, iters, shapes=None, emit=None):
+    """Causal attention core of one layer (bf16, fused kernel): TFLOP/s on the causal-necessary FLOP."""
+    from sptorch_b200.backend import BF16
+    lib, out = b.lib, []
+    for (B_, T_, H_, hd_) in (shapes or ATTENTION_SWEEP_SHAPES):
+        d_ = H_ * hd_
+        q, k, v, o = (b.alloc(B_ * T_ * d_, 2) for _ in range(4))
+        for i, buf in enumerate((q, k, v)):
+            _fill(b, buf, B_ * T_ * d_, 2, 20 + i)
+        ws = b.alloc(lib.sptorch_ext_attention_workspace(B_, T_, H_, hd_, BF16), 1)
+        fn = lambda: b._check(lib.sptorch_ext_attention_causal(q.handle, k.handle, v.handle, o.handle, ws.handle, B_, T_, H_, hd_, d_, BF16), "attention")
+        med, best = _time_op(b, fn, iters)
+        flop = 2.0 * B_ * H_ * T_ * (T_ + 1) * hd_
+        out.append({"op": "attention_causal", "B": B_, "T": T_, "H": H_, "hd": hd_, "dtype": "bf16", "ms": med, "ms_best": best,
+                    "tflops": flop / (med * 1e-3) / 1e12, "frac": flop / (med * 1e-3) / 1e12 / peaks["tf"], "peak": peaks["tf"],
+                    "note": "FLOP counted on the causal-necessary half (2 T (T+1) hd per sequence and head)"})
+        if emit:
+            emit(out[-1])
+        for buf in (q, k, v, o, ws):
+            buf.free()
+    return out
+
+
+def sweep_rowops(b, peaks, iters, emit=None):
+    """LayerNorm (65536 rows of 768 / 2048 / 4096), causal softmax [16, 12, 1024, 1024] and GELU over 64 Mi elements, f32 and bf16:
+    achieved GB/s on the minimal necessary traffic and the fraction of the measured copy bandwidth."""
+    from sptorch_b200.backend import BF16, F32
+    lib, out = b.lib, []
+
+    def rec(entry):
+        out.append(entry)
+        if emit:
+            emit(entry)
+
+    for dim in (768, 2048, 4096):
+        for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+            rows = 65536
+            x, y = b.alloc(rows * dim, es), b.alloc(rows * dim, es)
+            g, be = b.upload(np.ones(dim, np.float32)), b.upload(np.zeros(dim, np.float32))
+            _fill(b, x, rows * dim, es, 4, mean=0.5, std=3.0)
+            fn = lambda: b._check(lib.sptorch_ext_layernorm(x.handle, g.handle, be.handle, y.handle, rows, dim, C.c_float(1e-5), dt), "layernorm")
+            med, best = _time_op(b, fn, iters)
+            nbytes = 2 * rows * dim * es + 2 * dim * 4
+            rec({"op": "layernorm", "rows": rows, "dim": dim, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+                 "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
+            for buf in (x, y, g, be):
+                buf.free()
+    for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+        B_, H_, T_ = 16, 12, 1024
+        n = B_ * H_ * T_ * T_
+        x, y = b.alloc(n, es), b.alloc(n, es)
+        _fill(b, x, n, es, 5, std=2.0)
+        fn = lambda: b._check(lib.sptorch_ext_causal_softmax(x.handle, y.handle, B_ * H_, T_, C.c_float(1.0), dt), "causal_softmax")
+        med, best = _time_op(b, fn, iters)
+        nbytes = (T_ * (T_ + 1) // 2 + T_ * T_) * B_ * H_ * es
+        rec({"op": "causal_softmax", "shape": [B_, H_, T_, T_], "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes, "full_read_bytes": 2 * n * es})
+        x.free(); y.free()
+    for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
+        n = 64 << 20
+        x, y = b.alloc(n, es), b.alloc(n, es)
+        _fill(b, x, n, es, 6)
+        fn = lambda: b._check(lib.sptorch_ext_gelu(x.handle, y.handle, n, dt), "gelu")
+        med, best = _time_op(b, fn, iters)
+        nbytes = 2 * n * es
+        rec({"op": "gelu", "n": n, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
+             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
+        x.free(); y.free()
+    return out
+
+
+def compact_sweeps(b, peaks, iters):
+    """The three sweeps in the short form the bench line carries: one entry per case with its time and fraction of the roof
+    (Linear and attention: measured burst bf16 tensor peak, TF32 against half of it; row ops: measured copy bandwidth)."""
+    lin = sweep_linear(b, peaks, iters)
+    att = sweep_attention(b, peaks, iters)
+    row = sweep_rowops(b, peaks, iters)
+    r3 = lambda v: float(f"{v:.4g}")
+    return {
+        "timing": f"median of {iters} launches, CUDA events on the library stream, 256 MiB L2 flush before each launch, 3 warm-up launches",
+        "linear": [{"M": e["M"], "K": e["K"], "N": e["N"], "mode": e["mode"], "ms": r3(e["ms"]), "tflops": r3(e["tflops"]), "frac": r3(e["frac"])} for e in lin],
+        "linear_roof": f"{peaks['tf']} TFLOP/s bf16 ({peaks['source']} burst), TF32 against half of it",
+        "attention": [{"B": e["B"], "T": e["T"], "H": e["H"], "hd": e["hd"], "ms": r3(e["ms"]), "tflops": r3(e["tflops"]), "frac": r3(e["frac"])} for e in att],
+        "rowops": [{"op": e["op"], "dtype": e["dtype"], **({"dim": e["dim"]} if "dim" in e else {}), "ms": r3(e["ms"]), "gbs": r3(e["gbs"]), "frac": r3(e["frac"])} for e in row],
+        "rowops_roof": f"{peaks['hbm']} GB/s ({peaks['source']} copy bandwidth)",
+    }
+
+
 def run_sweep(args):
-    """BASELINE config 2 (standalone Linear) and config 3 (row ops): one JSON line per case."""
+    """The standalone Linear sweep, the row-op sweep and the attention core: one JSON line per case."""
     os.environ.setdefault("SPTORCH_B200_DEVICE", "0")
-    from sptorch_b200.backend import BF16, F32, MM_BF16, MM_TF32, FfiBackend
+    from sptorch_b200.backend import FfiBackend
     b = FfiBackend.load()
-    lib = b.lib
     peaks = read_peaks()
-    out = []
+    emit = lambda e: print(json.dumps(e), flush=True)
+    one = [tuple(int(v) for v in args.shape.split(","))] if args.shape else None
     if args.sweep in ("linear", "all"):
-        shapes = [(M, K, N) for M in (512, 4096, 16384) for (K, N) in ((768, 768), (768, 3072), (3072, 768), (4096, 4096))]
-        if args.shape:
-            shapes = [tuple(int(v) for v in args.shape.split(","))]
-        for (M, K, N) in shapes:
-            for mode, name, es in ((MM_BF16, "bf16", 2), (MM_TF32, "tf32", 4)):
-                x, w, y = b.alloc(M * K, es), b.alloc(N * K, es), b.alloc(M * N, es)
-                bias = b.alloc(N)
-                _fill(b, x, M * K, es, 1); _fill(b, w, N * K, es, 2, std=0.02); _fill(b, bias, N, 4, 3, std=0.01)
-                fn = lambda: b._check(lib.sptorch_ext_linear(x.handle, w.handle, bias.handle, None, y.handle, M, K, N, 0, C.c_float(1.0), 0, mode,
-                                                             BF16 if mode == MM_BF16 else F32), "linear")
-                med, best = _time_op(b, fn, args.iters)
-                tf = 2.0 * M * K * N / (med * 1e-3) / 1e12
-                peak = peaks["tf"] if mode == MM_BF16 else peaks["tf"] / 2
-                out.append({"op": "linear", "M": M, "K": K, "N": N, "mode": name, "ms": med, "ms_best": best, "tflops": tf,
-                            "frac": tf / peak, "peak": peak, "peak_note": f"{peaks['source']} burst cuBLAS bf16" + ("" if mode == MM_BF16 else " / 2 (TF32 runs at half the bf16 rate)"),
-                            "frac_nominal": tf / (2250.0 if mode == MM_BF16 else 1125.0)})
-                print(json.dumps(out[-1]), flush=True)
-                for buf in (x, w, y, bias):
-                    buf.free()
+        sweep_linear(b, peaks, args.iters, one if args.sweep == "linear" else None, emit)
     if args.sweep == "abi":
         sweep_abi(args, b)
     if args.sweep in ("attention", "all"):
-        # causal attention core of one layer: BASELINE config 4 (12 heads x 64) and config 5 (16 heads x 128) shapes, bf16
-        shapes = [(64, 1024, 12, 64), (16, 2048, 16, 128)]
-        if args.shape:
-            shapes = [tuple(int(v) for v in args.shape.split(","))]
-        for (B_, T_, H_, hd_) in shapes:
-            d_ = H_ * hd_
-            q, k, v, o = (b.alloc(B_ * T_ * d_, 2) for _ in range(4))
-            for i, buf in enumerate((q, k, v)):
-                _fill(b, buf, B_ * T_ * d_, 2, 20 + i)
-            ws = b.alloc(lib.sptorch_ext_attention_workspace(B_, T_, H_, hd_, BF16), 1)
-            fn = lambda: b._check(lib.sptorch_ext_attention_causal(q.handle, k.handle, v.handle, o.handle, ws.handle, B_, T_, H_, hd_, d_, BF16), "attention")
-            med, best = _time_op(b, fn, args.iters)
-            flop = 2.0 * B_ * H_ * T_ * (T_ + 1) * hd_
-            out.append({"op": "attention_causal", "B": B_, "T": T_, "H": H_, "hd": hd_, "dtype": "bf16", "ms": med, "ms_best": best,
-                        "tflops": flop / (med * 1e-3) / 1e12, "frac": flop / (med * 1e-3) / 1e12 / peaks["tf"], "peak": peaks["tf"],
-                        "note": "includes the V transpose kernel; FLOP counted on the causal-necessary half"})
-            print(json.dumps(out[-1]), flush=True)
-            for buf in (q, k, v, o, ws):
-                buf.free()
+        sweep_attention(b, peaks, args.iters, one if args.sweep == "attention" else None, emit)
     if args.sweep in ("rowops", "all"):
-        for dim in (768, 2048, 4096):
-            for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
-                rows = 65536
-                x, y = b.alloc(rows * dim, es), b.alloc(rows * dim, es)
-                g, be = b.upload(np.ones(dim, np.float32)), b.upload(np.zeros(dim, np.float32))
-                _fill(b, x, rows * dim, es, 4, mean=0.5, std=3.0)
-                fn = lambda: b._check(lib.sptorch_ext_layernorm(x.handle, g.handle, be.handle, y.handle, rows, dim, C.c_float(1e-5), dt), "layernorm")
-                med, best = _time_op(b, fn, args.iters)
-                nbytes = 2 * rows * dim * es + 2 * dim * 4
-                out.append({"op": "layernorm", "rows": rows, "dim": dim, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-                            "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
-                print(json.dumps(out[-1]), flush=True)
-                for buf in (x, y, g, be):
-                    buf.free()
-        for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
-            B_, H_, T_ = 16, 12, 1024
-            n = B_ * H_ * T_ * T_
-            x, y = b.alloc(n, es), b.alloc(n, es)
-            _fill(b, x, n, es, 5, std=2.0)
-            fn = lambda: b._check(lib.sptorch_ext_causal_softmax(x.handle, y.handle, B_ * H_, T_, C.c_float(1.0), dt), "causal_softmax")
-            med, best = _time_op(b, fn, args.iters)
-            nbytes = (T_ * (T_ + 1) // 2 + T_ * T_) * B_ * H_ * es
-            out.append({"op": "causal_softmax", "shape": [B_, H_, T_, T_], "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-                        "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes,
-                        "full_read_bytes": 2 * n * es})
-            print(json.dumps(out[-1]), flush=True)
-            x.free(); y.free()
-        for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
-            n = 64 << 20
-            x, y = b.alloc(n, es), b.alloc(n, es)
-            _fill(b, x, n, es, 6)
-            fn = lambda: b._check(lib.sptorch_ext_gelu(x.handle, y.handle, n, dt), "gelu")
-            med, best = _time_op(b, fn, args.iters)
-            nbytes = 2 * n * es
-            out.append({"op": "gelu", "n": n, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-                        "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
-            print(json.dumps(out[-1]), flush=True)
-            x.free(); y.free()
+        sweep_rowops(b, peaks, args.iters, emit)
     b.close()
     return 0
 
 
+def _load_timing_weights(model, cfg, seed=0):
+    """Weights for a timing run of a model too large to draw element by element on every rank: each matrix is a seeded
+    4 Mi-element N(0, 0.02) block repeated to size (residual projections scaled by 1/sqrt(2 L), biases 0, gamma 1, beta 0),
+    uploaded one parameter at a time.  Parity runs use synth.gpt_params instead."""
+    block = synth.normal(seed, 1 << 22, 0.0, 0.02)
+    rs = np.float32(1.0 / np.sqrt(2.0 * cfg["n_layer"]))
+    for i, (name, shape) in enumerate(model.named_parameters()):
+        n = int(np.prod(shape))
+        if name.endswith(".gamma"):
+            w = np.ones(n, np.float32)
+        elif name.endswith(".beta") or name.endswith(".bias"):
+            w = np.zeros(n, np.float32)
+        else:
+            w = np.resize(np.roll(block, 7919 * i), n)
+            if name.endswith("attn.wo.weight") or name.endswith("ffn_down.weight"):
+                w = w * rs
+        model.set_param(name, w)
+
+
+def _nccl_for_model(b, lib, dist, rank, world, model):
+    uid = C.create_string_buffer(128)
+    if rank == 0:
+        b._check(lib.sptorch_ext_nccl_unique_id(None, uid), "nccl_unique_id")
+    box = [uid.raw]
+    dist.broadcast_object_list(box, src=0)
+    uid = C.create_string_buffer(box[0], 128)
+    b._check(lib.sptorch_ext_nccl_init(None, uid, rank, world), "nccl_init")
+
+
+def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overlap=0, sm_reserve=16, check_only=False):
+    """Tensor-parallel forward over the launched ranks (wq/wk/wv/ffn_up split by rows, wo/ffn_down along K, one NCCL all-reduce per
+    attention and per MLP block).  Two parts: a small model (d 256, 4 heads, 2 layers) whose logits are compared with the CPU
+    oracle on rank 0, and -- unless check_only -- the 1.3B shape c5_1p3b (vocab 50257, d 2048, 24 layers, 16 heads of 128,
+    d_ff 8192, batch 16 x 2048 tokens, bf16) timed on the device, max over ranks.  Returns the record rank 0 prints."""
+    import torch
+    from sptorch_b200.backend import BF16
+    from sptorch_b200.gpt import GPT
+    lib = b.lib
+    if world > 1:
+        _nccl_for_model(b, lib, dist, rank, world, None)
+    rec = {}
+    # ---- parity of the partition on a small model ----
+    cfg = dict(vocab=1000, d_model=256, n_layer=2, n_head=4 if world <= 4 else 8, d_ff=1024, seq_len=256, batch=2, ctx=256)
+    model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16,
+                max_batch=2, tp_rank=rank, tp_size=world)
+    params, index = synth.gpt_params(cfg, 0, residual_scale=True, randomize_affine=True)
+    model.load_flat(params, index)
+    if world > 1:
+        b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
+    ids = synth.randint(1, 2 * 256, cfg["vocab"]).reshape(2, 256).astype(np.int32)
+    out = model.forward(ids)
+    model.close()
+    if rank == 0:
+        from oracle import binding as O
+        O.build()
+        ref = O.gpt_forward(cfg, params, ids, fast=1, threads=host_threads())
+        err = float(np.abs(out - ref).max() / np.abs(ref).max())
+        rec.update({"tp_size": world, "check_model": "vocab 1000, d 256, 2 layers, %d heads, d_ff 1024, 2 x 256 tokens, bf16" % cfg["n_head"],
+                    "max_rel_err_vs_oracle": err, "tolerance": 2e-2, "check_ok": bool(err <= 2e-2)})
+    if check_only:
+        if world > 1:
+            lib.sptorch_ext_nccl_shutdown()
+        return rec
+    # ---- the 1.3B shape, timed ----
+    cfg = dict(synth.CONFIGS["c5_1p3b"])
+    if layers:
+        cfg["n_layer"] = layers
+    T, B = cfg["ctx"], batch or cfg["batch"]
+    model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16,
+                max_batch=B, tp_rank=rank, tp_size=world)
+    _load_timing_weights(model, cfg)
+    if world > 1:
+        b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
+        b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, int(tp_overlap)), "tp_overlap")
+        if tp_overlap:
+            b._check(lib.sptorch_ext_set_sm_reserve(sm_reserve), "sm_reserve")
+    ids = synth.randint(1, B * T, cfg["vocab"]).reshape(B, T).astype(np.int32)
+    d_ids, d_logits = model.stage_ids(ids), model.logits_buffer(B * T)
+
+    def sync():
+        b.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(warmup, 3)):
+        model.forward_device(d_ids, B, T, d_logits)
+    sync()
+    lib.sptorch_ext_prof_enable(1); lib.sptorch_ext_prof_read(None, None, 0)
+    b.timer_begin()
+    for _ in range(steps):
+        model.forward_device(d_ids, B, T, d_logits)
+    ms = b.timer_end()
+    sync()
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+    pm, pn = (C.c_float * 7)(), (C.c_uint32 * 7)()
+    lib.sptorch_ext_prof_read(pm, pn, 7); lib.sptorch_ext_prof_enable(0)
+    if tp_overlap:
+        b._check(lib.sptorch_ext_set_sm_reserve(0), "sm_reserve")
+    model.close()
+    if world > 1:
+        lib.sptorch_ext_nccl_shutdown()
+    if rank == 0:
+        cats = ["linear_gemm", "attention_gemm", "causal_softmax", "layernorm", "embedding", "allreduce_and_other", "attention_fused"]
+        lin, attn = flops_per_forward(cfg, B, T)
+        rec.update({"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}",
+                    "tp_overlap": bool(tp_overlap), "steps": steps, "ms_per_step": ms / steps, "tokens_per_s": B * T * steps / (ms * 1e-3),
+                    "achieved_tflops_whole_job": (lin + attn) / (ms / steps * 1e-3) / 1e12,
+                    "allreduce_ms_per_step_rank0": float(pm[5]) / steps, "allreduces_per_step": 2 * cfg["n_layer"],
+                    "allreduce_bytes_each": B * T * cfg["d_model"] * 2,
+                    "breakdown_rank0_ms": {c: float(pm[i]) / steps for i, c in enumerate(cats) if pn[i]},
+                    "weights": "seeded N(0,0.02) block repeated per matrix (timing only; parity is the small check model above)"})
+    return rec
+
+
 def run_tp(args):
-    """Tensor-parallel forward (BASELINE config 5 shape, or a small model checked against the oracle with --workload tp_check):
-    wq/wk/wv/ffn_up split by rows, wo/ffn_down along K, one NCCL all-reduce per attention and per MLP block."""
+    """Stand-alone tensor-parallel run (--workload c5_1p3b, or tp_check for the parity part alone)."""
     rank, local_rank, world = dist_env()
     import torch
     import torch.distributed as dist
@@ -525,70 +709,12 @@ def run_tp(args):
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    from sptorch_b200.backend import BF16, FfiBackend
-    from sptorch_b200.gpt import GPT
+    from sptorch_b200.backend import FfiBackend
     b = FfiBackend.load()
-    lib = b.lib
-    check = args.workload == "tp_check"
-    if check:
-        cfg = dict(vocab=1000, d_model=256, n_layer=2, n_head=4, d_ff=1024, seq_len=256, batch=2, ctx=256)
-    else:
-        cfg = dict(synth.CONFIGS["c5_1p3b"])
-        if args.layers:
-            cfg["n_layer"] = args.layers
-    T, B = cfg["ctx"], args.batch or cfg["batch"]
-    model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16,
-                max_batch=B, tp_rank=rank, tp_size=world)
-    params, index = synth.gpt_params(cfg, 0, residual_scale=True, randomize_affine=check)
-    model.load_flat(params, index)
-    if world > 1:
-        uid = C.create_string_buffer(128)
-        if rank == 0:
-            b._check(lib.sptorch_ext_nccl_unique_id(None, uid), "nccl_unique_id")
-        box = [uid.raw]
-        dist.broadcast_object_list(box, src=0)
-        uid = C.create_string_buffer(box[0], 128)
-        b._check(lib.sptorch_ext_nccl_init(None, uid, rank, world), "nccl_init")
-        b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
-        b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, int(args.tp_overlap)), "tp_overlap")
-        if args.tp_overlap:
-            b._check(lib.sptorch_ext_set_sm_reserve(args.sm_reserve), "sm_reserve")
-    ids = synth.randint(1, B * T, cfg["vocab"]).reshape(B, T).astype(np.int32)
-    if check:
-        out = model.forward(ids)
-        if rank == 0:
-            from oracle import binding as O
-            ref = O.gpt_forward(cfg, params, ids, fast=1, threads=host_threads())
-            err = float(np.abs(out - ref).max() / np.abs(ref).max())
-            print(json.dumps({"workload": "tp_check", "tp_size": world, "max_rel_err_vs_oracle": err, "tolerance": 2e-2, "ok": err <= 2e-2}), flush=True)
-    else:
-        del params
-        d_ids, d_logits = model.stage_ids(ids), model.logits_buffer(B * T)
-        sync = lambda: (b.synchronize(), torch.cuda.synchronize(), dist.barrier() if world > 1 else None, torch.cuda.synchronize())
-        for _ in range(max(args.warmup, 3)):
-            model.forward_device(d_ids, B, T, d_logits)
-        sync()
-        lib.sptorch_ext_prof_enable(1); lib.sptorch_ext_prof_read(None, None, 0)
-        b.timer_begin()
-        for _ in range(args.steps):
-            model.forward_device(d_ids, B, T, d_logits)
-        ms = b.timer_end()
-        sync()
-        if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
-        pm, pn = (C.c_float * 7)(), (C.c_uint32 * 7)()
-        lib.sptorch_ext_prof_read(pm, pn, 7); lib.sptorch_ext_prof_enable(0)
-        if rank == 0:
-            cats = ["linear_gemm", "attention_gemm", "causal_softmax", "layernorm", "embedding", "allreduce", "attention_fused"]
-            lin, attn = flops_per_forward(cfg, B, T)
-            print(json.dumps({"metric": "gpt_forward_tokens_per_s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-                              "steps": args.steps, "ms_per_step": ms / args.steps, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-                              "config": {"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}", "tp_overlap": bool(args.tp_overlap), "sm_reserve": args.sm_reserve if args.tp_overlap else 0},
-                              "achieved_tflops_whole_job": (lin + attn) / (ms / args.steps * 1e-3) / 1e12,
-                              "breakdown_rank0": {c: float(pm[i]) / args.steps for i, c in enumerate(cats) if pn[i]}}), flush=True)
-    model.close()
-    if world > 1:
-        lib.sptorch_ext_nccl_shutdown()
+    rec = tp_measure(b, rank, world, dist, args.steps, args.warmup, layers=args.layers, batch=args.batch, tp_overlap=args.tp_overlap,
+                     sm_reserve=args.sm_reserve, check_only=args.workload == "tp_check")
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
     b.close()
     if world > 1:
         dist.destroy_process_group()
@@ -605,7 +731,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=8, help="sequences per micro-batch of the host-buffer call")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "abi", "all"], help="standalone op sweeps (BASELINE configs 2 and 3) instead of the GPT step")
+    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "abi", "all"], help="standalone op sweeps (the standalone Linear and row-op sweeps) instead of the GPT step")
     ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
@@ -613,7 +739,10 @@ def main():
     ap.add_argument("--ln-fold", type=int, default=0, help="1: LayerNorm folded into the GEMM epilogues instead of separate kernels")
     ap.add_argument("--tp-overlap", type=int, default=0, help="tensor parallel: overlap the all-reduces with the other half of the batch")
     ap.add_argument("--sm-reserve", type=int, default=16, help="SMs left free for NCCL when --tp-overlap is on")
-    ap.add_argument("--layers", type=int, default=0, help="with --workload c5_1p3b: run fewer layers")
+    ap.add_argument("--layers", type=int, default=0, help="tensor-parallel model: run fewer than its 24 layers")
+    ap.add_argument("--sweeps", type=int, default=1, help="1 GPU: append the compact Linear / row-op / attention sweeps to the line (0 = skip)")
+    ap.add_argument("--sweep-iters", type=int, default=7, help="timed launches per case of the compact sweeps")
+    ap.add_argument("--tp", type=int, default=1, help="several GPUs: append the tensor-parallel record c5_tp to the line (0 = skip)")
     args = ap.parse_args()
     if args.sweep:
         return run_sweep(args)

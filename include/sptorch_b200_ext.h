@@ -118,9 +118,10 @@ int sptorch_ext_set_gemm_pair(int mode);
 /* No counterpart in the reference.  sptorch_matmul_f32 for callers that must not allocate device memory (fixed,
  * audited memory budgets; loops that may not touch the allocator; an exhausted pool): the transposed-B scratch is a
  * static 8 MiB array inside the library, so k * n is limited to 2,097,152 elements and larger products are rejected.
- * No cudaMalloc/cudaFree/pool call is made.  The first call on a device resolves the array's address and should come
- * before any stream capture.  All calls share the array (it keeps the last call's contents; none of it needs
- * clearing) -- calls that overlap on the GPU race. */
+ * No cudaMalloc/cudaFree/pool call is made.  The array's device address is resolved when the backend is initialised; if that
+ * lookup failed, the first call repeats it, so the first call should come before any stream capture.  All calls share the
+ * array (it keeps the last call's contents; none of it needs clearing) -- calls that overlap on the GPU, or that two host
+ * threads issue at the same time (their transpose and product kernels can interleave on the stream), race. */
 int sptorch_ext_matmul_f32_static(const void* a, const void* b, void* out, size_t m, size_t k, size_t n);
 
 int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const void* residual, void* out,
@@ -132,9 +133,6 @@ int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const
  * workspace of sptorch_ext_attention_workspace() bytes. */
 /* 0 (default): bf16 with head_dim 64 or 128 runs the fused kernel, everything else the materialised form; 1: always materialised */
 int sptorch_ext_set_attention_mode(int mode);
-/* diagnostics: with SPTORCH_B200_ATTN_PROF set in the environment, the last fused-attention launch's cycle counters of CTA 0
- * (8 phases of one softmax thread, 8 of the MMA-issuing thread) */
-int sptorch_ext_debug_attn_prof(unsigned long long* host16);
 size_t sptorch_ext_attention_workspace(size_t B, size_t T, size_t H, size_t hd, int dtype);
 int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, void* out, void* workspace,
                                  size_t B, size_t T, size_t H, size_t hd, size_t ld_qkv, int dtype);
@@ -191,14 +189,26 @@ int   sptorch_ext_gpt_launches(void* gpt, int batch, int T);
  * projections; the callee must enqueue a sum-all-reduce of n elements at buf onto cuda_stream. */
 typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_stream, void* user);
 /* 1: bf16 GPT models apply LayerNorm inside the epilogue of the GEMMs that consume it (weights pre-multiplied by gamma, a per-token
- * statistics pass instead of a normalising pass).  Default 0: on B200 the statistics passes save 0.57 ms per step of BASELINE
- * config 4 and the heavier epilogues cost 0.5 ms, so the step time does not move (19.2 ms either way). */
+ * statistics pass instead of a normalising pass).  Default 0: on B200 the statistics passes save 0.57 ms per step of the
+ * GPT-2-small-shape benchmark and the heavier epilogues cost 0.5 ms, so the step time does not move (19.2 ms either way). */
 int   sptorch_ext_gpt_enable_ln_fold(void* gpt, int on);
 /* tensor parallel: reduce one half of the batch on a second stream while the other half computes (default off: with
  * the statically scheduled persistent GEMM the SMs given up cost as much as the overlap gains; needs an even batch;
  * combine with sptorch_ext_set_sm_reserve so that the collective finds free SMs) */
 int   sptorch_ext_gpt_enable_tp_overlap(void* gpt, int on);
 int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
+/* The tensor-parallel shard rule that sptorch_ext_gpt_set_param applies (host code: usable without a GPU).  For the parameter
+ * `name` (GPT::named_parameters, nn/src/lib.rs:1382-1392) of full shape [rows, cols] (a vector is [rows, 1]) and rank tp_rank of
+ * tp_size: *kind = 0 replicated, 1 the rows [*begin, *begin + *count) (wq / wk / wv / ffn_up / ffn_gate and their biases: the
+ * column-parallel projections), 2 the columns [*begin, *begin + *count) (wo / ffn_down: the row-parallel projections, whose partial
+ * products one all-reduce per attention and per MLP block sums).  sptorch_ext_tp_slice_host copies that slice of a full host tensor
+ * into out (rows: count * cols values; columns: rows * count values).  Only the rank for which
+ * sptorch_ext_tp_rank_folds_residual is non-zero adds the residual and the ffn_down bias to its partial product, so that the
+ * all-reduced sum is the new residual stream (the reference's split of work across workers: crates/distributed/src/data_parallel.rs:21-59
+ * shards the batch; this is the same idea applied to the weight matrices). */
+int   sptorch_ext_tp_param_shard(const char* name, int tp_rank, int tp_size, size_t rows, size_t cols, int* kind, size_t* begin, size_t* count);
+int   sptorch_ext_tp_slice_host(const float* full, size_t rows, size_t cols, int kind, size_t begin, size_t count, float* out);
+int   sptorch_ext_tp_rank_folds_residual(int tp_rank);
 
 /* ---- the step after the forward: sampling candidates (nn/src/lib.rs:2381-2418) ----
  * One row of logits on the device (f32 or bf16, at least vocab_size values) -> candidates on the host in the reference's

@@ -26,7 +26,9 @@ def build(force: bool = False) -> None:
     so = os.path.join(_HERE, "liboracle.so")
     src_newer = (not os.path.exists(so)) or any(
         os.path.getmtime(os.path.join(_HERE, f)) > os.path.getmtime(so) for f in ("oracle.c", "oracle.h"))
-    ref_missing = os.path.isdir("/root/reference") and not os.path.exists(os.path.join(_HERE, "_ref", "libmock_npu.so"))
+    # the reference checkout: SPTORCH_REFERENCE in the environment, else a directory named reference beside this repository
+    ref_dir = os.environ.get("SPTORCH_REFERENCE") or os.path.abspath(os.path.join(_HERE, "..", "..", "reference"))
+    ref_missing = os.path.isdir(ref_dir) and not os.path.exists(os.path.join(_HERE, "_ref", "libmock_npu.so"))
     if force or src_newer or ref_missing:
         subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
 

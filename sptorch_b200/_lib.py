@@ -86,7 +86,6 @@ EXT_SYMBOLS = {
     "sptorch_ext_matmul_f32_static": (_i, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "sptorch_ext_linear": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _f, _i, _i, _i]),
     "sptorch_ext_set_attention_mode": (_i, [_i]),
-    "sptorch_ext_debug_attn_prof": (_i, [C.POINTER(C.c_uint64)]),
     "sptorch_ext_attention_workspace": (_sz, [_sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_attention_causal": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "sptorch_ext_gpt_create": (_vp, [C.POINTER(GptConfig)]),
@@ -124,6 +123,9 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_load_weights": (_i, [_vp, _vp, C.POINTER(C.c_char_p), _sz]),
     "sptorch_ext_gpt_load_bundle": (_i, [_vp, C.c_char_p]),
     "sptorch_ext_gpt_set_allreduce": (_i, [_vp, ALLREDUCE_FN, _vp]),
+    "sptorch_ext_tp_param_shard": (_i, [C.c_char_p, _i, _i, _sz, _sz, C.POINTER(_i), C.POINTER(_sz), C.POINTER(_sz)]),
+    "sptorch_ext_tp_slice_host": (_i, [_vp, _sz, _sz, _i, _sz, _sz, _vp]),
+    "sptorch_ext_tp_rank_folds_residual": (_i, [_i]),
     "sptorch_ext_nccl_unique_id": (_i, [C.c_char_p, _vp]),
     "sptorch_ext_nccl_init": (_i, [C.c_char_p, _vp, _i, _i]),
     "sptorch_ext_nccl_allreduce_sum": (_i, [_vp, _sz, _i]),

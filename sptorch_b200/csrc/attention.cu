@@ -33,19 +33,16 @@ __global__ void head_transpose_kernel(const T* __restrict__ v, T* __restrict__ v
 
 int attention_materialized(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
                            void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
-bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
-int attention_fused(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch, void* out,
-                    int B, int T, int H, int hd, long long ld_qk, long long ld_out);
+bool attention_fused_supported(int T, int hd, long long ld_q, long long ld_kv);
+int attention_fused(const void* q, const void* k, const void* v, void* out, int B, int T, int H, int hd, long long ld_q, long long ld_k,
+                    long long ld_v, long long ld_out);
 
 static std::atomic<int> g_attn_mode{0};   // 0 = fused kernel whenever it applies, 1 = always the materialised three-launch form
 int attention_mode() { return g_attn_mode.load(); }
 
-// Picks the fused kernel (bf16, head_dim 64/128) or the materialised form.
-int attention_dispatch(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
-                       void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype) {
-    if (dtype == BF16 && g_attn_mode.load() == 0 && attention_fused_supported(Tn, hd, ld_qk, vt_ld, vt_s_head, vt_s_batch))
-        return attention_fused(q, k, vt, vt_ld, vt_s_head, vt_s_batch, out, B, Tn, H, hd, ld_qk, ld_out);
-    return attention_materialized(q, k, vt, vt_ld, vt_s_head, vt_s_batch, out, scores, B, Tn, H, hd, ld_qk, ld_out, dtype);
+// true when the fused kernel takes this problem (bf16, head_dim 64 or 128, 16-byte aligned row pitches, not switched off)
+bool attention_uses_fused(int dtype, int Tn, int hd, long long ld_q, long long ld_kv) {
+    return dtype == BF16 && g_attn_mode.load() == 0 && attention_fused_supported(Tn, hd, ld_q, ld_kv);
 }
 
 // q,k: [B*T, ld_qk]; vt: V^T with element (b,h,e,t) at vt[b*vt_s_batch + h*vt_s_head + e*vt_ld + t];
@@ -103,23 +100,27 @@ int sptorch_ext_attention_causal(const void* q, const void* k, const void* v, vo
     if (dtype != SPT_F32 && dtype != SPT_BF16) return fail("attention: unknown dtype %d", dtype);
     if (B * H > 65535) return fail("attention: B*H exceeds one launch of the V transpose");
     size_t es = dtype == SPT_BF16 ? 2 : 4;
-    if ((T * es) % 16) return fail("attention: T must be a multiple of %zu for this dtype", 16 / es);
+    const bool fused = attention_uses_fused(dtype, (int)T, (int)hd, (long long)ld_qkv, (long long)ld_qkv);
+    if (!fused && (T * es) % 16) return fail("attention: T must be a multiple of %zu for this dtype", 16 / es);
     size_t scores_bytes = ((B * H * T * T * es + 255) / 256) * 256;
     void* scores = workspace;
     void* vt = (uint8_t*)workspace + scores_bytes;
+    if (fused)
+        return attention_fused(q, k, v, out, (int)B, (int)T, (int)H, (int)hd, (long long)ld_qkv, (long long)ld_qkv, (long long)ld_qkv, (long long)(H * hd));
     dim3 grid((unsigned)((T + 31) / 32), (unsigned)((hd + 31) / 32), (unsigned)(B * H));
     if (dtype == SPT_BF16)
         head_transpose_kernel<__nv_bfloat16><<<grid, dim3(32, 8), 0, rt().stream>>>((const __nv_bfloat16*)v, (__nv_bfloat16*)vt, (int)T, (int)H, (int)hd, (long long)ld_qkv);
     else
         head_transpose_kernel<float><<<grid, dim3(32, 8), 0, rt().stream>>>((const float*)v, (float*)vt, (int)T, (int)H, (int)hd, (long long)ld_qkv);
     SPT_LAUNCH_CHECK("head_transpose");
-    return attention_dispatch(q, k, vt, (long long)T, (long long)(hd * T), (long long)(H * hd * T), out, scores, (int)B, (int)T, (int)H,
-                              (int)hd, (long long)ld_qkv, (long long)(H * hd), dtype);
+    return attention_materialized(q, k, vt, (long long)T, (long long)(hd * T), (long long)(H * hd * T), out, scores, (int)B, (int)T, (int)H,
+                                  (int)hd, (long long)ld_qkv, (long long)(H * hd), dtype);
 }
 
 int sptorch_ext_set_attention_mode(int mode) {
     if (mode != 0 && mode != 1) return fail("set_attention_mode: 0 = fused when possible, 1 = materialised");
     g_attn_mode.store(mode);
+    bump_config_epoch();          // a captured forward holds the other path's launches
     return 0;
 }
 

@@ -1,27 +1,34 @@
 // attention_fused.cu -- fused causal attention for bf16, head_dim 64 or 128 (sm_100a, tcgen05 + TMEM + TMA).
 //
 // Same function as crates/nn/src/lib.rs:600-637 (scores = Q K^T * 1/sqrt(hd); entries j > i set to -inf; row
-// softmax; P V; heads merged back) but the [T,T] score and probability matrices never reach HBM: one CTA owns
-// one 128-row query tile of one (sequence, head) and walks the key/value tiles (64 keys each) up to the diagonal
-// with a running row maximum and row sum (the softmax is exact; only the order of the sums differs).
+// softmax; P V; heads merged back) but the [T,T] score and probability matrices never reach HBM, and the head
+// split / merge and the K transpose (nn/src/lib.rs:763-793, 822-850, 879-903) are strides of the tensor maps.
 //
-//   warp 0      TMA: Q tile once, then K tile [64 keys, hd] and V^T tile [hd, 64 keys] per step, 3-stage ring
-//   warp 1      tcgen05.mma: S_j = Q K_j^T (M128 N64) into one of two TMEM buffers, issued one step AHEAD of the
-//               softmax; O_j = P_j V_j (M128 N=hd) into one of two TMEM buffers when P_j is ready
-//   warps 2..9  two threads per query row (32 of the 64 key columns each): S_j from TMEM into registers, causal
-//               mask on the diagonal tiles, running maximum agreed with the partner thread, exp2, P_j as bf16 into
-//               one of two shared-memory buffers in the 128-byte-swizzled K-major layout the P V MMA reads; the
-//               product O_{j-1} of the PREVIOUS step is folded into the register accumulator afterwards, so no
-//               thread ever waits for the MMA it has just enabled
-// Two CTAs are resident per SM for hd = 64 (97 KB of shared memory and 256 TMEM columns each).  Heavy (late)
-// query tiles are scheduled first.
+// One CTA owns TWO 128-row query tiles of one (sequence, head) at a time and walks the 128-key tiles up to the
+// diagonal with a running row maximum and row sum (the softmax is exact; only the order of the sums differs):
+//
+//   warp 0      TMA: both Q tiles once per work item, then per key tile K [128 keys, hd] and V [128 keys, hd]
+//               (V in its natural token-major layout: it is the MN-major B operand of P V, no transposed copy)
+//   warp 1      tcgen05.mma, one lane: S_g = Q_g K_j^T (M128 N128) into the TMEM buffer of tile g, and
+//               O_g += P_g V_j with P read straight from TMEM; the two query tiles alternate, so the tensor
+//               core works on one tile while the softmax warps work on the other
+//   warps 2..5  softmax of query tile 0, warps 6..9 of query tile 1: ONE THREAD PER QUERY ROW.  A thread reads
+//               its 128 scores from TMEM twice (once for the row maximum, which no other thread has a part in, once
+//               for the exponentials: a whole row held in registers would not fit beside the other warps), evaluates
+//               2^(s*c - m*c) (part on the special-function unit, part as a cubic polynomial on the FMA pipe,
+//               because the 16-per-clock exponential unit would otherwise be the limit), and writes P as bf16
+//               back into the TMEM columns the scores came from
+// O accumulates in TMEM over the key tiles of an item and is rescaled in place only when a row maximum grows by
+// more than 2^8 (lazy rescaling).  TMEM: S/P of tile 0 at columns 0..127, of tile 1 at 128..255, O_0 at 256,
+// O_1 at 384 (512 columns, one CTA per SM).
 // Algorithmic work per (sequence, head): 2 * T(T+1) * hd FLOP; HBM traffic: Q, K, V read once per query tile
-// (K/V re-reads hit L2), O written once.
+// (K/V re-reads hit L2 thanks to the work schedule below), O written once.
 #include "gemm.h"
 #include "sm100.cuh"
 #include "../../include/sptorch_b200_ext.h"
 #include <algorithm>
 #include <array>
+#include <type_traits>
 #include <cstdlib>
 #include <map>
 #include <mutex>
@@ -32,17 +39,16 @@ namespace spt {
 
 using namespace sm100;
 
-constexpr int kAttnThreads = 320;           // TMA warp + MMA warp + 8 softmax warps
-constexpr int kQTile = 128, kKvTile = 64;
-constexpr int kKvStages = 3;
+constexpr int kAttnThreads = 320;           // TMA warp + MMA warp + 2 x 4 softmax warps
+constexpr int kQTile = 128, kKvTile = 128;
+constexpr int kQPair = 2 * kQTile;          // query rows per work item
 
 struct AttnParams {
     __nv_bfloat16* out;
     long long ld_out;       // row stride of out in elements
     int T, H, B;
-    int n_qtiles;
+    int n_ptiles;           // 256-row query tile pairs per sequence
     float scale_log2;       // 1/sqrt(hd) * log2(e)
-    unsigned long long* prof;   // diagnostics: cycle counters of CTA 0 (softmax warp 2 lane 0: [0..7], MMA warp lane 0: [8..15]); may be null
     uint32_t* status;
     const int* sched;       // work schedule [sched_len][gridDim.x]: item of CTA c at step k, -1 past the end of its list
     int sched_len;
@@ -55,58 +61,93 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// 2^x for two values on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic (relative error
+// 7.5e-5 = 2^-13.7, far below the 2^-9 of the bf16 rounding that follows); n goes straight into the exponent field.
+// x is clamped at -125 so that the exponent arithmetic cannot wrap (the result is then 2^-125, nothing in any sum).
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    const float kMagic = 12582912.0f;               // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+    x.x = fmaxf(x.x, -125.0f); x.y = fmaxf(x.y, -125.0f);
+    const float2 r = __fadd2_rn(x, make_float2(kMagic, kMagic));
+    const float2 n = __fadd2_rn(r, make_float2(-kMagic, -kMagic));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.055171654f, 0.055171654f), make_float2(0.24261113f, 0.24261113f));
+    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
+    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23)));
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
 
+// tcgen05.mma with the A operand in TMEM (rows = lanes, two bf16 per 32-bit column) and B in shared memory
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Shared-memory descriptor of an MN-major operand tile stored as k-rows of exactly 128 bytes (64 bf16 along the MN
+// dimension) with the 128-byte swizzle: what a TMA box of {64 elements, rows} writes for a row-major [k, n] matrix.
+//   leading byte offset = distance between 64-element chunks along MN (for N = 128: the second TMA box)
+//   stride byte offset  = distance between groups of 8 k-rows = 1024 B
+// Advancing along K by one MMA (16 rows) adds 2048 B to the start address.
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t chunk_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)(chunk_bytes >> 4) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 template <int HD>
 struct AttnSmem {
-    static constexpr int kQBytes = kQTile * HD * 2;
-    static constexpr int kKBytes = kKvTile * HD * 2;          // HD/64 k-blocks of [64 keys x 128 B]
-    static constexpr int kVBytes = HD * kKvTile * 2;          // [HD rows x 128 B]
+    static constexpr int kStages = HD == 64 ? 4 : 2;
+    static constexpr int kQTileBytes = kQTile * HD * 2;       // HD/64 k-blocks of [128 rows x 128 B]
+    static constexpr int kKBytes = kKvTile * HD * 2;          // HD/64 k-blocks of [128 keys x 128 B]
+    static constexpr int kVBytes = kKvTile * HD * 2;          // HD/64 chunks of [128 keys x 128 B] (64 head columns each)
     static constexpr int kStageBytes = kKBytes + kVBytes;
-    static constexpr int kPBytes = kQTile * kKvTile * 2;      // [128 rows x 128 B]
     static constexpr int kQ = 0;
-    static constexpr int kKV = kQ + kQBytes;
-    static constexpr int kP = kKV + kKvStages * kStageBytes;
-    static constexpr int kBars = kP + 2 * kPBytes;            // mbarriers + TMEM slot + abort flag (256 B)
-    static constexpr int kX = kBars + 256;                    // running-maximum exchange: [parity][half][128] floats
-    static constexpr int kTotal = kX + 2048;
+    static constexpr int kKV = kQ + 2 * kQTileBytes;
+    static constexpr int kBars = kKV + kStages * kStageBytes; // mbarriers + TMEM slot + abort flag (256 B)
+    static constexpr int kTotal = kBars + 256;
 };
 
 // Persistent kernel: CTA c works through column c of a schedule built on the host (attention_schedule below), and all
-// three roles run straight through item boundaries (barrier phases are driven by running counters), so the loads and
-// the first Q K^T of the next item are in flight while the current one drains.
-template <int HD, bool PROF>
-__global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
+// roles run straight through item boundaries (barrier phases are driven by running counters), so the loads and the
+// first Q K^T of the next item are in flight while the current one drains.
+template <int HD, int NPOLY>
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
     using L = AttnSmem<HD>;
-    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;    // S: 2 x 64 columns at 0; O: 2 x HD columns at 128
+    constexpr uint32_t TMEM_COLS = 512;
     constexpr uint32_t IDESC_S = make_idesc(false, 128, kKvTile);
-    constexpr uint32_t IDESC_O = make_idesc(false, 128, HD);
-    constexpr int KB_Q = HD / 64;                           // 128-byte k-blocks along head_dim
-    constexpr int NS = kKvStages;
+    constexpr uint32_t IDESC_O = make_idesc(false, 128, HD) | (1u << 16);      // B operand (V) is MN-major
+    constexpr int KB = HD / 64;                               // 128-byte blocks along head_dim
+    constexpr int NS = L::kStages;
 
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = smem_u32(smem);
-    // barrier slots (8 bytes each)
     const uint32_t bar = base + L::kBars;
-    const uint32_t q_full = bar;                    // 2
-    const uint32_t q_free = q_full + 16;            // 2
-    const uint32_t kv_full = q_free + 16;           // NS
+    const uint32_t q_full = bar;                    // 1
+    const uint32_t q_free = q_full + 8;             // 1
+    const uint32_t kv_full = q_free + 8;            // NS
     const uint32_t kv_empty = kv_full + 8 * NS;     // NS
-    const uint32_t s_full = kv_empty + 8 * NS;      // 2
-    const uint32_t s_free = s_full + 16;            // 2
-    const uint32_t p_full = s_free + 16;            // 2
-    const uint32_t o_full = p_full + 16;            // 2
-    const uint32_t o_free = o_full + 16;            // 2
-    const uint32_t mx_bar = o_free + 16;            // 4, one per TMEM lane quarter
+    const uint32_t s_full = kv_empty + 8 * NS;      // 2 (per query tile)
+    const uint32_t p_full = s_full + 16;            // 2
+    const uint32_t pv_done = p_full + 16;           // 2
+    const uint32_t o_free = pv_done + 16;           // 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBars + 240);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBars + 244);
-    static_assert(8 * (4 + 2 * NS + 10 + 4) <= 240, "barrier block overflows");
+    static_assert(8 * (2 + 2 * NS + 8) <= 240, "barrier block overflows");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = p.B * p.H;
@@ -117,13 +158,14 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         return;
     }
     if (threadIdx.x == 0) {
+        mbar_init(q_full, 1); mbar_init(q_free, 1);
         for (int s = 0; s < NS; s++) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_empty + 8 * s, 1); }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(q_full + 8 * i, 1); mbar_init(q_free + 8 * i, 1);
-            mbar_init(s_full + 8 * i, 1); mbar_init(s_free + 8 * i, 8); mbar_init(p_full + 8 * i, 8);      // one arrival per softmax warp
-            mbar_init(o_full + 8 * i, 1); mbar_init(o_free + 8 * i, 8);
+        for (int g = 0; g < 2; g++) {
+            mbar_init(s_full + 8 * g, 1);
+            mbar_init(p_full + 8 * g, 4);           // one arrival per softmax warp of the tile
+            mbar_init(pv_done + 8 * g, 1);
+            mbar_init(o_free + 8 * g, 4);
         }
-        for (int q = 0; q < 4; q++) mbar_init(mx_bar + 8 * q, 2);           // the two warps of a lane quarter
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -132,17 +174,17 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
 
     // step k of this CTA's list; the entry of the next step is fetched while the current item runs
     auto fetch = [&](int k) -> int { return k < p.sched_len ? __ldg(p.sched + (size_t)k * gridDim.x + blockIdx.x) : -1; };
-    // work item -> (query tile, sequence, head, number of key tiles)
-    auto decode = [&](int item, int& q0, int& bb, int& hh, int& n_kv) {
-        const int qt = p.n_qtiles - 1 - item / BH;
+    // work item -> (first query row, sequence, head, key tiles of query tile 0 and of query tile 1)
+    auto decode = [&](int item, int& q0, int& bb, int& hh, int& n0, int& n1) {
+        const int pt = p.n_ptiles - 1 - item / BH;
         const int bh = item % BH;
         bb = bh / p.H; hh = bh % p.H;
-        q0 = qt * kQTile;
-        n_kv = min((q0 + kQTile + kKvTile - 1) / kKvTile, n_kv_seq);       // causal: keys 0 .. q0+127, clipped to the sequence
+        q0 = pt * kQPair;
+        n0 = min(q0 / kKvTile + 1, n_kv_seq);                             // causal: keys 0 .. q0+127
+        n1 = (q0 + kQTile < p.T) ? min(q0 / kKvTile + 2, n_kv_seq) : 0;   // second tile exists only inside the sequence
     };
 
     if (warp == 0) {
@@ -152,17 +194,19 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         uint32_t g = 0, it = 0;
         for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
             const int item_next = fetch(k + 1);
-            int q0, bb, hh, n_kv;
-            decode(item, q0, bb, hh, n_kv);
+            int q0, bb, hh, n0, n1;
+            decode(item, q0, bb, hh, n0, n1);
             item = item_next;
-            const uint32_t qb = 0;       // one Q buffer: reloaded as soon as the last Q K^T of the previous item has read it
-            ok = mbar_wait(q_free + 8 * qb, (it & 1) ^ 1, abort_flag, p.status, kErrProducerWait);
+            const int nmax = max(n0, n1);
+            ok = mbar_wait(q_free, (it & 1) ^ 1, abort_flag, p.status, kErrProducerWait);
             if (!ok) break;
             if (lane == 0) {
-                mbar_expect_tx(q_full + 8 * qb, L::kQBytes);
-                for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(base + L::kQ + qb * L::kQBytes + kb * (kQTile * 128), &tmQ, q_full + 8 * qb, kb * 64, q0, hh, bb);
+                mbar_expect_tx(q_full, 2 * L::kQTileBytes);
+                for (int t = 0; t < 2; t++)
+                    for (int kb = 0; kb < KB; kb++)
+                        tma_load_4d(base + L::kQ + t * L::kQTileBytes + kb * (kQTile * 128), &tmQ, q_full, kb * 64, q0 + t * kQTile, hh, bb);
             }
-            for (int j = 0; j < n_kv && ok; j++, g++) {
+            for (int j = 0; j < nmax && ok; j++, g++) {
                 const uint32_t s = g % NS, u = (g / NS) & 1;
                 ok = mbar_wait(kv_empty + 8 * s, u ^ 1, abort_flag, p.status, kErrProducerWait);
                 if (!ok) break;
@@ -170,8 +214,8 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     const int k0 = j * kKvTile;
                     const uint32_t dst = base + L::kKV + s * L::kStageBytes;
                     mbar_expect_tx(kv_full + 8 * s, L::kStageBytes);
-                    for (int kb = 0; kb < KB_Q; kb++) tma_load_4d(dst + kb * (kKvTile * 128), &tmK, kv_full + 8 * s, kb * 64, k0, hh, bb);
-                    tma_load_4d(dst + L::kKBytes, &tmV, kv_full + 8 * s, k0, 0, hh, bb);
+                    for (int kb = 0; kb < KB; kb++) tma_load_4d(dst + kb * (kKvTile * 128), &tmK, kv_full + 8 * s, kb * 64, k0, hh, bb);
+                    for (int kb = 0; kb < KB; kb++) tma_load_4d(dst + L::kKBytes + kb * (kKvTile * 128), &tmV, kv_full + 8 * s, kb * 64, k0, hh, bb);
                 }
                 __syncwarp();
             }
@@ -179,175 +223,131 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         bool ok = true;
-        uint32_t g = 0, it = 0;
-        const bool pr = PROF && p.prof != nullptr && blockIdx.x == 0 && lane == 0;
-        unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        long long tprev = clock64();
-#define SPT_TICK(i) do { if (PROF && pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
-        auto issue_s = [&](uint32_t gg, uint32_t qb) {        // S = Q K^T of global step gg into S buffer gg & 1
+        uint32_t g = 0, it = 0;                 // key tiles loaded so far (stage ring position); items so far
+        uint32_t steps[2] = {0, 0};             // softmax steps of each query tile so far (phases of p_full)
+        // S_t = Q_t K^T with the key tile of ring position gg
+        auto issue_s = [&](int t, uint32_t gg) {
             const uint32_t kaddr = base + L::kKV + (gg % NS) * L::kStageBytes;
 #pragma unroll
-            for (int kb = 0; kb < KB_Q; kb++) {
-                const uint64_t adesc = make_kmajor_sw128_desc(base + L::kQ + qb * L::kQBytes + kb * (kQTile * 128));
+            for (int kb = 0; kb < KB; kb++) {
+                const uint64_t adesc = make_kmajor_sw128_desc(base + L::kQ + t * L::kQTileBytes + kb * (kQTile * 128));
                 const uint64_t bdesc = make_kmajor_sw128_desc(kaddr + kb * (kKvTile * 128));
 #pragma unroll
-                for (int k = 0; k < 4; k++) mma_ss<false>(tmem_s + (gg & 1) * kKvTile, adesc + 2 * k, bdesc + 2 * k, IDESC_S, (kb | k) != 0 ? 1u : 0u);
+                for (int k = 0; k < 4; k++) mma_ss<false>(tmem_base + t * 128, adesc + 2 * k, bdesc + 2 * k, IDESC_S, (kb | k) != 0 ? 1u : 0u);
             }
-            mma_commit(s_full + 8 * (gg & 1));
+            mma_commit(s_full + 8 * t);
         };
-        // waits until the operands of global step gg are loaded and its S buffer has been drained
-        auto s_ready = [&](uint32_t gg) -> bool {
-            return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait) &&
-                   mbar_wait(s_free + 8 * (gg & 1), ((gg >> 1) & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
+        // O_t (+)= P_t V with the value tile of ring position gg; P is read from the TMEM columns of S_t
+        auto issue_pv = [&](int t, uint32_t gg, bool accumulate) {
+            const uint64_t bdesc = make_mnmajor_sw128_desc(base + L::kKV + (gg % NS) * L::kStageBytes + L::kKBytes, kKvTile * 128);
+#pragma unroll
+            for (int k = 0; k < kKvTile / 16; k++)
+                mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
+            mma_commit(pv_done + 8 * t);
         };
+        auto kv_ready = [&](uint32_t gg) -> bool { return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait); };
         for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
             const int item_next = fetch(k + 1);
-            int q0, bb, hh, n_kv;
-            decode(item, q0, bb, hh, n_kv);
+            int q0, bb, hh, n0, n1;
+            decode(item, q0, bb, hh, n0, n1);
             item = item_next;
-            const uint32_t qb = 0;
-            SPT_TICK(7);
-            ok = mbar_wait(q_full + 8 * qb, it & 1, abort_flag, p.status, kErrMmaWait) && s_ready(g);
+            const int nt[2] = {n0, n1};
+            const int nmax = max(n0, n1);
+            const int last_t = n1 > 0 ? 1 : 0;             // the tile whose last Q K^T is the item's last read of Q
+            ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kErrMmaWait) && kv_ready(g);
             if (!ok) break;
-            SPT_TICK(0);
             tc_fence_after();
             if (lane == 0) {
-                issue_s(g, qb);
-                if (n_kv == 1) mma_commit(q_free + 8 * qb);
+                issue_s(0, g);
+                if (n1 > 0) issue_s(1, g);
+                if (nt[last_t] == 1) mma_commit(q_free);
             }
             __syncwarp();
-            for (int j = 0; j < n_kv && ok; j++, g++) {
-                const uint32_t u2 = (g >> 1) & 1;
-                if (j + 1 < n_kv) {
-                    // next scores while the softmax warps work on this step
-                    SPT_TICK(7);
-                    ok = s_ready(g + 1);
+            for (int j = 0; j < nmax && ok; j++, g++) {
+                if (j + 1 < nmax) { ok = kv_ready(g + 1); if (!ok) break; }
+                for (int t = 0; t < 2 && ok; t++) {
+                    if (j >= nt[t]) continue;
+                    ok = mbar_wait(p_full + 8 * t, steps[t] & 1, abort_flag, p.status, kErrMmaWait);
+                    // the item's first product overwrites the accumulator: the previous item's output must have been read
+                    if (ok && j == 0) ok = mbar_wait(o_free + 8 * t, (it & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
                     if (!ok) break;
-                    SPT_TICK(1);
+                    steps[t]++;
                     tc_fence_after();
                     if (lane == 0) {
-                        issue_s(g + 1, qb);
-                        if (j + 2 == n_kv) mma_commit(q_free + 8 * qb);   // last read of this item's Q
+                        issue_pv(t, g, j > 0);
+                        // the next scores of this tile go into the columns P was just read from: the tensor pipe runs the
+                        // MMAs of one thread in order, so the product above has consumed P before these overwrite it
+                        if (j + 1 < nt[t]) {
+                            issue_s(t, g + 1);
+                            if (t == last_t && j + 2 == nt[t]) mma_commit(q_free);
+                        }
                     }
                     __syncwarp();
                 }
-                SPT_TICK(7);
-                ok = mbar_wait(p_full + 8 * (g & 1), u2, abort_flag, p.status, kErrMmaWait);
-                SPT_TICK(2);
-                // the output accumulator of an item (buffer = item parity) is written for the first time: the item two back must
-                // have been read out of it
-                if (j == 0) ok = ok && mbar_wait(o_free + 8 * (it & 1), ((it >> 1) & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
-                if (!ok) break;
-                SPT_TICK(3);
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint64_t adesc = make_kmajor_sw128_desc(base + L::kP + (g & 1) * L::kPBytes);
-                    const uint64_t bdesc = make_kmajor_sw128_desc(base + L::kKV + (g % NS) * L::kStageBytes + L::kKBytes);
-                    // O accumulates in TMEM over the key tiles of the item (the softmax warps rescale it in place when a row
-                    // maximum grows enough)
-#pragma unroll
-                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_o + (it & 1) * HD, adesc + 2 * k, bdesc + 2 * k, IDESC_O, (j | k) != 0 ? 1u : 0u);
-                    mma_commit(o_full + 8 * (g & 1));
-                    mma_commit(kv_empty + 8 * (g % NS));
-                }
+                if (ok && lane == 0) mma_commit(kv_empty + 8 * (g % NS));     // every MMA that reads this stage has been issued
                 __syncwarp();
             }
         }
-        if (pr) { for (int i = 0; i < 8; i++) p.prof[8 + i] = pc[i]; }
-#undef SPT_TICK
     } else {
-        // ---------------- softmax + accumulate: two threads per query row ----------------
-        // Warps w and w+4 share a TMEM lane quarter.  Of query row r the thread in the lower warp owns key columns
-        // 0..31 of every tile and the first half of the output columns, its partner the other halves.  The two only
-        // have to agree on the running maximum (exchanged through shared memory); row sums stay per thread and are
-        // added once at the end.
-        const int quarter = warp & 3;
-        const int ch = (warp - 2) >> 2;                          // column half
+        // ---------------- softmax + output: one thread per query row ----------------
+        const int t = (warp - 2) >> 2;                           // query tile of this warp
+        const int quarter = warp & 3;                            // TMEM lane quarter a warp may access = warp index % 4
         const int r = quarter * 32 + lane;                       // row inside the tile = TMEM lane
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        constexpr int OC = HD / 2;                               // output columns per thread
-        const int prow_off = (r >> 3) * 1024 + (r & 7) * 128;    // row r of a [128 x 128 B] swizzled block
-        const int rx = r & 7;
-        float* xmax = reinterpret_cast<float*>(smem + L::kX);
-        const uint32_t pair_bar = mx_bar + 8 * quarter;
+        const uint32_t s_addr = tmem_base + lane_off + t * 128;          // scores, and P over their first 64 columns
+        const uint32_t o_addr = tmem_base + lane_off + 256 + t * 128;
         bool ok = true;
-        uint32_t g = 0, px = 0, it = 0;                          // global step; pair exchanges done so far; items done so far
-        const bool pr = PROF && p.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
-        unsigned long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        long long tprev = clock64();
-#define SPT_TICK(i) do { if (PROF && pr) { long long _t = clock64(); pc[i] += (unsigned long long)(_t - tprev); tprev = _t; } } while (0)
-        // P V of global step gg has completed (its commit arrives on o_full[gg & 1]; a thread never waits for a step whose
-        // successor two steps on could already have been committed, because that commit needs this thread's own P)
-        auto pv_done = [&](uint32_t gg) -> bool {
-            return mbar_wait(o_full + 8 * (gg & 1), (gg >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
-        };
-        for (int k = 0, item = fetch(0); item >= 0 && ok; k++) {
+        uint32_t step = 0, it = 0;                               // softmax steps of this tile so far; items so far
+        for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
             const int item_next = fetch(k + 1);
-            int q0, bb, hh, n_kv;
-            decode(item, q0, bb, hh, n_kv);
+            int q0, bb, hh, n0, n1;
+            decode(item, q0, bb, hh, n0, n1);
             item = item_next;
-            const int qrow = q0 + r;
+            const int n_kv = t == 0 ? n0 : n1;
+            const int qrow = q0 + t * kQTile + r;
             float m = -INFINITY, l = 0.0f;
-            const uint32_t o_addr = tmem_o + lane_off + (it & 1) * HD + ch * OC;      // this thread's half of its output row
-            for (int j = 0; j < n_kv && ok; j++, g++) {
-                const uint32_t sb = g & 1;
-                const int kcol0 = j * kKvTile + ch * 32;             // key index of this thread's first column
-                const bool diag = (j * kKvTile + kKvTile - 1 > q0);  // tile reaches past the first row of the query tile
-                SPT_TICK(7);
-                ok = mbar_wait(s_full + 8 * sb, (g >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);
+            for (int j = 0; j < n_kv && ok; j++, step++) {
+                ok = mbar_wait(s_full + 8 * t, step & 1, abort_flag, p.status, kErrEpilogueWait);
                 if (!ok) break;
-                SPT_TICK(0);
                 tc_fence_after();
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_s + lane_off + sb * kKvTile + ch * 32, v);
-                tmem_ld_wait();
-                tc_fence_before();
-                // One arrival per warp on every barrier of this role, after __syncwarp has ordered the lanes' accesses (per-thread
-                // arrivals measured the same speed; this form issues 24 shared-memory atomics per step instead of 768).
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_free + 8 * sb);         // scores are in registers: the buffer can take the S after next
-                SPT_TICK(1);
-                float mx = -INFINITY;
-                if (diag) {
+                const bool diag = (j == n_kv - 1);               // the tile on the diagonal: keys q .. q+127 of rows q .. q+127
+                // pass 1: the row maximum, 64 scores at a time (entries right of the diagonal do not take part)
+                float mx;
+                {
+                    float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int i = 0; i < 32; i++) if (kcol0 + i > qrow) v[i] = 0xff800000u;     // -inf
-                }
-                {   // four independent chains instead of one 16-deep dependent chain
-                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t v[64];
+                        tmem_ld_32x32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                        tmem_ld_32x32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+                        tmem_ld_wait();
+                        if (diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-                        m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                        m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-                        m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                            for (int i = 0; i < 64; i++) if (half * 64 + i > r) v[i] = 0xff800000u;       // -inf
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 2) mm[q] = max3(mm[q], __uint_as_float(v[16 * q + i]), __uint_as_float(v[16 * q + i + 1]));
+                        }
                     }
-                    mx = fmaxf(max3(m0, m1, m2), m3);
+                    mx = fmaxf(max3(mm[0], mm[1], mm[2]), mm[3]);
                 }
-                // double buffered by exchange parity: the partner may still be reading the previous value
-                float* xm = xmax + (px & 1) * 256;
-                xm[ch * 128 + r] = mx;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pair_bar);
-                ok = mbar_wait(pair_bar, px & 1, abort_flag, p.status, kErrEpilogueWait);
-                if (!ok) break;
-                px++;
-                SPT_TICK(2);
                 // Lazy rescaling: the reference maximum of a row only moves when the new maximum exceeds it by more than 8 in the
                 // exponent (P then stays below 2^8, exact enough in bf16 and harmless in the f32 sums); the accumulated output
-                // in TMEM and the row sum are multiplied by 2^(old - new) at that moment.  Both threads of a row see the same
-                // maxima and take the same decision; tcgen05.ld / st are warp-wide, so a warp rescales when any of its rows does
-                // (the others multiply by one).
-                const float m_cand = fmaxf(m, fmaxf(mx, xm[(ch ^ 1) * 128 + r]));
-                if (j == 0) m = m_cand;
-                const bool grow = j > 0 && (m_cand - m) * p.scale_log2 > 8.0f;
+                // in TMEM and the row sum are multiplied by 2^(old - new) at that moment.  tcgen05.ld / st are warp-wide, so a
+                // warp rescales when any of its rows does (the others multiply by one).
+                if (j == 0) m = mx;
+                const bool grow = j > 0 && (mx - m) * p.scale_log2 > 8.0f;
                 if (__any_sync(0xffffffffu, grow)) {
                     float alpha = 1.0f;
-                    if (grow) { alpha = ex2_approx((m - m_cand) * p.scale_log2); m = m_cand; l *= alpha; }
-                    ok = pv_done(g - 1);                               // every product accumulated so far is in place
+                    if (grow) { alpha = ex2_approx((m - mx) * p.scale_log2); m = mx; l *= alpha; }
+                    // every product accumulated so far is in place (the commit of step - 1; the next one needs this thread's P)
+                    ok = mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll
-                    for (int c = 0; c < OC / 32; c++) {
+                    for (int c = 0; c < HD / 32; c++) {
                         uint32_t o[32];
                         tmem_ld_32x32(o_addr + c * 32, o);
                         tmem_ld_wait();
@@ -356,82 +356,83 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         tmem_st_32x32(o_addr + c * 32, o);
                     }
                     tmem_st_wait();
-                    tc_fence_before();
                 }
                 const float mb = m * p.scale_log2;
-                // the softmax warps are bound by instruction issue: scale/subtract, the row sum and the accumulator
-                // update run on pairs of floats (fma.rn.f32x2 / add.rn.f32x2), the maximum on three inputs at a time
-                float2 sum2 = make_float2(0.0f, 0.0f), sum2b = make_float2(0.0f, 0.0f);
+                // scale/subtract, the row sum and the conversions run on pairs of floats; of every 16 pairs NPOLY take the
+                // polynomial (FMA pipe) and the rest the special-function unit.  The diagonal tile uses the special-function
+                // unit alone, where 2^(-inf) is exactly 0.
+                float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
                 const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nmb2 = make_float2(-mb, -mb);
-                uint32_t packed[16];
+                // pass 2: 64 scores at a time -> 2^(s*c - m*c) -> bf16 pairs into the columns the first scores of the row came from
+                // (P of keys 64h .. 64h+63 lands in columns 32h .. 32h+31, which hold scores that have been read by then)
+                auto exps = [&](auto npoly_tag, auto diag_tag) {
+                    constexpr int NP = decltype(npoly_tag)::value;
+                    constexpr bool DIAG = decltype(diag_tag)::value;
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float2 t = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nmb2);
-                    float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));                   // exp2(-inf) = 0 for masked entries
-                    if (i & 2) sum2b = __fadd2_rn(sum2b, e); else sum2 = __fadd2_rn(sum2, e);     // two chains
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h2);
-                }
-                const float sum = (sum2.x + sum2.y) + (sum2b.x + sum2b.y);
-                // P buffer sb was last read by the P V two steps back
-                if (g >= 2) { ok = pv_done(g - 2); if (!ok) break; }
-                uint8_t* prow = smem + L::kP + sb * L::kPBytes + prow_off;
+                    for (int half = 0; half < 2; half++) {
+                        uint32_t v[64];
+                        tmem_ld_32x32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+                        tmem_ld_32x32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+                        tmem_ld_wait();
+                        if (DIAG) {
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const int chunk = (ch * 4 + q) ^ rx;               // 32 columns = 64 bytes = 16-byte chunks ch*4 .. ch*4+3
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P visible to the MMA's async-proxy reads
-                SPT_TICK(3);
+                            for (int i = 0; i < 64; i++) if (half * 64 + i > r) v[i] = 0xff800000u;       // -inf
+                        }
+                        uint32_t packed[32];
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), c2, nmb2);
+                            float2 e;
+                            if ((i & 15) < NP) e = ex2_poly2(x);
+                            else e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                            if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
+                            packed[i] = *reinterpret_cast<uint32_t*>(&h2);
+                        }
+                        tmem_st_32x32(s_addr + half * 32, packed);
+                    }
+                };
+                if (diag) exps(std::integral_constant<int, 0>(), std::true_type()); else exps(std::integral_constant<int, NPOLY>(), std::false_type());
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full + 8 * sb);
-                l += sum;
-                SPT_TICK(4);
+                if (lane == 0) mbar_arrive(p_full + 8 * t);
+                l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
             }
             if (!ok) break;
-            SPT_TICK(5);
-            // total row sum = own half + partner's half
-            float* xm = xmax + (px & 1) * 256;
-            xm[ch * 128 + r] = l;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pair_bar);
-            ok = mbar_wait(pair_bar, px & 1, abort_flag, p.status, kErrEpilogueWait);
-            if (!ok) break;
-            px++;
-            const float inv = 1.0f / (l + xm[(ch ^ 1) * 128 + r]);
-            ok = pv_done(g - 1);                                       // the item's last product
-            if (!ok) break;
-            tc_fence_after();
-            __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD + ch * OC;
+            if (n_kv > 0) {
+                const float inv = 1.0f / l;
+                ok = mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait);     // the item's last product
+                if (!ok) break;
+                tc_fence_after();
+                __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD;
 #pragma unroll
-            for (int c = 0; c < OC / 32; c++) {
-                uint32_t o[32];
-                tmem_ld_32x32(o_addr + c * 32, o);
-                tmem_ld_wait();
-                if (qrow < p.T) {
+                for (int c = 0; c < HD / 32; c++) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(o_addr + c * 32, o);
+                    tmem_ld_wait();
+                    if (qrow < p.T) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 w;
-                        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&w);
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-                        for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * q]) * inv, __uint_as_float(o[i + 2 * q + 1]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                            for (int q = 0; q < 4; q++) oh[q] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * q]) * inv, __uint_as_float(o[i + 2 * q + 1]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+                        }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(o_free + 8 * (it & 1));         // the accumulator may be overwritten by the item after next
-            it++;
-            SPT_TICK(6);
+            if (lane == 0) mbar_arrive(o_free + 8 * t);              // the accumulator may be overwritten by the next item
         }
-        if (pr) { for (int i = 0; i < 8; i++) p.prof[i] = pc[i]; }
-#undef SPT_TICK
     }
 
     tc_fence_before();
     __syncthreads();
     if (*abort_flag) {
+        // give loads that may still be in flight time to land before shared memory is released
         unsigned long long t0 = globaltimer();
         while (globaltimer() - t0 < 200000ull) { }
         __syncthreads();
@@ -454,13 +455,14 @@ static EncodeTiledFn attn_encode() {
     return fn;
 }
 
-// bf16 rank-4 map: dims (d0, d1, H, B) with element strides (1, s1, sH, sB), box (64, box1, 1, 1), 128-byte swizzle
-static int encode4(CUtensorMap* map, const void* ptr, long long d0, long long d1, int H, int B, long long s1, long long sH, long long sB, int box1) {
+// bf16 rank-4 map over a token-major [B*T, ld] matrix seen as (head_dim, T, H, B): box (64, 128, 1, 1), 128-byte swizzle.
+// Rows past T read as zero (they belong to the next sequence in memory, but the T dimension of the map ends there).
+static int encode_heads(CUtensorMap* map, const void* ptr, int hd, int T, int H, int B, long long ld) {
     EncodeTiledFn enc = attn_encode();
     if (!enc) return fail("cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[4] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)H, (cuuint64_t)B};
-    cuuint64_t st[3] = {(cuuint64_t)s1 * 2, (cuuint64_t)(H > 1 ? sH : s1) * 2, (cuuint64_t)(B > 1 ? sB : s1) * 2};
-    cuuint32_t box[4] = {64, (cuuint32_t)box1, 1, 1};
+    cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t st[3] = {(cuuint64_t)ld * 2, (cuuint64_t)(H > 1 ? hd : ld) * 2, (cuuint64_t)(B > 1 ? (long long)T * ld : ld) * 2};
+    cuuint32_t box[4] = {64, 128, 1, 1};
     cuuint32_t es[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, st, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -468,39 +470,37 @@ static int encode4(CUtensorMap* map, const void* ptr, long long d0, long long d1
     return 0;
 }
 
-// diagnostics: when SPTORCH_B200_ATTN_PROF is set, CTA 0 of every fused-attention launch records where one softmax
-// thread and the MMA thread spend their cycles (read back with sptorch_ext_debug_attn_prof)
-static unsigned long long* g_attn_prof = nullptr;
-static unsigned long long* attn_prof_buffer() {
-    static const bool on = getenv("SPTORCH_B200_ATTN_PROF") != nullptr;
-    if (!on) return nullptr;
-    if (!g_attn_prof) { if (cudaMalloc(&g_attn_prof, 16 * sizeof(unsigned long long)) != cudaSuccess) g_attn_prof = nullptr; }
-    return g_attn_prof;
-}
-extern "C" int sptorch_ext_debug_attn_prof(unsigned long long* host16) {
-    if (enter() || !g_attn_prof || !host16) return 1;
-    cudaStreamSynchronize(rt().stream);
-    return cudaMemcpy(host16, g_attn_prof, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
-}
-
-// Work schedule of the persistent kernel.  Items are (query tile, sequence*head); a query tile q reads the keys and values
-// 0 .. 128 q + 127 of its pair, so the eight tiles of one pair re-read the same K/V.  The list is cut into groups of pairs
-// whose K/V fit in L2 together, each group ordered longest tile first, and the items are dealt out in that order to the CTA
-// that has the least work so far (list scheduling with cost = key tiles + 1): the tiles of a pair then run close together
-// in time and their K/V come from L2 instead of DRAM, while the CTAs still finish together.
+// Work schedule of the persistent kernel.  Items are (query tile pair, sequence*head); pair q reads the keys and values
+// 0 .. 256 q + 255 of its (sequence, head), so the tiles of one (sequence, head) re-read the same K/V.  The list is cut into
+// groups of (sequence, head)s whose K/V fit in L2 together, each group ordered longest item first, and the items are dealt out
+// in that order to the CTA that has the least work so far (list scheduling, cost = key tiles of both query tiles + 1): the
+// items of one (sequence, head) then run close together in time and their K/V come from L2 instead of DRAM, while the CTAs
+// still finish together.  Schedules are cached per shape and released when the backend shuts down.
 struct AttnSchedule { std::vector<int> host; int* dev = nullptr; int len = 0; };
 static std::mutex g_sched_mu;
 static std::map<std::array<int, 6>, AttnSchedule> g_sched;
 
-static int attention_schedule(int B, int H, int T, int hd, int nq, int grid, const int** dev, int* len) {
+static void attention_schedules_release() {
+    std::lock_guard<std::mutex> lk(g_sched_mu);
+    for (auto& kv : g_sched) if (kv.second.dev) cudaFree(kv.second.dev);
+    g_sched.clear();
+}
+
+static int attention_schedule(int B, int H, int T, int hd, int npt, int grid, const int** dev, int* len) {
     static const int l2_mb = getenv("SPTORCH_B200_ATTN_L2_MB") ? atoi(getenv("SPTORCH_B200_ATTN_L2_MB")) : 32;
     const int BH = B * H;
     const long long pair_bytes = 2LL * T * hd * 2;                       // K and V of one (sequence, head)
     long long group = l2_mb > 0 ? ((long long)l2_mb << 20) / pair_bytes : BH;
     group = group < 1 ? 1 : (group > BH ? BH : group);
     std::lock_guard<std::mutex> lk(g_sched_mu);
+    if (g_sched.size() > 64) {                                           // a bound on the cache: drop everything not in flight
+        if (stream_wait()) return 1;
+        for (auto& kv : g_sched) if (kv.second.dev) cudaFree(kv.second.dev);
+        g_sched.clear();
+    }
     AttnSchedule& s = g_sched[{B, H, T, hd, grid, (int)group}];
     if (!s.dev) {
+        at_shutdown(attention_schedules_release);
         const int n_kv_seq = ceil_div(T, kKvTile);
         std::vector<std::vector<int>> lists(grid);
         using Slot = std::pair<long long, int>;                          // (work so far, CTA)
@@ -508,12 +508,14 @@ static int attention_schedule(int B, int H, int T, int hd, int nq, int grid, con
         for (int c = 0; c < grid; c++) heap.push({0, c});
         for (int g0 = 0; g0 < BH; g0 += (int)group) {
             const int g1 = std::min<long long>(BH, g0 + group);
-            for (int qt = nq - 1; qt >= 0; qt--) {
-                const int n_kv = std::min(ceil_div(qt * kQTile + kQTile, kKvTile), n_kv_seq);
+            for (int pt = npt - 1; pt >= 0; pt--) {
+                const int q0 = pt * kQPair;
+                const int n0 = std::min(q0 / kKvTile + 1, n_kv_seq);
+                const int n1 = q0 + kQTile < T ? std::min(q0 / kKvTile + 2, n_kv_seq) : 0;
                 for (int bh = g0; bh < g1; bh++) {
                     Slot t = heap.top(); heap.pop();
-                    lists[t.second].push_back((nq - 1 - qt) * BH + bh);
-                    heap.push({t.first + n_kv + 1, t.second});
+                    lists[t.second].push_back((npt - 1 - pt) * BH + bh);
+                    heap.push({t.first + n0 + n1 + 1, t.second});
                 }
             }
         }
@@ -531,42 +533,57 @@ static int attention_schedule(int B, int H, int T, int hd, int nq, int grid, con
     return 0;
 }
 
-bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch) {
-    return (hd == 64 || hd == 128) && T % 8 == 0 && ld_qk % 8 == 0 && vt_ld % 8 == 0 && vt_s_head % 8 == 0 && vt_s_batch % 8 == 0;
+bool attention_fused_supported(int T, int hd, long long ld_q, long long ld_kv) {
+    return (hd == 64 || hd == 128) && T > 0 && ld_q % 8 == 0 && ld_kv % 8 == 0;
 }
 
-// q, k: [B*T, ld_qk] bf16, head h at columns h*hd; vt: V^T, element (b,h,e,t) at vt[b*vt_s_batch + h*vt_s_head + e*vt_ld + t];
+// share of the exponentials evaluated on the FMA pipe (of every 16 pairs), per head size; tunable for experiments
+static int attn_npoly(int hd) {
+    static const int e64 = getenv("SPTORCH_B200_ATTN_NPOLY64") ? atoi(getenv("SPTORCH_B200_ATTN_NPOLY64")) : 5;
+    static const int e128 = getenv("SPTORCH_B200_ATTN_NPOLY128") ? atoi(getenv("SPTORCH_B200_ATTN_NPOLY128")) : 0;
+    return hd == 64 ? e64 : e128;
+}
+
+// q, k, v: [B*T, ld] bf16, head h at columns h*hd (token-major: the layout the QKV projection writes);
 // out: [B*T, ld_out] bf16, head h at columns h*hd.
-int attention_fused(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch, void* out,
-                    int B, int T, int H, int hd, long long ld_qk, long long ld_out) {
-    if (!attention_fused_supported(T, hd, ld_qk, vt_ld, vt_s_head, vt_s_batch)) return fail("attention_fused: unsupported shape or stride");
-    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(vt) | reinterpret_cast<uintptr_t>(out)) & 15)
+int attention_fused(const void* q, const void* k, const void* v, void* out, int B, int T, int H, int hd, long long ld_q, long long ld_k,
+                    long long ld_v, long long ld_out) {
+    if (!attention_fused_supported(T, hd, ld_q, ld_k) || ld_v % 8) return fail("attention_fused: unsupported shape or stride");
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail("attention_fused: buffers must be 16-byte aligned");
     if (ld_out % 8) return fail("attention_fused: ld_out must be a multiple of 8");
     CUtensorMap tq, tk, tv;
-    if (encode4(&tq, q, hd, T, H, B, ld_qk, hd, (long long)T * ld_qk, kQTile)) return 1;
-    if (encode4(&tk, k, hd, T, H, B, ld_qk, hd, (long long)T * ld_qk, kKvTile)) return 1;
-    if (encode4(&tv, vt, T, hd, H, B, vt_ld, vt_s_head, vt_s_batch, hd)) return 1;
+    if (encode_heads(&tq, q, hd, T, H, B, ld_q)) return 1;
+    if (encode_heads(&tk, k, hd, T, H, B, ld_k)) return 1;
+    if (encode_heads(&tv, v, hd, T, H, B, ld_v)) return 1;
     AttnParams prm;
     prm.out = (__nv_bfloat16*)out; prm.ld_out = ld_out; prm.T = T; prm.H = H; prm.B = B;
-    prm.n_qtiles = ceil_div(T, kQTile);
+    prm.n_ptiles = ceil_div(T, kQPair);
     prm.scale_log2 = (1.0f / sqrtf((float)hd)) * 1.4426950408889634f;
     prm.status = rt().dev_status;
-    prm.prof = attn_prof_buffer();
-    long long items = (long long)B * H * prm.n_qtiles;
+    long long items = (long long)B * H * prm.n_ptiles;
     if (items > INT32_MAX) return fail("attention_fused: too many work items");
-    const long long slots = (long long)compute_sms() * (hd == 64 ? 2 : 1);      // resident CTAs
+    const long long slots = compute_sms();                                      // one resident CTA per SM
     long long grid = items < slots ? items : slots;
-    if (attention_schedule(B, H, T, hd, prm.n_qtiles, (int)grid, &prm.sched, &prm.sched_len)) return 1;
+    if (attention_schedule(B, H, T, hd, prm.n_ptiles, (int)grid, &prm.sched, &prm.sched_len)) return 1;
     ProfScope ps(PROF_ATTN_FUSED);
     auto launch = [&](auto kern, int smem_bytes) -> int {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         kern<<<(unsigned)grid, kAttnThreads, smem_bytes, rt().stream>>>(tq, tk, tv, prm);
         return 0;
     };
+    const int np = attn_npoly(hd);
     int lrc;
-    if (hd == 64) lrc = prm.prof ? launch(attn_fused_kernel<64, true>, AttnSmem<64>::kTotal) : launch(attn_fused_kernel<64, false>, AttnSmem<64>::kTotal);
-    else lrc = prm.prof ? launch(attn_fused_kernel<128, true>, AttnSmem<128>::kTotal) : launch(attn_fused_kernel<128, false>, AttnSmem<128>::kTotal);
+    if (hd == 64) {
+        if (np <= 0) lrc = launch(attn_fused_kernel<64, 0>, AttnSmem<64>::kTotal);
+        else if (np <= 4) lrc = launch(attn_fused_kernel<64, 4>, AttnSmem<64>::kTotal);
+        else if (np <= 5) lrc = launch(attn_fused_kernel<64, 5>, AttnSmem<64>::kTotal);
+        else if (np <= 6) lrc = launch(attn_fused_kernel<64, 6>, AttnSmem<64>::kTotal);
+        else lrc = launch(attn_fused_kernel<64, 8>, AttnSmem<64>::kTotal);
+    } else {
+        if (np <= 0) lrc = launch(attn_fused_kernel<128, 0>, AttnSmem<128>::kTotal);
+        else lrc = launch(attn_fused_kernel<128, 4>, AttnSmem<128>::kTotal);
+    }
     if (lrc) return lrc;
     SPT_LAUNCH_CHECK("attn_fused");
     return 0;

@@ -44,6 +44,14 @@ int fail_host(const char* fmt, ...);
 int enter();
 // Waits for the library stream without consuming the sticky error flag (internal uploads use this).
 int stream_wait();
+// Registers a callback run once at backend shutdown, while the device is still current (frees per-process device caches).
+void at_shutdown(void (*fn)());
+// Counter bumped by every setter that changes which kernels or grids a forward launches (attention mode, GEMM tile mode,
+// matmul arithmetic, SM reserve): a captured CUDA graph is only replayed while the counter still has the value it was captured at.
+uint64_t config_epoch();
+void bump_config_epoch();
+// Resolves the device address of the allocation-free matmul's static scratch for the runtime's device (gemm.cu).
+void static_scratch_prepare();
 inline void note_submit() { rt().submitted.fetch_add(1, std::memory_order_relaxed); }
 
 #define SPT_CUDA(expr)                                                                     \

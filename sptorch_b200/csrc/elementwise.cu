@@ -324,6 +324,41 @@ __global__ void __launch_bounds__(kThreads) bf16_to_f32_kernel(const __nv_bfloat
     for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) out[i] = __bfloat162float(in[i]);
 }
 
+// [rows, ld] (ld >= cols) -> dense [rows, cols], elements of ES bytes (2 or 4).  The dense matrix is produced in aligned 16-byte
+// vectors (its rows need not be: cols may be odd); each vector's elements are fetched one by one from wherever they lie in the
+// padded matrix, neighbouring threads reading neighbouring elements.  One HBM pass: rows * cols * ES bytes in and out.
+template <typename E>
+__global__ void __launch_bounds__(256) compact_rows_kernel(const E* __restrict__ src, E* __restrict__ dst, size_t rows, size_t cols, size_t ld) {
+    constexpr int VE = 16 / (int)sizeof(E);
+    const size_t total = rows * cols;
+    const size_t nvec = total / VE;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+        const size_t f = v * VE;
+        size_t r = f / cols, c = f - r * cols;
+        E e[VE];
+#pragma unroll
+        for (int i = 0; i < VE; i++) {
+            e[i] = src[r * ld + c];
+            if (++c == cols) { c = 0; r++; }
+        }
+        *reinterpret_cast<uint4*>(dst + f) = *reinterpret_cast<const uint4*>(e);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {          // the last, partial vector
+        for (size_t f = nvec * VE; f < total; f++) { const size_t r = f / cols; dst[f] = src[r * ld + (f - r * cols)]; }
+    }
+}
+
+int compact_rows_launch(const void* src, void* dst, size_t rows, size_t cols, size_t ld, int es) {
+    if (rows == 0 || cols == 0) return 0;
+    if (reinterpret_cast<uintptr_t>(dst) & 15) return fail("compact_rows: destination must be 16-byte aligned");
+    const int grid = rt().sm_count * 8;
+    if (es == 2) compact_rows_kernel<uint16_t><<<grid, 256, 0, rt().stream>>>((const uint16_t*)src, (uint16_t*)dst, rows, cols, ld);
+    else compact_rows_kernel<uint32_t><<<grid, 256, 0, rt().stream>>>((const uint32_t*)src, (uint32_t*)dst, rows, cols, ld);
+    SPT_LAUNCH_CHECK("compact_rows");
+    return 0;
+}
+
 }  // namespace spt
 
 using namespace spt;

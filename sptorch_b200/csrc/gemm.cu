@@ -57,7 +57,7 @@ struct GemmParams {
 };
 
 // LayerNorm folded into the epilogue (see GemmDesc): a kernel argument of its own, read by the NORM variants only
-struct NormArgs { const float2* stats; const float* s; const float* c; };
+struct NormArgs { const float2* stats; const float* s; };
 
 __device__ __forceinline__ float gelu_exact(float x) {
     const float k = 0.7978845608028654f;
@@ -105,7 +105,6 @@ __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int
 // what an epilogue thread keeps per tile for its output row when LayerNorm is folded into the product (nothing otherwise)
 template <int NORM> struct NormRow {};
 template <> struct NormRow<1> { float2 stat; };
-template <> struct NormRow<2> { float s, c; };
 
 // PAIR: two CTAs of a cluster work on one 256 x BN tile with cta_group::2 MMAs issued by the even CTA.  Each CTA loads its
 // own 128 rows of A and its own half (BN/2 rows) of the B tile, keeps its 128 rows of the accumulator in its own TMEM and
@@ -305,7 +304,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // folded LayerNorm: what this thread's output row needs for the whole tile
             NormRow<NORM> nr;
             if constexpr (NORM == 1) { nr.stat = row_ok ? __ldg(na.stats + (long long)z * p.M + row) : make_float2(1.0f, 0.0f); }
-            if constexpr (NORM == 2) { nr.s = row_ok ? __ldg(na.s + row) : 0.0f; nr.c = row_ok ? __ldg(na.c + row) : 0.0f; }
             // residual row segment of one chunk (row-per-thread layout)
             uint4 rnext[NV];
             auto fetch_residual = [&](int c) {
@@ -362,16 +360,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         float2 lo = __ffma2_rn(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), inv2, __ffma2_rn(nmi2, make_float2(s4.x, s4.y), make_float2(b4.x, b4.y)));
                         float2 hi = __ffma2_rn(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), inv2, __ffma2_rn(nmi2, make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
                         f[j] = lo.x; f[j + 1] = lo.y; f[j + 2] = hi.x; f[j + 3] = hi.y;
-                    }
-                } else if constexpr (NORM == 2) {
-                    // the normalised operand is B: statistics per output column, s / c per output row (this thread's row)
-                    const float2* stp = na.stats + (long long)z * p.N + n0 + c * 32;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const bool in = n0 + c * 32 + j + 1 < p.N;
-                        const float4 st2 = in ? __ldg(reinterpret_cast<const float4*>(stp + j)) : make_float4(0.f, 0.f, 0.f, 0.f);   // (inv, mi) of two columns
-                        f[j] = __uint_as_float(v[j]) * st2.x + (nr.c - st2.y * nr.s);
-                        f[j + 1] = __uint_as_float(v[j + 1]) * st2.z + (nr.c - st2.w * nr.s);
                     }
                 } else {
                 const float2 al2 = make_float2(p.alpha, p.alpha);
@@ -564,11 +552,9 @@ bool gemm_supported(const GemmDesc& d, const char** why) {
     if ((long long)d.lda * es >= (1ll << 40) || (long long)d.ldb * es >= (1ll << 40)) return bad("row pitch too large for a tensor map");
     if (d.mode == MM_TF32 && d.out_dtype != F32) return bad("TF32 mode writes f32 only");
     if (d.norm_axis) {
-        if (d.norm_axis != 1 && d.norm_axis != 2) return bad("norm_axis is not 0, 1 or 2");
-        if (!d.norm_stats || !d.norm_s || (d.norm_axis == 2 && !d.norm_c)) return bad("folded LayerNorm needs its statistics and column sums");
-        if (d.norm_axis == 2 && d.bias) return bad("norm_axis 2 takes its constants through norm_c, not bias");
+        if (d.norm_axis != 1) return bad("norm_axis is not 0 or 1");
+        if (!d.norm_stats || !d.norm_s) return bad("folded LayerNorm needs its statistics and column sums");
         if ((reinterpret_cast<uintptr_t>(d.norm_stats) | reinterpret_cast<uintptr_t>(d.norm_s)) & 15) return bad("folded LayerNorm vectors must be 16-byte aligned");
-        if (d.norm_axis == 2 && d.N % 2) return bad("folded LayerNorm along columns needs an even N");
         if (d.alpha != 1.0f) return bad("folded LayerNorm does not combine with alpha");
     }
     if (why) *why = ok;
@@ -583,7 +569,7 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr, nullptr});
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr});
     SPT_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
@@ -597,7 +583,7 @@ static int launch_norm_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{pl.d.norm_stats, pl.d.norm_s, pl.d.norm_c});
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{pl.d.norm_stats, pl.d.norm_s});
     SPT_LAUNCH_CHECK("gemm_tcgen05 (folded LayerNorm)");
     return 0;
 }
@@ -619,7 +605,7 @@ static int launch_pair_t(const GemmPlan& pl, const GemmParams& prm) {
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr, nullptr}));
+    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr}));
     SPT_LAUNCH_CHECK("gemm_tcgen05 (pair)");
     return 0;
 }
@@ -722,7 +708,7 @@ int gemm_run(const GemmPlan& pl) {
     const bool out_bf16 = d.out_dtype == BF16;
     if (d.norm_axis) {
         if (tf32 || !out_bf16 || pl.bn != 256 || pl.pair) return fail("gemm_run: the folded-LayerNorm epilogue needs bf16 operands and output and N > 128");
-        return d.norm_axis == 1 ? launch_norm_t<1>(pl, prm) : launch_norm_t<2>(pl, prm);
+        return launch_norm_t<1>(pl, prm);
     }
     if (pl.pair) {
         if (tf32) return launch_pair_t<true, float>(pl, prm);
@@ -814,6 +800,7 @@ static std::atomic<int> g_abi_mode{MM_TF32};
 extern "C" int sptorch_ext_set_gemm_pair(int mode) {
     if (mode < 0 || mode > 2) return fail("set_gemm_pair: mode %d is not 0, 1 or 2", mode);
     g_pair_mode.store(mode);
+    bump_config_epoch();
     return 0;
 }
 
@@ -856,6 +843,23 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 static float* g_static_scratch_addr[64] = {};                            // device address per CUDA ordinal, filled on first use
 static std::mutex g_static_scratch_mu;
 
+// Device address of the array for the runtime's device; looked up once per CUDA ordinal with that device current.
+// In host code the array's name is only a stand-in: a kernel must be given the address the runtime reports.
+static float* static_scratch_address(int dev) {
+    if (dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) { cudaGetLastError(); return nullptr; }
+        g_static_scratch_addr[dev] = (float*)p;
+    }
+    return g_static_scratch_addr[dev];
+}
+// Called by the backend's initialisation (device current, nothing captured yet), so that later calls of
+// sptorch_ext_matmul_f32_static find the address cached; a failure here is retried by the first call.
+void static_scratch_prepare() { (void)static_scratch_address(rt().device); }
+
 }  // namespace spt
 
 using namespace spt;
@@ -870,8 +874,9 @@ extern "C" {
 // call performs no cudaMalloc / cudaFree / pool allocation of any kind.
 //   * limit: k * n <= 2,097,152 elements (for example 1024 x 2048); larger products are rejected with an error.
 //     Every GPU that loads the library carries the 8 MiB until the process exits.
-//   * the first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
-//     before starting any stream capture.
+//   * the array's device address is looked up (cudaGetSymbolAddress) when the backend is initialised, with the
+//     backend's device current; should that lookup have failed, the first call here repeats it, so make the first
+//     call before starting any stream capture.
 //   * all calls share the one array and it keeps the previous call's contents; nothing in it has to start at zero
 //     (each call overwrites the k * n elements it then reads).  Two calls whose kernels overlap on the GPU -- from
 //     different streams or threads -- would race on it: issue them on the library's stream, one after the other.
@@ -881,27 +886,17 @@ int sptorch_ext_matmul_f32_static(const void* a, const void* b, void* out, size_
     if (m == 0 || n == 0) return 0;
     if (!a || !b || !out) return fail("matmul_f32_static: null handle");
     if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return fail("matmul_f32_static: dimension too large");
-    if (k * n > kStaticScratchFloats)
-        return fail("matmul_f32_static: k*n = %zu exceeds the static scratch of %zu elements; use sptorch_matmul_f32", k * n, (size_t)kStaticScratchFloats);
     if (k == 0) {
         SPT_CUDA(cudaMemsetAsync(out, 0, m * n * sizeof(float), rt().stream));
         note_submit();
         return 0;
     }
+    if (k * n > kStaticScratchFloats)
+        return fail("matmul_f32_static: k*n = %zu exceeds the static scratch of %zu elements; use sptorch_matmul_f32", k * n, (size_t)kStaticScratchFloats);
     const int dev = rt().device;
     if (dev < 0 || dev >= 64) return fail("matmul_f32_static: device ordinal %d out of range", dev);
-    float* scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> lk(g_static_scratch_mu);
-        if (!g_static_scratch_addr[dev]) {
-            // in host code the array's name is only a stand-in: the kernel needs the address the runtime reports
-            void* p = nullptr;
-            cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-            if (e != cudaSuccess || !p) return fail("matmul_f32_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-            g_static_scratch_addr[dev] = (float*)p;
-        }
-        scratch = g_static_scratch_addr[dev];
-    }
+    float* scratch = static_scratch_address(dev);
+    if (!scratch) return fail("matmul_f32_static: cudaGetSymbolAddress could not resolve the static scratch on device %d", dev);
     GemmDesc d;
     d.mode = MM_TF32; d.out_dtype = F32;
     d.M = (int)m; d.N = (int)n; d.K = (int)k;
@@ -923,6 +918,7 @@ int sptorch_batch_matmul_f32(const void* a, const void* b, void* out, size_t bat
 int sptorch_ext_set_matmul_mode(int mode) {
     if (mode != SPT_MM_TF32 && mode != SPT_MM_F32) return fail("set_matmul_mode: the f32 C-ABI accepts SPT_MM_TF32 or SPT_MM_F32");
     g_abi_mode.store(mode);
+    bump_config_epoch();
     return 0;
 }
 

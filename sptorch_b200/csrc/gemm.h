@@ -29,13 +29,11 @@ struct GemmDesc {
     // LayerNorm folded into the product.  With W' = W * gamma (per input feature), s[n] = sum_k W'[n,k], c[n] = sum_k beta[k] W[n,k] + bias[n]:
     //   LN(x) W^T + bias = inv[m] * (x W'^T)[m,n] - (mean[m] inv[m]) * s[n] + c[n]
     // so the GEMM reads the un-normalised rows and the epilogue applies the row statistics.  norm_axis 1: the normalised operand
-    // is A (statistics per output row, s / c per output column, c passed as `bias`); norm_axis 2: it is B (statistics per output
-    // column, norm_s / norm_c per output row) -- the transposed V projection.  stats[i] = (inv_std, mean * inv_std).
-    // norm_s (axis 1) must be readable up to N rounded up to 32 elements, norm_stats (axis 2) likewise.
+    // is A (statistics per output row, s / c per output column, c passed as `bias`).  stats[i] = (inv_std, mean * inv_std).
+    // norm_s must be readable up to N rounded up to 32 elements.
     int norm_axis = 0;
     const float2* norm_stats = nullptr;
     const float* norm_s = nullptr;
-    const float* norm_c = nullptr;   // norm_axis 2 only
 };
 
 // A prepared launch: tensor maps are encoded once and can be replayed (the GPT driver caches these).

@@ -2,9 +2,11 @@
 //
 // The reference runs one sequence per call and allocates + copies on every op; here a batch of
 // sequences is one [B*T, d] activation matrix (every op of the path is row- or sequence-local, so the
-// per-sequence results are unchanged) and a layer is ten launches:
-//   LN1 | [Wq;Wk] GEMM | V^T GEMM (swapped operands, writes V^T directly) | S=QK^T | causal softmax |
-//   O=PV | Wo GEMM (+residual) | LN2 | W_up GEMM (+bias, GELU) | W_down GEMM (+bias, +residual)
+// per-sequence results are unchanged) and a layer is seven launches:
+//   LN1 | [Wq;Wk;Wv] GEMM | fused causal attention | Wo GEMM (+residual) | LN2 | W_up GEMM (+bias, GELU) |
+//   W_down GEMM (+bias, +residual)
+// (models the fused attention kernel does not take -- f32, head sizes other than 64 / 128 -- run the attention as
+// V^T GEMM | S = Q K^T | causal softmax | O = P V instead: eleven launches)
 // Dropout (nn/src/lib.rs:168-182) is the identity in eval mode and is not launched.
 // Weights keep the reference's [out,in] layout; parameter names are GPT::named_parameters' (nn/src/lib.rs:1382-1392).
 // Tensor parallel (tp_size > 1): wq/wk/wv/ffn_up split by output rows (heads / d_ff columns), wo/ffn_down
@@ -20,21 +22,24 @@
 
 namespace spt {
 
-int attention_dispatch(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
-                       void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
-bool attention_fused_supported(int T, int hd, long long ld_qk, long long vt_ld, long long vt_s_head, long long vt_s_batch);
-int attention_mode();
+int attention_materialized(const void* q, const void* k, const void* vt, long long vt_ld, long long vt_s_head, long long vt_s_batch,
+                           void* out, void* scores, int B, int Tn, int H, int hd, long long ld_qk, long long ld_out, int dtype);
+int attention_fused(const void* q, const void* k, const void* v, void* out, int B, int T, int H, int hd, long long ld_q, long long ld_k,
+                    long long ld_v, long long ld_out);
+bool attention_uses_fused(int dtype, int Tn, int hd, long long ld_q, long long ld_kv);
 int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype);
+int compact_rows_launch(const void* src, void* dst, size_t rows, size_t cols, size_t ld, int es);
 int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
                          int n, long long seq_stride, long long row_stride, int dtype);
 
 struct Layer {
     float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;     // Qwen-like: ln1g / ln2g hold the RMSNorm weights, the betas are unused
-    void *wqk, *wv, *wo, *w1, *w2;
+    void *wqkv;                                      // [Wq; Wk; Wv] of this rank, one [3*d_loc, d] matrix
+    void *wqk, *wv, *wo, *w1, *w2;                   // wqk = rows 0..2*d_loc of wqkv, wv = rows 2*d_loc..
     void* wg = nullptr; float* bg = nullptr;         // Qwen-like: gate projection of the SwiGLU MLP
     // LayerNorm folded into the GEMMs that consume it (bf16 GPT): weights times gamma, their row sums s, and c = W beta (+ bias)
-    void *wqk_f = nullptr, *wv_f = nullptr, *w1_f = nullptr;
-    float *s_qk = nullptr, *c_qk = nullptr, *s_v = nullptr, *c_v = nullptr, *s_1 = nullptr, *c_1 = nullptr;
+    void *wqkv_f = nullptr, *w1_f = nullptr;
+    float *s_qkv = nullptr, *c_qkv = nullptr, *s_1 = nullptr, *c_1 = nullptr;
 };
 
 struct Gpt {
@@ -46,8 +51,9 @@ struct Gpt {
     float *lnfg, *lnfb;
     std::vector<Layer> L;
     // activations for max_batch * seq_len tokens
-    void *x, *y, *h, *qk, *vt, *ao, *f, *scores;
-    size_t scores_elems;
+    void *x, *y, *h, *qkv, *ao, *f;                // qkv: [tokens, 3*d_loc] = [q | k | v] of every token
+    void *vt = nullptr, *scores = nullptr;          // materialised attention only (ensure_scores): V^T [d_loc, tokens], scores [batch, heads, T, T]
+    size_t scores_elems = 0, vt_elems = 0;
     std::vector<void*> taps; bool taps_on = false;
     sptorch_allreduce_fn ar = nullptr; void* ar_user = nullptr;
     std::vector<void*> owned;
@@ -59,18 +65,41 @@ struct Gpt {
     void *kcache = nullptr, *vcache = nullptr;
     int cache_ctx = 0, cached_len = 0, cache_batch = 0;
     bool fill_cache = false;      // set while a prefill runs
-    void *dq = nullptr, *dv = nullptr;   // decode scratch: [max_batch, 2*d_loc] and [max_batch, d_loc]
+    void *dq = nullptr;                  // decode scratch: [max_batch, 3*d_loc] = [q | k | v] of the new tokens
     // CUDA graph of one forward, keyed by everything that is baked into its kernel arguments
-    struct GraphKey { const void* ids; void* logits; int batch, T; bool taps; cudaStream_t stream; };
-    GraphKey gkey = {nullptr, nullptr, 0, 0, false, nullptr};
-    cudaGraphExec_t gexec = nullptr;
-    int eager_runs = 0;        // forwards of the current key run eagerly so far (the first one sets function attributes)
+    // (the config epoch covers the process-wide setters that change which kernels or grids a forward launches)
+    struct GraphKey {
+        const void* ids; void* logits; int batch, T; bool taps; cudaStream_t stream; uint64_t epoch;
+        bool operator==(const GraphKey& o) const {
+            return ids == o.ids && logits == o.logits && batch == o.batch && T == o.T && taps == o.taps && stream == o.stream && epoch == o.epoch;
+        }
+    };
+    // a few keys are kept so that callers alternating between buffers (double buffering) replay instead of re-capturing
+    struct GraphSlot { GraphKey key; cudaGraphExec_t exec = nullptr; int eager_runs = 0; uint64_t last_use = 0; };
+    static constexpr int kGraphSlots = 4;
+    GraphSlot gslots[kGraphSlots];
+    uint64_t guse = 0;
     bool graphs = true;
     // folded LayerNorm (see forward): per-token statistics, the head's folded copy, and whether the copies are stale
     float2* ln_stats = nullptr; void* head_f = nullptr; float *s_h = nullptr, *c_h = nullptr;
     bool ln_fold = false, fold_ready = false, fold_dirty = true;     // opt-in: measured neutral (see sptorch_ext_gpt_enable_ln_fold)
     bool tp_overlap = false;   // tensor parallel: reduce one half of the batch while the other half computes (opt-in)
 };
+
+static void drop_graphs(Gpt* g) {
+    for (auto& sl : g->gslots) {
+        if (sl.exec) cudaGraphExecDestroy(sl.exec);
+        sl = Gpt::GraphSlot();
+    }
+}
+
+// returns a block of the model to the pool before the model itself goes (buffers that are re-allocated larger)
+static void gfree(Gpt* g, void* p) {
+    if (!p) return;
+    for (auto it = g->owned.begin(); it != g->owned.end(); ++it)
+        if (*it == p) { g->owned.erase(it); break; }
+    sptorch_free(p);
+}
 
 static void* galloc(Gpt* g, size_t bytes) {
     void* p = sptorch_ext_alloc_bytes(bytes);
@@ -90,16 +119,77 @@ static int upload_rows(Gpt* g, void* dst_model_dtype, const float* host, size_t 
     return rc;
 }
 
-// rows [r0, r0+nr) of a [R, C] host matrix
-static int upload_row_slice(Gpt* g, void* dst, const float* host, size_t C, size_t r0, size_t nr) {
-    return upload_rows(g, dst, host + r0 * C, nr * C);
+// ---- tensor-parallel shard rule (host code, no device needed) ----
+// Megatron split of the block's projections over tp_size ranks: wq / wk / wv / ffn_up (and the Qwen-like ffn_gate) are cut by
+// OUTPUT rows (heads, d_ff columns), their biases with them; wo / ffn_down are cut along K (input columns) so that every rank
+// produces a partial [M, d] sum; everything else is replicated.  Rank 0 alone adds the residual and the row-parallel bias
+// (ffn_down.bias) to its partial, so that the all-reduced sum is the new residual stream.
+enum TpKind : int { TP_REPLICATED = 0, TP_ROWS = 1, TP_COLS = 2 };
+static int tp_kind_of(const std::string& name) {
+    auto ends = [&](const char* suf) { const size_t n = strlen(suf); return name.size() >= n && name.compare(name.size() - n, n, suf) == 0; };
+    if (name.compare(0, 7, "blocks.") != 0) return TP_REPLICATED;
+    if (ends("attn.wq.weight") || ends("attn.wk.weight") || ends("attn.wv.weight") || ends("ffn_up.weight") || ends("ffn_up.bias") ||
+        ends("ffn_gate.weight") || ends("ffn_gate.bias")) return TP_ROWS;
+    if (ends("attn.wo.weight") || ends("ffn_down.weight")) return TP_COLS;
+    return TP_REPLICATED;
 }
-// columns [c0, c0+nc) of a [R, C] host matrix -> dense [R, nc]
-static int upload_col_slice(Gpt* g, void* dst, const float* host, size_t R, size_t C, size_t c0, size_t nc) {
-    if (nc == C) return upload_rows(g, dst, host, R * C);
-    std::vector<float> tmp(R * nc);
-    for (size_t r = 0; r < R; r++) memcpy(&tmp[r * nc], host + r * C + c0, nc * sizeof(float));
-    return upload_rows(g, dst, tmp.data(), R * nc);
+
+}  // namespace spt
+
+extern "C" {
+
+int sptorch_ext_tp_param_shard(const char* name, int tp_rank, int tp_size, size_t rows, size_t cols, int* kind, size_t* begin, size_t* count) {
+    using namespace spt;
+    if (!name || !kind || !begin || !count) return fail_host("tp_param_shard: null argument");
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail_host("tp_param_shard: rank %d of %d", tp_rank, tp_size);
+    const int k = tp_kind_of(name);
+    *kind = k;
+    if (k == TP_REPLICATED) { *begin = 0; *count = rows; return 0; }
+    const size_t extent = k == TP_ROWS ? rows : cols;
+    if (extent % (size_t)tp_size) return fail_host("tp_param_shard(%s): extent %zu does not divide by tp_size %d", name, extent, tp_size);
+    *count = extent / (size_t)tp_size;
+    *begin = (size_t)tp_rank * *count;
+    return 0;
+}
+
+int sptorch_ext_tp_slice_host(const float* full, size_t rows, size_t cols, int kind, size_t begin, size_t count, float* out) {
+    using namespace spt;
+    if (!full || !out) return fail_host("tp_slice_host: null argument");
+    if (kind == TP_REPLICATED) { memcpy(out, full, rows * cols * sizeof(float)); return 0; }
+    if (kind == TP_ROWS) {
+        if (begin + count > rows) return fail_host("tp_slice_host: rows [%zu, %zu) outside %zu", begin, begin + count, rows);
+        memcpy(out, full + begin * cols, count * cols * sizeof(float));
+        return 0;
+    }
+    if (kind == TP_COLS) {
+        if (begin + count > cols) return fail_host("tp_slice_host: columns [%zu, %zu) outside %zu", begin, begin + count, cols);
+        for (size_t r = 0; r < rows; r++) memcpy(out + r * count, full + r * cols + begin, count * sizeof(float));
+        return 0;
+    }
+    return fail_host("tp_slice_host: unknown kind %d", kind);
+}
+
+int sptorch_ext_tp_rank_folds_residual(int tp_rank) { return tp_rank == 0 ? 1 : 0; }
+
+}  // extern "C"
+
+namespace spt {
+
+// this rank's shard of a full [R, C] host tensor (a vector is [R, 1]) -> device, in the model dtype (f32 for vectors)
+static int upload_shard(Gpt* g, void* dst, const char* name, const float* host, size_t R, size_t C, bool as_f32) {
+    int kind; size_t begin, count;
+    if (sptorch_ext_tp_param_shard(name, g->c.tp_rank, g->c.tp_size, R, C, &kind, &begin, &count)) return fail("gpt_set_param(%s): no shard rule", name);
+    const size_t n = kind == TP_COLS ? R * count : count * C;
+    const float* src = host;
+    std::vector<float> tmp;
+    if (kind == TP_ROWS) src = host + begin * C;                        // contiguous
+    else if (kind == TP_COLS && count != C) {
+        tmp.resize(n);
+        if (sptorch_ext_tp_slice_host(host, R, C, kind, begin, count, tmp.data())) return 1;
+        src = tmp.data();
+    }
+    if (as_f32) return sptorch_ext_copy_h2d_bytes(src, dst, n * 4) || stream_wait();
+    return upload_rows(g, dst, src, n);
 }
 
 static int linear(Gpt* g, const void* x, const void* w, const float* bias, const void* res, void* out, int M, int K, int N,
@@ -134,10 +224,11 @@ static int allreduce(Gpt* g, void* buf, size_t n) {
 // LN(x) W^T + b = inv * (x (W gamma)^T) - (mean inv) * s + c with s = rowsum(W gamma), c = W beta + b.  The forward then launches,
 // instead of a LayerNorm pass that reads and writes every activation, a statistics pass that only reads them (8 bytes per token
 // out), and the GEMMs consume the residual stream directly.  Used for bf16 GPT models whose GEMMs all take the 256-column tile.
-static bool fold_applicable(const Gpt* g, int M) {
+static bool model_uses_fused(const Gpt* g, int T);
+static bool fold_applicable(const Gpt* g, int M, int T) {
     const sptorch_gpt_config& c = g->c;
     return g->ln_fold && c.arch == SPT_ARCH_GPT && c.dtype == SPT_BF16 && !g->fill_cache && layernorm_stats_supported((size_t)c.d_model, c.dtype) &&
-           2 * g->d_loc > 128 && g->F_loc > 128 && c.vocab > 128 && M > 128 && M % 2 == 0;
+           3 * g->d_loc > 128 && g->F_loc > 128 && c.vocab > 128 && M > 128 && M % 2 == 0 && model_uses_fused(g, T);
 }
 
 static int fold_prepare(Gpt* g) {
@@ -149,8 +240,8 @@ static int fold_prepare(Gpt* g) {
         auto A = [&](size_t bytes) { void* p = galloc(g, bytes); if (!p) ok = false; return p; };
         auto Z = [&](size_t n) { float* p = (float*)A(pad32(n) * 4); if (p && sptorch_ext_memset(p, 0, pad32(n) * 4)) ok = false; return p; };
         for (auto& w : g->L) {
-            w.wqk_f = A(2 * dl * d * es); w.wv_f = A(dl * d * es); w.w1_f = A(Fl * d * es);
-            w.s_qk = Z(2 * dl); w.c_qk = Z(2 * dl); w.s_v = Z(dl); w.c_v = Z(dl); w.s_1 = Z(Fl); w.c_1 = Z(Fl);
+            w.wqkv_f = A(3 * dl * d * es); w.w1_f = A(Fl * d * es);
+            w.s_qkv = Z(3 * dl); w.c_qkv = Z(3 * dl); w.s_1 = Z(Fl); w.c_1 = Z(Fl);
         }
         g->head_f = A(V * d * es); g->s_h = Z(V); g->c_h = Z(V);
         g->ln_stats = (float2*)A(((size_t)c.max_batch * c.seq_len + 32) * sizeof(float2));
@@ -160,8 +251,7 @@ static int fold_prepare(Gpt* g) {
     }
     if (g->fold_dirty) {
         for (auto& w : g->L) {
-            if (layernorm_fold_launch(w.wqk, w.ln1g, w.ln1b, nullptr, w.wqk_f, w.s_qk, w.c_qk, 2 * dl, d, c.dtype)) return 1;
-            if (layernorm_fold_launch(w.wv, w.ln1g, w.ln1b, nullptr, w.wv_f, w.s_v, w.c_v, dl, d, c.dtype)) return 1;
+            if (layernorm_fold_launch(w.wqkv, w.ln1g, w.ln1b, nullptr, w.wqkv_f, w.s_qkv, w.c_qkv, 3 * dl, d, c.dtype)) return 1;
             if (layernorm_fold_launch(w.w1, w.ln2g, w.ln2b, w.b1, w.w1_f, w.s_1, w.c_1, Fl, d, c.dtype)) return 1;
         }
         if (layernorm_fold_launch(g->head, g->lnfg, g->lnfb, nullptr, g->head_f, g->s_h, g->c_h, V, d, c.dtype)) return 1;
@@ -188,17 +278,67 @@ static int linear_folded(Gpt* g, const void* x, const void* wf, const float* cve
     return gemm_run(pl);
 }
 
-// out[N_w, M] = (LN(x) W^T)^T: the weights are the A operand, the tokens the columns (the transposed V projection)
-static int linear_folded_t(Gpt* g, const void* wf, const void* x, const float* svec, const float* cvec, void* out, int Nw, int K, int M) {
-    GemmDesc d;
-    d.A = wf; d.B = x; d.C = out;
-    d.M = Nw; d.N = M; d.K = K; d.lda = K; d.ldb = K; d.ldc = M;
-    d.mode = MM_BF16; d.out_dtype = SPT_BF16;
-    d.norm_axis = 2; d.norm_stats = g->ln_stats; d.norm_s = svec; d.norm_c = cvec;
-    GemmPlan pl;
-    if (gemm_plan(d, &pl)) return 1;
-    ProfScope ps(PROF_LINEAR);
-    return gemm_run(pl);
+// true when the blocks of this model run the fused attention kernel on sequences of T tokens
+static bool model_uses_fused(const Gpt* g, int T) {
+    return attention_uses_fused(g->c.dtype, T, g->c.d_model / g->c.n_head, 3 * g->d_loc, 3 * g->d_loc);
+}
+
+// The [batch, heads, T, T] score workspace and the V^T buffer exist only for the materialised attention (f32 models, head sizes
+// other than 64 / 128, or sptorch_ext_set_attention_mode(1)); the fused kernel never touches them.  They are sized for the batch
+// actually run and grown on demand, outside any graph capture.
+static int ensure_scores(Gpt* g, int batch, int T) {
+    if (model_uses_fused(g, T)) return 0;
+    const size_t need = (size_t)batch * g->H_loc * T * T, need_vt = (size_t)g->d_loc * batch * T;
+    if (need <= g->scores_elems && need_vt <= g->vt_elems) return 0;
+    if (stream_wait()) return 1;                   // nothing in flight may still read the old workspace
+    drop_graphs(g);                                // captured launches hold its address
+    if (need > g->scores_elems) {
+        gfree(g, g->scores);
+        g->scores = galloc(g, need * g->es);
+        g->scores_elems = g->scores ? need : 0;
+        if (!g->scores) return 1;
+    }
+    if (need_vt > g->vt_elems) {
+        gfree(g, g->vt);
+        g->vt = galloc(g, need_vt * g->es);
+        g->vt_elems = g->vt ? need_vt : 0;
+        if (!g->vt) return 1;
+    }
+    return 0;
+}
+
+// One block's attention from the normalised rows h [M, d] (M = B*T tokens) to the merged heads ao [M, d_loc]:
+//   [q | k | v] = h [Wq;Wk;Wv]^T  (one GEMM, N = 3*d_loc)  ->  (Qwen-like: RoPE on the q and k columns)  ->  causal attention.
+// The fused kernel reads q, k and v in place from the [M, 3*d_loc] buffer.  The materialised form needs V^T as the K-major
+// operand of P V, which one more GEMM with swapped operands produces (V^T = Wv h^T).
+// During a prefill the (rotated) keys and the values of every position are also copied into the cache rows
+// [sequence][position][d_loc] of layer l (project_kv_cache_with_offset, nn/src/lib.rs:672-683).
+// qkv / ao / scores / vt: the buffers of this call (the pipelined tensor-parallel forward passes halves of them).
+static int attention_block(Gpt* g, const Layer& w, int l, const void* h, void* qkv, void* ao, int B, int T, bool folded, const void* x_unnorm) {
+    const sptorch_gpt_config& c = g->c;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Hl = g->H_loc, hd = d / c.n_head, dt = c.dtype;
+    const size_t es = g->es;
+    if (folded) { if (linear_folded(g, x_unnorm, w.wqkv_f, w.c_qkv, w.s_qkv, qkv, M, d, 3 * dl, 3 * dl, EPI_NONE)) return 1; }
+    else if (linear(g, h, w.wqkv, nullptr, nullptr, qkv, M, d, 3 * dl, 3 * dl, EPI_NONE)) return 1;
+    if (c.arch == SPT_ARCH_QWEN_LIKE) { ProfScope ps(PROF_OTHER); if (rope_launch(qkv, M, T, 2 * Hl, hd, 3 * dl, c.rope_base, 0, dt)) return 1; }
+    const uint8_t* qp = (const uint8_t*)qkv;
+    const uint8_t* kp = qp + (size_t)dl * es;
+    const uint8_t* vp = qp + (size_t)2 * dl * es;
+    if (g->fill_cache) {
+        const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es;
+        ProfScope ps(PROF_OTHER);
+        for (int b = 0; b < B; b++) {
+            const size_t dst = lay + (size_t)b * g->cache_ctx * dl * es, src = (size_t)b * T * 3 * dl * es;
+            SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)g->kcache + dst, (size_t)dl * es, kp + src, (size_t)3 * dl * es, (size_t)dl * es, (size_t)T,
+                                       cudaMemcpyDeviceToDevice, rt().stream));
+            SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)g->vcache + dst, (size_t)dl * es, vp + src, (size_t)3 * dl * es, (size_t)dl * es, (size_t)T,
+                                       cudaMemcpyDeviceToDevice, rt().stream));
+        }
+    }
+    if (model_uses_fused(g, T)) return attention_fused(qp, kp, vp, ao, B, T, Hl, hd, 3 * dl, 3 * dl, 3 * dl, dl);
+    if (folded) return fail("gpt: the folded LayerNorm runs with the fused attention only");
+    if (linear(g, w.wv, h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
+    return attention_materialized(qp, kp, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M, /*batch*/ T, ao, g->scores, B, T, Hl, hd, 3 * dl, dl, dt);
 }
 
 // Tensor-parallel forward with the all-reduces taken off the critical path: the batch is cut into two halves that go
@@ -206,7 +346,7 @@ static int linear_folded_t(Gpt* g, const void* wf, const void* x, const float* s
 // half computes.  (The persistent kernels must leave a few SMs free for the collective: sptorch_ext_set_sm_reserve.)
 static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits) {
     const sptorch_gpt_config& c = g->c;
-    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head, dt = c.dtype;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
     const size_t es = g->es;
     const int Bc = B / 2, Mc = Bc * T;
@@ -237,13 +377,9 @@ static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* log
         const Layer& w = g->L[l];
         for (int ch = 0; ch < 2; ch++) {
             if (wait_reduced(ch)) return 1;
-            void* h = rows(g->h, ch, d); void* qk = rows(g->qk, ch, 2 * dl); void* ao = rows(g->ao, ch, dl);
-            void* vt = (uint8_t*)g->vt + (size_t)ch * Mc * es;                      // columns of V^T [dl, M]
+            void* h = rows(g->h, ch, d); void* qkv = rows(g->qkv, ch, 3 * dl); void* ao = rows(g->ao, ch, dl);
             if (ln(xb[ch], w.ln1g, w.ln1b, h, (size_t)Mc, (size_t)d, c.eps, dt)) return 1;
-            if (linear(g, h, w.wqk, nullptr, nullptr, qk, Mc, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
-            if (linear(g, w.wv, h, nullptr, nullptr, vt, dl, d, Mc, M, EPI_NONE)) return 1;
-            if (attention_dispatch(qk, (const uint8_t*)qk + (size_t)dl * es, vt, M, (long long)hd * M, T, ao,
-                                   (uint8_t*)g->scores + (size_t)ch * Bc * Hl * T * T * es, Bc, T, Hl, hd, 2 * dl, dl, dt)) return 1;
+            if (attention_block(g, w, l, h, qkv, ao, Bc, T, false, nullptr)) return 1;
             if (linear(g, ao, w.wo, nullptr, lead ? xb[ch] : nullptr, yb[ch], Mc, dl, d, d, EPI_NONE)) return 1;
             if (reduce_async(ch)) return 1;
         }
@@ -272,11 +408,11 @@ int rms_launch(const void* x, const float* w, void* out, size_t rows, size_t dim
 
 // QwenLikeGPT::forward_ids (nn/src/lib.rs:1454-1467) over a batch; block = QwenLikeBlock::forward_seq_inference (:1106-1117):
 //   x += Wo attn(rope(q), rope(k), v) of rms(x);  x += Wdown (up * gate * sigmoid(gate)) + bdown of rms(x)
-// Launches per layer: RMSNorm, [q|k] GEMM, RoPE over both, V^T GEMM, attention, Wo GEMM (+residual), RMSNorm, up GEMM (+bias),
+// Launches per layer: RMSNorm, [q|k|v] GEMM, RoPE over q and k, attention, Wo GEMM (+residual), RMSNorm, up GEMM (+bias),
 // gate GEMM (+bias, SwiGLU product with the up output in the epilogue), down GEMM (+bias, +residual).
 static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
     const sptorch_gpt_config& c = g->c;
-    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head, dt = c.dtype;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
     { ProfScope ps(PROF_EMBED); if (sptorch_ext_embedding_sum(g->tok, nullptr, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1; }
     void* x = g->x; void* y = g->y;
@@ -289,29 +425,7 @@ static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
     for (int l = 0; l < c.n_layer; l++) {
         const Layer& w = g->L[l];
         if (rms_launch(x, w.ln1g, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
-        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
-        { ProfScope ps(PROF_OTHER); if (rope_launch(g->qk, M, T, 2 * Hl, hd, 2 * dl, c.rope_base, 0, dt)) return 1; }
-        if (g->fill_cache) {
-            // prefill (project_kv_cache_with_offset, nn/src/lib.rs:672-683): the ROTATED keys and the values of every position go to
-            // the cache rows [sequence][position][dl]; keys are copied out of the [q|k] buffer, values come from one more projection
-            const size_t es_ = g->es;
-            const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es_;
-            for (int b = 0; b < B; b++)
-                SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)g->kcache + lay + (size_t)b * g->cache_ctx * dl * es_, (size_t)dl * es_,
-                                           (const uint8_t*)g->qk + ((size_t)b * T * 2 * dl + dl) * es_, (size_t)2 * dl * es_,
-                                           (size_t)dl * es_, (size_t)T, cudaMemcpyDeviceToDevice, rt().stream));
-            GemmDesc vd;
-            vd.A = g->h; vd.B = w.wv; vd.C = (uint8_t*)g->vcache + lay;
-            vd.M = T; vd.N = dl; vd.K = d; vd.lda = d; vd.ldb = d; vd.ldc = dl;
-            vd.nb1 = 1; vd.nb2 = B; vd.sA2 = (long long)T * d; vd.b_broadcast = 1; vd.sC2 = (long long)g->cache_ctx * dl;
-            vd.mode = dt == SPT_BF16 ? MM_BF16 : MM_TF32; vd.out_dtype = dt;
-            GemmPlan pv;
-            if (gemm_plan(vd, &pv)) return 1;
-            { ProfScope ps(PROF_LINEAR); if (gemm_run(pv)) return 1; }
-        }
-        if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
-        if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, M, (long long)hd * M, T, g->ao, g->scores,
-                               B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
+        if (attention_block(g, w, l, g->h, g->qkv, g->ao, B, T, false, nullptr)) return 1;
         if (c.tp_size <= 1) {
             if (linear(g, g->ao, w.wo, nullptr, x, x, M, dl, d, d, EPI_NONE)) return 1;
         } else {
@@ -339,10 +453,10 @@ static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
 
 static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
     if (g->c.arch == SPT_ARCH_QWEN_LIKE) return forward_qwen(g, ids, B, T, logits);
-    if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0)
+    if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0 && model_uses_fused(g, T))
         return forward_tp_pipelined(g, ids, B, T, logits);
     const sptorch_gpt_config& c = g->c;
-    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, Hl = g->H_loc, hd = d / c.n_head;
+    const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc;
     const int dt = c.dtype;
     const bool lead = c.tp_rank == 0;
     { ProfScope ps(PROF_EMBED); if (sptorch_ext_embedding_sum(g->tok, g->pos, ids, g->x, (size_t)M, (size_t)T, (size_t)c.vocab, (size_t)d, dt)) return 1; }
@@ -353,39 +467,16 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         return 0;
     };
     if (tap(0, x)) return 1;
-    const bool fold = fold_applicable(g, M) && g->fold_ready && !g->fold_dirty;
+    const bool fold = fold_applicable(g, M, T) && g->fold_ready && !g->fold_dirty;
     for (int l = 0; l < c.n_layer; l++) {
         const Layer& w = g->L[l];
         if (fold) {
             if (ln_stats(g, x, M)) return 1;
-            if (linear_folded(g, x, w.wqk_f, w.c_qk, w.s_qk, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+            if (attention_block(g, w, l, nullptr, g->qkv, g->ao, B, T, true, x)) return 1;
         } else {
             if (ln(x, w.ln1g, w.ln1b, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
-            // [q | k] = h [Wq;Wk]^T : [M, 2*dl]
-            if (linear(g, g->h, w.wqk, nullptr, nullptr, g->qk, M, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;
+            if (attention_block(g, w, l, g->h, g->qkv, g->ao, B, T, false, nullptr)) return 1;
         }
-        if (g->fill_cache) {
-            // prefill: K and V of every position go to the cache rows [sequence][position][dl] (two more projections of h;
-            // the attention below keeps reading the [q|k] and V^T buffers)
-            const size_t lay = (size_t)l * g->c.max_batch * g->cache_ctx * dl * g->es;
-            GemmDesc kd;
-            kd.A = g->h; kd.C = (uint8_t*)g->kcache + lay;
-            kd.B = (const uint8_t*)w.wqk + (size_t)dl * d * g->es;          // the Wk half of [Wq;Wk]
-            kd.M = T; kd.N = dl; kd.K = d; kd.lda = d; kd.ldb = d; kd.ldc = dl;
-            kd.nb1 = 1; kd.nb2 = B; kd.sA2 = (long long)T * d; kd.b_broadcast = 1; kd.sC2 = (long long)g->cache_ctx * dl;
-            kd.mode = dt == SPT_BF16 ? MM_BF16 : MM_TF32; kd.out_dtype = dt;
-            GemmDesc vd = kd;
-            vd.B = w.wv; vd.C = (uint8_t*)g->vcache + lay;
-            GemmPlan pk, pv;
-            if (gemm_plan(kd, &pk) || gemm_plan(vd, &pv)) return 1;
-            { ProfScope ps(PROF_LINEAR); if (gemm_run(pk)) return 1; }
-            { ProfScope ps(PROF_LINEAR); if (gemm_run(pv)) return 1; }
-        }
-        // V^T = Wv h^T : [dl, M]  (operands swapped so the product lands transposed, ready to be the K-major B of P V)
-        if (fold) { if (linear_folded_t(g, w.wv_f, x, w.s_v, w.c_v, g->vt, dl, d, M)) return 1; }
-        else if (linear(g, w.wv, g->h, nullptr, nullptr, g->vt, dl, d, M, M, EPI_NONE)) return 1;
-        if (attention_dispatch(g->qk, (const uint8_t*)g->qk + (size_t)dl * g->es, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M,
-                                   /*batch*/ T, g->ao, g->scores, B, T, Hl, hd, 2 * dl, dl, dt)) return 1;
         if (c.tp_size <= 1) {
             if (linear(g, g->ao, w.wo, nullptr, x, x, M, dl, d, d, EPI_NONE)) return 1;       // x += attn
         } else {
@@ -490,13 +581,11 @@ void* sptorch_ext_gpt_create(const sptorch_gpt_config* cfg) {
     for (auto& w : g->L) {
         w.ln1g = (float*)A(d * 4); w.ln1b = (float*)A(d * 4); w.ln2g = (float*)A(d * 4); w.ln2b = (float*)A(d * 4);
         w.b1 = (float*)A(Fl * 4); w.b2 = (float*)A(d * 4);
-        w.wqk = A(2 * dl * d * es); w.wv = A(dl * d * es); w.wo = A(d * dl * es); w.w1 = A(Fl * d * es); w.w2 = A(d * Fl * es);
+        w.wqkv = A(3 * dl * d * es); w.wqk = w.wqkv; w.wv = w.wqkv ? (uint8_t*)w.wqkv + 2 * dl * d * es : nullptr; w.wo = A(d * dl * es); w.w1 = A(Fl * d * es); w.w2 = A(d * Fl * es);
         if (c.arch == SPT_ARCH_QWEN_LIKE) { w.wg = A(Fl * d * es); w.bg = (float*)A(Fl * 4); }
     }
     g->x = A(Mmax * d * es); g->y = A(Mmax * d * es); g->h = A(Mmax * d * es);
-    g->qk = A(Mmax * 2 * dl * es); g->vt = A(dl * Mmax * es); g->ao = A(Mmax * dl * es); g->f = A(Mmax * Fl * es);
-    g->scores_elems = (size_t)c.max_batch * g->H_loc * S * S;
-    g->scores = A(g->scores_elems * es);
+    g->qkv = A(Mmax * 3 * dl * es); g->ao = A(Mmax * dl * es); g->f = A(Mmax * Fl * es);
     if (!ok) { sptorch_ext_gpt_destroy(g); return nullptr; }
     return g;
 }
@@ -507,7 +596,7 @@ void sptorch_ext_gpt_destroy(void* gp) {
     if (!enter()) {
         cudaStreamSynchronize(rt().stream);
         cudaStreamSynchronize(rt().copy_stream);
-        if (g->gexec) cudaGraphExecDestroy(g->gexec);
+        drop_graphs(g);
         for (void* p : g->owned) sptorch_free(p);
         for (int i = 0; i < 2; i++) {
             if (g->ev_compute[i]) cudaEventDestroy(g->ev_compute[i]);
@@ -525,7 +614,6 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
     Gpt* g = (Gpt*)gp;
     const sptorch_gpt_config& c = g->c;
     const size_t d = c.d_model, V = c.vocab, S = c.seq_len, F = c.d_ff, dl = g->d_loc, Fl = g->F_loc, es = g->es;
-    const size_t r = c.tp_rank;
     auto need = [&](size_t want) { return n == want ? 0 : fail("gpt_set_param(%s): got %zu values, expected %zu", name, n, want); };
     auto f32 = [&](float* dst, size_t off, size_t cnt) { return sptorch_ext_copy_h2d_bytes(host + off, dst, cnt * 4) || stream_wait(); };
     std::string s(name);
@@ -546,21 +634,22 @@ int sptorch_ext_gpt_set_param(void* gp, const char* name, const float* host, siz
             // QwenLikeBlock::named_parameters (nn/src/lib.rs:1157-1166)
             if (t == "norm1.weight") return need(d) || f32(w.ln1g, 0, d);
             if (t == "norm2.weight") return need(d) || f32(w.ln2g, 0, d);
-            if (t == "ffn_gate.weight") return need(F * d) || upload_row_slice(g, w.wg, host, d, r * Fl, Fl);
-            if (t == "ffn_gate.bias") return need(F) || f32(w.bg, r * Fl, Fl);
+            if (t == "ffn_gate.weight") return need(F * d) || upload_shard(g, w.wg, name, host, F, d, false);
+            if (t == "ffn_gate.bias") return need(F) || upload_shard(g, w.bg, name, host, F, 1, true);
             if (t.compare(0, 2, "ln") == 0) return fail("gpt_set_param: '%s' is not a parameter of the Qwen-like model", name);
         }
         if (t == "ln1.gamma") return need(d) || f32(w.ln1g, 0, d);
         if (t == "ln1.beta") return need(d) || f32(w.ln1b, 0, d);
         if (t == "ln2.gamma") return need(d) || f32(w.ln2g, 0, d);
         if (t == "ln2.beta") return need(d) || f32(w.ln2b, 0, d);
-        if (t == "attn.wq.weight") return need(d * d) || upload_row_slice(g, w.wqk, host, d, r * dl, dl);
-        if (t == "attn.wk.weight") return need(d * d) || upload_row_slice(g, (uint8_t*)w.wqk + dl * d * es, host, d, r * dl, dl);
-        if (t == "attn.wv.weight") return need(d * d) || upload_row_slice(g, w.wv, host, d, r * dl, dl);
-        if (t == "attn.wo.weight") return need(d * d) || upload_col_slice(g, w.wo, host, d, d, r * dl, dl);
-        if (t == "ffn_up.weight") return need(F * d) || upload_row_slice(g, w.w1, host, d, r * Fl, Fl);
-        if (t == "ffn_up.bias") return need(F) || f32(w.b1, r * Fl, Fl);
-        if (t == "ffn_down.weight") return need(d * F) || upload_col_slice(g, w.w2, host, d, F, r * Fl, Fl);
+        // the shard of this rank (sptorch_ext_tp_param_shard): rows of wq / wk / wv / ffn_up, columns of wo / ffn_down
+        if (t == "attn.wq.weight") return need(d * d) || upload_shard(g, w.wqkv, name, host, d, d, false);
+        if (t == "attn.wk.weight") return need(d * d) || upload_shard(g, (uint8_t*)w.wqkv + dl * d * es, name, host, d, d, false);
+        if (t == "attn.wv.weight") return need(d * d) || upload_shard(g, (uint8_t*)w.wqkv + 2 * dl * d * es, name, host, d, d, false);
+        if (t == "attn.wo.weight") return need(d * d) || upload_shard(g, w.wo, name, host, d, d, false);
+        if (t == "ffn_up.weight") return need(F * d) || upload_shard(g, w.w1, name, host, F, d, false);
+        if (t == "ffn_up.bias") return need(F) || upload_shard(g, w.b1, name, host, F, 1, true);
+        if (t == "ffn_down.weight") return need(d * F) || upload_shard(g, w.w2, name, host, d, F, false);
         if (t == "ffn_down.bias") return need(d) || f32(w.b2, 0, d);
     }
     return fail("gpt_set_param: unknown parameter name '%s'", name);
@@ -572,7 +661,7 @@ static int check_shape(Gpt* g, int batch, int T) {
     if (batch <= 0 || T <= 0) return fail("gpt_forward: empty batch or sequence");
     if (T > g->c.seq_len) return fail("gpt_forward: T=%d exceeds seq_len=%d", T, g->c.seq_len);   // nn/src/lib.rs:1351 asserts the same
     if ((size_t)batch * T > (size_t)g->c.max_batch * g->c.seq_len) return fail("gpt_forward: batch*T exceeds the activation capacity");
-    if ((size_t)batch * g->H_loc * T * T > g->scores_elems) return fail("gpt_forward: score workspace too small");
+    if (ensure_scores(g, batch, T)) return 1;      // outside any graph capture
     const int vec = 16 / g->es;
     if (T % vec) return fail("gpt_forward: T must be a multiple of %d for this dtype", vec);
     return 0;
@@ -583,25 +672,28 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
     if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
     Gpt* g = (Gpt*)gp;
     if (check_shape(g, batch, T)) return 1;
-    if (fold_applicable(g, batch * T) && fold_prepare(g)) return 1;      // outside any graph capture
+    if (fold_applicable(g, batch * T, T) && fold_prepare(g)) return 1;      // outside any graph capture
     // The launch-bound inner loop (about 100 kernels, each a few microseconds when the batch is sharded 8 ways) is
     // replayed as one CUDA graph: the first forward of a given (ids, logits, batch, T) runs eagerly, the second is
     // captured, later ones are a single cudaGraphLaunch.  Per-kernel timing and tensor-parallel hooks run eagerly.
     const bool graph_ok = g->graphs && !prof_enabled() && g->c.tp_size <= 1;
     if (!graph_ok) return forward(g, ids, batch, T, logits);
-    Gpt::GraphKey key = {ids, logits, batch, T, g->taps_on, rt().stream};
-    const bool same = key.ids == g->gkey.ids && key.logits == g->gkey.logits && key.batch == g->gkey.batch && key.T == g->gkey.T &&
-                      key.taps == g->gkey.taps && key.stream == g->gkey.stream;
-    if (!same) {
-        if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; }
-        g->gkey = key; g->eager_runs = 0;
+    Gpt::GraphKey key = {ids, logits, batch, T, g->taps_on, rt().stream, config_epoch()};
+    Gpt::GraphSlot* slot = nullptr;
+    for (auto& sl : g->gslots) if ((sl.exec || sl.eager_runs) && sl.key == key) slot = &sl;
+    if (!slot) {                                   // least recently used slot takes the new key
+        slot = &g->gslots[0];
+        for (auto& sl : g->gslots) if (sl.last_use < slot->last_use) slot = &sl;
+        if (slot->exec) { cudaGraphExecDestroy(slot->exec); slot->exec = nullptr; }
+        slot->key = key; slot->eager_runs = 0;
     }
-    if (g->gexec) {
-        SPT_CUDA(cudaGraphLaunch(g->gexec, rt().stream));
+    slot->last_use = ++g->guse;
+    if (slot->exec) {
+        SPT_CUDA(cudaGraphLaunch(slot->exec, rt().stream));
         note_submit();
         return 0;
     }
-    if (g->eager_runs++ == 0) return forward(g, ids, batch, T, logits);
+    if (slot->eager_runs++ == 0) return forward(g, ids, batch, T, logits);
     cudaGraph_t graph = nullptr;
     SPT_CUDA(cudaStreamBeginCapture(rt().stream, cudaStreamCaptureModeThreadLocal));
     int rc = forward(g, ids, batch, T, logits);
@@ -613,10 +705,10 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
         if (rc != 0) return rc;
         return forward(g, ids, batch, T, logits);
     }
-    e = cudaGraphInstantiate(&g->gexec, graph, 0);
+    e = cudaGraphInstantiate(&slot->exec, graph, 0);
     cudaGraphDestroy(graph);
-    if (e != cudaSuccess) { g->gexec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits); }
-    SPT_CUDA(cudaGraphLaunch(g->gexec, rt().stream));
+    if (e != cudaSuccess) { slot->exec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits); }
+    SPT_CUDA(cudaGraphLaunch(slot->exec, rt().stream));
     note_submit();
     return 0;
 }
@@ -632,9 +724,8 @@ int sptorch_ext_gpt_enable_kv_cache(void* gp, int max_context) {
     if (g->kcache) return max_context == g->cache_ctx ? 0 : fail("gpt_enable_kv_cache: cache already allocated with %d positions", g->cache_ctx);
     const size_t bytes = (size_t)g->c.n_layer * g->c.max_batch * max_context * g->d_loc * g->es;
     g->kcache = galloc(g, bytes); g->vcache = galloc(g, bytes);
-    g->dq = galloc(g, (size_t)g->c.max_batch * 2 * g->d_loc * g->es);
-    g->dv = galloc(g, (size_t)g->c.max_batch * g->d_loc * g->es);
-    if (!g->kcache || !g->vcache || !g->dq || !g->dv) return 1;
+    g->dq = galloc(g, (size_t)g->c.max_batch * 3 * g->d_loc * g->es);
+    if (!g->kcache || !g->vcache || !g->dq) return 1;
     g->cache_ctx = max_context; g->cached_len = 0; g->cache_batch = 0;
     return 0;
 }
@@ -692,19 +783,18 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
         uint8_t* kc = (uint8_t*)g->kcache + lay;
         uint8_t* vc = (uint8_t*)g->vcache + lay;
         if (norm(x, w.ln1g, w.ln1b, g->h)) return 1;
-        if (linear(g, g->h, w.wqk, nullptr, nullptr, g->dq, B, d, 2 * dl, 2 * dl, EPI_NONE)) return 1;     // [q | k] of the token
+        if (linear(g, g->h, w.wqkv, nullptr, nullptr, g->dq, B, d, 3 * dl, 3 * dl, EPI_NONE)) return 1;     // [q | k | v] of the token
         // the query (and the key about to be cached) are rotated to the token's absolute position (nn/src/lib.rs:718-721, 678-680)
-        if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 2 * dl, c.rope_base, pos, dt)) return 1; }
+        if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 3 * dl, c.rope_base, pos, dt)) return 1; }
         if (append) {
-            if (linear(g, g->h, w.wv, nullptr, nullptr, g->dv, B, d, dl, dl, EPI_NONE)) return 1;
             // one cache row per sequence and layer
-            SPT_CUDA(cudaMemcpy2DAsync(kc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)dl * es, (size_t)2 * dl * es,
+            SPT_CUDA(cudaMemcpy2DAsync(kc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)dl * es, (size_t)3 * dl * es,
                                        (size_t)dl * es, (size_t)B, cudaMemcpyDeviceToDevice, rt().stream));
-            SPT_CUDA(cudaMemcpy2DAsync(vc + (size_t)pos * dl * es, (size_t)seq * es, g->dv, (size_t)dl * es, (size_t)dl * es, (size_t)B,
-                                       cudaMemcpyDeviceToDevice, rt().stream));
+            SPT_CUDA(cudaMemcpy2DAsync(vc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)2 * dl * es, (size_t)3 * dl * es,
+                                       (size_t)dl * es, (size_t)B, cudaMemcpyDeviceToDevice, rt().stream));
         }
         { ProfScope ps(PROF_ATTN_FUSED);
-          if (attention_last_token(g->dq, 2 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, n, seq, row, dt)) return 1; }
+          if (attention_last_token(g->dq, 3 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, n, seq, row, dt)) return 1; }
         if (linear(g, g->ao, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
         if (norm(x, w.ln2g, w.ln2b, g->h)) return 1;
         if (qwen) {
@@ -724,7 +814,7 @@ int sptorch_ext_gpt_enable_ln_fold(void* gp, int on) {
     Gpt* g = (Gpt*)gp;
     if (g->ln_fold != (on != 0)) {
         g->ln_fold = on != 0;
-        if (g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; g->eager_runs = 0; }     // the captured launches belong to the other path
+        drop_graphs(g);                          // the captured launches belong to the other path
     }
     return 0;
 }
@@ -739,7 +829,7 @@ int sptorch_ext_gpt_enable_graphs(void* gp, int on) {
     if (!gp) return fail("gpt_enable_graphs: null model");
     Gpt* g = (Gpt*)gp;
     g->graphs = on != 0;
-    if (!on && g->gexec) { cudaGraphExecDestroy(g->gexec); g->gexec = nullptr; g->eager_runs = 0; }
+    if (!on) drop_graphs(g);
     return 0;
 }
 
@@ -774,12 +864,11 @@ int sptorch_ext_gpt_set_allreduce(void* gp, sptorch_allreduce_fn fn, void* user)
 int sptorch_ext_gpt_launches(void* gp, int batch, int T) {
     if (!gp) return 0;
     Gpt* g = (Gpt*)gp;
-    const int hd = g->c.d_model / g->c.n_head;
-    const long long M = (long long)batch * T;
-    const bool fused = g->c.dtype == SPT_BF16 && attention_mode() == 0 && attention_fused_supported(T, hd, 2 * g->d_loc, M, (long long)hd * M, T);
-    // embedding + per layer (LN1, QK, V^T, attention [1 fused | S, softmax, PV], Wo, LN2, up, down) + ln_f + head;
+    (void)batch;
+    const bool fused = model_uses_fused(g, T);
+    // embedding + per layer (LN1, QKV, attention [1 fused | V^T, S, softmax, PV], Wo, LN2, up, down) + ln_f + head;
     // the Qwen-like block adds the RoPE pass and the gate projection
-    return 1 + g->c.n_layer * ((fused ? 8 : 10) + (g->c.arch == SPT_ARCH_QWEN_LIKE ? 2 : 0)) + 2;
+    return 1 + g->c.n_layer * ((fused ? 7 : 10) + (g->c.arch == SPT_ARCH_QWEN_LIKE ? 2 : 0)) + 2;
 }
 
 int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk) {
@@ -789,17 +878,25 @@ int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, i
     if (chunk <= 0 || chunk > batch) chunk = batch;
     if (chunk > g->c.max_batch) chunk = g->c.max_batch;
     if (check_shape(g, chunk, T)) return 1;
-    if (fold_applicable(g, chunk * T) && fold_prepare(g)) return 1;
+    if (fold_applicable(g, chunk * T, T) && fold_prepare(g)) return 1;
     const size_t es = g->es, V = g->c.vocab, ldl = g->ldl;
-    const size_t need_logits = (size_t)chunk * T * ldl * es;
+    // per slot: the padded logits the head GEMM writes ([rows, ldl]: TMA stores need a 16-byte row pitch) and the dense
+    // [rows, V] copy of them that leaves the device (a strided 2-D device-to-host copy of 100 514-byte rows ran far below the
+    // link's rate when several GPUs copied at once; one contiguous copy per chunk does not)
+    const size_t need_padded = ((size_t)chunk * T * ldl * es + 255) / 256 * 256;
+    const size_t need_logits = need_padded + ((size_t)chunk * T * V * es + 255) / 256 * 256;
     if (g->logits_cap < need_logits) {
+        if (g->logits_cap) { SPT_CUDA(cudaStreamSynchronize(rt().copy_stream)); if (stream_wait()) return 1; }
         for (int i = 0; i < 2; i++) {
+            gfree(g, g->logits_dev[i]);
             g->logits_dev[i] = galloc(g, need_logits);
             if (!g->logits_dev[i]) return 1;
         }
         g->logits_cap = need_logits;
     }
     if (g->ids_cap < batch * T) {
+        if (g->ids_cap && stream_wait()) return 1;
+        gfree(g, g->ids_dev);
         g->ids_dev = (int*)galloc(g, (size_t)batch * T * 4);
         if (!g->ids_dev) return 1;
         g->ids_cap = batch * T;
@@ -814,12 +911,14 @@ int sptorch_ext_gpt_forward_host(void* gp, const int32_t* ids_host, int batch, i
     for (int b0 = 0; b0 < batch; b0 += chunk, slot ^= 1, issued++) {
         int nb = batch - b0 < chunk ? batch - b0 : chunk;
         if (issued >= 2) SPT_CUDA(cudaStreamWaitEvent(cs, g->ev_copy[slot], 0));      // buffer free again
-        if (forward(g, g->ids_dev + (size_t)b0 * T, nb, T, g->logits_dev[slot])) return 1;
+        void* padded = g->logits_dev[slot];
+        void* dense = (uint8_t*)g->logits_dev[slot] + need_padded;
+        if (forward(g, g->ids_dev + (size_t)b0 * T, nb, T, padded)) return 1;
+        if (ldl != V) { ProfScope ps(PROF_OTHER); if (compact_rows_launch(padded, dense, (size_t)nb * T, V, ldl, (int)es)) return 1; }
+        else dense = padded;
         SPT_CUDA(cudaEventRecord(g->ev_compute[slot], cs));
         SPT_CUDA(cudaStreamWaitEvent(ds, g->ev_compute[slot], 0));
-        // dense [rows, V] on the host <- [rows, ldl] on the device
-        SPT_CUDA(cudaMemcpy2DAsync((uint8_t*)logits_host + (size_t)b0 * T * V * es, V * es, g->logits_dev[slot], ldl * es, V * es,
-                                   (size_t)nb * T, cudaMemcpyDeviceToHost, ds));
+        SPT_CUDA(cudaMemcpyAsync((uint8_t*)logits_host + (size_t)b0 * T * V * es, dense, (size_t)nb * T * V * es, cudaMemcpyDeviceToHost, ds));
         SPT_CUDA(cudaEventRecord(g->ev_copy[slot], ds));
     }
     SPT_CUDA(cudaStreamSynchronize(ds));

@@ -117,7 +117,13 @@ static int do_init() {
     SPT_CUDA(cudaStreamCreateWithFlags(&g_rt.own_stream, cudaStreamNonBlocking));
     SPT_CUDA(cudaStreamCreateWithFlags(&g_rt.copy_stream, cudaStreamNonBlocking));
     g_rt.stream = g_rt.own_stream;
-    SPT_CUDA(cudaDeviceGetDefaultMemPool(&g_rt.pool, dev));
+    // A pool of the library's own: the device's default pool stays as the process's other users configured it.
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    SPT_CUDA(cudaMemPoolCreate(&g_rt.pool, &props));
     uint64_t keep = UINT64_MAX;   // never hand cached blocks back to the driver between ops
     SPT_CUDA(cudaMemPoolSetAttribute(g_rt.pool, cudaMemPoolAttrReleaseThreshold, &keep));
     SPT_CUDA(cudaMalloc(&g_rt.dev_status, 256));
@@ -125,8 +131,20 @@ static int do_init() {
     SPT_CUDA(cudaEventCreate(&g_rt.t0));
     SPT_CUDA(cudaEventCreate(&g_rt.t1));
     g_rt.sticky.store(0);
+    static_scratch_prepare();     // the allocation-free matmul's scratch address, resolved while no capture can be open
     return 0;
 }
+
+// callbacks that release per-process device caches of other translation units (attention schedules, ...) at shutdown
+static std::vector<void (*)()> g_shutdown_hooks;
+void at_shutdown(void (*fn)()) {
+    for (auto f : g_shutdown_hooks) if (f == fn) return;
+    g_shutdown_hooks.push_back(fn);
+}
+
+static std::atomic<uint64_t> g_config_epoch{0};
+uint64_t config_epoch() { return g_config_epoch.load(); }
+void bump_config_epoch() { g_config_epoch.fetch_add(1); }
 
 }  // namespace spt
 
@@ -148,6 +166,7 @@ void sptorch_backend_shutdown(void) {
     if (--g_rt.refcount > 0) return;
     cudaSetDevice(g_rt.device);
     cudaStreamSynchronize(g_rt.stream);
+    for (auto fn : g_shutdown_hooks) fn();
     if (g_flush) { cudaFree(g_flush); g_flush = nullptr; }
     if (g_rt.dev_status) { cudaFree(g_rt.dev_status); g_rt.dev_status = nullptr; }
     if (g_rt.t0) cudaEventDestroy(g_rt.t0);
@@ -156,6 +175,7 @@ void sptorch_backend_shutdown(void) {
     if (g_rt.own_stream) cudaStreamDestroy(g_rt.own_stream);
     if (g_rt.copy_stream) cudaStreamDestroy(g_rt.copy_stream);
     g_rt.own_stream = g_rt.copy_stream = g_rt.stream = nullptr;
+    if (g_rt.pool) { cudaMemPoolDestroy(g_rt.pool); g_rt.pool = nullptr; }
     g_rt.device = -1;
 }
 
@@ -171,7 +191,7 @@ void* sptorch_ext_alloc_bytes(size_t bytes) {
         return nullptr;
     }
     void* p = nullptr;
-    cudaError_t e = cudaMallocAsync(&p, rounded, g_rt.stream);
+    cudaError_t e = cudaMallocFromPoolAsync(&p, rounded, g_rt.pool, g_rt.stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         fail("cudaMallocAsync(%zu) failed: %s", rounded, cudaGetErrorString(e));
@@ -296,6 +316,7 @@ int sptorch_ext_set_alloc_budget(size_t bytes) { g_rt.budget = bytes; return 0; 
 int sptorch_ext_set_sm_reserve(int n) {
     if (n < 0 || (g_rt.sm_count > 0 && n >= g_rt.sm_count)) return fail("set_sm_reserve: %d is outside 0..%d", n, g_rt.sm_count - 1);
     g_rt.sm_reserve = n;
+    bump_config_epoch();          // grid sizes of captured launches depend on it
     return 0;
 }
 

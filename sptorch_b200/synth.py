@@ -152,10 +152,10 @@ def gpt_params(cfg: dict, seed: int = 0, residual_scale: bool = False, randomize
 
 
 CONFIGS = {
-    # BASELINE config 1: tiny char-level GPT (f32)
+    # the tiny character model c1_tiny: tiny char-level GPT (f32)
     "c1_tiny": dict(vocab=256, d_model=128, n_layer=4, n_head=4, d_ff=512, seq_len=64, batch=8, ctx=64),
-    # BASELINE config 4: GPT-2-small shape (bf16)
+    # the GPT-2-small shape c4_gpt2s: GPT-2-small shape (bf16)
     "c4_gpt2s": dict(vocab=50257, d_model=768, n_layer=12, n_head=12, d_ff=3072, seq_len=1024, batch=64, ctx=1024),
-    # BASELINE config 5: 1.3B shape (bf16, tensor parallel)
+    # the 1.3B shape c5_1p3b: 1.3B shape (bf16, tensor parallel)
     "c5_1p3b": dict(vocab=50257, d_model=2048, n_layer=24, n_head=16, d_ff=8192, seq_len=2048, batch=16, ctx=2048),
 }

@@ -1,7 +1,7 @@
 """Writes the committed golden fixtures.  Run from the repo root in a checkout that has the reference
 beside it:  python tests/golden/make_golden.py
 
-c1_tiny.npz   BASELINE config 1 (tiny char GPT, f32), first two sequences: ids, logits[:, :, :64], argmax,
+c1_tiny.npz   the tiny character model c1_tiny (tiny char GPT, f32), first two sequences: ids, logits[:, :, :64], argmax,
               per-layer taps of sequence 0 -- from the CPU oracle in strict order (fast=0).
 abi_ops.npz   inputs + outputs of the eleven C-ABI ops produced by the REFERENCE's own C implementation
               (crates/hal-ffi/mock_npu/mock_npu.c compiled in place as oracle/_ref/libmock_npu.so).

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from conftest import relerr
+from conftest import elementwise_excess, parity_record, relerr
 from sptorch_b200.backend import BF16, EPI_GELU, F32, MM_BF16, MM_F32, MM_TF32, bf16_bits_to_f32, f32_to_bf16_bits
 
 pytestmark = pytest.mark.gpu
@@ -32,6 +32,27 @@ def test_linear_tf32_and_bf16_vs_oracle(backend, oracle, M, K, N):
     assert relerr(backend.linear(x, w, b, mode=MM_BF16, out_dtype=F32), refb) <= 1e-5
 
 
+@pytest.mark.parametrize("M", [4096, 16384])
+@pytest.mark.parametrize("K,N", [(768, 768), (768, 3072), (3072, 768), (4096, 4096)])
+def test_linear_sweep_shapes_vs_oracle(backend, oracle, M, K, N):
+    """The standalone Linear sweep at its large row counts with the inputs it specifies (x ~ N(0,1), W ~ N(0,0.02), b ~ N(0,0.01),
+    seeded per shape): every output element of the bf16 and the TF32 path against the oracle's f32 product (blocked, all host
+    threads; no rows are left out)."""
+    from sptorch_b200 import synth
+    seed = 1000 * (M // 512) + K + N
+    x = synth.normal(seed, M * K).reshape(M, K)
+    w = synth.normal(seed + 1, N * K, std=0.02).reshape(N, K)
+    b = synth.normal(seed + 2, N, std=0.01)
+    ref = oracle.linear(x, w, b, fast=1)
+    for mode, tol, name in ((MM_TF32, 2e-3, "tf32"), (MM_BF16, 2e-2, "bf16")):
+        out = backend.linear(x, w, b, mode=mode)
+        err = relerr(out, ref)
+        outside, worst = elementwise_excess(out, ref, tol)
+        parity_record(f"linear {M}x{K}->{N} {name}", relerr=err, elementwise_worst=worst)
+        assert err <= tol, (name, err)
+        assert worst <= 1.0, (name, outside, worst)
+
+
 def test_linear_fused_epilogues(backend, oracle):
     rng = np.random.default_rng(1)
     M, K, N = 200, 128, 328
@@ -48,7 +69,7 @@ def test_linear_fused_epilogues(backend, oracle):
 
 
 def test_linear_is_linear_at_full_size(backend):
-    """Size-independent property at a BASELINE config 2 shape (M 4096, K 768, N 3072): f(x1 + x2) = f(x1) + f(x2) and
+    """Size-independent property at a shape of the standalone Linear sweep (M 4096, K 768, N 3072): f(x1 + x2) = f(x1) + f(x2) and
     integer-valued operands give exact integers."""
     rng = np.random.default_rng(2)
     M, K, N = 4096, 768, 3072

@@ -78,7 +78,7 @@ def test_qwen_like_reference_test_shape(backend, oracle):
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_qwen_like_forward_vs_oracle_per_layer(backend, oracle, dtype):
-    cfg = dict(vocab=256, d_model=128, n_layer=4, n_head=4, d_ff=512, seq_len=64)     # BASELINE config 1 dimensions
+    cfg = dict(vocab=256, d_model=128, n_layer=4, n_head=4, d_ff=512, seq_len=64)     # the dimensions of c1_tiny
     params, index = synth.gpt_params(cfg, 3, arch="qwen", randomize_affine=True)
     ids = synth.randint(7, 8 * 64, 256).reshape(8, 64)
     ref, taps = oracle.qwen_forward(cfg, params, ids, fast=0, threads=oracle.max_threads(), want_taps=True)
@@ -100,7 +100,7 @@ def test_qwen_like_forward_vs_oracle_per_layer(backend, oracle, dtype):
 
 
 def test_qwen_like_gpt2_small_shape_layer_slice(backend, oracle):
-    """Two layers at the BASELINE config 4 widths (d 768, 12 heads x 64, d_ff 3072, T 256): the fused attention kernel and the
+    """Two layers at the c4_gpt2s widths (d 768, 12 heads x 64, d_ff 3072, T 256): the fused attention kernel and the
     wide GEMMs on the RoPE / SwiGLU path."""
     cfg = dict(vocab=1000, d_model=768, n_layer=2, n_head=12, d_ff=3072, seq_len=256)
     params, index = synth.gpt_params(cfg, 5, arch="qwen", residual_scale=True, randomize_affine=True)

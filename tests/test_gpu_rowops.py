@@ -1,6 +1,6 @@
 """GPU parity tests of the row kernels (LayerNorm, softmax family, embedding sum) against the CPU oracle,
 with the edge cases the reference tests (ragged sizes, fully masked rows, -inf entries) and size-independent
-properties at the BASELINE config 3 sizes."""
+properties at the sizes of the row-op sweep."""
 import numpy as np
 import pytest
 
@@ -36,7 +36,7 @@ def test_layernorm_bf16_vs_oracle(backend, oracle, rows, dim):
 
 
 def test_layernorm_mean_zero_property_full_size(backend):
-    # crates/nn/src/lib.rs:3239-3262 at the BASELINE row-op size (65536 x 768): gamma=1, beta=0 -> row mean ~ 0, var ~ 1
+    # crates/nn/src/lib.rs:3239-3262 at the row-op sweep's size (65536 x 768): gamma=1, beta=0 -> row mean ~ 0, var ~ 1
     rows, dim = 65536, 768
     x = (np.random.default_rng(0).standard_normal((rows, dim)) * 3 + 0.5).astype(np.float32)
     y = backend.layernorm(x, np.ones(dim, np.float32), np.zeros(dim, np.float32))
@@ -78,7 +78,7 @@ def test_causal_softmax_bf16(backend, oracle):
 
 
 def test_causal_softmax_rows_sum_to_one_full_size(backend):
-    # BASELINE config 3 shape per (batch, head): T = 1024; here 24 matrices (100 MB)
+    # the row-op sweep's shape per (batch, head): T = 1024; here 24 matrices (100 MB)
     s = (np.random.default_rng(4).standard_normal((24, 1024, 1024)) * 2).astype(np.float32)
     out = backend.causal_softmax(s, 1.0)
     assert np.abs(out.sum(-1) - 1).max() < 1e-5 and (np.triu(out, 1) == 0).all()

@@ -104,10 +104,24 @@ def test_batch_sharding_two_gloo_ranks():
     assert abs(tmax - 0.2) < 1e-12
 
 
+def _tp_shard(lib, name, full, rank, world):
+    """This rank's shard of a full parameter, cut by the library's own rule (the functions gpt_set_param uses on upload)."""
+    import ctypes as C
+    full = np.ascontiguousarray(full, dtype=np.float32)
+    rows, cols = (full.shape[0], 1) if full.ndim == 1 else full.shape
+    kind, begin, count = C.c_int(), C.c_size_t(), C.c_size_t()
+    assert lib.sptorch_ext_tp_param_shard(name.encode(), rank, world, rows, cols, C.byref(kind), C.byref(begin), C.byref(count)) == 0
+    shape = {0: (rows, cols), 1: (count.value, cols), 2: (rows, count.value)}[kind.value]
+    out = np.empty(shape, dtype=np.float32)
+    assert lib.sptorch_ext_tp_slice_host(full.ctypes.data, rows, cols, kind.value, begin.value, count.value, out.ctypes.data) == 0
+    return (out.reshape(-1) if full.ndim == 1 else out), kind.value, begin.value, count.value
+
+
 def _tp_worker(rank, world, port, q):
-    """Tensor-parallel MLP + attention-output partition on CPU ranks: the slicing rule of sptorch_b200/csrc/gpt.cu
-    (ffn_up / wq,wk,wv split by output rows, ffn_down / wo split along K, residual and ffn_down bias folded into rank
-    0's partial) followed by a sum all-reduce must reproduce the unsharded block."""
+    """One transformer block (attention + MLP) cut over CPU ranks with the LIBRARY's shard rule -- sptorch_ext_tp_param_shard /
+    sptorch_ext_tp_slice_host / sptorch_ext_tp_rank_folds_residual, the host functions sptorch_ext_gpt_set_param itself applies
+    when it uploads a rank's weights -- followed by one sum all-reduce per attention and per MLP block, must reproduce the
+    unsharded block.  (The arithmetic around the slices is the oracle's; what is under test is which slice each rank owns.)"""
     import torch
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -115,23 +129,50 @@ def _tp_worker(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     sys.path.insert(0, ROOT)
     from oracle import binding as O
-    from sptorch_b200 import synth
-    d, F, M = 32, 64, 10
-    x = synth.normal(1, M * d).reshape(M, d)
-    h = synth.normal(2, M * d).reshape(M, d)                 # LayerNorm output feeding the MLP
-    w1 = synth.normal(3, F * d, std=0.1).reshape(F, d); b1 = synth.normal(4, F, std=0.1)
-    w2 = synth.normal(5, d * F, std=0.1).reshape(d, F); b2 = synth.normal(6, d, std=0.1)
-    Fl = F // world
-    rows = slice(rank * Fl, (rank + 1) * Fl)
-    f = O.unary("gelu", O.linear(h, w1[rows], b1[rows]))     # column-parallel up projection + GELU
-    part = O.linear(f, np.ascontiguousarray(w2[:, rows]), b2 if rank == 0 else None)   # row-parallel down projection
+    from sptorch_b200 import _lib, synth
+    lib = _lib.load()                                         # host functions only: no device is needed
+    d, F, T, H = 32, 64, 10, 4
+    hd = d // H
+    x = synth.normal(1, T * d).reshape(T, d)
+    h1 = synth.normal(2, T * d).reshape(T, d)                 # LayerNorm outputs feeding attention / the MLP
+    h2 = synth.normal(7, T * d).reshape(T, d)
+    full = {"attn.wq.weight": synth.normal(10, d * d, std=0.2).reshape(d, d), "attn.wk.weight": synth.normal(11, d * d, std=0.2).reshape(d, d),
+            "attn.wv.weight": synth.normal(12, d * d, std=0.2).reshape(d, d), "attn.wo.weight": synth.normal(13, d * d, std=0.2).reshape(d, d),
+            "ffn_up.weight": synth.normal(3, F * d, std=0.1).reshape(F, d), "ffn_up.bias": synth.normal(4, F, std=0.1),
+            "ffn_down.weight": synth.normal(5, d * F, std=0.1).reshape(d, F), "ffn_down.bias": synth.normal(6, d, std=0.1)}
+    mine = {}
+    kinds = {}
+    for name, w in full.items():
+        mine[name], kinds[name], begin, count = _tp_shard(lib, "blocks.0." + name, w, rank, world)
+    lead = bool(lib.sptorch_ext_tp_rank_folds_residual(rank))
+    Hl = H // world
+    # attention: this rank's heads (rows of wq / wk / wv), then its K-slice of wo; partial [T, d]
+    ql, kl, vl = (O.linear(h1, mine[n]) for n in ("attn.wq.weight", "attn.wk.weight", "attn.wv.weight"))
+    # the attention core of the local heads: per head softmax(q k^T / sqrt(hd)) v under the causal mask
+    ao = np.empty((T, Hl * hd), np.float32)
+    for hh in range(Hl):
+        sl = slice(hh * hd, (hh + 1) * hd)
+        sc = O.matmul(ql[:, sl], O.transpose(kl[:, sl]))[None]
+        p = O.causal_softmax(sc, 1.0 / np.sqrt(np.float32(hd)))[0]
+        ao[:, sl] = O.matmul(p, vl[:, sl])
+    part = O.linear(ao, mine["attn.wo.weight"])
+    if lead:
+        part = part + x
+    t1 = torch.from_numpy(part.copy())
+    dist.all_reduce(t1)                                       # the one collective of the attention block
+    x1 = t1.numpy()
+    # MLP: rows of ffn_up (+ its bias slice), GELU, K-slice of ffn_down; bias and residual on the folding rank only
+    f = O.unary("gelu", O.linear(h2, mine["ffn_up.weight"], mine["ffn_up.bias"]))
+    part = O.linear(f, mine["ffn_down.weight"], mine["ffn_down.bias"] if lead else None)
+    if lead:
+        part = part + x1
+    t2 = torch.from_numpy(part.copy())
+    dist.all_reduce(t2)                                       # the one collective of the MLP block
     if rank == 0:
-        part = part + x                                      # residual folded into rank 0's partial
-    t = torch.from_numpy(part.copy())
-    dist.all_reduce(t)                                       # the one collective of the MLP block
-    if rank == 0:
-        full = x + O.linear(O.unary("gelu", O.linear(h, w1, b1)), w2, b2)
-        q.put(float(np.abs(t.numpy() - full).max()))
+        attn_full = O.mha_causal(h1, full["attn.wq.weight"], full["attn.wk.weight"], full["attn.wv.weight"], full["attn.wo.weight"], H)
+        x1_full = x + attn_full
+        x2_full = x1_full + O.linear(O.unary("gelu", O.linear(h2, full["ffn_up.weight"], full["ffn_up.bias"])), full["ffn_down.weight"], full["ffn_down.bias"])
+        q.put((float(np.abs(x1 - x1_full).max()), float(np.abs(t2.numpy() - x2_full).max()), kinds, mine["ffn_down.bias"].shape[0]))
     dist.destroy_process_group()
 
 
@@ -143,11 +184,35 @@ def test_tensor_parallel_partition_two_gloo_ranks():
     procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    err = q.get(timeout=120)
+    err_attn, err_mlp, kinds, bias_len = q.get(timeout=120)
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert err < 1e-5
+    assert err_attn < 1e-5 and err_mlp < 1e-5
+    assert kinds == {"attn.wq.weight": 1, "attn.wk.weight": 1, "attn.wv.weight": 1, "attn.wo.weight": 2, "ffn_up.weight": 1,
+                     "ffn_up.bias": 1, "ffn_down.weight": 2, "ffn_down.bias": 0}
+    assert bias_len == 32                                     # the row-parallel bias is replicated, added by one rank only
+
+
+def test_tensor_parallel_shard_rule_edges():
+    """Replicated parameters, a rank outside the group, an extent that does not divide."""
+    import ctypes as C
+    from sptorch_b200 import _lib
+    lib = _lib.load()
+    kind, begin, count = C.c_int(), C.c_size_t(), C.c_size_t()
+    for name in (b"token_emb.weight", b"pos_emb.weight", b"lm_head.weight", b"ln_f.gamma", b"blocks.3.ln1.gamma", b"blocks.3.ffn_down.bias"):
+        assert lib.sptorch_ext_tp_param_shard(name, 1, 4, 8, 8, C.byref(kind), C.byref(begin), C.byref(count)) == 0
+        assert (kind.value, begin.value, count.value) == (0, 0, 8)
+    assert lib.sptorch_ext_tp_param_shard(b"blocks.0.ffn_gate.weight", 3, 4, 16, 8, C.byref(kind), C.byref(begin), C.byref(count)) == 0
+    assert (kind.value, begin.value, count.value) == (1, 12, 4)
+    assert lib.sptorch_ext_tp_param_shard(b"blocks.0.attn.wo.weight", 4, 4, 8, 8, C.byref(kind), C.byref(begin), C.byref(count)) != 0
+    assert lib.sptorch_ext_tp_param_shard(b"blocks.0.attn.wo.weight", 0, 3, 8, 8, C.byref(kind), C.byref(begin), C.byref(count)) != 0
+    assert [lib.sptorch_ext_tp_rank_folds_residual(r) for r in range(4)] == [1, 0, 0, 0]
+    full = np.arange(12, dtype=np.float32).reshape(3, 4)
+    out = np.empty((3, 2), np.float32)
+    assert lib.sptorch_ext_tp_slice_host(full.ctypes.data, 3, 4, 2, 2, 2, out.ctypes.data) == 0
+    assert np.array_equal(out, full[:, 2:4])
+    assert lib.sptorch_ext_tp_slice_host(full.ctypes.data, 3, 4, 2, 3, 2, out.ctypes.data) != 0
 
 
 def test_kv_cache_metadata_mirrors_the_reference():

@@ -42,6 +42,34 @@ def test_static_scratch_matmul_matches_pool_matmul_twice_in_a_row(backend):
         assert np.abs(got - a.astype(np.float64) @ b.astype(np.float64)).max() <= 2e-3 * np.abs(ref).max()   # TF32 tolerance of the other tests
 
 
+def test_static_scratch_at_its_size_limit(backend):
+    """k * n exactly at the limit of 2,097,152 elements (the whole 8 MiB array in use) on the tensor-core path with the pool
+    closed, and four elements past it, which must be refused before anything runs."""
+    lib = backend.lib
+    rng = np.random.default_rng(12)
+    m, k, n = 128, 1024, 2048
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    ref = _run(backend, lib.sptorch_matmul_f32, a, b, m, k, n)
+    da, db, do = backend.upload(a), backend.upload(b), backend.alloc(m * n)
+    try:
+        lib.sptorch_ext_set_alloc_budget(1)
+        rc = lib.sptorch_ext_matmul_f32_static(da.handle, db.handle, do.handle, m, k, n)
+        lib.sptorch_ext_set_alloc_budget(0)
+        backend._check(rc, "matmul_f32_static")
+        got = do.to_host().reshape(m, n)
+        backend.synchronize()
+        assert np.array_equal(got, ref)
+        assert np.abs(got - a.astype(np.float64) @ b.astype(np.float64)).max() <= 2e-3 * np.abs(ref).max()
+        # four elements past the limit: k * n = 4 * (2^19 + 1) = 2^21 + 4
+        assert lib.sptorch_ext_matmul_f32_static(da.handle, db.handle, do.handle, 8, 4, (1 << 19) + 1) != 0
+        assert b"static scratch" in lib.sptorch_ext_last_error()
+        assert lib.sptorch_sync() != 0 and lib.sptorch_sync() == 0
+    finally:
+        lib.sptorch_ext_set_alloc_budget(0)
+        da.free(); db.free(); do.free()
+
+
 def test_static_scratch_rejects_oversize_and_handles_small(backend):
     lib = backend.lib
     d = backend.alloc(16)
