@@ -297,8 +297,33 @@ def run_ours(args):
                                 "(whole-job GB/s, max time over ranks): the end-to-end call cannot be faster than this copy",
                "api": "sptorch_ext_gpt_forward_host (pinned ids in, dense bf16 logits [B*T,V] out; the padded logits are compacted on the device "
                       "and leave as one contiguous copy per micro-batch, overlapped with the next micro-batch's compute)"}
-        lib.sptorch_ext_free_pinned(ids_pinned)
         lib.sptorch_ext_free_pinned(out_pinned)
+        out_pinned = None
+    # ---- the same step when the caller wants the loss and the greedy tokens, not the logits: LM head fused with both ----
+    e2e_loss = None
+    tgt_pinned = lib.sptorch_ext_alloc_pinned(nseq * T * 8)
+    arg_pinned = lib.sptorch_ext_alloc_pinned(nseq * T * 4)
+    if ids_pinned and tgt_pinned and arg_pinned and args.e2e_steps > 0:
+        targets = np.ascontiguousarray(np.roll(ids_all, -1, axis=1)[start:start + nseq], dtype=np.int64)      # next-token targets
+        C.memmove(ids_pinned, ids.ctypes.data, ids.nbytes)
+        C.memmove(tgt_pinned, targets.ctypes.data, targets.nbytes)
+        steps_l = max(1, min(args.steps, max(args.e2e_steps, 5)))
+        for _ in range(3):                                   # eager, captured, replayed
+            loss = model.forward_loss_host(ids_pinned, tgt_pinned, nseq, T, arg_pinned, chunk)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps_l):
+            loss = model.forward_loss_host(ids_pinned, tgt_pinned, nseq, T, arg_pinned, chunk)
+        b.synchronize()
+        dt = max_over_ranks(time.perf_counter() - t0)
+        e2e_loss = {"value": tokens_per_step * steps_l / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(GB * T * 12),
+                    "d2h_bytes_per_step": int(GB * T * 4 + 4 * world), "steps": steps_l, "chunk_sequences": chunk, "ms_per_step": 1e3 * dt / steps_l,
+                    "mean_loss_rank0": loss,
+                    "api": "sptorch_ext_gpt_forward_loss_host (pinned ids and next-token targets in; greedy tokens and the mean cross-entropy "
+                           "loss out; the LM head's epilogue reduces the logits tile by tile, the [B*T, V] matrix is never written)"}
+    for ptr in (ids_pinned, out_pinned, tgt_pinned, arg_pinned):
+        if ptr:
+            lib.sptorch_ext_free_pinned(ptr)
     barrier()
 
     if rank == 0:
@@ -318,6 +343,7 @@ def run_ours(args):
                        "model": "vocab 50257, d 768, 12 layers, 12 heads, d_ff 3072, pre-LN, untied head; N(0,0.02) seed 0, residual projections / sqrt(24)"},
             "clocks": clocks,
             "e2e": e2e,
+            "e2e_loss": e2e_loss,
             "gpu_launches": int(sum(prof_n)) if sum(prof_n) else model.launches(nseq, T) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (Linear: QK, V^T, Wo, up, down, LM head)",
                          "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
@@ -546,12 +572,48 @@ def sweep_rowops(b, peaks, iters, emit=None):
     return out
 
 
+def sweep_decode(b, peaks, steps=32, emit=None):
+    """Incremental decode of the GPT-2-small shape through the key/value cache: `batch` sequences with 512 cached positions, one
+    new token each per step.  HBM-bound: a step reads every weight once (325 MB in bf16) plus the cached keys and values."""
+    from sptorch_b200.backend import BF16
+    from sptorch_b200.gpt import GPT
+    cfg = dict(synth.CONFIGS[WORKLOAD])
+    d, F, V, L = cfg["d_model"], cfg["d_ff"], cfg["vocab"], cfg["n_layer"]
+    out = []
+    for batch in (1, 8, 64):
+        model = GPT(b, V, d, cfg["n_head"], L, F, cfg["seq_len"], dtype=BF16, max_batch=batch)
+        _load_timing_weights(model, cfg)
+        model.enable_kv_cache(1024)
+        ctx0 = 512
+        ids = synth.randint(1, batch * ctx0, V).reshape(batch, ctx0)
+        model.prefill_kv_cache(ids)
+        nxt = synth.randint(2, batch, V).astype(np.int32)
+        d_ids, d_log = model.stage_ids(nxt), model.logits_buffer(batch)
+        for _ in range(3):
+            b._check(b.lib.sptorch_ext_gpt_decode(model.h, d_ids.handle, batch, 1, d_log.handle), "gpt_decode")
+        b.synchronize()
+        b.timer_begin()
+        for _ in range(steps):
+            b._check(b.lib.sptorch_ext_gpt_decode(model.h, d_ids.handle, batch, 1, d_log.handle), "gpt_decode")
+        ms = b.timer_end() / steps
+        n_ctx = ctx0 + 3 + steps // 2
+        nbytes = 2 * (L * (4 * d * d + 2 * d * F) + V * d) + 2 * 2 * L * batch * n_ctx * d
+        out.append({"op": "decode_step", "batch": batch, "cached_positions": n_ctx, "ms_per_step": ms, "tokens_per_s": batch / (ms * 1e-3),
+                    "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"],
+                    "algorithmic_bytes": nbytes})
+        if emit:
+            emit(out[-1])
+        model.close()
+    return out
+
+
 def compact_sweeps(b, peaks, iters):
     """The three sweeps in the short form the bench line carries: one entry per case with its time and fraction of the roof
     (Linear and attention: measured burst bf16 tensor peak, TF32 against half of it; row ops: measured copy bandwidth)."""
     lin = sweep_linear(b, peaks, iters)
     att = sweep_attention(b, peaks, iters)
     row = sweep_rowops(b, peaks, iters)
+    dec = sweep_decode(b, peaks)
     r3 = lambda v: float(f"{v:.4g}")
     return {
         "timing": f"median of {iters} launches, CUDA events on the library stream, 256 MiB L2 flush before each launch, 3 warm-up launches",
@@ -560,6 +622,9 @@ def compact_sweeps(b, peaks, iters):
         "attention": [{"B": e["B"], "T": e["T"], "H": e["H"], "hd": e["hd"], "ms": r3(e["ms"]), "tflops": r3(e["tflops"]), "frac": r3(e["frac"])} for e in att],
         "rowops": [{"op": e["op"], "dtype": e["dtype"], **({"dim": e["dim"]} if "dim" in e else {}), "ms": r3(e["ms"]), "gbs": r3(e["gbs"]), "frac": r3(e["frac"])} for e in row],
         "rowops_roof": f"{peaks['hbm']} GB/s ({peaks['source']} copy bandwidth)",
+        "decode": [{"batch": e["batch"], "cached_positions": e["cached_positions"], "ms_per_step": r3(e["ms_per_step"]), "tokens_per_s": r3(e["tokens_per_s"]),
+                    "frac": r3(e["frac"])} for e in dec],
+        "decode_note": "one new token per sequence through the key/value cache of the GPT-2-small shape; frac = (weights + cached K/V bytes) per step over the copy bandwidth",
     }
 
 
@@ -579,6 +644,8 @@ def run_sweep(args):
         sweep_attention(b, peaks, args.iters, one if args.sweep == "attention" else None, emit)
     if args.sweep in ("rowops", "all"):
         sweep_rowops(b, peaks, args.iters, emit)
+    if args.sweep in ("decode", "all"):
+        sweep_decode(b, peaks, emit=emit)
     b.close()
     return 0
 
@@ -731,7 +798,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=8, help="sequences per micro-batch of the host-buffer call")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "abi", "all"], help="standalone op sweeps (the standalone Linear and row-op sweeps) instead of the GPT step")
+    ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "decode", "abi", "all"], help="standalone op sweeps (the standalone Linear and row-op sweeps) instead of the GPT step")
     ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],

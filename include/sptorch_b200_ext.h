@@ -169,14 +169,28 @@ const void* sptorch_ext_gpt_tap(void* gpt, int i);
  * logits on the host out (model dtype), copies included.  Processes micro-batches of `chunk`
  * sequences and overlaps the device->host copy of one chunk with the compute of the next. */
 int   sptorch_ext_gpt_forward_host(void* gpt, const int32_t* ids_host, int batch, int T, void* logits_host, int chunk);
+/* Forward fused with the step after it (cross_entropy_loss / cross_entropy_loss_ignore_index, core-ops/src/lib.rs:1079-1194; the
+ * greedy token = the first candidate of sampling_candidates, nn/src/lib.rs:2381-2418): the [batch*T, vocab] logits are never
+ * written.  The LM head's epilogue reduces every tile of logits -- rounded to the model dtype first, so the values are exactly
+ * those sptorch_ext_gpt_forward would have stored -- to per-row partial (max, sum exp, first argmax, target logit), and a second
+ * kernel merges them.  targets_i64 [batch*T] on the device (NULL: no loss); argmax_i32 [batch*T] on the device (NULL: not wanted);
+ * row_loss_f32: device scratch of batch*T + 1 floats (per-row losses, then their mean; rows whose target equals ignore_index are
+ * left out when has_ignore != 0); the mean is also copied to *host_mean.  Needs vocab > 128; not for tensor-parallel shards. */
+int   sptorch_ext_gpt_forward_loss(void* gpt, const void* ids_i32, const void* targets_i64, int batch, int T, int has_ignore,
+                                   long long ignore_index, void* argmax_i32, void* row_loss_f32, float* host_mean);
+/* the same with host buffers: ids (and targets) in, greedy tokens [batch*T] and the mean loss out; 4 bytes per token leave the device */
+int   sptorch_ext_gpt_forward_loss_host(void* gpt, const int32_t* ids_host, const int64_t* targets_host, int batch, int T, int has_ignore,
+                                        long long ignore_index, int32_t* argmax_host, float* host_mean, int chunk);
 /* ---- incremental decode with a key/value cache (nn/src/lib.rs:1540-1573, 1619-1646, 706-760) ----
  * enable_kv_cache allocates [layer][sequence][position][d_model] K and V caches for max_context positions (<= seq_len).
  * prefill = forward over ids [batch, T] that also fills the cache.  decode runs one token per sequence through the
  * blocks against the cache: append = 1 takes NEW tokens (their K,V are appended, logits of the new position);
  * append = 0 recomputes the logits of the last cached token (decode_logits_from_cache right after a prefill).
- * logits of decode: [batch, ld]. */
+ * logits of decode: [batch, ld].  The cache is a ring: appending to a full cache replaces the oldest position, the last max_context
+ * positions stay (append_kv_tensor, nn/src/lib.rs:2165-2203) and the window start moves on by one; nothing is copied or recomputed. */
 int   sptorch_ext_gpt_enable_kv_cache(void* gpt, int max_context);
 int   sptorch_ext_gpt_cached_len(void* gpt);
+long long sptorch_ext_gpt_window_start(void* gpt);        /* absolute position of the oldest cached token (0 until the cache slides) */
 int   sptorch_ext_gpt_prefill(void* gpt, const void* ids_i32, int batch, int T, void* logits);
 int   sptorch_ext_gpt_decode(void* gpt, const void* last_ids_i32, int batch, int append, void* logits);
 /* the attention of one new token over a cache (nn/src/lib.rs:706-760 without the projections): q [B, H*hd];

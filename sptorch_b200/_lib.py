@@ -97,8 +97,11 @@ EXT_SYMBOLS = {
     "sptorch_ext_gpt_enable_taps": (_i, [_vp, _i]),
     "sptorch_ext_gpt_tap": (_vp, [_vp, _i]),
     "sptorch_ext_gpt_forward_host": (_i, [_vp, _vp, _i, _i, _vp, _i]),
+    "sptorch_ext_gpt_forward_loss": (_i, [_vp, _vp, _vp, _i, _i, _i, C.c_longlong, _vp, _vp, C.POINTER(C.c_float)]),
+    "sptorch_ext_gpt_forward_loss_host": (_i, [_vp, _vp, _vp, _i, _i, _i, C.c_longlong, _vp, C.POINTER(C.c_float), _i]),
     "sptorch_ext_gpt_enable_kv_cache": (_i, [_vp, _i]),
     "sptorch_ext_gpt_cached_len": (_i, [_vp]),
+    "sptorch_ext_gpt_window_start": (C.c_longlong, [_vp]),
     "sptorch_ext_gpt_prefill": (_i, [_vp, _vp, _i, _i, _vp]),
     "sptorch_ext_gpt_decode": (_i, [_vp, _vp, _i, _i, _vp]),
     "sptorch_ext_attention_last_token": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),

@@ -13,8 +13,8 @@
 //               O_g += P_g V_j with P read straight from TMEM; the two query tiles alternate, so the tensor
 //               core works on one tile while the softmax warps work on the other
 //   warps 2..5  softmax of query tile 0, warps 6..9 of query tile 1: ONE THREAD PER QUERY ROW.  A thread reads
-//               its 128 scores from TMEM twice (once for the row maximum, which no other thread has a part in, once
-//               for the exponentials: a whole row held in registers would not fit beside the other warps), evaluates
+//               its 128 scores from TMEM in four chunks of 32 (the next chunk's load in flight while one is worked on;
+//               the running row maximum is the thread's own business, no other thread has a part in it), evaluates
 //               2^(s*c - m*c) (part on the special-function unit, part as a cubic polynomial on the FMA pipe,
 //               because the 16-per-clock exponential unit would otherwise be the limit), and writes P as bf16
 //               back into the TMEM columns the scores came from
@@ -81,6 +81,23 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
+}
+
+// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp owns lane (base_lane + i)
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 
 // tcgen05.mma with the A operand in TMEM (rows = lanes, two bf16 per 32-bit column) and B in shared memory
@@ -257,7 +274,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kErrMmaWait) && kv_ready(g);
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) {
+            if (elect_one_sync()) {
                 issue_s(0, g);
                 if (n1 > 0) issue_s(1, g);
                 if (nt[last_t] == 1) mma_commit(q_free);
@@ -273,7 +290,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     if (!ok) break;
                     steps[t]++;
                     tc_fence_after();
-                    if (lane == 0) {
+                    if (elect_one_sync()) {
                         issue_pv(t, g, j > 0);
                         // the next scores of this tile go into the columns P was just read from: the tensor pipe runs the
                         // MMAs of one thread in order, so the product above has consumed P before these overwrite it
@@ -284,7 +301,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     }
                     __syncwarp();
                 }
-                if (ok && lane == 0) mma_commit(kv_empty + 8 * (g % NS));     // every MMA that reads this stage has been issued
+                if (ok && elect_one_sync()) mma_commit(kv_empty + 8 * (g % NS));     // every MMA that reads this stage has been issued
                 __syncwarp();
             }
         }
@@ -311,88 +328,100 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (!ok) break;
                 tc_fence_after();
                 const bool diag = (j == n_kv - 1);               // the tile on the diagonal: keys q .. q+127 of rows q .. q+127
-                // pass 1: the row maximum, 64 scores at a time (entries right of the diagonal do not take part)
-                float mx;
-                {
-                    float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        uint32_t v[64];
-                        tmem_ld_32x32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-                        tmem_ld_32x32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-                        tmem_ld_wait();
-                        if (diag) {
-#pragma unroll
-                            for (int i = 0; i < 64; i++) if (half * 64 + i > r) v[i] = 0xff800000u;       // -inf
-                        }
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 2) mm[q] = max3(mm[q], __uint_as_float(v[16 * q + i]), __uint_as_float(v[16 * q + i + 1]));
-                        }
-                    }
-                    mx = fmaxf(max3(mm[0], mm[1], mm[2]), mm[3]);
-                }
-                // Lazy rescaling: the reference maximum of a row only moves when the new maximum exceeds it by more than 8 in the
-                // exponent (P then stays below 2^8, exact enough in bf16 and harmless in the f32 sums); the accumulated output
-                // in TMEM and the row sum are multiplied by 2^(old - new) at that moment.  tcgen05.ld / st are warp-wide, so a
-                // warp rescales when any of its rows does (the others multiply by one).
-                if (j == 0) m = mx;
-                const bool grow = j > 0 && (mx - m) * p.scale_log2 > 8.0f;
-                if (__any_sync(0xffffffffu, grow)) {
-                    float alpha = 1.0f;
-                    if (grow) { alpha = ex2_approx((m - mx) * p.scale_log2); m = mx; l *= alpha; }
-                    // every product accumulated so far is in place (the commit of step - 1; the next one needs this thread's P)
-                    ok = mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < HD / 32; c++) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(o_addr + c * 32, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(o_addr + c * 32, o);
-                    }
-                    tmem_st_wait();
-                }
-                const float mb = m * p.scale_log2;
-                // scale/subtract, the row sum and the conversions run on pairs of floats; of every 16 pairs NPOLY take the
-                // polynomial (FMA pipe) and the rest the special-function unit.  The diagonal tile uses the special-function
-                // unit alone, where 2^(-inf) is exactly 0.
+                // The 128 scores of the row are taken in four chunks of 32: the load of chunk c + 1 is in flight while chunk c is
+                // worked on, and a chunk needs only 32 registers.  The reference maximum m of the row is allowed to lag the true
+                // maximum by up to 2^8 (lazy rescaling): a chunk whose maximum exceeds m by more moves m, and everything already
+                // accumulated under the old m -- the row sum, the output in TMEM, and the chunks of P of this tile that are already
+                // written -- is multiplied by 2^(old - new) at that moment.  tcgen05.ld / st are warp-wide, so a warp rescales when any
+                // of its rows does (the others multiply by one).
                 float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
-                const float2 c2 = make_float2(p.scale_log2, p.scale_log2), nmb2 = make_float2(-mb, -mb);
-                // pass 2: 64 scores at a time -> 2^(s*c - m*c) -> bf16 pairs into the columns the first scores of the row came from
-                // (P of keys 64h .. 64h+63 lands in columns 32h .. 32h+31, which hold scores that have been read by then)
-                auto exps = [&](auto npoly_tag, auto diag_tag) {
+                const float2 c2 = make_float2(p.scale_log2, p.scale_log2);
+                uint32_t va[32], vb[32];
+                tmem_ld_32x32(s_addr, va);
+                auto chunk = [&](auto c_tag, uint32_t (&v)[32], uint32_t (&vnext)[32], auto npoly_tag, auto diag_tag) -> bool {
+                    constexpr int c = decltype(c_tag)::value;
                     constexpr int NP = decltype(npoly_tag)::value;
                     constexpr bool DIAG = decltype(diag_tag)::value;
+                    tmem_ld_wait();
+                    if (c < 3) tmem_ld_32x32(s_addr + (c + 1) * 32, vnext);
+                    if (DIAG) {
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        uint32_t v[64];
-                        tmem_ld_32x32(s_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-                        tmem_ld_32x32(s_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-                        tmem_ld_wait();
-                        if (DIAG) {
-#pragma unroll
-                            for (int i = 0; i < 64; i++) if (half * 64 + i > r) v[i] = 0xff800000u;       // -inf
-                        }
-                        uint32_t packed[32];
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), c2, nmb2);
-                            float2 e;
-                            if ((i & 15) < NP) e = ex2_poly2(x);
-                            else e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-                            if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
-                            packed[i] = *reinterpret_cast<uint32_t*>(&h2);
-                        }
-                        tmem_st_32x32(s_addr + half * 32, packed);
+                        for (int i = 0; i < 32; i++) if (c * 32 + i > r) v[i] = 0xff800000u;       // -inf right of the diagonal
                     }
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                        m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                        m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                        m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                    }
+                    const float mx = fmaxf(max3(m0, m1, m2), m3);
+                    if (j == 0 && c == 0) m = mx;                    // the first chunk of a row always holds key 0: finite
+                    const bool grow = (mx - m) * p.scale_log2 > 8.0f;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        float alpha = 1.0f;
+                        if (grow) { alpha = ex2_approx((m - mx) * p.scale_log2); m = mx; }
+                        l *= alpha;
+                        sum_a.x *= alpha; sum_a.y *= alpha; sum_b.x *= alpha; sum_b.y *= alpha;
+                        if (j > 0) {
+                            // every product accumulated so far is in place (the commit of step - 1; the next one needs this thread's P)
+                            if (!mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
+                            tc_fence_after();
+#pragma unroll
+                            for (int cc = 0; cc < HD / 32; cc++) {
+                                uint32_t o[32];
+                                tmem_ld_32x32(o_addr + cc * 32, o);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                                tmem_st_32x32(o_addr + cc * 32, o);
+                            }
+                        }
+                        if (c > 0) {
+                            // the chunks of P of this tile written so far: 16 columns (32 bf16) each
+                            uint32_t w[16];
+#pragma unroll
+                            for (int cc = 0; cc < c; cc++) {
+                                tmem_ld_32x32b_x16(s_addr + cc * 16, w);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 16; i++) {
+                                    const float lo = __uint_as_float(w[i] << 16) * alpha, hi = __uint_as_float(w[i] & 0xffff0000u) * alpha;
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+                                    w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                                }
+                                tmem_st_32x32b_x16(s_addr + cc * 16, w);
+                            }
+                        }
+                        tmem_st_wait();
+                        // the load of the next chunk was issued before this branch: the wait of the next chunk() call still covers it
+                    }
+                    const float mb = m * p.scale_log2;
+                    const float2 nmb2 = make_float2(-mb, -mb);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), c2, nmb2);
+                        float2 e;
+                        if (i < NP) e = ex2_poly2(x);
+                        else e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                        if (i & 1) sum_b = __fadd2_rn(sum_b, e); else sum_a = __fadd2_rn(sum_a, e);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(e.x, e.y);
+                        packed[i] = *reinterpret_cast<uint32_t*>(&h2);
+                    }
+                    // keys 32c .. 32c+31 of this row, two per column: columns 16c .. 16c+15, whose scores have been read (c' <= c)
+                    tmem_st_32x32b_x16(s_addr + c * 16, packed);
+                    return true;
                 };
-                if (diag) exps(std::integral_constant<int, 0>(), std::true_type()); else exps(std::integral_constant<int, NPOLY>(), std::false_type());
+                auto tile = [&](auto npoly_tag, auto diag_tag) -> bool {
+                    return chunk(std::integral_constant<int, 0>(), va, vb, npoly_tag, diag_tag) &&
+                           chunk(std::integral_constant<int, 1>(), vb, va, npoly_tag, diag_tag) &&
+                           chunk(std::integral_constant<int, 2>(), va, vb, npoly_tag, diag_tag) &&
+                           chunk(std::integral_constant<int, 3>(), vb, va, npoly_tag, diag_tag);
+                };
+                ok = diag ? tile(std::integral_constant<int, 0>(), std::true_type()) : tile(std::integral_constant<int, NPOLY>(), std::false_type());
+                if (!ok) break;
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -539,7 +568,7 @@ bool attention_fused_supported(int T, int hd, long long ld_q, long long ld_kv) {
 
 // share of the exponentials evaluated on the FMA pipe (of every 16 pairs), per head size; tunable for experiments
 static int attn_npoly(int hd) {
-    static const int e64 = getenv("SPTORCH_B200_ATTN_NPOLY64") ? atoi(getenv("SPTORCH_B200_ATTN_NPOLY64")) : 5;
+    static const int e64 = getenv("SPTORCH_B200_ATTN_NPOLY64") ? atoi(getenv("SPTORCH_B200_ATTN_NPOLY64")) : 0;
     static const int e128 = getenv("SPTORCH_B200_ATTN_NPOLY128") ? atoi(getenv("SPTORCH_B200_ATTN_NPOLY128")) : 0;
     return hd == 64 ? e64 : e128;
 }

@@ -36,6 +36,7 @@ constexpr int kStagesPair = 6;               // pair kernel: a stage is 32 KB pe
 constexpr int kGemmThreads = 320;           // producer warp + MMA warp + 8 epilogue warps
 constexpr int kEpiThreads = 256;
 constexpr int kGroupM = 8;                   // default m-tiles per rasterisation band (L2 reuse of the B tiles)
+constexpr double kNarrowTileCost = 0.68;     // time of a 128 x 128 tile relative to a 128 x 256 tile of the same K (measured)
 
 struct GemmParams {
     void* C; const float* bias; const void* R;
@@ -58,6 +59,8 @@ struct GemmParams {
 
 // LayerNorm folded into the epilogue (see GemmDesc): a kernel argument of its own, read by the NORM variants only
 struct NormArgs { const float2* stats; const float* s; };
+// row reductions instead of the output (see GemmDesc::reduce): read by the REDUCE variants only
+struct ReduceArgs { float2* part; int* arg; const long long* targets; float* tgt; int parts; };
 
 __device__ __forceinline__ float gelu_exact(float x) {
     const float k = 0.7978845608028654f;
@@ -77,6 +80,13 @@ __device__ __forceinline__ float2 gelu_fast2(float2 x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(u.y));
     float2 hx = __fmul2_rn(x, half);
     return __ffma2_rn(hx, t, hx);
+}
+
+// e^x through ex2.approx (relative error 2^-22); e^(-inf) = 0
+__device__ __forceinline__ float exp_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+    return y;
 }
 
 // g * sigmoid(g) (core-ops/src/lib.rs:1537-1538: s = 1 / (1 + exp(-g)), the product with x follows in the caller)
@@ -112,10 +122,10 @@ template <> struct NormRow<1> { float2 stat; };
 // Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' loads; `empty` and `tmem_full` exist in both
 // CTAs and are signalled by two commits of the issuing thread; `tmem_empty` lives in the even CTA and collects the
 // epilogue threads of both.
-template <bool TF32, typename TOut, int BN, bool PAIR, int NORM = 0>
+template <bool TF32, typename TOut, int BN, bool PAIR, int NORM = 0, bool REDUCE = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const GemmParams p, const NormArgs na) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p, const NormArgs na, const ReduceArgs ra) {
     constexpr int NSTG = PAIR ? kStagesPair : kStages;
     constexpr int TM = PAIR ? 2 * BM : BM;             // rows of one scheduled tile
     constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of B this CTA loads
@@ -225,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMmaWait);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
+                if (elect_one_sync()) {
                     const uint32_t sa = base + stage * STAGE_BYTES;
                     const uint64_t adesc = make_kmajor_sw128_desc(sa);
                     const uint64_t bdesc = make_kmajor_sw128_desc(sa + A_BYTES);
@@ -304,6 +314,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // folded LayerNorm: what this thread's output row needs for the whole tile
             NormRow<NORM> nr;
             if constexpr (NORM == 1) { nr.stat = row_ok ? __ldg(na.stats + (long long)z * p.M + row) : make_float2(1.0f, 0.0f); }
+            // row reductions: running (maximum, sum of exp(x - maximum)), column of the first maximum, and the target's logit
+            float r_mx = -INFINITY, r_s = 0.0f; int r_arg = 0;
+            long long r_tgt = -1;
+            if constexpr (REDUCE) { if (ra.targets && row_ok) r_tgt = ra.targets[row]; }
             // residual row segment of one chunk (row-per-thread layout)
             uint4 rnext[NV];
             auto fetch_residual = [&](int c) {
@@ -373,6 +387,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
                 if (c + 1 < c_end) { tmem_ld_32x32(t_row + (c + 1) * 32, v); fetch_residual(c + 1); }
                 else release_acc(acc);                                            // this warp has drained its part of the accumulator
+                if constexpr (REDUCE) {
+                    float cm = -INFINITY; int ca = 0;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float x = f[j];
+                        if constexpr (sizeof(TOut) == 2) x = __bfloat162float(__float2bfloat16_rn(x));       // the logit as it would be stored
+                        if (col0 + j >= p.N) x = -INFINITY;
+                        f[j] = x;
+                        if (x > cm) { cm = x; ca = j; }
+                    }
+                    if (cm > r_mx) { r_s *= exp_fast(r_mx - cm); r_mx = cm; r_arg = col0 + ca; }
+                    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) { s0 += exp_fast(f[j] - r_mx); s1 += exp_fast(f[j + 1] - r_mx); }
+                    r_s += s0 + s1;
+                    const long long tj = r_tgt - col0;
+                    if (tj >= 0 && tj < 32) {
+                        float tv = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (j == (int)tj) tv = f[j];
+                        ra.tgt[row] = tv;
+                    }
+                    continue;
+                }
                 if (p.epilogue == EPI_GELU) {
                     if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
@@ -461,6 +499,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
             }
             if (c_begin >= c_end) release_acc(acc);
+            if constexpr (REDUCE) {
+                if (row_ok) {
+                    const size_t slot = (size_t)row * ra.parts + 2 * tn + half;
+                    ra.part[slot] = make_float2(r_mx, r_s);
+                    ra.arg[slot] = r_arg;
+                }
+            }
             tile_par ^= 1;
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -557,6 +602,12 @@ bool gemm_supported(const GemmDesc& d, const char** why) {
         if ((reinterpret_cast<uintptr_t>(d.norm_stats) | reinterpret_cast<uintptr_t>(d.norm_s)) & 15) return bad("folded LayerNorm vectors must be 16-byte aligned");
         if (d.alpha != 1.0f) return bad("folded LayerNorm does not combine with alpha");
     }
+    if (d.reduce) {
+        if (d.norm_axis || d.R || d.epilogue != EPI_NONE) return bad("row reductions do not combine with a folded LayerNorm, a residual or an activation");
+        if (d.N <= 128) return bad("row reductions need N > 128");
+        if (d.nb1 != 1 || d.nb2 != 1 || d.causal_lower || d.causal_k) return bad("row reductions take one plain matrix product");
+        if (!d.red_part || !d.red_arg || (d.red_targets && !d.red_tgt)) return bad("row reductions need their output buffers");
+    }
     if (why) *why = ok;
     return true;
 }
@@ -569,7 +620,7 @@ static int launch_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr});
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr}, ReduceArgs{});
     SPT_LAUNCH_CHECK("gemm_tcgen05");
     return 0;
 }
@@ -583,8 +634,24 @@ static int launch_norm_t(const GemmPlan& pl, const GemmParams& prm) {
         SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         attr_set = true;
     }
-    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{pl.d.norm_stats, pl.d.norm_s});
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{pl.d.norm_stats, pl.d.norm_s}, ReduceArgs{});
     SPT_LAUNCH_CHECK("gemm_tcgen05 (folded LayerNorm)");
+    return 0;
+}
+
+// row-reduction epilogues exist for 256-column tiles, one CTA per tile: bf16 operands with the values rounded to bf16, or TF32 / f32
+template <bool TF32, typename TOut>
+static int launch_reduce_t(const GemmPlan& pl, const GemmParams& prm) {
+    auto kern = gemm_tcgen05_kernel<TF32, TOut, 256, false, 0, true>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        attr_set = true;
+    }
+    const GemmDesc& d = pl.d;
+    kern<<<pl.grid, kGemmThreads, pl.smem, rt().stream>>>(pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr},
+                                                          ReduceArgs{d.red_part, d.red_arg, d.red_targets, d.red_tgt, gemm_reduce_parts(d.N)});
+    SPT_LAUNCH_CHECK("gemm_tcgen05 (row reductions)");
     return 0;
 }
 
@@ -605,7 +672,7 @@ static int launch_pair_t(const GemmPlan& pl, const GemmParams& prm) {
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
-    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr}));
+    SPT_CUDA(cudaLaunchKernelEx(&cfg, kern, pl.tmA, pl.tmB, pl.tmC, prm, NormArgs{nullptr, nullptr}, ReduceArgs{}));
     SPT_LAUNCH_CHECK("gemm_tcgen05 (pair)");
     return 0;
 }
@@ -640,11 +707,24 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     if (!gemm_supported(d, &why)) return fail("gemm: %s", why);
     plan->d = d;
     int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
+    if (bn == 256 && !d.norm_axis && !d.reduce) {
+        // Tile width by the number of waves the tiles make over the SMs.  A problem with few 128 x 256 tiles leaves most SMs idle in
+        // its last wave (8192 x 768 -> 768: 192 tiles on 148 SMs are two waves, the second 30 % full); 128-column tiles cost
+        // kNarrowTileCost of a 256-column tile each (they re-read the A tile twice as often and amortise the per-tile overhead
+        // over half the work) but round up to fewer idle SMs.  SPTORCH_B200_GEMM_BN forces a width (experiments).
+        static const int forced = getenv("SPTORCH_B200_GEMM_BN") ? atoi(getenv("SPTORCH_B200_GEMM_BN")) : 0;
+        static const double narrow_cost = getenv("SPTORCH_B200_GEMM_NARROW_COST") ? atof(getenv("SPTORCH_B200_GEMM_NARROW_COST")) : kNarrowTileCost;
+        const long long sms = compute_sms();
+        const long long tm = (long long)ceil_div(d.M, BM) * d.nb1 * d.nb2;
+        auto waves = [&](int w) { const long long tiles = tm * ceil_div(d.N, w); return (double)((tiles + sms - 1) / sms); };
+        if (forced == 128 || forced == 256) bn = forced;
+        else if (!d.causal_lower && !d.causal_k && waves(128) * narrow_cost < waves(256) * 0.97) bn = 128;
+    }
     plan->bn = bn;
     // wide problems run on CTA pairs (each SM then loads half of the B tile); the triangular attention products do not
     int pairs = 0;
     const int pm = g_pair_mode.load();
-    if (!d.norm_axis && (pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
+    if (!d.norm_axis && !d.reduce && (pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
     plan->pair = pairs > 0;
     plan->tiles_m = ceil_div(d.M, plan->pair ? 2 * BM : BM);
     plan->tiles_n = ceil_div(d.N, bn);
@@ -672,7 +752,7 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     else if (encode_operand(&plan->tmB, d.B, tf32, d.K, d.N, d.ldb, d.nb1, d.nb2, d.sB1, d.sB2, b_box)) return 1;
     // output map: 32x32 boxes, swizzled to match the conflict-free staging layout of the epilogue
     const long long oes = d.out_dtype == BF16 ? 2 : 4;
-    plan->tma_store = ((reinterpret_cast<uintptr_t>(d.C) & 15) == 0) && (d.ldc * oes) % 16 == 0 && d.ldc >= d.N &&
+    plan->tma_store = !d.reduce && ((reinterpret_cast<uintptr_t>(d.C) & 15) == 0) && (d.ldc * oes) % 16 == 0 && d.ldc >= d.N &&
                       (d.nb1 <= 1 || (d.sC1 * oes) % 16 == 0) && (d.nb2 <= 1 || (d.sC2 * oes) % 16 == 0);
     if (plan->tma_store) {
         if (encode_output(&plan->tmC, d.C, d.out_dtype == BF16, d.N, d.M, d.ldc, d.nb1, d.nb2, d.sC1, d.sC2)) return 1;
@@ -706,6 +786,12 @@ int gemm_run(const GemmPlan& pl) {
     prm.status = rt().dev_status;
     const bool tf32 = d.mode == MM_TF32;
     const bool out_bf16 = d.out_dtype == BF16;
+    if (d.reduce) {
+        if (pl.bn != 256 || pl.pair) return fail("gemm_run: the row-reduction epilogue needs N > 128");
+        if (tf32) return launch_reduce_t<true, float>(pl, prm);
+        if (out_bf16) return launch_reduce_t<false, __nv_bfloat16>(pl, prm);
+        return launch_reduce_t<false, float>(pl, prm);
+    }
     if (d.norm_axis) {
         if (tf32 || !out_bf16 || pl.bn != 256 || pl.pair) return fail("gemm_run: the folded-LayerNorm epilogue needs bf16 operands and output and N > 128");
         return launch_norm_t<1>(pl, prm);

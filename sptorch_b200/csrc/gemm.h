@@ -34,7 +34,18 @@ struct GemmDesc {
     int norm_axis = 0;
     const float2* norm_stats = nullptr;
     const float* norm_s = nullptr;
+    // Row reductions instead of the output (the LM head followed by a loss / an argmax): C is not written.  Every epilogue thread
+    // reduces the part of its output row it holds -- the values rounded to out_dtype first, so that they are exactly the logits the
+    // ordinary epilogue would have stored -- to (maximum, sum of exp(x - maximum)) and the column of the first maximum, and writes
+    // them to red_part / red_arg at [row * red_parts + 2 * n_tile + half]; red_parts = 2 * ceil(N / 256).  When red_targets is given,
+    // the thread that holds column red_targets[row] also writes that logit to red_tgt[row].  Needs N > 128, no batch dims.
+    int reduce = 0;
+    float2* red_part = nullptr;
+    int* red_arg = nullptr;
+    const long long* red_targets = nullptr;
+    float* red_tgt = nullptr;
 };
+inline int gemm_reduce_parts(int N) { return 2 * ((N + 255) / 256); }
 
 // A prepared launch: tensor maps are encoded once and can be replayed (the GPT driver caches these).
 struct GemmPlan {

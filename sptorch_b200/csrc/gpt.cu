@@ -27,10 +27,17 @@ int attention_materialized(const void* q, const void* k, const void* vt, long lo
 int attention_fused(const void* q, const void* k, const void* v, void* out, int B, int T, int H, int hd, long long ld_q, long long ld_k,
                     long long ld_v, long long ld_out);
 bool attention_uses_fused(int dtype, int Tn, int hd, long long ld_q, long long ld_kv);
-int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype);
+int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype, const int* offset_dev = nullptr);
 int compact_rows_launch(const void* src, void* dst, size_t rows, size_t cols, size_t ld, int es);
+int head_reduce_combine_launch(const float2* part, const int* arg, const float* tgt_logit, const long long* targets, size_t rows, int parts,
+                               int classes, int has_ignore, long long ignore_index, int* argmax_out, float* row_loss);
+int cross_entropy_mean_launch(float* row_loss, size_t rows);
 int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
-                         int n, long long seq_stride, long long row_stride, int dtype);
+                         int n, long long seq_stride, long long row_stride, int dtype, const int* state, int n_cap);
+int decode_state_launch(int* state, int pos, int n, int slot, int pos_row);
+int kv_append_launch(const void* qkv, void* kc, void* vc, int B, int dl, long long seq_stride, int slot, const int* state, int dtype);
+int embedding_sum_launch(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T, size_t vocab, size_t dim,
+                         int dtype, const int* pos_row_dev);
 
 struct Layer {
     float *ln1g, *ln1b, *ln2g, *ln2b, *b1, *b2;     // Qwen-like: ln1g / ln2g hold the RMSNorm weights, the betas are unused
@@ -64,14 +71,25 @@ struct Gpt {
     // key/value cache for incremental decode: [layer][sequence][position][d_loc], allocated by gpt_enable_kv_cache
     void *kcache = nullptr, *vcache = nullptr;
     int cache_ctx = 0, cached_len = 0, cache_batch = 0;
+    long long window_start = 0;   // absolute position of the oldest cached token (grows once the cache is full and slides)
+    int* dstate = nullptr;        // device words of the current decode step: position, valid positions, ring slot, position-table row
+    struct DecodeKey {
+        const void* ids; void* logits; int batch, append; cudaStream_t stream; uint64_t epoch;
+        bool operator==(const DecodeKey& o) const { return ids == o.ids && logits == o.logits && batch == o.batch && append == o.append && stream == o.stream && epoch == o.epoch; }
+    };
+    DecodeKey dkey = {nullptr, nullptr, 0, 0, nullptr, 0};
+    cudaGraphExec_t dexec = nullptr; int d_eager = 0;
     bool fill_cache = false;      // set while a prefill runs
     void *dq = nullptr;                  // decode scratch: [max_batch, 3*d_loc] = [q | k | v] of the new tokens
     // CUDA graph of one forward, keyed by everything that is baked into its kernel arguments
     // (the config epoch covers the process-wide setters that change which kernels or grids a forward launches)
     struct GraphKey {
         const void* ids; void* logits; int batch, T; bool taps; cudaStream_t stream; uint64_t epoch;
+        const void *targets, *argmax, *row_loss; int has_ignore; long long ignore_index; bool reduce;      // fused LM head (HeadReduce)
         bool operator==(const GraphKey& o) const {
-            return ids == o.ids && logits == o.logits && batch == o.batch && T == o.T && taps == o.taps && stream == o.stream && epoch == o.epoch;
+            return ids == o.ids && logits == o.logits && batch == o.batch && T == o.T && taps == o.taps && stream == o.stream && epoch == o.epoch &&
+                   targets == o.targets && argmax == o.argmax && row_loss == o.row_loss && has_ignore == o.has_ignore &&
+                   ignore_index == o.ignore_index && reduce == o.reduce;
         }
     };
     // a few keys are kept so that callers alternating between buffers (double buffering) replay instead of re-capturing
@@ -84,9 +102,15 @@ struct Gpt {
     float2* ln_stats = nullptr; void* head_f = nullptr; float *s_h = nullptr, *c_h = nullptr;
     bool ln_fold = false, fold_ready = false, fold_dirty = true;     // opt-in: measured neutral (see sptorch_ext_gpt_enable_ln_fold)
     bool tp_overlap = false;   // tensor parallel: reduce one half of the batch while the other half computes (opt-in)
+    // LM head fused with the loss / greedy choice: per-row partial reductions of the head GEMM's tiles
+    float2* red_part = nullptr; int* red_arg = nullptr; float* red_tgt = nullptr; size_t red_rows = 0;
+    // host-buffer loss call: targets, greedy tokens and row losses of the whole batch on the device
+    long long* loss_targets = nullptr; int* loss_argmax = nullptr; float* loss_rows = nullptr; size_t loss_cap = 0;
 };
 
 static void drop_graphs(Gpt* g) {
+    if (g->dexec) { cudaGraphExecDestroy(g->dexec); g->dexec = nullptr; }
+    g->d_eager = 0;
     for (auto& sl : g->gslots) {
         if (sl.exec) cudaGraphExecDestroy(sl.exec);
         sl = Gpt::GraphSlot();
@@ -341,10 +365,46 @@ static int attention_block(Gpt* g, const Layer& w, int l, const void* h, void* q
     return attention_materialized(qp, kp, g->vt, /*vt_ld*/ M, /*head*/ (long long)hd * M, /*batch*/ T, ao, g->scores, B, T, Hl, hd, 3 * dl, dl, dt);
 }
 
+// What replaces the logits when the LM head is fused with the step after it (cross_entropy_loss(_ignore_index), core-ops/src/lib.rs:1079-1194;
+// the greedy token = first candidate of sampling_candidates, nn/src/lib.rs:2381-2418): per-row loss and / or the column of the row maximum.
+struct HeadReduce { const long long* targets; int has_ignore; long long ignore_index; int* argmax; float* row_loss; };
+
+// partial-reduction buffers for `rows` tokens (grown outside any graph capture)
+static int ensure_reduce(Gpt* g, size_t rows) {
+    if (rows <= g->red_rows) return 0;
+    if (stream_wait()) return 1;
+    drop_graphs(g);
+    const size_t parts = (size_t)gemm_reduce_parts(g->c.vocab);
+    gfree(g, g->red_part); gfree(g, g->red_arg); gfree(g, g->red_tgt);
+    g->red_part = (float2*)galloc(g, rows * parts * sizeof(float2));
+    g->red_arg = (int*)galloc(g, rows * parts * sizeof(int));
+    g->red_tgt = (float*)galloc(g, rows * sizeof(float));
+    g->red_rows = (g->red_part && g->red_arg && g->red_tgt) ? rows : 0;
+    return g->red_rows ? 0 : 1;
+}
+
+// logits = h head^T, or -- with hr -- the row reductions of that product without the [M, vocab] matrix ever reaching HBM
+static int lm_head(Gpt* g, const void* h, int M, void* logits, const HeadReduce* hr) {
+    const sptorch_gpt_config& c = g->c;
+    if (!hr) return linear(g, h, g->head, nullptr, nullptr, logits, M, c.d_model, c.vocab, (long long)g->ldl, EPI_NONE);
+    if ((size_t)M > g->red_rows) return fail("gpt: reduction buffers not prepared for %d rows", M);
+    GemmDesc d;
+    d.A = h; d.B = g->head; d.C = nullptr;
+    d.M = M; d.N = c.vocab; d.K = c.d_model; d.lda = c.d_model; d.ldb = c.d_model; d.ldc = (long long)g->ldl;
+    d.mode = c.dtype == SPT_BF16 ? MM_BF16 : MM_TF32; d.out_dtype = c.dtype;
+    d.reduce = 1; d.red_part = g->red_part; d.red_arg = g->red_arg; d.red_targets = hr->row_loss ? hr->targets : nullptr; d.red_tgt = g->red_tgt;
+    GemmPlan pl;
+    if (gemm_plan(d, &pl)) return 1;
+    { ProfScope ps(PROF_LINEAR); if (gemm_run(pl)) return 1; }
+    ProfScope ps(PROF_OTHER);
+    return head_reduce_combine_launch(g->red_part, g->red_arg, g->red_tgt, hr->targets, (size_t)M, gemm_reduce_parts(c.vocab), c.vocab, hr->has_ignore,
+                                      hr->ignore_index, hr->argmax, hr->row_loss);
+}
+
 // Tensor-parallel forward with the all-reduces taken off the critical path: the batch is cut into two halves that go
 // through each half-block alternately, the partial sums of one half are reduced on a second stream while the other
 // half computes.  (The persistent kernels must leave a few SMs free for the collective: sptorch_ext_set_sm_reserve.)
-static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits) {
+static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr) {
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
@@ -396,7 +456,7 @@ static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* log
     // two swaps per layer and half: both halves are back in the same base buffer, contiguous
     void* x = xb[0];
     if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
-    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
+    if (lm_head(g, g->h, M, logits, hr)) return 1;
     note_submit();
     return 0;
 }
@@ -410,7 +470,7 @@ int rms_launch(const void* x, const float* w, void* out, size_t rows, size_t dim
 //   x += Wo attn(rope(q), rope(k), v) of rms(x);  x += Wdown (up * gate * sigmoid(gate)) + bdown of rms(x)
 // Launches per layer: RMSNorm, [q|k|v] GEMM, RoPE over q and k, attention, Wo GEMM (+residual), RMSNorm, up GEMM (+bias),
 // gate GEMM (+bias, SwiGLU product with the up output in the epilogue), down GEMM (+bias, +residual).
-static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
+static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr) {
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
@@ -447,14 +507,13 @@ static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits) {
     }
     if (rms_launch(x, g->lnfg, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
     if (tap(c.n_layer + 1, g->h)) return 1;
-    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
-    return 0;
+    return lm_head(g, g->h, M, logits, hr);
 }
 
-static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
-    if (g->c.arch == SPT_ARCH_QWEN_LIKE) return forward_qwen(g, ids, B, T, logits);
+static int forward(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr = nullptr) {
+    if (g->c.arch == SPT_ARCH_QWEN_LIKE) return forward_qwen(g, ids, B, T, logits, hr);
     if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0 && model_uses_fused(g, T))
-        return forward_tp_pipelined(g, ids, B, T, logits);
+        return forward_tp_pipelined(g, ids, B, T, logits, hr);
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc;
     const int dt = c.dtype;
@@ -500,7 +559,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
         }
         if (tap(l + 1, x)) return 1;
     }
-    if (fold) {
+    if (fold && !hr) {
         if (g->taps_on) {          // the tap of ln_f's output is the only reader of the normalised rows
             if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
             if (tap(c.n_layer + 1, g->h)) return 1;
@@ -510,8 +569,7 @@ static int forward(Gpt* g, const void* ids, int B, int T, void* logits) {
     }
     if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
     if (tap(c.n_layer + 1, g->h)) return 1;
-    if (linear(g, g->h, g->head, nullptr, nullptr, logits, M, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
-    return 0;
+    return lm_head(g, g->h, M, logits, hr);
 }
 
 // GPT::named_parameters (nn/src/lib.rs:1382-1392) / QwenLikeGPT::named_parameters (:1483-1492) with the full (unsharded) shapes
@@ -667,18 +725,16 @@ static int check_shape(Gpt* g, int batch, int T) {
     return 0;
 }
 
-int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* logits) {
-    if (enter()) return 1;
-    if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
-    Gpt* g = (Gpt*)gp;
-    if (check_shape(g, batch, T)) return 1;
-    if (fold_applicable(g, batch * T, T) && fold_prepare(g)) return 1;      // outside any graph capture
-    // The launch-bound inner loop (about 100 kernels, each a few microseconds when the batch is sharded 8 ways) is
-    // replayed as one CUDA graph: the first forward of a given (ids, logits, batch, T) runs eagerly, the second is
-    // captured, later ones are a single cudaGraphLaunch.  Per-kernel timing and tensor-parallel hooks run eagerly.
+// One forward, replayed as a CUDA graph when it repeats.  The launch-bound inner loop (about 90 kernels, each a few microseconds
+// when the batch is sharded 8 ways) is captured once per key: the first forward of a given key runs eagerly (it also sets function
+// attributes), the second is captured, later ones are a single cudaGraphLaunch.  Per-kernel timing and tensor-parallel hooks run
+// eagerly.  The key holds everything that is baked into the captured kernel arguments.
+static int forward_graphed(Gpt* g, const void* ids, int batch, int T, void* logits, const HeadReduce* hr) {
     const bool graph_ok = g->graphs && !prof_enabled() && g->c.tp_size <= 1;
-    if (!graph_ok) return forward(g, ids, batch, T, logits);
-    Gpt::GraphKey key = {ids, logits, batch, T, g->taps_on, rt().stream, config_epoch()};
+    if (!graph_ok) return forward(g, ids, batch, T, logits, hr);
+    Gpt::GraphKey key = {ids, logits, batch, T, g->taps_on, rt().stream, config_epoch(),
+                         hr ? (const void*)hr->targets : nullptr, hr ? (const void*)hr->argmax : nullptr, hr ? (const void*)hr->row_loss : nullptr,
+                         hr ? hr->has_ignore : 0, hr ? hr->ignore_index : 0, hr != nullptr};
     Gpt::GraphSlot* slot = nullptr;
     for (auto& sl : g->gslots) if ((sl.exec || sl.eager_runs) && sl.key == key) slot = &sl;
     if (!slot) {                                   // least recently used slot takes the new key
@@ -693,23 +749,109 @@ int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* l
         note_submit();
         return 0;
     }
-    if (slot->eager_runs++ == 0) return forward(g, ids, batch, T, logits);
+    if (slot->eager_runs++ == 0) return forward(g, ids, batch, T, logits, hr);
     cudaGraph_t graph = nullptr;
     SPT_CUDA(cudaStreamBeginCapture(rt().stream, cudaStreamCaptureModeThreadLocal));
-    int rc = forward(g, ids, batch, T, logits);
+    int rc = forward(g, ids, batch, T, logits, hr);
     cudaError_t e = cudaStreamEndCapture(rt().stream, &graph);
     if (rc != 0 || e != cudaSuccess || !graph) {
         if (graph) cudaGraphDestroy(graph);
         cudaGetLastError();
         g->graphs = false;                                   // capture is not possible here: stay eager from now on
         if (rc != 0) return rc;
-        return forward(g, ids, batch, T, logits);
+        return forward(g, ids, batch, T, logits, hr);
     }
     e = cudaGraphInstantiate(&slot->exec, graph, 0);
     cudaGraphDestroy(graph);
-    if (e != cudaSuccess) { slot->exec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits); }
+    if (e != cudaSuccess) { slot->exec = nullptr; g->graphs = false; cudaGetLastError(); return forward(g, ids, batch, T, logits, hr); }
     SPT_CUDA(cudaGraphLaunch(slot->exec, rt().stream));
     note_submit();
+    return 0;
+}
+
+int sptorch_ext_gpt_forward(void* gp, const void* ids, int batch, int T, void* logits) {
+    if (enter()) return 1;
+    if (!gp || !ids || !logits) return fail("gpt_forward: null argument");
+    Gpt* g = (Gpt*)gp;
+    if (check_shape(g, batch, T)) return 1;
+    if (fold_applicable(g, batch * T, T) && fold_prepare(g)) return 1;      // outside any graph capture
+    return forward_graphed(g, ids, batch, T, logits, nullptr);
+}
+
+static int check_reduce(Gpt* g, const char* who) {
+    if (g->c.vocab <= 128) return fail("%s: the fused LM head needs a vocabulary larger than 128", who);
+    if (g->c.tp_size > 1) return fail("%s: not available with tensor parallel shards", who);
+    return 0;
+}
+
+// Forward + the step after it without the logits: the LM head's epilogue reduces every 128 x 256 tile of logits to per-row partial
+// (max, sum exp, first argmax, target logit) and a second small kernel merges them.  Same values as the unfused path: the logits
+// are rounded to the model dtype before they are reduced.
+int sptorch_ext_gpt_forward_loss(void* gp, const void* ids, const void* targets_i64, int batch, int T, int has_ignore, long long ignore_index,
+                                 void* argmax_i32, void* row_loss_f32, float* host_mean) {
+    if (enter()) return 1;
+    if (host_mean) *host_mean = 0.0f;
+    if (!gp || !ids) return fail("gpt_forward_loss: null argument");
+    if (!argmax_i32 && !row_loss_f32) return fail("gpt_forward_loss: neither the greedy tokens nor the loss were asked for");
+    if (row_loss_f32 && !targets_i64) return fail("gpt_forward_loss: a loss needs targets");
+    Gpt* g = (Gpt*)gp;
+    if (check_reduce(g, "gpt_forward_loss") || check_shape(g, batch, T)) return 1;
+    if (ensure_reduce(g, (size_t)batch * T)) return 1;
+    HeadReduce hr = {(const long long*)targets_i64, has_ignore, ignore_index, (int*)argmax_i32, (float*)row_loss_f32};
+    if (forward_graphed(g, ids, batch, T, nullptr, &hr)) return 1;
+    if (row_loss_f32) {
+        if (cross_entropy_mean_launch((float*)row_loss_f32, (size_t)batch * T)) return 1;
+        if (host_mean) return sptorch_ext_copy_d2h_bytes((float*)row_loss_f32 + (size_t)batch * T, host_mean, sizeof(float));
+    }
+    return 0;
+}
+
+// The same through host buffers: ids (and targets) in, greedy tokens and the mean loss out; the only device-to-host traffic is 4
+// bytes per token.  Micro-batches of `chunk` sequences as in sptorch_ext_gpt_forward_host.
+int sptorch_ext_gpt_forward_loss_host(void* gp, const int32_t* ids_host, const int64_t* targets_host, int batch, int T, int has_ignore,
+                                      long long ignore_index, int32_t* argmax_host, float* host_mean, int chunk) {
+    if (enter()) return 1;
+    if (host_mean) *host_mean = 0.0f;
+    if (!gp || !ids_host) return fail("gpt_forward_loss_host: null argument");
+    if (!argmax_host && !targets_host) return fail("gpt_forward_loss_host: neither the greedy tokens nor the loss were asked for");
+    if (targets_host && !host_mean) return fail("gpt_forward_loss_host: null result pointer for the loss");
+    Gpt* g = (Gpt*)gp;
+    if (chunk <= 0 || chunk > batch) chunk = batch;
+    if (chunk > g->c.max_batch) chunk = g->c.max_batch;
+    if (check_reduce(g, "gpt_forward_loss_host") || check_shape(g, chunk, T)) return 1;
+    if (ensure_reduce(g, (size_t)chunk * T)) return 1;
+    const size_t n = (size_t)batch * T;
+    if (g->loss_cap < n) {
+        if (g->loss_cap && stream_wait()) return 1;
+        gfree(g, g->loss_targets); gfree(g, g->loss_argmax); gfree(g, g->loss_rows);
+        g->loss_targets = (long long*)galloc(g, n * sizeof(long long));
+        g->loss_argmax = (int*)galloc(g, n * sizeof(int));
+        g->loss_rows = (float*)galloc(g, (n + 1) * sizeof(float));
+        g->loss_cap = (g->loss_targets && g->loss_argmax && g->loss_rows) ? n : 0;
+        if (!g->loss_cap) return 1;
+    }
+    if (g->ids_cap < batch * T) {
+        if (g->ids_cap && stream_wait()) return 1;
+        gfree(g, g->ids_dev);
+        g->ids_dev = (int*)galloc(g, n * 4);
+        if (!g->ids_dev) return 1;
+        g->ids_cap = batch * T;
+    }
+    cudaStream_t cs = rt().stream;
+    SPT_CUDA(cudaMemcpyAsync(g->ids_dev, ids_host, n * 4, cudaMemcpyHostToDevice, cs));
+    if (targets_host) SPT_CUDA(cudaMemcpyAsync(g->loss_targets, targets_host, n * sizeof(long long), cudaMemcpyHostToDevice, cs));
+    for (int b0 = 0; b0 < batch; b0 += chunk) {
+        const int nb = batch - b0 < chunk ? batch - b0 : chunk;
+        const size_t off = (size_t)b0 * T;
+        HeadReduce hr = {targets_host ? g->loss_targets + off : nullptr, has_ignore, ignore_index, argmax_host ? g->loss_argmax + off : nullptr,
+                         targets_host ? g->loss_rows + off : nullptr};
+        if (forward_graphed(g, g->ids_dev + off, nb, T, nullptr, &hr)) return 1;
+    }
+    if (targets_host && cross_entropy_mean_launch(g->loss_rows, n)) return 1;
+    if (argmax_host) SPT_CUDA(cudaMemcpyAsync(argmax_host, g->loss_argmax, n * sizeof(int), cudaMemcpyDeviceToHost, cs));
+    if (targets_host) SPT_CUDA(cudaMemcpyAsync(host_mean, g->loss_rows + n, sizeof(float), cudaMemcpyDeviceToHost, cs));
+    SPT_CUDA(cudaStreamSynchronize(cs));
+    rt().retired.store(rt().submitted.load());
     return 0;
 }
 
@@ -725,12 +867,14 @@ int sptorch_ext_gpt_enable_kv_cache(void* gp, int max_context) {
     const size_t bytes = (size_t)g->c.n_layer * g->c.max_batch * max_context * g->d_loc * g->es;
     g->kcache = galloc(g, bytes); g->vcache = galloc(g, bytes);
     g->dq = galloc(g, (size_t)g->c.max_batch * 3 * g->d_loc * g->es);
-    if (!g->kcache || !g->vcache || !g->dq) return 1;
-    g->cache_ctx = max_context; g->cached_len = 0; g->cache_batch = 0;
+    g->dstate = (int*)galloc(g, 256);
+    if (!g->kcache || !g->vcache || !g->dq || !g->dstate) return 1;
+    g->cache_ctx = max_context; g->cached_len = 0; g->cache_batch = 0; g->window_start = 0;
     return 0;
 }
 
 int sptorch_ext_gpt_cached_len(void* gp) { return gp ? ((Gpt*)gp)->cached_len : 0; }
+long long sptorch_ext_gpt_window_start(void* gp) { return gp ? ((Gpt*)gp)->window_start : 0; }
 
 // prefill: the ordinary forward over ids [batch, T], which also fills the cache with K and V of all T positions.
 // logits may be NULL (then an internal scratch of the activations is NOT available: pass a buffer if logits are wanted).
@@ -745,7 +889,7 @@ int sptorch_ext_gpt_prefill(void* gp, const void* ids, int batch, int T, void* l
     int rc = forward(g, ids, batch, T, logits);
     g->fill_cache = false;
     if (rc) return rc;
-    g->cached_len = T; g->cache_batch = batch;
+    g->cached_len = T; g->cache_batch = batch; g->window_start = 0;
     return 0;
 }
 
@@ -755,26 +899,20 @@ int sptorch_ext_gpt_prefill(void* gp, const void* ids, int batch, int T, void* l
 //   append = 0: last_ids are the tokens already at position cached_len-1: nothing is written, the logits of that last
 //               cached token are recomputed from the cache (decode_logits_from_cache right after a prefill).
 // logits: [batch, ld] in the model dtype, ld = sptorch_ext_gpt_logits_ld.
-int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append, void* logits) {
-    if (enter()) return 1;
-    if (!gp || !last_ids || !logits) return fail("gpt_decode: null argument");
-    Gpt* g = (Gpt*)gp;
+// The launches of one decode step.  Everything that changes from step to step -- the token's position, the number of valid cached
+// positions, the ring slot, the row of the position table -- is read by the kernels from the device words `g->dstate`, so the same
+// sequence of launches serves every step and can be replayed as a CUDA graph.
+static int decode_launches(Gpt* g, const void* last_ids, int B, int append, void* logits) {
     const sptorch_gpt_config& c = g->c;
-    if (!g->kcache || g->cached_len <= 0) return fail("gpt_decode: the cache is empty (prefill first)");
-    if (batch != g->cache_batch) return fail("gpt_decode: batch %d differs from the cached batch %d", batch, g->cache_batch);
-    if (append && g->cached_len >= g->cache_ctx) return fail("gpt_decode: the cache of %d positions is full", g->cache_ctx);
-    const int d = c.d_model, dl = g->d_loc, Fl = g->F_loc, hd = d / c.n_head, dt = c.dtype, B = batch;
-    const int pos = append ? g->cached_len : g->cached_len - 1;
-    const int n = pos + 1;
-    const int pos_row = pos < c.seq_len - 1 ? pos : c.seq_len - 1;            // last_pos.min(seq_len - 1), nn/src/lib.rs:1631
+    const int d = c.d_model, dl = g->d_loc, Fl = g->F_loc, hd = d / c.n_head, dt = c.dtype;
     const size_t es = g->es;
     const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;     // QwenLikeBlock::forward_last_token_incremental, nn/src/lib.rs:1119-1131
+    const int* st = g->dstate;
     auto norm = [&](const void* in, const float* gamma, const float* beta, void* out) {
         return qwen ? rms_launch(in, gamma, out, (size_t)B, (size_t)d, c.eps, dt) : ln(in, gamma, beta, out, (size_t)B, (size_t)d, c.eps, dt);
     };
     { ProfScope ps(PROF_EMBED);
-      if (sptorch_ext_embedding_sum(g->tok, qwen ? nullptr : (const uint8_t*)g->pos + (size_t)pos_row * d * es, last_ids, g->x, (size_t)B, 1,
-                                    (size_t)c.vocab, (size_t)d, dt)) return 1; }
+      if (embedding_sum_launch(g->tok, qwen ? nullptr : g->pos, last_ids, g->x, (size_t)B, 1, (size_t)c.vocab, (size_t)d, dt, st + 3)) return 1; }
     void* x = g->x;
     const long long row = dl, seq = (long long)g->cache_ctx * dl;
     for (int l = 0; l < c.n_layer; l++) {
@@ -785,16 +923,10 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
         if (norm(x, w.ln1g, w.ln1b, g->h)) return 1;
         if (linear(g, g->h, w.wqkv, nullptr, nullptr, g->dq, B, d, 3 * dl, 3 * dl, EPI_NONE)) return 1;     // [q | k | v] of the token
         // the query (and the key about to be cached) are rotated to the token's absolute position (nn/src/lib.rs:718-721, 678-680)
-        if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 3 * dl, c.rope_base, pos, dt)) return 1; }
-        if (append) {
-            // one cache row per sequence and layer
-            SPT_CUDA(cudaMemcpy2DAsync(kc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)dl * es, (size_t)3 * dl * es,
-                                       (size_t)dl * es, (size_t)B, cudaMemcpyDeviceToDevice, rt().stream));
-            SPT_CUDA(cudaMemcpy2DAsync(vc + (size_t)pos * dl * es, (size_t)seq * es, (const uint8_t*)g->dq + (size_t)2 * dl * es, (size_t)3 * dl * es,
-                                       (size_t)dl * es, (size_t)B, cudaMemcpyDeviceToDevice, rt().stream));
-        }
+        if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 3 * dl, c.rope_base, 0, dt, st + 0)) return 1; }
+        if (append) { ProfScope ps(PROF_OTHER); if (kv_append_launch(g->dq, kc, vc, B, dl, seq, 0, st, dt)) return 1; }      // one cache row per sequence and layer
         { ProfScope ps(PROF_ATTN_FUSED);
-          if (attention_last_token(g->dq, 3 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, n, seq, row, dt)) return 1; }
+          if (attention_last_token(g->dq, 3 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, g->cache_ctx, seq, row, dt, st, g->cache_ctx)) return 1; }
         if (linear(g, g->ao, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
         if (norm(x, w.ln2g, w.ln2b, g->h)) return 1;
         if (qwen) {
@@ -804,8 +936,60 @@ int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append
         if (linear(g, g->f, w.w2, w.b2, x, x, B, Fl, d, d, EPI_NONE)) return 1;
     }
     if (norm(x, g->lnfg, g->lnfb, g->h)) return 1;
-    if (linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE)) return 1;
-    if (append) g->cached_len++;
+    return linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE);
+}
+
+int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append, void* logits) {
+    if (enter()) return 1;
+    if (!gp || !last_ids || !logits) return fail("gpt_decode: null argument");
+    Gpt* g = (Gpt*)gp;
+    const sptorch_gpt_config& c = g->c;
+    if (!g->kcache || g->cached_len <= 0) return fail("gpt_decode: the cache is empty (prefill first)");
+    if (batch != g->cache_batch) return fail("gpt_decode: batch %d differs from the cached batch %d", batch, g->cache_batch);
+    // The cache is a ring over absolute positions (slot = position % capacity): once it is full an appended token takes the slot
+    // of the oldest one, which is how append_kv_tensor (nn/src/lib.rs:2165-2203) keeps the last max_context positions; the window
+    // start then moves on by one (KvCacheWindowState::append, hal/src/lib.rs:129-239).  The attention reads the n valid slots;
+    // their order in memory does not matter to a softmax-weighted sum.
+    const bool full = g->cached_len >= g->cache_ctx;
+    const long long apos = append ? g->window_start + g->cached_len : g->window_start + g->cached_len - 1;   // absolute position of the token
+    if (apos > INT32_MAX) return fail("gpt_decode: position overflow");
+    const int pos = (int)apos;
+    const int slot = (int)(apos % g->cache_ctx);
+    const int n = append ? (full ? g->cache_ctx : g->cached_len + 1) : g->cached_len;
+    const int pos_row = pos < c.seq_len - 1 ? pos : c.seq_len - 1;            // last_pos.min(seq_len - 1), nn/src/lib.rs:1631
+    if (decode_state_launch(g->dstate, pos, n, slot, pos_row)) return 1;      // by value: nothing of the host's is read later
+    // Replay: a decode step is about a hundred small launches, host-bound when issued one by one.  The first step of a key runs
+    // eagerly, the second is captured, later ones are one cudaGraphLaunch.
+    Gpt::DecodeKey key = {last_ids, logits, batch, append, rt().stream, config_epoch()};
+    const bool graph_ok = g->graphs && !prof_enabled();
+    int rc;
+    if (!graph_ok) rc = decode_launches(g, last_ids, batch, append, logits);
+    else {
+        if (!(g->dkey == key)) {
+            if (g->dexec) { cudaGraphExecDestroy(g->dexec); g->dexec = nullptr; }
+            g->dkey = key; g->d_eager = 0;
+        }
+        if (g->dexec) { SPT_CUDA(cudaGraphLaunch(g->dexec, rt().stream)); note_submit(); rc = 0; }
+        else if (g->d_eager++ == 0) rc = decode_launches(g, last_ids, batch, append, logits);
+        else {
+            cudaGraph_t graph = nullptr;
+            SPT_CUDA(cudaStreamBeginCapture(rt().stream, cudaStreamCaptureModeThreadLocal));
+            rc = decode_launches(g, last_ids, batch, append, logits);
+            cudaError_t e = cudaStreamEndCapture(rt().stream, &graph);
+            if (rc == 0 && e == cudaSuccess && graph && cudaGraphInstantiate(&g->dexec, graph, 0) == cudaSuccess) {
+                cudaGraphDestroy(graph);
+                SPT_CUDA(cudaGraphLaunch(g->dexec, rt().stream));
+                note_submit();
+            } else {
+                if (graph) cudaGraphDestroy(graph);
+                cudaGetLastError();
+                g->dexec = nullptr; g->graphs = false;                       // capture is not possible here: stay eager from now on
+                if (rc == 0) rc = decode_launches(g, last_ids, batch, append, logits);
+            }
+        }
+    }
+    if (rc) return rc;
+    if (append) { if (full) g->window_start++; else g->cached_len++; }
     return 0;
 }
 

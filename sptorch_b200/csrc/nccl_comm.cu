@@ -12,6 +12,7 @@
 #include <nccl.h>
 #include <dlfcn.h>
 #include <cstring>
+#include <cstdlib>
 
 namespace spt {
 
@@ -19,6 +20,7 @@ struct NcclApi {
     void* h = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;      // optional
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -40,6 +42,7 @@ static int load_nccl(const char* path) {
     g_nccl.h = h;
     g_nccl.GetUniqueId = (decltype(g_nccl.GetUniqueId))dlsym(h, "ncclGetUniqueId");
     g_nccl.CommInitRank = (decltype(g_nccl.CommInitRank))dlsym(h, "ncclCommInitRank");
+    g_nccl.CommInitRankConfig = (decltype(g_nccl.CommInitRankConfig))dlsym(h, "ncclCommInitRankConfig");
     g_nccl.AllReduce = (decltype(g_nccl.AllReduce))dlsym(h, "ncclAllReduce");
     g_nccl.CommDestroy = (decltype(g_nccl.CommDestroy))dlsym(h, "ncclCommDestroy");
     g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(h, "ncclGetErrorString");
@@ -91,7 +94,17 @@ int sptorch_ext_nccl_init(const char* libnccl_path, const void* id128, int rank,
     if (load_nccl(libnccl_path)) return 1;
     ncclUniqueId id;
     memcpy(&id, id128, 128);
-    SPT_NCCL(g_nccl.CommInitRank(&g_comm, world, id, rank));
+    // SPTORCH_B200_NCCL_MAX_CTAS caps the CTAs a collective of this communicator may use, so that a collective running beside the
+    // persistent GEMM / attention kernels (sptorch_ext_set_sm_reserve leaves it that many SMs) fits into the SMs left free
+    const char* cap = getenv("SPTORCH_B200_NCCL_MAX_CTAS");
+    if (cap && atoi(cap) > 0 && g_nccl.CommInitRankConfig) {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        cfg.maxCTAs = atoi(cap);
+        cfg.minCTAs = 1;
+        SPT_NCCL(g_nccl.CommInitRankConfig(&g_comm, world, id, rank, &cfg));
+    } else {
+        SPT_NCCL(g_nccl.CommInitRank(&g_comm, world, id, rank));
+    }
     g_world = world; g_rank = rank;
     return 0;
 }

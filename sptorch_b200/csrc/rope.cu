@@ -23,8 +23,9 @@ template <> struct RopeVec<__nv_bfloat16> { static constexpr int N = 8; };
 
 template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ x, const float* __restrict__ denom, long long rows, int Tn, int n_slots,
-                                                   int hd, long long ld, int offset) {
+                                                   int hd, long long ld, int offset, const int* __restrict__ offset_dev) {
     constexpr int N = RopeVec<T>::N;
+    if (offset_dev) offset = *offset_dev;                      // decode graphs: the position lives in a device word
     const int vec_per_head = hd / N;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * vec_per_head) return;
@@ -63,8 +64,9 @@ __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ x, const floa
 // element-wise form for head dims or strides that 16-byte vectors cannot take
 template <typename T>
 __global__ void __launch_bounds__(256) rope_generic_kernel(T* __restrict__ x, const float* __restrict__ denom, long long rows, int Tn,
-                                                           int n_slots, int hd, long long ld, int offset) {
+                                                           int n_slots, int hd, long long ld, int offset, const int* __restrict__ offset_dev) {
     const int half = hd / 2;
+    if (offset_dev) offset = *offset_dev;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * half) return;
     const long long row = idx / half;
@@ -99,7 +101,7 @@ static const float* rope_denominators(int hd, float base) {
     return t.dev;
 }
 
-int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype) {
+int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long ld, float base, int offset, int dtype, const int* offset_dev) {
     if (rows == 0 || n_slots == 0) return 0;
     if (hd <= 0 || hd % 2) return fail("rope: head_dim %d is not even", hd);          // the reference asserts (nn/src/lib.rs:938)
     const float* den = rope_denominators(hd, base);
@@ -110,11 +112,11 @@ int rope_launch(void* x, long long rows, int Tn, int n_slots, int hd, long long 
     const long long work = rows * (vec ? hd / N : hd / 2);
     const unsigned grid = (unsigned)((work + 255) / 256);
     if (dtype == SPT_BF16) {
-        if (vec) rope_kernel<__nv_bfloat16><<<grid, 256, 0, rt().stream>>>((__nv_bfloat16*)x, den, rows, Tn, n_slots, hd, ld, offset);
-        else rope_generic_kernel<__nv_bfloat16><<<grid, 256, 0, rt().stream>>>((__nv_bfloat16*)x, den, rows, Tn, n_slots, hd, ld, offset);
+        if (vec) rope_kernel<__nv_bfloat16><<<grid, 256, 0, rt().stream>>>((__nv_bfloat16*)x, den, rows, Tn, n_slots, hd, ld, offset, offset_dev);
+        else rope_generic_kernel<__nv_bfloat16><<<grid, 256, 0, rt().stream>>>((__nv_bfloat16*)x, den, rows, Tn, n_slots, hd, ld, offset, offset_dev);
     } else {
-        if (vec) rope_kernel<float><<<grid, 256, 0, rt().stream>>>((float*)x, den, rows, Tn, n_slots, hd, ld, offset);
-        else rope_generic_kernel<float><<<grid, 256, 0, rt().stream>>>((float*)x, den, rows, Tn, n_slots, hd, ld, offset);
+        if (vec) rope_kernel<float><<<grid, 256, 0, rt().stream>>>((float*)x, den, rows, Tn, n_slots, hd, ld, offset, offset_dev);
+        else rope_generic_kernel<float><<<grid, 256, 0, rt().stream>>>((float*)x, den, rows, Tn, n_slots, hd, ld, offset, offset_dev);
     }
     SPT_LAUNCH_CHECK("rope");
     return 0;
@@ -133,5 +135,5 @@ extern "C" int sptorch_ext_rope(void* x, size_t rows, size_t seq_len, size_t n_h
     if (ld == 0) ld = n_heads * head_dim;
     if (ld < n_heads * head_dim) return fail("rope: ld smaller than n_heads * head_dim");
     if (head_dim > 65536 || n_heads > 65536 || position_offset + seq_len > (size_t)1 << 24) return fail("rope: dimension too large");
-    return rope_launch(x, (long long)rows, (int)seq_len, (int)n_heads, (int)head_dim, (long long)ld, rope_base, (int)position_offset, dtype);
+    return rope_launch(x, (long long)rows, (int)seq_len, (int)n_heads, (int)head_dim, (long long)ld, rope_base, (int)position_offset, dtype, nullptr);
 }

@@ -7,6 +7,7 @@
 // (crates/nn/src/lib.rs:397-418; crates/core-ops/src/lib.rs:888-935, 1601-1645, 1220-1255, 825-850) and its
 // CUDA backend round-trips through the host for them (crates/runtime-cuda/src/lib.rs:302-490).
 #include "common.h"
+#include "sm100.cuh"
 #include <cstdlib>
 #include "../../include/sptorch_b200_hal.h"
 #include "../../include/sptorch_b200_ext.h"
@@ -225,6 +226,176 @@ __global__ void __launch_bounds__(kRowThreads, 4) layernorm_bf16_kernel(const __
             }
         }
     }
+}
+
+// bf16 LayerNorm for rows of 768 / 1024 / 2048 elements with the memory traffic taken off the compute warps.
+// The kernel above is bound by load latency (ncu: DRAM 44 %, 7.6 stall cycles on loads per issued instruction): its threads
+// load, reduce and store in turn, so a CTA has bytes in flight only part of the time.  Here one CTA per SM runs a ring of
+// shared-memory stages: warp 0 streams blocks of rows in with bulk asynchronous copies (rows are contiguous, a block of rows is
+// ONE copy of 24..64 KB), sixteen compute warps normalise one row each of a stage in
+// place, warp 1 streams finished stages out with bulk stores -- about 190 KB per SM are in flight at every moment, whatever the
+// compute warps are doing.  A compute warp owns a whole row (lane l holds the 16-byte vectors l, l + 32, ...), so the two
+// reductions are five shuffles each, and for 768-wide rows gamma / beta of the lane's columns stay in registers for the whole
+// kernel (wider rows read them through L1).  The kernel is used for every row count, so that a row's result does not depend on
+// how many rows are normalised with it.
+// Same arithmetic as above (mean, then centred variance, f32 pairs), only the order of the partial sums differs.
+template <int VPL, int CW>
+__global__ void __launch_bounds__(64 + 32 * CW, 1) layernorm_bf16_async_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+                                                                      const float* __restrict__ beta, __nv_bfloat16* __restrict__ out,
+                                                                      size_t rows, float eps, int stages, uint32_t* status) {
+    using namespace sm100;
+    constexpr int DIM = VPL * 256;                 // 32 lanes x VPL vectors x 8 elements
+    constexpr int R = CW;                          // rows per stage: one per compute warp
+    constexpr uint32_t ROW_BYTES = DIM * 2, STAGE_BYTES = R * ROW_BYTES;
+    constexpr bool GB_REGS = VPL <= 3;             // wider rows: the registers go to the row itself
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t base = smem_u32(smem);
+    const uint32_t bars = base + stages * STAGE_BYTES;           // full[stages], done[stages], empty[stages]
+    const uint32_t full = bars, done = bars + 8 * stages, empty = bars + 16 * stages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (size_t)stages * STAGE_BYTES + 24 * stages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) { mbar_init(full + 8 * s, 1); mbar_init(done + 8 * s, CW); mbar_init(empty + 8 * s, 1); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const size_t n_tiles = (rows + R - 1) / R;
+    auto tile_bytes = [&](size_t tile) -> uint32_t {
+        const size_t left = rows - tile * R;
+        return (uint32_t)(left < (size_t)R ? left : (size_t)R) * ROW_BYTES;
+    };
+    if (warp == 0) {
+        // ---- loads ----
+        uint32_t i = 0;
+        for (size_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            if (!mbar_wait(empty + 8 * s, ph ^ 1, abort_flag, status, kErrProducerWait)) break;
+            if (lane == 0) {
+                const uint32_t bytes = tile_bytes(tile);
+                mbar_expect_tx(full + 8 * s, bytes);
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(base + s * STAGE_BYTES), "l"(reinterpret_cast<uint64_t>(x + tile * (size_t)R * DIM)), "r"(bytes), "r"(full + 8 * s)
+                             : "memory");
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---- stores ----
+        uint32_t i = 0;
+        for (size_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            if (!mbar_wait(done + 8 * s, ph, abort_flag, status, kErrEpilogueWait)) break;
+            if (lane == 0) {
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(reinterpret_cast<uint64_t>(out + tile * (size_t)R * DIM)), "r"(base + s * STAGE_BYTES), "r"(tile_bytes(tile))
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the stage has been read: it may be refilled
+                mbar_arrive(empty + 8 * s);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+        // ---- compute: warp w owns row w of every stage ----
+        const int w = warp - 2;
+        float2 g[GB_REGS ? VPL * 4 : 1], b[GB_REGS ? VPL * 4 : 1];
+        if constexpr (GB_REGS) {
+#pragma unroll
+            for (int i = 0; i < VPL; i++) {
+                const int c = (i * 32 + lane) * 8;
+                const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c + 4));
+                g[4 * i] = make_float2(g0.x, g0.y); g[4 * i + 1] = make_float2(g0.z, g0.w); g[4 * i + 2] = make_float2(g1.x, g1.y); g[4 * i + 3] = make_float2(g1.z, g1.w);
+                b[4 * i] = make_float2(b0.x, b0.y); b[4 * i + 1] = make_float2(b0.z, b0.w); b[4 * i + 2] = make_float2(b1.x, b1.y); b[4 * i + 3] = make_float2(b1.z, b1.w);
+            }
+        }
+        uint32_t i = 0;
+        bool ok = true;
+        for (size_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            ok = mbar_wait(full + 8 * s, ph, abort_flag, status, kErrMmaWait);
+            if (!ok) break;
+            const size_t left = rows - tile * R;
+            if ((size_t)w < left) {
+                const int lr = w;
+                uint8_t* rowp = smem + (size_t)s * STAGE_BYTES + (size_t)lr * ROW_BYTES;
+                float2 e[VPL * 4];
+                float2 acc = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const uint4 d = *reinterpret_cast<const uint4*>(rowp + (v * 32 + lane) * 16);
+                    const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        e[4 * v + j] = make_float2(__uint_as_float(wd[j] << 16), __uint_as_float(wd[j] & 0xffff0000u));
+                        acc = __fadd2_rn(acc, e[4 * v + j]);
+                    }
+                }
+                float sum = acc.x + acc.y;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float mean = sum / (float)DIM;
+                const float2 nmean = make_float2(-mean, -mean);
+                float2 qa = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int k = 0; k < VPL * 4; k++) { e[k] = __fadd2_rn(e[k], nmean); qa = __ffma2_rn(e[k], e[k], qa); }
+                float sq = qa.x + qa.y;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                const float inv = 1.0f / sqrtf(sq / (float)DIM + eps);
+                const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    float2 gg[4], bb[4];
+                    if constexpr (GB_REGS) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) { gg[j] = g[4 * v + j]; bb[j] = b[4 * v + j]; }
+                    } else {
+                        const int c = (v * 32 + lane) * 8;
+                        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
+                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c + 4));
+                        gg[0] = make_float2(g0.x, g0.y); gg[1] = make_float2(g0.z, g0.w); gg[2] = make_float2(g1.x, g1.y); gg[3] = make_float2(g1.z, g1.w);
+                        bb[0] = make_float2(b0.x, b0.y); bb[1] = make_float2(b0.z, b0.w); bb[2] = make_float2(b1.x, b1.y); bb[3] = make_float2(b1.z, b1.w);
+                    }
+                    uint4 o;
+                    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float2 y = __ffma2_rn(gg[j], __fmul2_rn(e[4 * v + j], inv2), bb[j]);
+                        oh[j] = __floats2bfloat162_rn(y.x, y.y);
+                    }
+                    *reinterpret_cast<uint4*>(rowp + (v * 32 + lane) * 16) = o;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the rows written above -> visible to the bulk store
+            __syncwarp();
+            if (lane == 0) mbar_arrive(done + 8 * s);
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        // copies that may still be in flight must land before shared memory is released
+        unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { }
+        __syncthreads();
+    }
+}
+
+template <int VPL, int CW>
+static int layernorm_bf16_async_launch(const __nv_bfloat16* x, const float* g, const float* b, __nv_bfloat16* out, size_t rows, float eps) {
+    constexpr size_t stage = (size_t)CW * VPL * 256 * 2;
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > 8) stages = 8;
+    const size_t smem = (size_t)stages * stage + 24 * stages + 16;
+    auto kern = layernorm_bf16_async_kernel<VPL, CW>;
+    static bool attr_set = false;
+    if (!attr_set) { SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_set = true; }
+    const size_t tiles = (rows + CW - 1) / CW;
+    const int grid = (int)(tiles < (size_t)rt().sm_count ? tiles : (size_t)rt().sm_count);
+    kern<<<grid, 64 + 32 * CW, smem, rt().stream>>>(x, g, b, out, rows, eps, stages, rt().dev_status);
+    return 0;
 }
 
 // Row statistics only: stats[row] = (1/sqrt(var + eps), mean/sqrt(var + eps)), the two numbers a GEMM epilogue needs to apply
@@ -549,10 +720,13 @@ __global__ void __launch_bounds__(kRowThreads) masked_softmax_kernel(const float
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads) embedding_sum_kernel(const T* __restrict__ tok, const T* __restrict__ pos,
                                                                     const int* __restrict__ ids, T* __restrict__ out,
-                                                                    size_t n_tokens, int Tn, int vocab, int dim, uint32_t* status) {
+                                                                    size_t n_tokens, int Tn, int vocab, int dim, uint32_t* status,
+                                                                    const int* __restrict__ pos_row_dev) {
     using VT = Vec<T>;
     constexpr int N = VT::N;
     const int lane = threadIdx.x & 31;
+    // incremental decode replayed as a CUDA graph: every token takes the position row a device word names
+    const int fixed_row = pos_row_dev ? *pos_row_dev : -1;
     const size_t warp = ((size_t)blockIdx.x * kRowThreads + threadIdx.x) >> 5;
     const size_t nwarps = ((size_t)gridDim.x * kRowThreads) >> 5;
     const int nvec = dim / N;
@@ -561,7 +735,7 @@ __global__ void __launch_bounds__(kRowThreads) embedding_sum_kernel(const T* __r
         bool ok = id >= 0 && id < vocab;
         if (!ok && lane == 0) atomicOr(status, 0x100u);
         const T* a = tok + (size_t)(ok ? id : 0) * dim;
-        const T* b = pos ? pos + (size_t)(t % Tn) * dim : nullptr;      // no position table: plain gather (RoPE models)
+        const T* b = pos ? pos + (size_t)(fixed_row >= 0 ? fixed_row : (int)(t % Tn)) * dim : nullptr;      // no position table: plain gather (RoPE models)
         T* y = out + t * (size_t)dim;
         for (int c = lane; c < nvec; c += 32) {
             VT u = VT::load_keep(a + c * N), r;
@@ -689,6 +863,62 @@ __global__ void __launch_bounds__(kRowThreads) cross_entropy_mean_kernel(const f
     if (threadIdx.x == 0) out[0] = sc[0] ? (float)(sd[0] / (double)sc[0]) : 0.0f;
 }
 
+// Second stage of the LM head fused with the loss / greedy choice (GemmDesc::reduce wrote, per row, `parts` partial results over
+// ascending column ranges): one warp per row merges them into the row's maximum, the column of its FIRST maximum (what a stable
+// descending sort puts first: nn/src/lib.rs:2381-2418) and log-sum-exp, and -- when targets are given -- the row's loss
+// -(x[target] - max - ln(sum)) with the conventions of cross_entropy_rows_kernel (ignored row: marker -1; bad target: status word).
+__global__ void __launch_bounds__(kRowThreads) head_reduce_combine_kernel(const float2* __restrict__ part, const int* __restrict__ arg,
+                                                                          const float* __restrict__ tgt_logit, const long long* __restrict__ targets,
+                                                                          size_t rows, int parts, int classes, int has_ignore, long long ignore_index,
+                                                                          int* __restrict__ argmax_out, float* __restrict__ row_loss, uint32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp0 = ((size_t)blockIdx.x * kRowThreads + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * kRowThreads) >> 5;
+    for (size_t r = warp0; r < rows; r += nwarps) {
+        const float2* pr = part + r * parts;
+        float m = -INFINITY; int best = 0x7fffffff;              // (maximum, index of the first partial that attains it)
+        for (int i = lane; i < parts; i += 32) { const float v = pr[i].x; if (v > m) { m = v; best = i; } }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, o);
+            const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+            if (om > m || (om == m && ob < best)) { m = om; best = ob; }
+        }
+        float s = 0.0f;
+        for (int i = lane; i < parts; i += 32) { const float2 v = pr[i]; if (v.x != -INFINITY) s += v.y * expf(v.x - m); }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) {
+            if (argmax_out) argmax_out[r] = best < parts ? arg[r * parts + best] : 0;
+            if (row_loss) {
+                const long long t = targets[r];
+                if (has_ignore && t == ignore_index) row_loss[r] = -1.0f;
+                else if (t < 0 || t >= classes) { atomicOr(status, 0x100u); row_loss[r] = -1.0f; }
+                else row_loss[r] = -(tgt_logit[r] - m - logf(s));
+            }
+        }
+    }
+}
+
+int head_reduce_combine_launch(const float2* part, const int* arg, const float* tgt_logit, const long long* targets, size_t rows, int parts,
+                               int classes, int has_ignore, long long ignore_index, int* argmax_out, float* row_loss) {
+    if (rows == 0) return 0;
+    const size_t warps_per_cta = kRowThreads / 32;
+    size_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+    const size_t cap = (size_t)rt().sm_count * 8;
+    if (ctas > cap) ctas = cap;
+    head_reduce_combine_kernel<<<(unsigned)ctas, kRowThreads, 0, rt().stream>>>(part, arg, tgt_logit, targets, rows, parts, classes, has_ignore, ignore_index,
+                                                                              argmax_out, row_loss, rt().dev_status);
+    SPT_LAUNCH_CHECK("head_reduce_combine");
+    return 0;
+}
+
+// mean of the row losses that are not markers into row_loss[rows] (cross_entropy_loss / _ignore_index: core-ops/src/lib.rs:1079-1194)
+int cross_entropy_mean_launch(float* row_loss, size_t rows) {
+    cross_entropy_mean_kernel<<<1, kRowThreads, 0, rt().stream>>>(row_loss, rows, row_loss + rows);
+    SPT_LAUNCH_CHECK("cross_entropy_mean");
+    return 0;
+}
+
 // ---------------- transpose (crates/core-ops/src/lib.rs:825-836) ----------------
 __global__ void transpose_kernel(const float* __restrict__ a, float* __restrict__ out, int rows, int cols) {
     __shared__ float tile[32][33];
@@ -741,6 +971,17 @@ static int layernorm_t(const void* x, const void* gamma, const void* beta, void*
     if (fast) {
         int nvec = (int)(dim / N);
         if constexpr (sizeof(T) == 2) {
+            // rows of 768 / 1024 / 2048: the pipelined kernel; a 4096-wide row does not fit one warp's registers unpacked and
+            // stays with the kernel below
+            static const bool async_on = !(getenv("SPTORCH_B200_LN_ASYNC") && getenv("SPTORCH_B200_LN_ASYNC")[0] == '0');
+            if (async_on && (dim == 768 || dim == 1024 || dim == 2048)) {
+                int rc = dim == 768 ? layernorm_bf16_async_launch<3, 16>(xp, g, b, op, rows, eps)
+                       : dim == 1024 ? layernorm_bf16_async_launch<4, 16>(xp, g, b, op, rows, eps)
+                                     : layernorm_bf16_async_launch<8, 16>(xp, g, b, op, rows, eps);
+                if (rc) return rc;
+                SPT_LAUNCH_CHECK("layernorm (pipelined)");
+                return 0;
+            }
             int tpr = 8;
             while (tpr * kRowVecs < nvec) tpr *= 2;
             const int rpb = kRowThreads / tpr;
@@ -881,9 +1122,26 @@ int sptorch_ext_masked_softmax_f32(const void* a, const void* keep, void* out, s
     return 0;
 }
 
+}  // extern "C"
+
+namespace spt {
+// embedding sum with an optional device word that names the position row of every token (decode graphs); else row t % T
+int embedding_sum_launch(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T, size_t vocab, size_t dim,
+                         int dtype, const int* pos_row_dev);
+}
+
+extern "C" {
+
 int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T,
                               size_t vocab, size_t dim, int dtype) {
     if (enter()) return 1;
+    return spt::embedding_sum_launch(tok_w, pos_w, ids, out, n_tokens, T, vocab, dim, dtype, nullptr);
+}
+
+}  // extern "C"
+
+int spt::embedding_sum_launch(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T, size_t vocab, size_t dim,
+                              int dtype, const int* pos_row_dev) {
     if (n_tokens == 0 || dim == 0) return 0;
     if (!tok_w || !ids || !out) return fail("embedding_sum: null handle");     // pos_w may be null: token rows only
     if (T == 0) return fail("embedding_sum: T == 0");
@@ -891,16 +1149,18 @@ int sptorch_ext_embedding_sum(const void* tok_w, const void* pos_w, const void* 
     if (dtype == SPT_F32) {
         if (dim % 4 || !aligned16(tok_w) || !aligned16(pos_w) || !aligned16(out)) return fail("embedding_sum: dim %% 4 != 0 or unaligned buffers");
         embedding_sum_kernel<float><<<grid, kRowThreads, 0, rt().stream>>>((const float*)tok_w, (const float*)pos_w, (const int*)ids, (float*)out,
-                                                                          n_tokens, (int)T, (int)vocab, (int)dim, rt().dev_status);
+                                                                          n_tokens, (int)T, (int)vocab, (int)dim, rt().dev_status, pos_row_dev);
     } else if (dtype == SPT_BF16) {
         if (dim % 8 || !aligned16(tok_w) || !aligned16(pos_w) || !aligned16(out)) return fail("embedding_sum: dim %% 8 != 0 or unaligned buffers");
         embedding_sum_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, rt().stream>>>((const __nv_bfloat16*)tok_w, (const __nv_bfloat16*)pos_w,
                                                                                   (const int*)ids, (__nv_bfloat16*)out, n_tokens, (int)T,
-                                                                                  (int)vocab, (int)dim, rt().dev_status);
+                                                                                  (int)vocab, (int)dim, rt().dev_status, pos_row_dev);
     } else return fail("embedding_sum: unknown dtype %d", dtype);
     SPT_LAUNCH_CHECK("embedding_sum");
     return 0;
 }
+
+extern "C" {
 
 int sptorch_ext_rms_norm(const void* x, const void* w, void* out, size_t rows, size_t dim, float eps, int dtype) {
     if (enter()) return 1;

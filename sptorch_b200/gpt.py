@@ -124,6 +124,47 @@ class GPT:
         out = bf16_bits_to_f32(raw) if self.dtype == BF16 else raw
         return out.reshape(B, T, self.ldl)[:, :T0, :V].copy()
 
+    def forward_loss(self, ids: np.ndarray, targets=None, ignore_index=None, want_argmax: bool = True):
+        """Forward fused with the step after it: ids [B, T] (T a multiple of the vector width) and int targets [B, T] ->
+        (mean cross-entropy loss or None, greedy tokens [B, T] or None) without the [B*T, vocab] logits ever being written
+        (cross_entropy_loss / cross_entropy_loss_ignore_index: core-ops/src/lib.rs:1079-1194; greedy token: the first of
+        sampling_candidates' sorted candidates, nn/src/lib.rs:2381-2418)."""
+        ids = np.asarray(ids)
+        B, T = ids.shape
+        d_ids = self.stage_ids(ids)
+        bufs = []
+        d_tgt = d_rows = d_arg = None
+        if targets is not None:
+            tg = np.ascontiguousarray(targets, dtype=np.int64).reshape(-1)
+            d_tgt = self.b.alloc(tg.size, 8); bufs.append(d_tgt)
+            self.b._check(self.b.lib.sptorch_ext_copy_h2d_bytes(tg.ctypes.data, d_tgt.handle, tg.nbytes), "targets h2d")
+            self.b.synchronize()
+            d_rows = self.b.alloc(B * T + 1); bufs.append(d_rows)
+        if want_argmax:
+            d_arg = self.b.alloc(B * T); bufs.append(d_arg)
+        mean = C.c_float(0.0)
+        try:
+            self.b._check(self.b.lib.sptorch_ext_gpt_forward_loss(self.h, d_ids.handle, d_tgt.handle if d_tgt else None, B, T,
+                                                                  int(ignore_index is not None), int(ignore_index or 0),
+                                                                  d_arg.handle if d_arg else None, d_rows.handle if d_rows else None, C.byref(mean)), "gpt_forward_loss")
+            arg = None
+            if d_arg is not None:
+                arg = np.empty(B * T, dtype=np.int32)
+                self.b._check(self.b.lib.sptorch_ext_copy_d2h_bytes(d_arg.handle, arg.ctypes.data, arg.nbytes), "argmax d2h")
+                arg = arg.reshape(B, T)
+            self.b.synchronize()
+            return (float(mean.value) if targets is not None else None), arg
+        finally:
+            for buf in bufs:
+                buf.free()
+
+    def forward_loss_host(self, ids_host_ptr: int, targets_host_ptr, batch: int, T: int, argmax_host_ptr, chunk: int, ignore_index=None) -> float:
+        """Host-buffer form of forward_loss: pinned ids (int32) and targets (int64) in, greedy tokens (int32) and the mean loss out."""
+        mean = C.c_float(0.0)
+        self.b._check(self.b.lib.sptorch_ext_gpt_forward_loss_host(self.h, ids_host_ptr, targets_host_ptr, batch, T, int(ignore_index is not None),
+                                                                   int(ignore_index or 0), argmax_host_ptr, C.byref(mean), chunk), "gpt_forward_loss_host")
+        return float(mean.value)
+
     def forward_ids(self, token_ids) -> np.ndarray:
         """GPT::forward_ids (nn/src/lib.rs:1349-1364): one sequence of ids -> logits [T, V]."""
         ids = np.asarray(token_ids).reshape(1, -1)

@@ -87,10 +87,61 @@ def test_decode_error_paths(backend):
     with pytest.raises(HalError):
         m.prefill_kv_cache(np.zeros((2, 12), dtype=np.int64))      # longer than the cache
     m.prefill_kv_cache(np.zeros((2, 8), dtype=np.int64))
-    with pytest.raises(HalError):
-        m.append_and_decode([1, 2])                                # cache full
+    assert np.isfinite(m.append_and_decode([1, 2])).all()          # cache full: the window slides, no error
+    assert m.cached_len() == 8 and backend.lib.sptorch_ext_gpt_window_start(m.h) == 1
     with pytest.raises(HalError):
         m.decode_logits_from_cache([1])                            # batch differs from the cached batch
     assert backend.lib.sptorch_sync() == 0                      # the wrapper consumed every reported failure
     assert np.isfinite(m.decode_logits_from_cache([0, 0])).all()
+    m.close()
+
+
+def _oracle_incremental(oracle, cfg, params, index, ids, ctx):
+    """decode_logits_from_cache after append_last_token_kv_cache for every token of one sequence, restated with the oracle's
+    ops (crates/nn/src/lib.rs:1619-1646, 1205-1214, 706-760, 2165-2203): per layer a first-in-first-out list of the last `ctx`
+    keys and values; the position table is read at min(position, seq_len - 1)."""
+    def P(name):
+        o, shape = index[name]
+        return params[o:o + int(np.prod(shape))].reshape(shape)
+    d, H, L, S = cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["seq_len"]
+    hd = d // H
+    K = [[] for _ in range(L)]
+    V = [[] for _ in range(L)]
+    out = []
+    for t, tok in enumerate(ids):
+        x = (P("token_emb.weight")[tok] + P("pos_emb.weight")[min(t, S - 1)])[None, :].astype(np.float32)
+        for l in range(L):
+            p = f"blocks.{l}."
+            h = oracle.layernorm(x, P(p + "ln1.gamma"), P(p + "ln1.beta"))
+            q, k, v = (oracle.linear(h, P(p + f"attn.{n}.weight")) for n in ("wq", "wk", "wv"))
+            K[l].append(k[0]); V[l].append(v[0])
+            K[l], V[l] = K[l][-ctx:], V[l][-ctx:]
+            kh = np.stack(K[l]).reshape(-1, H, hd).transpose(1, 0, 2)
+            vh = np.stack(V[l]).reshape(-1, H, hd).transpose(1, 0, 2)
+            a = oracle.attention_last_token(q[0], np.ascontiguousarray(kh), np.ascontiguousarray(vh))[None, :]
+            x = x + oracle.linear(a, P(p + "attn.wo.weight"))
+            h2 = oracle.layernorm(x, P(p + "ln2.gamma"), P(p + "ln2.beta"))
+            f = oracle.unary("gelu", oracle.linear(h2, P(p + "ffn_up.weight"), P(p + "ffn_up.bias")))
+            x = x + oracle.linear(f, P(p + "ffn_down.weight"), P(p + "ffn_down.bias"))
+        out.append(oracle.linear(oracle.layernorm(x, P("ln_f.gamma"), P("ln_f.beta")), P("lm_head.weight"))[0])
+    return np.stack(out)
+
+
+def test_cache_slides_on_the_device_like_append_kv_tensor(backend, oracle):
+    """Appending past the capacity of the cache keeps the last max_context positions (append_kv_tensor drops the oldest,
+    nn/src/lib.rs:2165-2203) and reads the position table at min(position, seq_len - 1): every step's logits against the
+    oracle's restatement of the incremental path, far past the point where the 8-position cache is full."""
+    cfg = dict(vocab=50, d_model=32, n_layer=2, n_head=2, d_ff=64, seq_len=12)
+    params, index = synth.gpt_params(cfg, 8, randomize_affine=True)
+    ids = synth.randint(5, 30, 50)
+    ref = _oracle_incremental(oracle, cfg, params, index, ids, ctx=8)
+    m = _model(backend, cfg, F32, 1, params, index)
+    m.enable_kv_cache(8)
+    m.prefill_kv_cache(ids[None, :4])
+    scale = np.abs(ref).max()
+    for t in range(4, 30):
+        step = m.append_and_decode(ids[t:t + 1])
+        assert m.cached_len() == min(t + 1, 8)
+        assert backend.lib.sptorch_ext_gpt_window_start(m.h) == max(0, t + 1 - 8)
+        assert np.abs(step[0] - ref[t]).max() <= 2e-3 * scale, f"position {t}"
     m.close()

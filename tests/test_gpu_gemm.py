@@ -162,3 +162,26 @@ def test_fused_attention_matches_materialised_and_oracle(backend, oracle, B, T, 
     assert relerr(fused, ref) <= 2e-2 and relerr(mat, ref) <= 2e-2
     assert relerr(fused, ref) <= 1.5 * 2 ** -8           # one bf16 rounding of P and of the output
     assert np.array_equal(fused[:, 0, :], v[:, 0, :])    # row 0 attends only to itself: output = V[0] exactly
+
+
+@pytest.mark.parametrize("T,hd", [(256, 64), (384, 128), (200, 64)])
+def test_fused_attention_with_steeply_rising_scores(backend, oracle, T, hd):
+    """Scores that grow by far more than 2^8 from one 32-key chunk to the next (key j = 8 (j // 4) u, query = u): the running row maximum
+    of the fused kernel moves at every chunk, so everything accumulated under the old maximum -- the row sum, the output in TMEM and
+    the part of P already written for the current tile -- is rescaled each time.  The softmax is then concentrated on the last
+    few visible keys; the result must still match the oracle within one bf16 rounding of P and of the output."""
+    rng = np.random.default_rng(T + hd)
+    H = 2
+    u = np.where(rng.random(hd) < 0.5, -0.125, 0.125).astype(np.float32)
+    q = np.tile(u, (1, T, H)).astype(np.float32)
+    k = np.concatenate([(8.0 * (j // 4)) * np.tile(u, H)[None, :] for j in range(T)])[None].astype(np.float32)
+    v = _bf16(rng.standard_normal((1, T, H * hd)).astype(np.float32))
+    assert np.array_equal(_bf16(k), k)                     # the keys are exact in bf16
+    fused = backend.attention_causal(q, k, v, H, dtype=BF16)
+    ref = _mha_core(oracle, q[0], k[0], v[0], H)[None]
+    assert relerr(fused, ref) <= 1.5 * 2 ** -8
+    # and the other way round: falling scores never move the maximum after the first chunk
+    k2 = k[:, ::-1].copy()
+    fused2 = backend.attention_causal(q, k2, v, H, dtype=BF16)
+    ref2 = _mha_core(oracle, q[0], k2[0], v[0], H)[None]
+    assert relerr(fused2, ref2) <= 1.5 * 2 ** -8

@@ -129,3 +129,78 @@ def test_constrained_sampling_vs_oracle(backend, oracle):
         assert set(got[0]) <= allowed
     assert len(backend.sampling_candidates(x, allowed=set())[0]) == 0            # an empty set leaves no candidate (NoCandidates)
     assert len(backend.sampling_candidates(x, allowed=None)[0]) == V
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_lm_head_fused_with_loss_and_greedy_token(backend, oracle, dtype):
+    """The forward whose LM-head epilogue reduces the logits instead of storing them: the greedy tokens equal the argmax of the
+    logits the ordinary forward stores, bit for bit (first maximum on ties), and the mean loss equals the reference's
+    cross_entropy_loss / cross_entropy_loss_ignore_index of those logits (core-ops/src/lib.rs:1079-1194) to 1e-5 relative.
+    Vocabulary 777: the last 256-column tile is ragged and its second half empty."""
+    from sptorch_b200 import synth
+    from sptorch_b200.gpt import GPT
+    cfg = dict(vocab=777, d_model=128, n_layer=2, n_head=2, d_ff=256, seq_len=64)
+    params, index = synth.gpt_params(cfg, 5, randomize_affine=True)
+    m = GPT(backend, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=dtype, max_batch=4)
+    m.load_flat(params, index)
+    ids = synth.randint(3, 4 * 64, 777).reshape(4, 64)
+    targets = synth.randint(4, 4 * 64, 777).reshape(4, 64).astype(np.int64)
+    logits = m.forward(ids)                                   # the stored logits (bf16 values widened, or f32)
+    for _ in range(3):                                        # eager, captured, replayed
+        loss, greedy = m.forward_loss(ids, targets)
+        assert np.array_equal(greedy, logits.argmax(-1))
+        ref = oracle.cross_entropy(logits.reshape(-1, 777), targets.reshape(-1))
+        assert abs(loss - ref) <= 1e-5 * abs(ref)
+    # rows to ignore
+    t2 = targets.copy(); t2[1, :] = -100; t2[3, 5:40] = -100
+    loss2, _ = m.forward_loss(ids, t2, ignore_index=-100)
+    ref2 = oracle.cross_entropy(logits.reshape(-1, 777), t2.reshape(-1), ignore_index=-100)
+    assert abs(loss2 - ref2) <= 1e-5 * abs(ref2)
+    # greedy tokens alone; loss alone
+    none_loss, g3 = m.forward_loss(ids)
+    assert none_loss is None and np.array_equal(g3, greedy)
+    loss4, none_arg = m.forward_loss(ids, targets, want_argmax=False)
+    assert none_arg is None and loss4 == loss
+    # a target outside the vocabulary is reported at the next sync (the reference panics)
+    t5 = targets.copy(); t5[0, 0] = 777
+    from sptorch_b200.backend import HalError
+    with pytest.raises(HalError):
+        m.forward_loss(ids, t5)
+        backend.synchronize()
+    m.close()
+    # ties: every logit of a row equal -> the first column wins, as a stable descending sort has it
+    cfg0 = dict(vocab=300, d_model=64, n_layer=0, n_head=2, d_ff=128, seq_len=8)
+    p0, i0 = synth.gpt_params(cfg0, 1)
+    o, shp = i0["lm_head.weight"]
+    p0[o:o + 300 * 64] = 0.0
+    m0 = GPT(backend, 300, 64, 2, 0, 128, 8, dtype=dtype, max_batch=1)
+    m0.load_flat(p0, i0)
+    _, g0 = m0.forward_loss(np.zeros((1, 8), dtype=np.int64))
+    assert (g0 == 0).all()
+    m0.close()
+
+
+def test_lm_head_fused_host_call_matches_device_call(backend, oracle):
+    import ctypes as C
+    from sptorch_b200 import synth
+    from sptorch_b200.gpt import GPT
+    cfg = dict(vocab=1000, d_model=64, n_layer=2, n_head=1, d_ff=128, seq_len=32)
+    params, index = synth.gpt_params(cfg, 1)
+    m = GPT(backend, 1000, 64, 1, 2, 128, 32, dtype=BF16, max_batch=6)
+    m.load_flat(params, index)
+    ids = synth.randint(2, 6 * 32, 1000).reshape(6, 32).astype(np.int32)
+    targets = synth.randint(9, 6 * 32, 1000).reshape(6, 32).astype(np.int64)
+    loss, greedy = m.forward_loss(ids, targets)
+    lib = backend.lib
+    pin_ids, pin_t, pin_a = lib.sptorch_ext_alloc_pinned(ids.nbytes), lib.sptorch_ext_alloc_pinned(targets.nbytes), lib.sptorch_ext_alloc_pinned(ids.nbytes)
+    C.memmove(pin_ids, ids.ctypes.data, ids.nbytes)
+    C.memmove(pin_t, targets.ctypes.data, targets.nbytes)
+    for chunk in (6, 4, 1):
+        C.memset(pin_a, 0xff, ids.nbytes)
+        l2 = m.forward_loss_host(pin_ids, pin_t, 6, 32, pin_a, chunk)
+        got = np.ctypeslib.as_array(C.cast(pin_a, C.POINTER(C.c_int32)), shape=(6 * 32,)).copy().reshape(6, 32)
+        assert np.array_equal(got, greedy), f"chunk {chunk}"
+        assert abs(l2 - loss) <= 1e-6 * abs(loss), f"chunk {chunk}"
+    for ptr in (pin_ids, pin_t, pin_a):
+        lib.sptorch_ext_free_pinned(ptr)
+    m.close()

@@ -35,6 +35,25 @@ def test_layernorm_bf16_vs_oracle(backend, oracle, rows, dim):
     assert np.abs(out - ref).max() <= 2 ** -8 * np.abs(ref).max()      # one bf16 rounding of the output
 
 
+@pytest.mark.parametrize("rows,dim", [(1, 768), (17, 1024), (4096, 768), (4099, 768), (4111, 1024), (4100, 2048), (65536, 768)])
+def test_layernorm_bf16_pipelined_kernel_vs_oracle(backend, oracle, rows, dim):
+    """bf16 rows of 768 / 1024 / 2048 run the kernel that streams blocks of rows through shared memory with bulk asynchronous
+    copies; row counts that are not a multiple of the 16 (8) rows of a block exercise the ragged last block.  Every output
+    element against the oracle within one bf16 rounding."""
+    rng = np.random.default_rng(rows + dim)
+    x = _bf16((rng.standard_normal((rows, dim)) * 3 + 0.5).astype(np.float32))
+    g = (1 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(dim)).astype(np.float32)
+    ref = oracle.layernorm(x, g, b)
+    out = backend.layernorm(x, g, b, dtype=BF16)
+    assert out.shape == ref.shape
+    assert np.abs(out - ref).max() <= 2 ** -8 * np.abs(ref).max()
+    # rows are independent: the same rows inside a different row count (another block phase, another CTA) give the same bits
+    if rows > 3:
+        sub = backend.layernorm(x[5:4101 + 5] if rows > 5000 else x[3:], g, b, dtype=BF16)
+        assert np.array_equal(sub, out[5:4101 + 5] if rows > 5000 else out[3:])
+
+
 def test_layernorm_mean_zero_property_full_size(backend):
     # crates/nn/src/lib.rs:3239-3262 at the row-op sweep's size (65536 x 768): gamma=1, beta=0 -> row mean ~ 0, var ~ 1
     rows, dim = 65536, 768
