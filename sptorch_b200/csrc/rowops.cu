@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kRowThreads, 4) layernorm_bf16_kernel(const __
 // place, warp 1 streams finished stages out with bulk stores -- about 190 KB per SM are in flight at every moment, whatever the
 // compute warps are doing.  A compute warp owns a whole row (lane l holds the 16-byte vectors l, l + 32, ...), so the two
 // reductions are five shuffles each, and for 768-wide rows gamma / beta of the lane's columns stay in registers for the whole
-// kernel (wider rows read them through L1).  The kernel is used for every row count, so that a row's result does not depend on
+// kernel (wider rows keep them in shared memory).  The kernel is used for every row count, so that a row's result does not depend on
 // how many rows are normalised with it.
 // Same arithmetic as above (mean, then centred variance, f32 pairs), only the order of the partial sums differs.
 template <int VPL, int CW>
@@ -253,7 +253,15 @@ __global__ void __launch_bounds__(64 + 32 * CW, 1) layernorm_bf16_async_kernel(c
     const uint32_t bars = base + stages * STAGE_BYTES;           // full[stages], done[stages], empty[stages]
     const uint32_t full = bars, done = bars + 8 * stages, empty = bars + 16 * stages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (size_t)stages * STAGE_BYTES + 24 * stages);
+    // wider rows: gamma and beta wait in shared memory (8 * DIM bytes) instead of being fetched through L1 for every row
+    float* gb = reinterpret_cast<float*>(smem + (size_t)stages * STAGE_BYTES + 256);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (!GB_REGS) {
+        for (int i = threadIdx.x; i < DIM / 4; i += blockDim.x) {
+            reinterpret_cast<float4*>(gb)[i] = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+            reinterpret_cast<float4*>(gb + DIM)[i] = __ldg(reinterpret_cast<const float4*>(beta) + i);
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; s++) { mbar_init(full + 8 * s, 1); mbar_init(done + 8 * s, CW); mbar_init(empty + 8 * s, 1); }
         *abort_flag = 0;
@@ -354,8 +362,8 @@ __global__ void __launch_bounds__(64 + 32 * CW, 1) layernorm_bf16_async_kernel(c
                         for (int j = 0; j < 4; j++) { gg[j] = g[4 * v + j]; bb[j] = b[4 * v + j]; }
                     } else {
                         const int c = (v * 32 + lane) * 8;
-                        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + c)), g1 = __ldg(reinterpret_cast<const float4*>(gamma + c + 4));
-                        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + c)), b1 = __ldg(reinterpret_cast<const float4*>(beta + c + 4));
+                        const float4 g0 = *reinterpret_cast<const float4*>(gb + c), g1 = *reinterpret_cast<const float4*>(gb + c + 4);
+                        const float4 b0 = *reinterpret_cast<const float4*>(gb + DIM + c), b1 = *reinterpret_cast<const float4*>(gb + DIM + c + 4);
                         gg[0] = make_float2(g0.x, g0.y); gg[1] = make_float2(g0.z, g0.w); gg[2] = make_float2(g1.x, g1.y); gg[3] = make_float2(g1.z, g1.w);
                         bb[0] = make_float2(b0.x, b0.y); bb[1] = make_float2(b0.z, b0.w); bb[2] = make_float2(b1.x, b1.y); bb[3] = make_float2(b1.z, b1.w);
                     }
@@ -386,9 +394,10 @@ __global__ void __launch_bounds__(64 + 32 * CW, 1) layernorm_bf16_async_kernel(c
 template <int VPL, int CW>
 static int layernorm_bf16_async_launch(const __nv_bfloat16* x, const float* g, const float* b, __nv_bfloat16* out, size_t rows, float eps) {
     constexpr size_t stage = (size_t)CW * VPL * 256 * 2;
-    int stages = (int)((200 * 1024) / stage);
+    constexpr size_t gb_bytes = VPL <= 3 ? 0 : (size_t)VPL * 256 * 8;          // gamma and beta in shared memory for the wider rows
+    int stages = (int)((216 * 1024 - gb_bytes) / stage);
     if (stages > 8) stages = 8;
-    const size_t smem = (size_t)stages * stage + 24 * stages + 16;
+    const size_t smem = (size_t)stages * stage + 256 + gb_bytes;
     auto kern = layernorm_bf16_async_kernel<VPL, CW>;
     static bool attr_set = false;
     if (!attr_set) { SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_set = true; }
