@@ -110,9 +110,9 @@ int sptorch_ext_cross_entropy(const void* logits, size_t ld, const void* targets
 /* arithmetic of the f32 C-ABI contractions sptorch_matmul_f32 / sptorch_batch_matmul_f32:
  * SPT_MM_TF32 (default, tensor cores) or SPT_MM_F32 (CUDA cores, f32 FMA in k order) */
 int sptorch_ext_set_matmul_mode(int mode);
-/* tiles of the wide GEMMs: 0 (default) = one CTA per 128 x 256 tile; 1 = pairs of CTAs on 256 x 256 tiles (tcgen05 cta_group::2,
- * each SM loads half of the B tile); 2 = pairs for TF32 problems only.  Pairs give bit-identical results and measured within
- * a few percent of the one-CTA kernel either way, so they are opt-in. */
+/* tiles of the wide GEMMs: 3 (default) = pairs of CTAs on 256 x 256 tiles (tcgen05 cta_group::2, each SM loads half of the B tile)
+ * where they measured faster (TF32 problems, bf16 problems with K >= 1536, from 2048 rows up), one CTA per 128 x 256 tile elsewhere;
+ * 0 = one CTA per tile always; 1 = pairs wherever they apply; 2 = pairs for TF32 problems only.  Pairs give bit-identical results. */
 int sptorch_ext_set_gemm_pair(int mode);
 
 /* No counterpart in the reference.  sptorch_matmul_f32 for callers that must not allocate device memory (fixed,

@@ -696,11 +696,15 @@ static int max_pairs() {
     return n;
 }
 
-// 0 (default): one-CTA tiles; 1: CTA pairs wherever they apply; 2: CTA pairs for TF32 problems only.  Measured on B200, bf16:
-// 65536 x 768 -> 3072 0.246 ms (one CTA) vs 0.252 ms (pairs), 16384 x 4096 -> 4096 0.366 vs 0.395 ms; TF32: 0.512 vs 0.490 ms
-// and 0.801 vs 0.814 ms.  With loads and epilogue switched off the pair kernel's MMA stream alone ran 18 % slower than the
-// one-CTA kernel's, so the halved B traffic does not pay.  SPTORCH_B200_GEMM_PAIR in the environment sets the initial value.
-static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GEMM_PAIR"); return (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0; }()};
+// 3 (default): CTA pairs where they measured faster -- TF32 problems, and bf16 problems with K >= 1536 -- from 2048 rows up;
+// 0: one-CTA tiles only; 1: CTA pairs wherever they apply; 2: CTA pairs for TF32 problems only.  Measured on B200 (median of 10,
+// L2 flushed, one CTA vs pairs): bf16 65536 x 3072 -> 768 0.223 vs 0.203 ms, 16384 x 4096 -> 4096 0.368 vs 0.343 ms (1603 TFLOP/s),
+// 16384 x 3072 -> 768 0.072 vs 0.064 ms, but 65536 x 768 -> 3072 0.244 vs 0.244 ms and 4096 x 768 -> 768 0.0164 vs 0.0174 ms (a
+// K = 768 tile is twelve k-blocks: its fixed cost, not the operand traffic the pair halves, sets its pace); TF32 16384 x 768 -> 3072
+// 0.135 vs 0.119 ms, 16384 x 3072 -> 768 0.139 vs 0.115 ms.  (Pairs were slower everywhere while the MMAs were issued under
+// `lane == 0`: their issue path is longer, and that path was the limit.)  SPTORCH_B200_GEMM_PAIR in the environment sets the
+// initial value.
+static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GEMM_PAIR"); return (e && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : 3; }()};
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;
@@ -724,7 +728,8 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     // wide problems run on CTA pairs (each SM then loads half of the B tile); the triangular attention products do not
     int pairs = 0;
     const int pm = g_pair_mode.load();
-    if (!d.norm_axis && !d.reduce && (pm == 1 || (pm == 2 && d.mode == MM_TF32)) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
+    const bool pair_auto = pm == 3 && d.M >= 2048 && d.nb1 * d.nb2 == 1 && (d.mode == MM_TF32 || d.K >= 1536);
+    if (!d.norm_axis && !d.reduce && (pm == 1 || (pm == 2 && d.mode == MM_TF32) || pair_auto) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
     plan->pair = pairs > 0;
     plan->tiles_m = ceil_div(d.M, plan->pair ? 2 * BM : BM);
     plan->tiles_n = ceil_div(d.N, bn);
@@ -884,7 +889,7 @@ int simt_matmul_f32(const float* A, const float* B, float* C, int batch, int M, 
 static std::atomic<int> g_abi_mode{MM_TF32};
 
 extern "C" int sptorch_ext_set_gemm_pair(int mode) {
-    if (mode < 0 || mode > 2) return fail("set_gemm_pair: mode %d is not 0, 1 or 2", mode);
+    if (mode < 0 || mode > 3) return fail("set_gemm_pair: mode %d is not 0 .. 3", mode);
     g_pair_mode.store(mode);
     bump_config_epoch();
     return 0;

@@ -107,15 +107,15 @@ def test_pair_tiles_equal_single_cta_tiles(backend, oracle, M, K, N):
     ref = oracle.unary("gelu", oracle.linear(x, w, b, fast=2)) + r
     try:
         outs = {}
-        for pair in (1, 0):
+        for pair in (1, 0, 3):
             backend._check(backend.lib.sptorch_ext_set_gemm_pair(pair), "set_gemm_pair")
             outs[pair] = [backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_TF32),
                           backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_BF16),
                           backend.linear(x, w, b, mode=MM_BF16, out_dtype=F32)]
     finally:
-        backend.lib.sptorch_ext_set_gemm_pair(0)
-    for a, c in zip(outs[1], outs[0]):
-        assert np.array_equal(a, c)
+        backend.lib.sptorch_ext_set_gemm_pair(3)           # the default: pairs where they measured faster
+    for a, c, d in zip(outs[1], outs[0], outs[3]):
+        assert np.array_equal(a, c) and np.array_equal(d, c)
     assert relerr(outs[1][0], ref) <= 2e-3
     assert relerr(outs[1][1], ref) <= 2e-2
 
