@@ -572,7 +572,7 @@ def sweep_rowops(b, peaks, iters, emit=None):
     return out
 
 
-def sweep_decode(b, peaks, steps=32, emit=None):
+def sweep_decode(b, peaks, steps=32, emit=None, batches=(1, 8, 64)):
     """Incremental decode of the GPT-2-small shape through the key/value cache: `batch` sequences with 512 cached positions, one
     new token each per step.  HBM-bound: a step reads every weight once (325 MB in bf16) plus the cached keys and values."""
     from sptorch_b200.backend import BF16
@@ -580,7 +580,7 @@ def sweep_decode(b, peaks, steps=32, emit=None):
     cfg = dict(synth.CONFIGS[WORKLOAD])
     d, F, V, L = cfg["d_model"], cfg["d_ff"], cfg["vocab"], cfg["n_layer"]
     out = []
-    for batch in (1, 8, 64):
+    for batch in batches:
         model = GPT(b, V, d, cfg["n_head"], L, F, cfg["seq_len"], dtype=BF16, max_batch=batch)
         _load_timing_weights(model, cfg)
         model.enable_kv_cache(1024)
@@ -645,7 +645,11 @@ def run_sweep(args):
     if args.sweep in ("rowops", "all"):
         sweep_rowops(b, peaks, args.iters, emit)
     if args.sweep in ("decode", "all"):
-        sweep_decode(b, peaks, emit=emit)
+        if args.sweep == "decode" and args.shape:       # a single batch size and step count: "batch,steps"
+            bt, st = (int(v) for v in args.shape.split(","))
+            sweep_decode(b, peaks, steps=st, emit=emit, batches=(bt,))
+        else:
+            sweep_decode(b, peaks, emit=emit)
     b.close()
     return 0
 
@@ -799,7 +803,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--sweep", default="", choices=["", "linear", "rowops", "attention", "decode", "abi", "all"], help="standalone op sweeps (the standalone Linear and row-op sweeps) instead of the GPT step")
-    ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N")
+    ap.add_argument("--shape", default="", help="with --sweep linear: a single M,K,N; with --sweep decode: batch,steps")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
                     help="c4_gpt2s: the bench line (batch sharding); c5_1p3b / tp_check: tensor parallel over the launched ranks")

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <cstdlib>
 #include <atomic>
 #include <mutex>
 
@@ -66,6 +67,25 @@ inline void note_submit() { rt().submitted.fetch_add(1, std::memory_order_relaxe
         if (_e != cudaSuccess) return ::spt::fail("launch of %s failed: %s", name, cudaGetErrorString(_e)); \
         ::spt::note_submit();                                                              \
     } while (0)
+
+// Launch on the library stream, optionally as a programmatic dependent of the kernel before it in the stream: the grid may then
+// begin (and run whatever precedes its griddepcontrol.wait) while that kernel is still running.  Only kernels that execute
+// griddepcontrol.wait before they touch anything an earlier kernel writes may be launched with dependent = true.
+// SPTORCH_B200_PDL=0 in the environment turns every such launch into an ordinary one.
+inline bool dependent_launch_enabled() {
+    static const bool on = [] { const char* e = getenv("SPTORCH_B200_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = rt().stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = (dependent && dependent_launch_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 // Per-category device timing (CUDA events around launches on the library stream); off by default.
 enum ProfCat : int { PROF_LINEAR = 0, PROF_ATTN_GEMM = 1, PROF_SOFTMAX = 2, PROF_LAYERNORM = 3, PROF_EMBED = 4, PROF_OTHER = 5, PROF_ATTN_FUSED = 6, PROF_NCAT = 7 };

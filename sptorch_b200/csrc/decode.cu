@@ -61,21 +61,34 @@ __global__ void __launch_bounds__(kDecThreads) attention_last_token_kernel(const
 // q: [B, ld_q] (head h at columns h*hd); kc/vc: first cached row of this layer, rows of H*hd elements, sequences
 // seq_stride apart; n cached positions (the newest included); out: [B, ld_out]
 // The same function for head sizes up to 128 whose rows are 16 .. 512 bytes (a power of two): the form the decode step uses.
-// One CTA of four warps per (sequence, head).  A row of K or V is read by LPR = row bytes / 16 neighbouring lanes with one 16-byte
-// load each, so a warp fetches 32 / LPR whole rows per instruction, fully coalesced, and several positions are in flight per lane;
-// the dot product is finished with log2(LPR) shuffles.  Every row group keeps a running (maximum, sum, weighted value sum) over the
-// positions it visits (online softmax: exp(s - max) / sum exp(s - max) evaluated incrementally), the groups of a warp and then the
-// four warps are merged at the end.  Same result as the kernel above up to the order of the f32 sums.
+// One CTA of 4 or 16 warps per (sequence, head).  A row of K or V is read by LPR = row bytes / 16 neighbouring lanes with one
+// 16-byte load each, so a warp fetches 32 / LPR whole rows per instruction, fully coalesced, and four positions are in flight per
+// lane (sixteen warps cover 256 positions of 128-byte rows per turn: the walk over a 1024-position cache is four dependent
+// rounds of loads, not thirty); the dot product is finished with log2(LPR) shuffles.  Every row group keeps a running (maximum,
+// sum, weighted value sum) over the positions it visits (online softmax), the groups of a warp and then the warps are merged at
+// the end.  Same result as the kernel above up to the order of the f32 sums.
+// fresh_k / fresh_v (optional): the newest token's key / value, still in the projection output (rows of ld_fresh elements, head h
+// at columns h*hd).  The CTA copies its head's part into cache row `slot` and uses the fresh rows for that position, which
+// saves the append launch in front of the attention.
+// The first round of cache rows is requested before the programmatic-launch wait: cache rows other than `slot` were written by
+// earlier steps, only q and the fresh rows come from the kernel before this one.
 // HBM traffic: 2 * n * hd * sizeof(T) bytes per (sequence, head), read once.
-template <typename T>
-__global__ void __launch_bounds__(128) attention_last_token_rows_kernel(const T* __restrict__ q, long long ld_q, const T* __restrict__ kc,
-                                                                        const T* __restrict__ vc, T* __restrict__ out, long long ld_out, int H, int hd,
-                                                                        int n, long long seq_stride, long long row_stride, float scale,
-                                                                        const int* __restrict__ state) {
+constexpr int kRowsMaxWarps = 16;
+// NW: warps per CTA.  Four-warp CTAs are held to 80 registers so that six share an SM (888 CTA slots: the 768 (sequence, head)
+// pairs of 64 sequences x 12 heads run as one wave; at 92 registers and five per SM they made two).
+template <typename T, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token_rows_kernel(const T* __restrict__ q, long long ld_q, const T* __restrict__ kc,
+                                                                                      const T* __restrict__ vc, T* __restrict__ out, long long ld_out, int H, int hd,
+                                                                                      int n, long long seq_stride, long long row_stride, float scale,
+                                                                                      const int* __restrict__ state, const T* __restrict__ fresh_k,
+                                                                                      const T* __restrict__ fresh_v, long long ld_fresh, int slot, T* kc_w, T* vc_w) {
     constexpr int VE = 16 / (int)sizeof(T);              // elements per 16-byte segment
-    __shared__ float sm[4 * 130];                         // per warp: maximum, sum, up to 128 value sums (f32 rows of 512 bytes, bf16 rows of 256)
-    if (state) n = state[1];
+    constexpr int U = 4;                                 // positions in flight per row group
+    __shared__ float sm[NW * 130];                       // per warp: maximum, sum, up to 128 value sums (f32 rows of 512 bytes, bf16 rows of 256)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (state) { n = state[1]; slot = state[2]; }        // written before the step's first kernel was launched
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int nw = NW;
     const int lpr = hd / VE;                             // lanes per row
     const int rpi = 32 / lpr;                            // rows per warp instruction
     const int seg = lane % lpr, grp = lane / lpr;
@@ -89,15 +102,38 @@ __global__ void __launch_bounds__(128) attention_last_token_rows_kernel(const T*
             f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
         }
     };
-    float qf[VE];
-    widen(*reinterpret_cast<const uint4*>(q + (long long)b * ld_q + (long long)h * hd + seg * VE), qf);
     const T* kb = kc + (long long)b * seq_stride + (long long)h * hd + seg * VE;
     const T* vb = vc + (long long)b * seq_stride + (long long)h * hd + seg * VE;
+    const int stride = nw * rpi;
+    uint4 kr[U], vr[U];
+    auto fetch = [&](int base) {                         // dead positions read row 0 (always valid) and are discarded by visit()
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int p = base + u * stride + grp;
+            const long long pp = p < n ? p : 0;
+            kr[u] = *reinterpret_cast<const uint4*>(kb + pp * row_stride);
+            vr[u] = *reinterpret_cast<const uint4*>(vb + pp * row_stride);
+        }
+    };
+    const int first = warp * rpi;
+    if (first < n) fetch(first);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float qf[VE];
+    widen(*reinterpret_cast<const uint4*>(q + (long long)b * ld_q + (long long)h * hd + seg * VE), qf);
+    uint4 fk = make_uint4(0, 0, 0, 0), fv = fk;
+    if (fresh_k) {
+        fk = *reinterpret_cast<const uint4*>(fresh_k + (long long)b * ld_fresh + (long long)h * hd + seg * VE);
+        fv = *reinterpret_cast<const uint4*>(fresh_v + (long long)b * ld_fresh + (long long)h * hd + seg * VE);
+        if (warp == 0 && grp == 0) {
+            const long long dst = (long long)b * seq_stride + (long long)slot * row_stride + (long long)h * hd + seg * VE;
+            *reinterpret_cast<uint4*>(kc_w + dst) = fk;
+            *reinterpret_cast<uint4*>(vc_w + dst) = fv;
+        }
+    }
     float m = -INFINITY, l = 0.0f, o[VE];
 #pragma unroll
     for (int i = 0; i < VE; i++) o[i] = 0.0f;
-    const int stride = 4 * rpi;
-    auto visit = [&](uint4 kraw, uint4 vraw) {
+    auto visit = [&](uint4 kraw, uint4 vraw, bool live) {
         float kf[VE], vf[VE];
         widen(kraw, kf);
         float s = 0.0f;
@@ -105,37 +141,23 @@ __global__ void __launch_bounds__(128) attention_last_token_rows_kernel(const T*
         for (int i = 0; i < VE; i++) s += qf[i] * kf[i];
         for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
         s *= scale;
-        const float mn = fmaxf(m, s);
-        const float corr = expf(m - mn), pr = expf(s - mn);        // m = -inf on the first visit: corr = 0, nothing accumulated yet
+        const float mn = live ? fmaxf(m, s) : m;
+        const float corr = live ? expf(m - mn) : 1.0f;             // m = -inf on the first live visit: corr = 0, nothing accumulated yet
+        const float pr = live ? expf(s - mn) : 0.0f;
         widen(vraw, vf);
         l = l * corr + pr;
 #pragma unroll
         for (int i = 0; i < VE; i++) o[i] = o[i] * corr + pr * vf[i];
         m = mn;
     };
-    // The loops run on a warp-uniform base position (the shuffles inside visit() are warp-wide).  First the part where every row
-    // group has two live positions, two rows per lane in flight; then what is left, one position per group and turn, where groups
-    // past the end still take part in the shuffles with a dead value.
-    int base = warp * rpi;
-    for (; base + stride + rpi <= n; base += 2 * stride) {
-        const long long p = base + grp;
-        const uint4 k0 = *reinterpret_cast<const uint4*>(kb + p * row_stride), k1 = *reinterpret_cast<const uint4*>(kb + (p + stride) * row_stride);
-        const uint4 v0 = *reinterpret_cast<const uint4*>(vb + p * row_stride), v1 = *reinterpret_cast<const uint4*>(vb + (p + stride) * row_stride);
-        visit(k0, v0); visit(k1, v1);
-    }
-    for (; base < n; base += stride) {
-        const bool live = base + grp < n;
-        const long long pp = live ? base + grp : 0;
-        const uint4 k0 = *reinterpret_cast<const uint4*>(kb + pp * row_stride), v0 = *reinterpret_cast<const uint4*>(vb + pp * row_stride);
-        const float m_keep = m, l_keep = l;
-        float o_keep[VE];
+    // warp-uniform trip count (the shuffles inside visit() are warp-wide)
+    for (int base = first; base < n; base += U * stride) {
+        if (base != first) fetch(base);
 #pragma unroll
-        for (int i = 0; i < VE; i++) o_keep[i] = o[i];
-        visit(k0, v0);
-        if (!live) {
-            m = m_keep; l = l_keep;
-#pragma unroll
-            for (int i = 0; i < VE; i++) o[i] = o_keep[i];
+        for (int u = 0; u < U; u++) {
+            const int p = base + u * stride + grp;
+            const bool is_fresh = fresh_k != nullptr && p == slot;
+            visit(is_fresh ? fk : kr[u], is_fresh ? fv : vr[u], p < n);
         }
     }
     // merge the row groups of the warp (groups that saw no position carry m = -inf, l = 0)
@@ -154,7 +176,7 @@ __global__ void __launch_bounds__(128) attention_last_token_rows_kernel(const T*
         for (int i = 0; i < VE; i++) oo[i] = __shfl_xor_sync(0xffffffffu, o[i], off);
         merge(mo, lo, oo);
     }
-    // ... and the four warps
+    // ... and the warps
     float* mine = sm + warp * 130;
     if (grp == 0) {
         if (seg == 0) { mine[0] = m; mine[1] = l; }
@@ -163,7 +185,7 @@ __global__ void __launch_bounds__(128) attention_last_token_rows_kernel(const T*
     }
     __syncthreads();
     if (warp == 0 && grp == 0) {
-        for (int w = 1; w < 4; w++) {
+        for (int w = 1; w < nw; w++) {
             const float* other = sm + w * 130;
             float oo[VE];
 #pragma unroll
@@ -221,29 +243,43 @@ int kv_append_launch(const void* qkv, void* kc, void* vc, int B, int dl, long lo
     return 0;
 }
 
-// state / n_cap: when state is given, n is read from state[1] at run time and shared memory is sized for n_cap positions
+// true when the coalesced kernel (the one that can also take the newest token's key / value rows straight from the projection
+// output) serves this head size: rows of 16 .. 512 bytes, a power of two
+bool attention_last_token_takes_fresh(int hd, int dtype) {
+    const size_t rb = (size_t)hd * (dtype == BF16 ? 2 : 4);
+    return rb >= 16 && rb <= 512 && hd <= 128 && (rb & (rb - 1)) == 0;
+}
+
+// state / n_cap: when state is given, n and the ring slot are read from state[1] / state[2] at run time; n_cap is the cache capacity
+// fresh_k / fresh_v / ld_fresh / slot: see the kernel; dependent: launched as a programmatic dependent of the kernel before it
 int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
-                         int n, long long seq_stride, long long row_stride, int dtype, const int* state, int n_cap) {
+                         int n, long long seq_stride, long long row_stride, int dtype, const int* state, int n_cap,
+                         const void* fresh_k, const void* fresh_v, long long ld_fresh, int slot, bool dependent) {
     if (B <= 0 || H <= 0 || n <= 0) return fail("attention_last_token: empty cache or batch");
     {
         // rows of 16 .. 512 bytes, a power of two, everything 16-byte aligned: the coalesced kernel
         const size_t es = dtype == BF16 ? 2 : 4;
-        const size_t rb = (size_t)hd * es;
-        const bool pow2 = rb >= 16 && rb <= 512 && hd <= 128 && (rb & (rb - 1)) == 0;
-        const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
-                             (ld_q * es) % 16 == 0 && (ld_out * es) % 16 == 0 && (seq_stride * es) % 16 == 0 && (row_stride * es) % 16 == 0;
-        if (pow2 && aligned) {
+        const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) | reinterpret_cast<uintptr_t>(out) |
+                               reinterpret_cast<uintptr_t>(fresh_k) | reinterpret_cast<uintptr_t>(fresh_v)) & 15) == 0 &&
+                             (ld_q * es) % 16 == 0 && (ld_out * es) % 16 == 0 && (seq_stride * es) % 16 == 0 && (row_stride * es) % 16 == 0 && (ld_fresh * es) % 16 == 0;
+        if (attention_last_token_takes_fresh(hd, dtype) && aligned) {
             const float scale = 1.0f / sqrtf((float)hd);
-            if (dtype == BF16)
-                attention_last_token_rows_kernel<__nv_bfloat16><<<B * H, 128, 0, rt().stream>>>((const __nv_bfloat16*)q, ld_q, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-                                                                                            (__nv_bfloat16*)out, ld_out, H, hd, n, seq_stride, row_stride, scale, state);
-            else
-                attention_last_token_rows_kernel<float><<<B * H, 128, 0, rt().stream>>>((const float*)q, ld_q, (const float*)kc, (const float*)vc, (float*)out, ld_out, H, hd, n,
-                                                                                    seq_stride, row_stride, scale, state);
-            SPT_LAUNCH_CHECK("attention_last_token");
+            // sixteen warps per (sequence, head) when the walk is long and the pairs alone do not fill the SMs (at 92 registers a
+            // 512-thread CTA is alone on its SM: 768 of them ran a 64-sequence step in 1.38 ms against 1.0 ms with four warps each)
+            const int span = state ? n_cap : n;
+            const int threads = (span > 128 && (long long)B * H < 2ll * rt().sm_count) ? kRowsMaxWarps * 32 : 128;
+#define SPT_ROWS_LAUNCH(T_, NW_)                                                                                                                      \
+    SPT_CUDA(launch_dependent(attention_last_token_rows_kernel<T_, NW_>, dim3(B * H), dim3(NW_ * 32), 0, dependent, (const T_*)q, ld_q, (const T_*)kc,      \
+                              (const T_*)vc, (T_*)out, ld_out, H, hd, n, seq_stride, row_stride, scale, state, (const T_*)fresh_k, (const T_*)fresh_v,    \
+                              ld_fresh, slot, (T_*)const_cast<void*>(kc), (T_*)const_cast<void*>(vc)))
+            if (dtype == BF16) { if (threads == 128) SPT_ROWS_LAUNCH(__nv_bfloat16, 4); else SPT_ROWS_LAUNCH(__nv_bfloat16, kRowsMaxWarps); }
+            else { if (threads == 128) SPT_ROWS_LAUNCH(float, 4); else SPT_ROWS_LAUNCH(float, kRowsMaxWarps); }
+#undef SPT_ROWS_LAUNCH
+            note_submit();
             return 0;
         }
     }
+    if (fresh_k || fresh_v) return fail("attention_last_token: the newest token's rows can only be taken from the projection output for 16 .. 512-byte head rows");
     const size_t smem = (size_t)(kDecThreads / 32) * (hd + (state ? n_cap : n)) * sizeof(float);
     if (smem > 200 * 1024) return fail("attention_last_token: %d cached positions exceed the shared-memory score buffer", n);
     const int grid = ceil_div((long long)B * H, kDecThreads / 32);
@@ -274,5 +310,6 @@ extern "C" int sptorch_ext_attention_last_token(const void* q, const void* k_cac
     if (dtype != SPT_F32 && dtype != SPT_BF16) return fail("attention_last_token: unknown dtype %d", dtype);
     if (n == 0 || n > cache_positions) return fail("attention_last_token: n must be in 1..cache_positions");
     const long long d = (long long)(H * hd);
-    return attention_last_token(q, d, k_cache, v_cache, out, d, (int)B, (int)H, (int)hd, (int)n, (long long)cache_positions * d, d, dtype, nullptr, 0);
+    return attention_last_token(q, d, k_cache, v_cache, out, d, (int)B, (int)H, (int)hd, (int)n, (long long)cache_positions * d, d, dtype, nullptr, 0,
+                                nullptr, nullptr, 0, 0, false);
 }

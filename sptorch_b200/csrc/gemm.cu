@@ -19,6 +19,7 @@
 //               staging block -> one TMA store per chunk (the store clips at the matrix edge)
 // Bound: tensor pipe.  Algorithmic work 2*M*N*K FLOP; bytes (M*K + N*K)*s_in + M*N*s_out.
 #include "gemm.h"
+#include "epilogue_math.cuh"
 #include "sm100.cuh"
 #include "../../include/sptorch_b200_hal.h"
 #include "../../include/sptorch_b200_ext.h"
@@ -61,43 +62,6 @@ struct GemmParams {
 struct NormArgs { const float2* stats; const float* s; };
 // row reductions instead of the output (see GemmDesc::reduce): read by the REDUCE variants only
 struct ReduceArgs { float2* part; int* arg; const long long* targets; float* tgt; int parts; };
-
-__device__ __forceinline__ float gelu_exact(float x) {
-    const float k = 0.7978845608028654f;
-    float x3 = (x * x) * x;
-    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x3)));
-}
-// bf16 outputs use tanh.approx (max rel. error 2^-11, far below one bf16 ulp of the result).
-// two GELUs at once on packed f32 pairs (fma.rn.f32x2 / mul.rn.f32x2): y = hx + hx * tanh(k x (1 + 0.044715 x^2)), hx = x / 2.
-// Seven issue slots per pair instead of about sixteen; the epilogue of the GELU GEMM is bound by instruction issue.
-__device__ __forceinline__ float2 gelu_fast2(float2 x) {
-    const float2 c1 = make_float2(0.044715f, 0.044715f), one = make_float2(1.0f, 1.0f);
-    const float2 k = make_float2(0.7978845608028654f, 0.7978845608028654f), half = make_float2(0.5f, 0.5f);
-    float2 w = __ffma2_rn(__fmul2_rn(x, x), c1, one);
-    float2 u = __fmul2_rn(__fmul2_rn(x, k), w);
-    float2 t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t.x) : "f"(u.x));
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t.y) : "f"(u.y));
-    float2 hx = __fmul2_rn(x, half);
-    return __ffma2_rn(hx, t, hx);
-}
-
-// e^x through ex2.approx (relative error 2^-22); e^(-inf) = 0
-__device__ __forceinline__ float exp_fast(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
-    return y;
-}
-
-// g * sigmoid(g) (core-ops/src/lib.rs:1537-1538: s = 1 / (1 + exp(-g)), the product with x follows in the caller)
-__device__ __forceinline__ float silu_exact(float g) { return g * (1.0f / (1.0f + expf(-g))); }
-// bf16 outputs: ex2.approx + rcp.approx, relative error 2^-21, below one bf16 ulp
-__device__ __forceinline__ float silu_fast(float g) {
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-    return g * r;
-}
 
 // tile index -> (batch z, m-tile, n-tile): bands of kGroupM m-tiles, n outer / m inner inside a band
 __device__ __forceinline__ void decode_tile(int t, int tiles_m, int tiles_n, int group_m, int& z, int& tm, int& tn) {
@@ -708,6 +672,13 @@ static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GE
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;
+    if (linear_few_rows_supported(d)) {
+        plan->d = d;
+        plan->few_rows = true;
+        plan->valid = true;
+        return 0;
+    }
+    plan->few_rows = false;
     if (!gemm_supported(d, &why)) return fail("gemm: %s", why);
     plan->d = d;
     int bn = d.N <= 64 ? 64 : d.N <= 128 ? 128 : 256;
@@ -771,6 +742,7 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
 int gemm_run(const GemmPlan& pl) {
     if (!pl.valid) return fail("gemm_run: plan not prepared");
     const GemmDesc& d = pl.d;
+    if (pl.few_rows) return linear_few_rows(d);
     GemmParams prm;
     prm.C = d.C; prm.bias = d.bias; prm.R = d.R;
     prm.M = d.M; prm.N = d.N; prm.K = d.K; prm.ldc = d.ldc;

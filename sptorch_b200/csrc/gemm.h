@@ -55,6 +55,7 @@ struct GemmPlan {
     int bn = 0, tiles_m = 0, tiles_n = 0, grid = 0, group_m = 8;
     size_t smem = 0;
     bool pair = false;       // two-CTA tiles (256 x 256, cta_group::2); grid counts CTAs, two per tile worker
+    bool few_rows = false;   // M <= 64 bf16: the weight-streaming kernel of linear_few_rows.cu instead of 128-row tiles
     bool valid = false;
 };
 
@@ -63,6 +64,16 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan);
 int gemm_run(const GemmPlan& plan);
 // true when the tcgen05 path can take this problem (alignment / stride rules of TMA)
 bool gemm_supported(const GemmDesc& d, const char** why);
+
+// Linear for at most 64 input rows (a decode step), bf16: a stream over the weight rows spread over all SMs (linear_few_rows.cu).
+// gemm_plan / gemm_run route there by themselves.
+// nrm: the rows of A are normalised on the fly (kind 1: LayerNorm with gamma / beta, kind 2: RMSNorm with gamma), which saves the
+// stand-alone normalisation launch in front of a projection.  dependent: launched as a programmatic dependent of the previous
+// kernel in the stream (see launch_dependent in common.h).
+struct RowNorm { int kind = 0; const float* gamma = nullptr; const float* beta = nullptr; float eps = 0.0f; };
+bool linear_few_rows_supported(const GemmDesc& d);
+bool linear_few_rows_norm_supported(const GemmDesc& d, const RowNorm& nrm);
+int linear_few_rows(const GemmDesc& d, const RowNorm* nrm = nullptr, bool dependent = false);
 
 // CUDA-core f32 FMA matmul for shapes the TMA path cannot express and for MM_F32.
 // B is [K,N] row-major when b_is_kn, else [N,K].

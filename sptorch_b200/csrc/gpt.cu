@@ -33,7 +33,9 @@ int head_reduce_combine_launch(const float2* part, const int* arg, const float* 
                                int classes, int has_ignore, long long ignore_index, int* argmax_out, float* row_loss);
 int cross_entropy_mean_launch(float* row_loss, size_t rows);
 int attention_last_token(const void* q, long long ld_q, const void* kc, const void* vc, void* out, long long ld_out, int B, int H, int hd,
-                         int n, long long seq_stride, long long row_stride, int dtype, const int* state, int n_cap);
+                         int n, long long seq_stride, long long row_stride, int dtype, const int* state, int n_cap,
+                         const void* fresh_k, const void* fresh_v, long long ld_fresh, int slot, bool dependent);
+bool attention_last_token_takes_fresh(int hd, int dtype);
 int decode_state_launch(int* state, int pos, int n, int slot, int pos_row);
 int kv_append_launch(const void* qkv, void* kc, void* vc, int B, int dl, long long seq_stride, int slot, const int* state, int dtype);
 int embedding_sum_launch(const void* tok_w, const void* pos_w, const void* ids, void* out, size_t n_tokens, size_t T, size_t vocab, size_t dim,
@@ -902,41 +904,68 @@ int sptorch_ext_gpt_prefill(void* gp, const void* ids, int batch, int T, void* l
 // The launches of one decode step.  Everything that changes from step to step -- the token's position, the number of valid cached
 // positions, the ring slot, the row of the position table -- is read by the kernels from the device words `g->dstate`, so the same
 // sequence of launches serves every step and can be replayed as a CUDA graph.
+// One projection of a decode step: out = act(norm(x) W^T + bias) (+ or * res).  With at most 64 sequences in bf16 it is one launch
+// of the weight-streaming kernel (linear_few_rows.cu) with the normalisation applied to the rows on the fly, started as a
+// programmatic dependent of the kernel before it; otherwise the stand-alone normalisation into g->h and the tcgen05 GEMM.
+static int decode_linear(Gpt* g, const void* x, const RowNorm* nrm, const void* w, const float* bias, const void* res, void* out, int B, int K, int N,
+                         long long ldo, int epi) {
+    const sptorch_gpt_config& c = g->c;
+    if (c.dtype == SPT_BF16) {
+        GemmDesc d;
+        d.A = x; d.B = w; d.C = out; d.bias = bias; d.R = res;
+        d.M = B; d.N = N; d.K = K; d.lda = K; d.ldb = K; d.ldc = ldo;
+        d.epilogue = epi; d.mode = MM_BF16; d.out_dtype = BF16;
+        if (linear_few_rows_supported(d) && (!nrm || linear_few_rows_norm_supported(d, *nrm))) {
+            ProfScope ps(PROF_LINEAR);
+            return linear_few_rows(d, nrm, true);
+        }
+    }
+    const void* a = x;
+    if (nrm) {
+        if (nrm->kind == 2 ? rms_launch(x, nrm->gamma, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)
+                           : ln(x, nrm->gamma, nrm->beta, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)) return 1;
+        a = g->h;
+    }
+    return linear(g, a, w, bias, res, out, B, K, N, ldo, epi);
+}
+
 static int decode_launches(Gpt* g, const void* last_ids, int B, int append, void* logits) {
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, dl = g->d_loc, Fl = g->F_loc, hd = d / c.n_head, dt = c.dtype;
     const size_t es = g->es;
     const bool qwen = c.arch == SPT_ARCH_QWEN_LIKE;     // QwenLikeBlock::forward_last_token_incremental, nn/src/lib.rs:1119-1131
     const int* st = g->dstate;
-    auto norm = [&](const void* in, const float* gamma, const float* beta, void* out) {
-        return qwen ? rms_launch(in, gamma, out, (size_t)B, (size_t)d, c.eps, dt) : ln(in, gamma, beta, out, (size_t)B, (size_t)d, c.eps, dt);
+    auto norm_of = [&](const float* gamma, const float* beta) {
+        RowNorm n; n.kind = qwen ? 2 : 1; n.gamma = gamma; n.beta = qwen ? nullptr : beta; n.eps = c.eps; return n;
     };
     { ProfScope ps(PROF_EMBED);
       if (embedding_sum_launch(g->tok, qwen ? nullptr : g->pos, last_ids, g->x, (size_t)B, 1, (size_t)c.vocab, (size_t)d, dt, st + 3)) return 1; }
     void* x = g->x;
     const long long row = dl, seq = (long long)g->cache_ctx * dl;
+    const bool fresh = append && attention_last_token_takes_fresh(hd, dt);     // the attention kernel appends the token's key / value itself
     for (int l = 0; l < c.n_layer; l++) {
         const Layer& w = g->L[l];
         const size_t lay = (size_t)l * c.max_batch * g->cache_ctx * dl * es;
         uint8_t* kc = (uint8_t*)g->kcache + lay;
         uint8_t* vc = (uint8_t*)g->vcache + lay;
-        if (norm(x, w.ln1g, w.ln1b, g->h)) return 1;
-        if (linear(g, g->h, w.wqkv, nullptr, nullptr, g->dq, B, d, 3 * dl, 3 * dl, EPI_NONE)) return 1;     // [q | k | v] of the token
+        const RowNorm n1 = norm_of(w.ln1g, w.ln1b), n2 = norm_of(w.ln2g, w.ln2b);
+        if (decode_linear(g, x, &n1, w.wqkv, nullptr, nullptr, g->dq, B, d, 3 * dl, 3 * dl, EPI_NONE)) return 1;     // [q | k | v] of the token
         // the query (and the key about to be cached) are rotated to the token's absolute position (nn/src/lib.rs:718-721, 678-680)
         if (qwen) { ProfScope ps(PROF_OTHER); if (rope_launch(g->dq, B, 1, 2 * g->H_loc, hd, 3 * dl, c.rope_base, 0, dt, st + 0)) return 1; }
-        if (append) { ProfScope ps(PROF_OTHER); if (kv_append_launch(g->dq, kc, vc, B, dl, seq, 0, st, dt)) return 1; }      // one cache row per sequence and layer
+        if (append && !fresh) { ProfScope ps(PROF_OTHER); if (kv_append_launch(g->dq, kc, vc, B, dl, seq, 0, st, dt)) return 1; }      // one cache row per sequence and layer
         { ProfScope ps(PROF_ATTN_FUSED);
-          if (attention_last_token(g->dq, 3 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, g->cache_ctx, seq, row, dt, st, g->cache_ctx)) return 1; }
-        if (linear(g, g->ao, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
-        if (norm(x, w.ln2g, w.ln2b, g->h)) return 1;
+          const uint8_t* dq = (const uint8_t*)g->dq;
+          if (attention_last_token(g->dq, 3 * dl, kc, vc, g->ao, dl, B, g->H_loc, hd, g->cache_ctx, seq, row, dt, st, g->cache_ctx,
+                                   fresh ? dq + (size_t)dl * es : nullptr, fresh ? dq + (size_t)2 * dl * es : nullptr, 3 * dl, 0, true)) return 1; }
+        if (decode_linear(g, g->ao, nullptr, w.wo, nullptr, x, x, B, dl, d, d, EPI_NONE)) return 1;
         if (qwen) {
-            if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_NONE)) return 1;
-            if (linear(g, g->h, w.wg, w.bg, g->f, g->f, B, d, Fl, Fl, EPI_SWIGLU)) return 1;
-        } else if (linear(g, g->h, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_GELU)) return 1;
-        if (linear(g, g->f, w.w2, w.b2, x, x, B, Fl, d, d, EPI_NONE)) return 1;
+            if (decode_linear(g, x, &n2, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_NONE)) return 1;
+            if (decode_linear(g, x, &n2, w.wg, w.bg, g->f, g->f, B, d, Fl, Fl, EPI_SWIGLU)) return 1;
+        } else if (decode_linear(g, x, &n2, w.w1, w.b1, nullptr, g->f, B, d, Fl, Fl, EPI_GELU)) return 1;
+        if (decode_linear(g, g->f, nullptr, w.w2, w.b2, x, x, B, Fl, d, d, EPI_NONE)) return 1;
     }
-    if (norm(x, g->lnfg, g->lnfb, g->h)) return 1;
-    return linear(g, g->h, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE);
+    const RowNorm nf = norm_of(g->lnfg, g->lnfb);
+    return decode_linear(g, x, &nf, g->head, nullptr, nullptr, logits, B, d, c.vocab, (long long)g->ldl, EPI_NONE);
 }
 
 int sptorch_ext_gpt_decode(void* gp, const void* last_ids, int batch, int append, void* logits) {

@@ -68,6 +68,65 @@ def test_linear_fused_epilogues(backend, oracle):
     assert relerr(backend.linear(x, w, None, alpha=0.5, mode=MM_TF32), 0.5 * oracle.linear(x, w, None, fast=2)) <= 2e-3
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("K,N", [(768, 768), (768, 2304), (3072, 768), (256, 50257 // 8), (96, 40)])
+def test_linear_with_few_rows_vs_oracle(backend, oracle, M, K, N):
+    """At most 64 input rows in bf16 (the projections of a decode step) run the weight-streaming kernel instead of 128-row
+    tiles: against the oracle on the same bf16-rounded operands (only the output rounding remains), with the fused epilogues,
+    and exactly on one-hot rows, where out[m, n] must be W[n, k_m]: every k position of an activation row has to meet the same
+    k position of every weight row, ragged row and column counts included."""
+    rng = np.random.default_rng(1000 * M + K + N)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((N, K))).astype(np.float32)
+    b = (0.01 * rng.standard_normal(N)).astype(np.float32)
+    r = rng.standard_normal((M, N)).astype(np.float32)
+    refb = oracle.linear(_bf16(x), _bf16(w), b, fast=2)
+    assert relerr(backend.linear(x, w, b, mode=MM_BF16), refb) <= 2 ** -8 * 1.1
+    assert relerr(backend.linear(x, w, b, mode=MM_BF16), oracle.linear(x, w, b, fast=2)) <= 2e-2
+    ref = oracle.unary("gelu", refb) + _bf16(r)
+    assert relerr(backend.linear(x, w, b, residual=r, epilogue=EPI_GELU, mode=MM_BF16), ref) <= 2 ** -8 * 1.1
+    assert relerr(backend.linear(x, w, None, alpha=0.5, mode=MM_BF16), 0.5 * oracle.linear(_bf16(x), _bf16(w), None, fast=2)) <= 2 ** -8 * 1.1
+    ks = rng.integers(0, K, M)
+    onehot = np.zeros((M, K), np.float32)
+    onehot[np.arange(M), ks] = 1.0
+    wi = rng.integers(-64, 65, (N, K)).astype(np.float32)
+    assert np.array_equal(backend.linear(onehot, wi, mode=MM_BF16), wi[:, ks].T)
+
+
+def test_linear_with_few_rows_kernel_up_to_64_rows():
+    """Row counts 33 .. 64 take the tcgen05 tiles by default; SPTORCH_B200_FEW_ROWS=64 (read once per process, hence the child
+    process) sends them through the weight-streaming kernel's four-row-group variants, which must agree with the oracle too."""
+    import os, subprocess, sys, textwrap
+    code = textwrap.dedent("""
+        import numpy as np
+        from sptorch_b200.backend import FfiBackend, MM_BF16, EPI_GELU, bf16_bits_to_f32, f32_to_bf16_bits
+        from oracle import binding as oracle
+        b = FfiBackend.load()
+        r16 = lambda x: bf16_bits_to_f32(f32_to_bf16_bits(x)).reshape(np.shape(x))
+        rel = lambda a, r: float(np.linalg.norm(a - r) / np.linalg.norm(r))
+        for M, K, N in [(33, 768, 768), (64, 768, 2304), (64, 3072, 768), (48, 256, 6282)]:
+            rng = np.random.default_rng(M + K + N)
+            x = rng.standard_normal((M, K)).astype(np.float32)
+            w = (0.02 * rng.standard_normal((N, K))).astype(np.float32)
+            bias = (0.01 * rng.standard_normal(N)).astype(np.float32)
+            res = rng.standard_normal((M, N)).astype(np.float32)
+            ref = oracle.linear(r16(x), r16(w), bias, fast=2)
+            assert rel(b.linear(x, w, bias, mode=MM_BF16), ref) <= 2 ** -8 * 1.1
+            assert rel(b.linear(x, w, bias, residual=res, epilogue=EPI_GELU, mode=MM_BF16), oracle.unary("gelu", ref) + r16(res)) <= 2 ** -8 * 1.1
+            ks = rng.integers(0, K, M)
+            onehot = np.zeros((M, K), np.float32)
+            onehot[np.arange(M), ks] = 1.0
+            wi = rng.integers(-64, 65, (N, K)).astype(np.float32)
+            assert np.array_equal(b.linear(onehot, wi, mode=MM_BF16), wi[:, ks].T)
+        b.close()
+        print("ok")
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SPTORCH_B200_FEW_ROWS="64", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
+
+
 def test_linear_is_linear_at_full_size(backend):
     """Size-independent property at a shape of the standalone Linear sweep (M 4096, K 768, N 3072): f(x1 + x2) = f(x1) + f(x2) and
     integer-valued operands give exact integers."""
