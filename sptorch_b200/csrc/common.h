@@ -76,14 +76,24 @@ inline bool dependent_launch_enabled() {
     static const bool on = [] { const char* e = getenv("SPTORCH_B200_PDL"); return !(e && e[0] == '0'); }();
     return on;
 }
+// cluster: CTAs per thread-block cluster along x (1 = none; the grid's x extent must be a multiple of it).
 template <typename... KArgs, typename... Args>
-cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, bool dependent, Args... args) {
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, bool dependent, int cluster, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = rt().stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = (dependent && dependent_launch_enabled()) ? 1 : 0;
+    cudaLaunchAttribute at[2];
+    int na = 0;
+    if (dependent && dependent_launch_enabled()) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (cluster > 1) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = (unsigned)cluster; at[na].val.clusterDim.y = 1; at[na].val.clusterDim.z = 1;
+        na++;
+    }
+    cfg.attrs = at; cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 

@@ -9,6 +9,7 @@
 #include "common.h"
 #include "../../include/sptorch_b200_ext.h"
 #include <math.h>
+#include <cooperative_groups.h>
 
 namespace spt {
 
@@ -81,9 +82,10 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
                                                                                       const T* __restrict__ vc, T* __restrict__ out, long long ld_out, int H, int hd,
                                                                                       int n, long long seq_stride, long long row_stride, float scale,
                                                                                       const int* __restrict__ state, const T* __restrict__ fresh_k,
-                                                                                      const T* __restrict__ fresh_v, long long ld_fresh, int slot, T* kc_w, T* vc_w) {
+                                                                                      const T* __restrict__ fresh_v, long long ld_fresh, int slot, T* kc_w, T* vc_w, int splits) {
     constexpr int VE = 16 / (int)sizeof(T);              // elements per 16-byte segment
     constexpr int U = 4;                                 // positions in flight per row group
+    __shared__ float res[132];                           // this CTA's merged (maximum, sum, value sums): read by the cluster's first CTA
     __shared__ float sm[NW * 130];                       // per warp: maximum, sum, up to 128 value sums (f32 rows of 512 bytes, bf16 rows of 256)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (state) { n = state[1]; slot = state[2]; }        // written before the step's first kernel was launched
@@ -92,7 +94,10 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
     const int lpr = hd / VE;                             // lanes per row
     const int rpi = 32 / lpr;                            // rows per warp instruction
     const int seg = lane % lpr, grp = lane / lpr;
-    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    // a cluster of `splits` CTAs shares one (sequence, head): CTA r of it walks the r-th part of the positions
+    const int pair = blockIdx.x / splits, rank = blockIdx.x % splits;
+    const int b = pair / H, h = pair % H;
+    const int part = (n + splits - 1) / splits, lo = rank * part, hi = min(n, lo + part);
     auto widen = [](uint4 raw, float (&f)[VE]) {
         if constexpr (sizeof(T) == 2) {
             const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -110,13 +115,13 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int p = base + u * stride + grp;
-            const long long pp = p < n ? p : 0;
+            const long long pp = p < hi ? p : 0;
             kr[u] = *reinterpret_cast<const uint4*>(kb + pp * row_stride);
             vr[u] = *reinterpret_cast<const uint4*>(vb + pp * row_stride);
         }
     };
-    const int first = warp * rpi;
-    if (first < n) fetch(first);
+    const int first = lo + warp * rpi;
+    if (first < hi) fetch(first);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     float qf[VE];
     widen(*reinterpret_cast<const uint4*>(q + (long long)b * ld_q + (long long)h * hd + seg * VE), qf);
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
     if (fresh_k) {
         fk = *reinterpret_cast<const uint4*>(fresh_k + (long long)b * ld_fresh + (long long)h * hd + seg * VE);
         fv = *reinterpret_cast<const uint4*>(fresh_v + (long long)b * ld_fresh + (long long)h * hd + seg * VE);
-        if (warp == 0 && grp == 0) {
+        if (rank == 0 && warp == 0 && grp == 0) {
             const long long dst = (long long)b * seq_stride + (long long)slot * row_stride + (long long)h * hd + seg * VE;
             *reinterpret_cast<uint4*>(kc_w + dst) = fk;
             *reinterpret_cast<uint4*>(vc_w + dst) = fv;
@@ -151,13 +156,13 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
         m = mn;
     };
     // warp-uniform trip count (the shuffles inside visit() are warp-wide)
-    for (int base = first; base < n; base += U * stride) {
+    for (int base = first; base < hi; base += U * stride) {
         if (base != first) fetch(base);
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int p = base + u * stride + grp;
             const bool is_fresh = fresh_k != nullptr && p == slot;
-            visit(is_fresh ? fk : kr[u], is_fresh ? fv : vr[u], p < n);
+            visit(is_fresh ? fk : kr[u], is_fresh ? fv : vr[u], p < hi);
         }
     }
     // merge the row groups of the warp (groups that saw no position carry m = -inf, l = 0)
@@ -192,6 +197,29 @@ __global__ void __launch_bounds__(NW * 32, NW == 4 ? 6 : 1) attention_last_token
             for (int i = 0; i < VE; i++) oo[i] = other[2 + seg * VE + i];
             merge(other[0], other[1], oo);
         }
+    }
+    if (splits > 1) {
+        // the parts meet in the first CTA of the cluster, which reads the others' results through distributed shared memory
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        if (warp == 0 && grp == 0) {
+            if (seg == 0) { res[0] = m; res[1] = l; }
+#pragma unroll
+            for (int i = 0; i < VE; i++) res[2 + seg * VE + i] = o[i];
+        }
+        cluster.sync();
+        if (rank == 0 && warp == 0 && grp == 0) {
+            for (int r = 1; r < splits; r++) {
+                const float* other = cluster.map_shared_rank(res, r);
+                float oo[VE];
+#pragma unroll
+                for (int i = 0; i < VE; i++) oo[i] = other[2 + seg * VE + i];
+                merge(other[0], other[1], oo);
+            }
+        }
+        cluster.sync();                                  // no CTA leaves while its shared memory may still be read
+    }
+    if (rank == 0 && warp == 0 && grp == 0) {
         const float inv = 1.0f / l;
         T* op = out + (long long)b * ld_out + (long long)h * hd + seg * VE;
         uint4 raw;
@@ -264,14 +292,30 @@ int attention_last_token(const void* q, long long ld_q, const void* kc, const vo
                              (ld_q * es) % 16 == 0 && (ld_out * es) % 16 == 0 && (seq_stride * es) % 16 == 0 && (row_stride * es) % 16 == 0 && (ld_fresh * es) % 16 == 0;
         if (attention_last_token_takes_fresh(hd, dtype) && aligned) {
             const float scale = 1.0f / sqrtf((float)hd);
-            // sixteen warps per (sequence, head) when the walk is long and the pairs alone do not fill the SMs (at 92 registers a
-            // 512-thread CTA is alone on its SM: 768 of them ran a 64-sequence step in 1.38 ms against 1.0 ms with four warps each)
+            // Few (sequence, head) pairs: a cluster of up to eight CTAs shares each pair, with four or sixteen warps per CTA -- whichever
+            // combination walks the cache in the fewest dependent rounds of loads while all CTAs are resident at once (a 16-warp CTA
+            // is alone on its SM at 90 registers, six 4-warp CTAs share one).  One sequence of 12 heads: 48 CTAs of 16 warps, one
+            // round; 8 sequences: 96 CTAs of 16 warps, no split; 64 sequences: 768 CTAs of 4 warps, no split.
             const int span = state ? n_cap : n;
-            const int threads = (span > 128 && (long long)B * H < 2ll * rt().sm_count) ? kRowsMaxWarps * 32 : 128;
+            const long long pairs = (long long)B * H;
+            const int per_warp_round = (32 / (hd / (16 / (int)es))) * 4;      // rows per warp instruction x positions in flight
+            int splits = 1, threads = 128, best = INT32_MAX;
+            for (int sp = 1; sp <= 8; sp *= 2)
+                for (int nw = 4; nw <= kRowsMaxWarps; nw *= 4) {
+                    const long long ctas = pairs * sp, cap = (long long)rt().sm_count * (nw == 4 ? 6 : 1);
+                    if (ctas > cap && !(sp == 1 && nw == 4)) continue;
+                    const int rounds = ceil_div(span, (long long)sp * nw * per_warp_round);
+                    // a round of loads costs about as much as 1.3 doublings of the cluster size (measured at 8 sequences x 12 heads over
+                    // a 1024-position cache: 96 CTAs of 16 warps, four rounds, 0.411 ms per step; 96 clusters of eight 4-warp CTAs, two
+                    // rounds, 0.443 ms)
+                    const int log2sp = sp == 1 ? 0 : sp == 2 ? 1 : sp == 4 ? 2 : 3;
+                    const int score = rounds * 8 + (nw == 4 ? 0 : 2) + 6 * log2sp;
+                    if (score < best) { best = score; splits = sp; threads = nw * 32; }
+                }
 #define SPT_ROWS_LAUNCH(T_, NW_)                                                                                                                      \
-    SPT_CUDA(launch_dependent(attention_last_token_rows_kernel<T_, NW_>, dim3(B * H), dim3(NW_ * 32), 0, dependent, (const T_*)q, ld_q, (const T_*)kc,      \
-                              (const T_*)vc, (T_*)out, ld_out, H, hd, n, seq_stride, row_stride, scale, state, (const T_*)fresh_k, (const T_*)fresh_v,    \
-                              ld_fresh, slot, (T_*)const_cast<void*>(kc), (T_*)const_cast<void*>(vc)))
+    SPT_CUDA(launch_dependent(attention_last_token_rows_kernel<T_, NW_>, dim3(B * H * splits), dim3(NW_ * 32), 0, dependent, splits, (const T_*)q, ld_q,   \
+                              (const T_*)kc, (const T_*)vc, (T_*)out, ld_out, H, hd, n, seq_stride, row_stride, scale, state, (const T_*)fresh_k,         \
+                              (const T_*)fresh_v, ld_fresh, slot, (T_*)const_cast<void*>(kc), (T_*)const_cast<void*>(vc), splits))
             if (dtype == BF16) { if (threads == 128) SPT_ROWS_LAUNCH(__nv_bfloat16, 4); else SPT_ROWS_LAUNCH(__nv_bfloat16, kRowsMaxWarps); }
             else { if (threads == 128) SPT_ROWS_LAUNCH(float, 4); else SPT_ROWS_LAUNCH(float, kRowsMaxWarps); }
 #undef SPT_ROWS_LAUNCH

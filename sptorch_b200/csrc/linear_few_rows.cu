@@ -38,6 +38,10 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Every CTA normalises all M rows itself: for a few rows that is noise, at 64 rows it cost more than the launch it saves
+// (decode step of a 12-layer, 768-wide model at 64 sequences: 2.30 ms with, 1.0 ms without).
+constexpr int kNormMaxRows = 16;
+
 // Programmatic dependent launch: a kernel launched with launch_dependent() may start while its predecessor in the stream still
 // runs.  pdl_release() lets the successor's CTAs be scheduled as soon as every CTA of this grid has called it (or exited);
 // pdl_acquire() returns once the predecessor grid has completed and its writes are visible.  Everything a kernel does before
@@ -101,28 +105,43 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
     const long long a_ld = NORM ? (long long)(K + 8) : lda;
     const __nv_bfloat16* a_base = NORM ? reinterpret_cast<const __nv_bfloat16*>(dyn) : A;
     if constexpr (NORM) {
-        const int nvec = K >> 3;
-        for (int r = warp; r < M; r += kWarps) {
+        // Warps are dealt over (row, part of the row): eight rows or more, one warp per row; a single row, eight warps on its eighths.
+        // The partial sums of a row's parts meet in shared memory.
+        __shared__ float part[kNormMaxRows][kWarps], part2[kNormMaxRows][kWarps];
+        const int P = M >= 8 ? 1 : M >= 4 ? 2 : M >= 2 ? 4 : 8, RP = kWarps / P;
+        const int my_p = warp % P, my_r = warp / P;
+        const int nvec = K >> 3, per = (nvec + P - 1) / P;
+        const int c_begin = my_p * per, c_end = min(nvec, c_begin + per);
+        const bool ln = nrm.kind == 1;
+#pragma unroll 1
+        for (int r = my_r; r < M; r += RP) {
             const uint4* src = reinterpret_cast<const uint4*>(A + (long long)r * lda);
             uint4* row = reinterpret_cast<uint4*>(dyn + (size_t)r * (K + 8) * 2);
-            float sum = 0.0f, sq = 0.0f;
-            for (int c = lane; c < nvec; c += 32) {
+            float acc1 = 0.0f;                                      // LayerNorm: sum; RMSNorm: sum of squares
+            for (int c = c_begin + lane; c < c_end; c += 32) {
                 const uint4 d = src[c];
                 row[c] = d;
                 const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const float lo = __uint_as_float(wd[j] << 16), hi = __uint_as_float(wd[j] & 0xffff0000u);
-                    sum += lo + hi; sq += lo * lo + hi * hi;
+                    acc1 += ln ? lo + hi : lo * lo + hi * hi;
                 }
             }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) { sum += __shfl_xor_sync(0xffffffffu, sum, o); sq += __shfl_xor_sync(0xffffffffu, sq, o); }
-            float mean = 0.0f, inv;
-            if (nrm.kind == 1) {
-                mean = sum / (float)K;
-                float var = 0.0f;                                   // centred second pass over the copy in shared memory
-                for (int c = lane; c < nvec; c += 32) {
+            for (int o = 16; o > 0; o >>= 1) acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+            if (lane == 0) part[r][my_p] = acc1;
+        }
+        __syncthreads();
+        if (ln) {
+#pragma unroll 1
+            for (int r = my_r; r < M; r += RP) {
+                float tot = 0.0f;
+                for (int q = 0; q < P; q++) tot += part[r][q];
+                const float mean = tot / (float)K;
+                const uint4* row = reinterpret_cast<const uint4*>(dyn + (size_t)r * (K + 8) * 2);
+                float var = 0.0f;                                   // centred second pass over this warp's part of the copy in shared memory
+                for (int c = c_begin + lane; c < c_end; c += 32) {
                     const uint4 d = row[c];
                     const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
@@ -133,17 +152,24 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
-                inv = 1.0f / sqrtf(var / (float)K + nrm.eps);
-            } else {
-                inv = 1.0f / sqrtf(sq / (float)K + nrm.eps);
+                if (lane == 0) part2[r][my_p] = var;
             }
-            for (int c = lane; c < nvec; c += 32) {
+            __syncthreads();
+        }
+#pragma unroll 1
+        for (int r = my_r; r < M; r += RP) {
+            float tot = 0.0f, tot2 = 0.0f;
+            for (int q = 0; q < P; q++) { tot += part[r][q]; tot2 += part2[r][q]; }
+            const float mean = ln ? tot / (float)K : 0.0f;
+            const float inv = 1.0f / sqrtf((ln ? tot2 : tot) / (float)K + nrm.eps);
+            uint4* row = reinterpret_cast<uint4*>(dyn + (size_t)r * (K + 8) * 2);
+            for (int c = c_begin + lane; c < c_end; c += 32) {
                 const uint4 d = row[c];
                 const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
                 const float4 g0 = __ldg(reinterpret_cast<const float4*>(nrm.gamma + 8 * c)), g1 = __ldg(reinterpret_cast<const float4*>(nrm.gamma + 8 * c + 4));
                 const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
                 float bb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                if (nrm.kind == 1) {
+                if (ln) {
                     const float4 b0 = __ldg(reinterpret_cast<const float4*>(nrm.beta + 8 * c)), b1 = __ldg(reinterpret_cast<const float4*>(nrm.beta + 8 * c + 4));
                     bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
                 }
@@ -153,7 +179,7 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
                 for (int j = 0; j < 4; j++) {
                     const float lo = __uint_as_float(wd[j] << 16), hi = __uint_as_float(wd[j] & 0xffff0000u);
                     float y0, y1;
-                    if (nrm.kind == 1) { y0 = fmaf(gg[2 * j], (lo - mean) * inv, bb[2 * j]); y1 = fmaf(gg[2 * j + 1], (hi - mean) * inv, bb[2 * j + 1]); }
+                    if (ln) { y0 = fmaf(gg[2 * j], (lo - mean) * inv, bb[2 * j]); y1 = fmaf(gg[2 * j + 1], (hi - mean) * inv, bb[2 * j + 1]); }
                     else { y0 = lo * inv * gg[2 * j]; y1 = hi * inv * gg[2 * j + 1]; }
                     oh[j] = __floats2bfloat162_rn(y0, y1);
                 }
@@ -211,9 +237,6 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
 }
 
 constexpr size_t kNormSmemLimit = 160 * 1024;
-// Every CTA normalises all M rows: up to two rows per warp that is noise, at 64 rows it cost more than the launch it saves
-// (decode step of a 12-layer, 768-wide model at 64 sequences: 2.30 ms with, 1.0 ms without).
-constexpr int kNormMaxRows = 16;
 size_t norm_smem(const GemmDesc& d) { return (size_t)d.M * (d.K + 8) * 2; }
 
 template <int MT, int NT, bool NORM>
@@ -226,7 +249,7 @@ int launch(const GemmDesc& d, const RowNorm& nrm, bool dependent) {
         if (!granted) { SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNormSmemLimit)); granted = true; }
     }
     const int grid = ceil_div(d.N, NT * 8);
-    SPT_CUDA(launch_dependent(kern, dim3(grid), dim3(kWarps * 32), smem, dependent,
+    SPT_CUDA(launch_dependent(kern, dim3(grid), dim3(kWarps * 32), smem, dependent, 1,
                               static_cast<const __nv_bfloat16*>(d.A), d.lda, static_cast<const __nv_bfloat16*>(d.B), d.ldb, static_cast<__nv_bfloat16*>(d.C), d.ldc,
                               d.bias, static_cast<const __nv_bfloat16*>(d.R), d.M, d.N, d.K, d.alpha, d.epilogue, nrm));
     note_submit();
@@ -241,15 +264,19 @@ int dispatch(const GemmDesc& d, const RowNorm& nrm, bool dependent) {
     int nt = 1;
     if (ceil_div(d.N, 16) >= want) nt = 2;
     if (mt <= 2 && ceil_div(d.N, 32) >= want) nt = 4;
-    switch (mt * 10 + nt) {
-        case 11: return launch<1, 1, NORM>(d, nrm, dependent);
-        case 12: return launch<1, 2, NORM>(d, nrm, dependent);
-        case 14: return launch<1, 4, NORM>(d, nrm, dependent);
-        case 21: return launch<2, 1, NORM>(d, nrm, dependent);
-        case 22: return launch<2, 2, NORM>(d, nrm, dependent);
-        case 24: return launch<2, 4, NORM>(d, nrm, dependent);
-        case 41: return launch<4, 1, NORM>(d, nrm, dependent);
-        default: return launch<4, 2, NORM>(d, nrm, dependent);
+    if constexpr (NORM) {            // at most kNormMaxRows = 16 rows: one row group
+        return nt == 1 ? launch<1, 1, true>(d, nrm, dependent) : nt == 2 ? launch<1, 2, true>(d, nrm, dependent) : launch<1, 4, true>(d, nrm, dependent);
+    } else {
+        switch (mt * 10 + nt) {
+            case 11: return launch<1, 1, false>(d, nrm, dependent);
+            case 12: return launch<1, 2, false>(d, nrm, dependent);
+            case 14: return launch<1, 4, false>(d, nrm, dependent);
+            case 21: return launch<2, 1, false>(d, nrm, dependent);
+            case 22: return launch<2, 2, false>(d, nrm, dependent);
+            case 24: return launch<2, 4, false>(d, nrm, dependent);
+            case 41: return launch<4, 1, false>(d, nrm, dependent);
+            default: return launch<4, 2, false>(d, nrm, dependent);
+        }
     }
 }
 

@@ -12,7 +12,11 @@ from sptorch_b200.gpt import GPT
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("B,H,hd,P,n", [(1, 2, 4, 6, 3), (3, 4, 32, 64, 64), (2, 12, 64, 256, 200), (2, 2, 128, 40, 1)])
+# the later cases spread one (sequence, head) pair over a cluster of CTAs (few pairs, long caches): parts of unequal length, parts
+# that are empty (n far below the capacity is a property of the graph-replayed step, here n == what the launch sees)
+@pytest.mark.parametrize("B,H,hd,P,n", [(1, 2, 4, 6, 3), (3, 4, 32, 64, 64), (2, 12, 64, 256, 200), (2, 2, 128, 40, 1),
+                                        (1, 12, 64, 1024, 531), (8, 12, 64, 1024, 700), (1, 2, 64, 2048, 2048), (1, 1, 128, 300, 257),
+                                        (1, 3, 64, 1024, 5), (2, 1, 32, 4096, 4001)])
 def test_attention_last_token_vs_oracle(backend, oracle, B, H, hd, P, n):
     rng = np.random.default_rng(P + n)
     d = H * hd
@@ -32,6 +36,23 @@ def _model(backend, cfg, dtype, max_batch, params, index):
     m = GPT(backend, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=dtype, max_batch=max_batch)
     m.load_flat(params, index)
     return m
+
+
+@pytest.mark.parametrize("dtype,tol", [(F32, 2e-3), (BF16, 3e-2)])
+def test_decode_over_a_long_cache_matches_full_forward(backend, dtype, tol):
+    """A 512-position cache with two heads: the graph-replayed step launches the last-token attention as clusters of CTAs sized
+    for the capacity while the number of valid positions (304, then growing) is read on the device, so some parts are empty.
+    Every appended token's logits equal the row of the full forward at its position."""
+    cfg = dict(vocab=96, d_model=128, n_layer=2, n_head=2, d_ff=256, seq_len=512)
+    params, index = synth.gpt_params(cfg, 11, randomize_affine=True)
+    m = _model(backend, cfg, dtype, 2, params, index)
+    m.enable_kv_cache(512)
+    ids = synth.randint(17, 2 * 312, 96).reshape(2, 312)
+    full = m.forward(ids)                                          # causal: row t is the last row of the forward over ids[:, :t + 1]
+    m.prefill_kv_cache(ids[:, :304])
+    for t in range(304, 312):
+        step = m.append_and_decode(ids[:, t])
+        assert np.abs(step - full[:, t]).max() <= tol * np.abs(full).max(), t
 
 
 # The reference asserts 1e-4 between its two exact-f32 paths.  Here the full forward contracts Q K^T and P V on the tensor
