@@ -674,6 +674,164 @@ __global__ void __launch_bounds__(kRowThreads, sizeof(T) == 4 ? 4 : 3) causal_so
     }
 }
 
+// bf16 causal softmax for T = 256 / 512 / 1024 / 2048 with the memory traffic taken off the compute warps (the structure of
+// layernorm_bf16_async_kernel): one CTA per SM, a ring of shared-memory stages of 16 rows; warp 0 streams in, per row, only the
+// live prefix (i + 1 scores, rounded up to 16 bytes) with one bulk asynchronous copy each, sixteen compute warps normalise one
+// row each in place and fill the dead part with zeros, warp 1 streams whole stages out with one bulk store.  The register
+// kernel above reaches 0.65 of the copy bandwidth on bf16 rows (a warp has one or two rows' loads in flight and then computes);
+// here the copies of up to ~190 KB per SM are in flight whatever the compute warps do.
+// Same arithmetic as causal_row<bf16>: 2^x on the special-function unit, e * (1 / sum).
+template <int VPL, int CW>
+__global__ void __launch_bounds__(64 + 32 * CW, 1) causal_softmax_bf16_async_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                                            size_t rows, float scale, int stages, uint32_t* status) {
+    using namespace sm100;
+    constexpr int T = VPL * 256;                   // 32 lanes x VPL vectors x 8 elements
+    constexpr int R = CW;                          // rows per stage: one per compute warp (T is a multiple of R: a stage never spans two matrices)
+    constexpr uint32_t ROW_BYTES = T * 2, STAGE_BYTES = R * ROW_BYTES;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t base = smem_u32(smem);
+    const uint32_t bars = base + stages * STAGE_BYTES;           // full[stages], done[stages], empty[stages]
+    const uint32_t full = bars, done = bars + 8 * stages, empty = bars + 16 * stages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (size_t)stages * STAGE_BYTES + 24 * stages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; s++) { mbar_init(full + 8 * s, 1); mbar_init(done + 8 * s, CW); mbar_init(empty + 8 * s, 1); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const size_t n_tiles = (rows + R - 1) / R;
+    if (warp == 0) {
+        // ---- loads: lane l fetches the live prefix of row l of the stage ----
+        uint32_t i = 0;
+        for (size_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            if (!mbar_wait(empty + 8 * s, ph ^ 1, abort_flag, status, kErrProducerWait)) break;
+            const size_t r = tile * R + lane;
+            const bool live = lane < R && r < rows;
+            const uint32_t pos = (uint32_t)(r % T);
+            const uint32_t bytes = live ? ((pos + 1) * 2 + 15) & ~15u : 0;
+            uint32_t total = bytes;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+            if (lane == 0) mbar_expect_tx(full + 8 * s, total);
+            __syncwarp();
+            if (live)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(base + s * STAGE_BYTES + lane * ROW_BYTES), "l"(reinterpret_cast<uint64_t>(x + r * (size_t)T)), "r"(bytes), "r"(full + 8 * s)
+                             : "memory");
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---- stores: a stage is one contiguous block of R rows ----
+        uint32_t i = 0;
+        for (size_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            if (!mbar_wait(done + 8 * s, ph, abort_flag, status, kErrEpilogueWait)) break;
+            if (lane == 0) {
+                const size_t left = rows - tile * R;
+                const uint32_t bytes = (uint32_t)(left < (size_t)R ? left : (size_t)R) * ROW_BYTES;
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(reinterpret_cast<uint64_t>(out + tile * (size_t)R * T)), "r"(base + s * STAGE_BYTES), "r"(bytes)
+                             : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the stage has been read: it may be refilled
+                mbar_arrive(empty + 8 * s);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+        // ---- compute: warp w owns row w of every stage ----
+        const int w = warp - 2;
+        uint32_t i = 0;
+        bool ok = true;
+        for (size_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, i++) {
+            const uint32_t s = i % stages, ph = (i / stages) & 1;
+            ok = mbar_wait(full + 8 * s, ph, abort_flag, status, kErrMmaWait);
+            if (!ok) break;
+            const size_t r = tile * R + w;
+            if (r < rows) {
+                const int pos = (int)(r % T);
+                const int live_vec = pos / 8 + 1;
+                uint8_t* rowp = smem + (size_t)s * STAGE_BYTES + (size_t)w * ROW_BYTES;
+                float e[VPL][8];
+                float mx = -INFINITY;
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = v * 32 + lane;
+                    if (c < live_vec) {
+                        const uint4 d = *reinterpret_cast<const uint4*>(rowp + c * 16);
+                        const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float lo = __uint_as_float(wd[j] << 16) * scale, hi = __uint_as_float(wd[j] & 0xffff0000u) * scale;
+                            e[v][2 * j] = (c * 8 + 2 * j > pos) ? -INFINITY : lo;
+                            e[v][2 * j + 1] = (c * 8 + 2 * j + 1 > pos) ? -INFINITY : hi;
+                            mx = fmaxf(mx, fmaxf(e[v][2 * j], e[v][2 * j + 1]));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                float sum = 0.0f;
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = v * 32 + lane;
+                    if (c < live_vec) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            float ex;
+                            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"((e[v][j] - mx) * 1.4426950408889634f));      // 2^(-inf) = 0 for the dead entries
+                            e[v][j] = ex; sum += ex;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                const float inv_sum = 1.0f / sum;
+#pragma unroll
+                for (int v = 0; v < VPL; v++) {
+                    const int c = v * 32 + lane;
+                    uint4 o = make_uint4(0, 0, 0, 0);
+                    if (c < live_vec) {
+                        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) oh[j] = __floats2bfloat162_rn(e[v][2 * j] * inv_sum, e[v][2 * j + 1] * inv_sum);
+                    }
+                    *reinterpret_cast<uint4*>(rowp + c * 16) = o;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the rows written above -> visible to the bulk store
+            __syncwarp();
+            if (lane == 0) mbar_arrive(done + 8 * s);
+        }
+    }
+    __syncthreads();
+    if (*abort_flag) {
+        // copies that may still be in flight must land before shared memory is released
+        unsigned long long t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) { }
+        __syncthreads();
+    }
+}
+
+template <int VPL>
+static int causal_softmax_bf16_async_launch(const __nv_bfloat16* x, __nv_bfloat16* out, size_t rows, float scale) {
+    constexpr int CW = 16;
+    constexpr size_t stage = (size_t)CW * VPL * 256 * 2;
+    int stages = (int)((216 * 1024) / stage);
+    if (stages > 16) stages = 16;
+    const size_t smem = (size_t)stages * stage + 512;
+    auto kern = causal_softmax_bf16_async_kernel<VPL, CW>;
+    static bool attr_set = false;
+    if (!attr_set) { SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr_set = true; }
+    const size_t tiles = (rows + CW - 1) / CW;
+    const int grid = (int)(tiles < (size_t)rt().sm_count ? tiles : (size_t)rt().sm_count);
+    kern<<<grid, 64 + 32 * CW, smem, rt().stream>>>(x, out, rows, scale, stages, rt().dev_status);
+    return 0;
+}
+
 // any T: CTA per row, scalar accesses
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads) causal_softmax_generic_kernel(const T* __restrict__ x, T* __restrict__ out,
@@ -1033,6 +1191,20 @@ static int causal_softmax_t(const void* x, void* out, size_t batch, size_t Tn, f
     constexpr int N = Vec<T>::N;
     const T* xp = (const T*)x; T* op = (T*)out;
     bool fast = Tn % N == 0 && Tn / N <= 256 && aligned16(x) && aligned16(out);
+    if constexpr (sizeof(T) == 2) {
+        // SPTORCH_B200_SOFTMAX_ASYNC=0 keeps the register kernel (experiments)
+        static const bool async_on = [] { const char* e = getenv("SPTORCH_B200_SOFTMAX_ASYNC"); return !(e && e[0] == '0'); }();
+        if (fast && async_on && batch * Tn >= 2048 && (Tn == 256 || Tn == 512 || Tn == 1024 || Tn == 2048)) {
+            int rc;
+            if (Tn == 256) rc = causal_softmax_bf16_async_launch<1>(xp, op, batch * Tn, scale);
+            else if (Tn == 512) rc = causal_softmax_bf16_async_launch<2>(xp, op, batch * Tn, scale);
+            else if (Tn == 1024) rc = causal_softmax_bf16_async_launch<4>(xp, op, batch * Tn, scale);
+            else rc = causal_softmax_bf16_async_launch<8>(xp, op, batch * Tn, scale);
+            if (rc) return rc;
+            SPT_LAUNCH_CHECK("causal_softmax");
+            return 0;
+        }
+    }
     if (fast) {
         int nvec = (int)(Tn / N);
         int v = (nvec + 31) / 32;

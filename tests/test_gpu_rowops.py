@@ -96,6 +96,21 @@ def test_causal_softmax_bf16(backend, oracle):
     assert (np.triu(out, 1) == 0).all()
 
 
+@pytest.mark.parametrize("bh,t", [(8, 256), (5, 512), (3, 1024), (2, 2048), (1, 256)])
+def test_causal_softmax_bf16_pipelined_kernel(backend, oracle, bh, t):
+    """bf16 matrices of 256 / 512 / 1024 / 2048 columns with at least 2048 rows run the kernel that streams row prefixes through a
+    ring of shared-memory stages (the last case, 256 rows, stays on the register kernel): against the oracle on the same
+    bf16-rounded scores, exact zeros above the diagonal, rows summing to one within the output rounding, a block of rows that
+    ends a matrix followed by one that begins the next."""
+    s = _bf16((np.random.default_rng(bh + t).standard_normal((bh, t, t)) * 2).astype(np.float32))
+    out = backend.causal_softmax(s, 0.125, dtype=BF16)
+    ref = oracle.causal_softmax(s, 0.125)
+    assert np.abs(out - ref).max() <= 2 ** -8
+    assert (np.triu(out, 1) == 0).all()
+    assert np.array_equal(out[:, 0, 0], np.ones(bh, np.float32))
+    assert np.abs(out.sum(-1) - 1).max() <= 2e-2
+
+
 def test_causal_softmax_rows_sum_to_one_full_size(backend):
     # the row-op sweep's shape per (batch, head): T = 1024; here 24 matrices (100 MB)
     s = (np.random.default_rng(4).standard_normal((24, 1024, 1024)) * 2).astype(np.float32)
