@@ -683,10 +683,10 @@ def _nccl_for_model(b, lib, dist, rank, world, model):
     b._check(lib.sptorch_ext_nccl_init(None, uid, rank, world), "nccl_init")
 
 
-def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overlap=0, sm_reserve=16, check_only=False):
+def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overlap=-1, sm_reserve=0, check_only=False):
     """Tensor-parallel forward over the launched ranks (wq/wk/wv/ffn_up split by rows, wo/ffn_down along K, one NCCL all-reduce per
-    attention and per MLP block).  Two parts: a small model (d 256, 4 heads, 2 layers) whose logits are compared with the CPU
-    oracle on rank 0, and -- unless check_only -- the 1.3B shape c5_1p3b (vocab 50257, d 2048, 24 layers, 16 heads of 128,
+    attention and per MLP block).  Two parts: a small model (4 or 8 heads of 64, 2 layers) whose logits are compared with the CPU
+    oracle on rank 0 -- once with the all-reduces in line and once with them overlapped with the other half of the batch -- and -- unless check_only -- the 1.3B shape c5_1p3b (vocab 50257, d 2048, 24 layers, 16 heads of 128,
     d_ff 8192, batch 16 x 2048 tokens, bf16) timed on the device, max over ranks.  Returns the record rank 0 prints."""
     import torch
     from sptorch_b200.backend import BF16
@@ -696,7 +696,8 @@ def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overla
         _nccl_for_model(b, lib, dist, rank, world, None)
     rec = {}
     # ---- parity of the partition on a small model ----
-    cfg = dict(vocab=1000, d_model=256, n_layer=2, n_head=4 if world <= 4 else 8, d_ff=1024, seq_len=256, batch=2, ctx=256)
+    heads = 4 if world <= 4 else 8                      # heads of 64: the fused attention, which the overlapped forward needs
+    cfg = dict(vocab=1000, d_model=64 * heads, n_layer=2, n_head=heads, d_ff=256 * heads, seq_len=256, batch=2, ctx=256)
     model = GPT(b, cfg["vocab"], cfg["d_model"], cfg["n_head"], cfg["n_layer"], cfg["d_ff"], cfg["seq_len"], dtype=BF16,
                 max_batch=2, tp_rank=rank, tp_size=world)
     params, index = synth.gpt_params(cfg, 0, residual_scale=True, randomize_affine=True)
@@ -704,15 +705,21 @@ def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overla
     if world > 1:
         b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
     ids = synth.randint(1, 2 * 256, cfg["vocab"]).reshape(2, 256).astype(np.int32)
-    out = model.forward(ids)
+    outs = []
+    for mode in (0, 1):
+        b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, mode), "tp_overlap")
+        outs.append(model.forward(ids))
+    out, out_ov = outs
     model.close()
     if rank == 0:
         from oracle import binding as O
         O.build()
         ref = O.gpt_forward(cfg, params, ids, fast=1, threads=host_threads())
         err = float(np.abs(out - ref).max() / np.abs(ref).max())
-        rec.update({"tp_size": world, "check_model": "vocab 1000, d 256, 2 layers, %d heads, d_ff 1024, 2 x 256 tokens, bf16" % cfg["n_head"],
-                    "max_rel_err_vs_oracle": err, "tolerance": 2e-2, "check_ok": bool(err <= 2e-2)})
+        err_ov = float(np.abs(out_ov - ref).max() / np.abs(ref).max())
+        rec.update({"tp_size": world, "check_model": "vocab 1000, d %d, 2 layers, %d heads, d_ff %d, 2 x 256 tokens, bf16" % (cfg["d_model"], heads, cfg["d_ff"]),
+                    "max_rel_err_vs_oracle": err, "max_rel_err_vs_oracle_overlapped": err_ov, "overlapped_equals_serial": bool(np.array_equal(out, out_ov)),
+                    "tolerance": 2e-2, "check_ok": bool(err <= 2e-2 and err_ov <= 2e-2)})
     if check_only:
         if world > 1:
             lib.sptorch_ext_nccl_shutdown()
@@ -727,9 +734,11 @@ def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overla
     _load_timing_weights(model, cfg)
     if world > 1:
         b._check(lib.sptorch_ext_gpt_use_nccl(model.h), "gpt_use_nccl")
-        b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, int(tp_overlap)), "tp_overlap")
-        if tp_overlap:
+        if tp_overlap >= 0:                              # otherwise the library's rule: overlapped from four ranks up
+            b._check(lib.sptorch_ext_gpt_enable_tp_overlap(model.h, int(tp_overlap)), "tp_overlap")
+        if sm_reserve > 0:                               # otherwise the library leaves 32 SMs free while an overlapped forward runs
             b._check(lib.sptorch_ext_set_sm_reserve(sm_reserve), "sm_reserve")
+    overlapped = world > 1 and (tp_overlap == 1 or (tp_overlap < 0 and world >= 4))
     ids = synth.randint(1, B * T, cfg["vocab"]).reshape(B, T).astype(np.int32)
     d_ids, d_logits = model.stage_ids(ids), model.logits_buffer(B * T)
 
@@ -753,7 +762,7 @@ def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overla
         t = torch.tensor([ms], dtype=torch.float64, device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
     pm, pn = (C.c_float * 7)(), (C.c_uint32 * 7)()
     lib.sptorch_ext_prof_read(pm, pn, 7); lib.sptorch_ext_prof_enable(0)
-    if tp_overlap:
+    if sm_reserve > 0:
         b._check(lib.sptorch_ext_set_sm_reserve(0), "sm_reserve")
     model.close()
     if world > 1:
@@ -762,9 +771,9 @@ def tp_measure(b, rank, world, dist, steps, warmup, layers=0, batch=0, tp_overla
         cats = ["linear_gemm", "attention_gemm", "causal_softmax", "layernorm", "embedding", "allreduce_and_other", "attention_fused"]
         lin, attn = flops_per_forward(cfg, B, T)
         rec.update({"workload": "c5_1p3b", "n_layer": cfg["n_layer"], "batch": B, "seq_len": T, "parallelism": f"tensor-parallel x{world}",
-                    "tp_overlap": bool(tp_overlap), "steps": steps, "ms_per_step": ms / steps, "tokens_per_s": B * T * steps / (ms * 1e-3),
+                    "tp_overlap": bool(overlapped), "steps": steps, "ms_per_step": ms / steps, "tokens_per_s": B * T * steps / (ms * 1e-3),
                     "achieved_tflops_whole_job": (lin + attn) / (ms / steps * 1e-3) / 1e12,
-                    "allreduce_ms_per_step_rank0": float(pm[5]) / steps, "allreduces_per_step": 2 * cfg["n_layer"],
+                    "allreduce_ms_per_step_rank0": None if overlapped else float(pm[5]) / steps, "allreduces_per_step": 2 * cfg["n_layer"],
                     "allreduce_bytes_each": B * T * cfg["d_model"] * 2,
                     "breakdown_rank0_ms": {c: float(pm[i]) / steps for i, c in enumerate(cats) if pn[i]},
                     "weights": "seeded N(0,0.02) block repeated per matrix (timing only; parity is the small check model above)"})
@@ -808,8 +817,8 @@ def main():
     ap.add_argument("--workload", default=WORKLOAD, choices=[WORKLOAD, "c5_1p3b", "tp_check"],
                     help="c4_gpt2s: the bench line (batch sharding); c5_1p3b / tp_check: tensor parallel over the launched ranks")
     ap.add_argument("--ln-fold", type=int, default=0, help="1: LayerNorm folded into the GEMM epilogues instead of separate kernels")
-    ap.add_argument("--tp-overlap", type=int, default=0, help="tensor parallel: overlap the all-reduces with the other half of the batch")
-    ap.add_argument("--sm-reserve", type=int, default=16, help="SMs left free for NCCL when --tp-overlap is on")
+    ap.add_argument("--tp-overlap", type=int, default=-1, help="tensor parallel: overlap the all-reduces with the other half of the batch (0 / 1; -1: the library's rule, on from four ranks up)")
+    ap.add_argument("--sm-reserve", type=int, default=0, help="SMs left free for NCCL by every persistent kernel (0: the library leaves 32 free during an overlapped forward)")
     ap.add_argument("--layers", type=int, default=0, help="tensor-parallel model: run fewer than its 24 layers")
     ap.add_argument("--sweeps", type=int, default=1, help="1 GPU: append the compact Linear / row-op / attention sweeps to the line (0 = skip)")
     ap.add_argument("--sweep-iters", type=int, default=7, help="timed launches per case of the compact sweeps")

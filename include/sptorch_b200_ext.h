@@ -206,9 +206,10 @@ typedef int (*sptorch_allreduce_fn)(void* buf, size_t n, int dtype, void* cuda_s
  * statistics pass instead of a normalising pass).  Default 0: on B200 the statistics passes save 0.57 ms per step of the
  * GPT-2-small-shape benchmark and the heavier epilogues cost 0.5 ms, so the step time does not move (19.2 ms either way). */
 int   sptorch_ext_gpt_enable_ln_fold(void* gpt, int on);
-/* tensor parallel: reduce one half of the batch on a second stream while the other half computes (default off: with
- * the statically scheduled persistent GEMM the SMs given up cost as much as the overlap gains; needs an even batch;
- * combine with sptorch_ext_set_sm_reserve so that the collective finds free SMs) */
+/* tensor parallel: reduce one half of the batch on a second stream while the other half computes.  mode 0: never; 1: whenever
+ * the batch is even; 2 (default): from four ranks up, where the all-reduces are two fifths of a step and hiding them gains more
+ * than the SMs left free for the collective cost (4 x B200, 12 layers of the 1.3B shape: 25.7 -> 21.1 ms per step; on two ranks
+ * 22.0 -> 21.5 at best).  The call leaves 32 SMs free for the collective unless sptorch_ext_set_sm_reserve has set a number. */
 int   sptorch_ext_gpt_enable_tp_overlap(void* gpt, int on);
 int   sptorch_ext_gpt_set_allreduce(void* gpt, sptorch_allreduce_fn fn, void* user);
 /* The tensor-parallel shard rule that sptorch_ext_gpt_set_param applies (host code: usable without a GPU).  For the parameter

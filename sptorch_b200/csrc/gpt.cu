@@ -103,7 +103,7 @@ struct Gpt {
     // folded LayerNorm (see forward): per-token statistics, the head's folded copy, and whether the copies are stale
     float2* ln_stats = nullptr; void* head_f = nullptr; float *s_h = nullptr, *c_h = nullptr;
     bool ln_fold = false, fold_ready = false, fold_dirty = true;     // opt-in: measured neutral (see sptorch_ext_gpt_enable_ln_fold)
-    bool tp_overlap = false;   // tensor parallel: reduce one half of the batch while the other half computes (opt-in)
+    int tp_overlap = 2;        // tensor parallel: reduce one half of the batch while the other half computes: 0 never, 1 always, 2 from 4 ranks up
     // LM head fused with the loss / greedy choice: per-row partial reductions of the head GEMM's tiles
     float2* red_part = nullptr; int* red_arg = nullptr; float* red_tgt = nullptr; size_t red_rows = 0;
     // host-buffer loss call: targets, greedy tokens and row losses of the whole batch on the device
@@ -405,8 +405,20 @@ static int lm_head(Gpt* g, const void* h, int M, void* logits, const HeadReduce*
 
 // Tensor-parallel forward with the all-reduces taken off the critical path: the batch is cut into two halves that go
 // through each half-block alternately, the partial sums of one half are reduced on a second stream while the other
-// half computes.  (The persistent kernels must leave a few SMs free for the collective: sptorch_ext_set_sm_reserve.)
+// half computes.  The persistent kernels must leave SMs free for the collective: unless the caller has set a reserve
+// (sptorch_ext_set_sm_reserve), kTpOverlapReserve SMs are left free for the duration of the call.
+// Measured on 4 x B200, 12 layers of the 1.3B shape (d 2048, 16 x 2048 tokens), ms per step: serial 25.7 (all-reduce 10.3);
+// overlapped with 16 / 24 / 32 / 40 / 48 / 64 SMs free: 23.0 / 22.2 / 21.1 / 21.6 / 22.0 / 23.9.  On 2 GPUs the all-reduce is a
+// fifth of the step and the SMs given up cost what the overlap hides (22.0 serial, 21.5 at best), hence from four ranks up.
+constexpr int kTpOverlapReserve = 32;
+constexpr int kTpOverlapFromRanks = 4;
+struct SmReserveScope {
+    int saved;
+    SmReserveScope() : saved(rt().sm_reserve) { if (saved == 0) rt().sm_reserve = kTpOverlapReserve; }
+    ~SmReserveScope() { rt().sm_reserve = saved; }
+};
 static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr) {
+    SmReserveScope reserve;
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
@@ -514,7 +526,8 @@ static int forward_qwen(Gpt* g, const void* ids, int B, int T, void* logits, con
 
 static int forward(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr = nullptr) {
     if (g->c.arch == SPT_ARCH_QWEN_LIKE) return forward_qwen(g, ids, B, T, logits, hr);
-    if (g->c.tp_size > 1 && g->ar && g->tp_overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0 && model_uses_fused(g, T))
+    const bool overlap = g->tp_overlap == 1 || (g->tp_overlap == 2 && g->c.tp_size >= kTpOverlapFromRanks);
+    if (g->c.tp_size > 1 && g->ar && overlap && !g->taps_on && !g->fill_cache && B >= 2 && B % 2 == 0 && model_uses_fused(g, T))
         return forward_tp_pipelined(g, ids, B, T, logits, hr);
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc;
@@ -1034,7 +1047,9 @@ int sptorch_ext_gpt_enable_ln_fold(void* gp, int on) {
 
 int sptorch_ext_gpt_enable_tp_overlap(void* gp, int on) {
     if (!gp) return fail("gpt_enable_tp_overlap: null model");
-    ((Gpt*)gp)->tp_overlap = on != 0;
+    if (on < 0 || on > 2) return fail("gpt_enable_tp_overlap: mode %d (0 never, 1 always, 2 from four ranks up)", on);
+    ((Gpt*)gp)->tp_overlap = on;
+    drop_graphs((Gpt*)gp);
     return 0;
 }
 
