@@ -15,16 +15,18 @@
 // A sum over k does not care about the order as long as both operands use the same one.
 #include "gemm.h"
 #include "epilogue_math.cuh"
+#include <cooperative_groups.h>
 
 namespace spt {
 
 namespace {
 
 constexpr int kWarps = 8;
-// Row counts up to this take the kernel by default.  Above it every CTA re-reads more activation rows from L2 than it streams weight
-// bytes and, with N = 768, fewer than one CTA per SM is left to hide that latency: a decode step of a 12-layer, 768-wide model at 64
-// sequences took 1.18 ms here against 1.09 ms on 128-row tcgen05 tiles; at 32 sequences 0.72 against 1.00 ms.
-constexpr int kDefaultMaxRows = 32;
+// Row counts up to this take the kernel by default (the limit of its four 16-row groups).  Decode step of a 12-layer, 768-wide
+// model, this kernel against 128-row tcgen05 tiles: 32 sequences 0.59 vs 1.00 ms, 48 sequences 0.90 vs 0.93 ms, 64 sequences
+// 0.92 vs 0.99 ms -- above 16 rows every CTA re-reads more activation bytes from L2 than it streams weight bytes, and the gap
+// closes.
+constexpr int kDefaultMaxRows = 64;
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {     // weights: read once, do not keep in L1
     uint4 v;
@@ -58,12 +60,15 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
                                                                      const __nv_bfloat16* __restrict__ W, long long ldb,
                                                                      __nv_bfloat16* C, long long ldc, const float* __restrict__ bias,
                                                                      const __nv_bfloat16* R, int M, int N, int K, float alpha, int epilogue,
-                                                                     RowNorm nrm) {
+                                                                     RowNorm nrm, int ksplit) {
     __shared__ float red[kWarps][MT * 16][NT * 8 + 1];
     extern __shared__ __align__(16) uint8_t dyn[];                       // NORM: M rows of (K + 8) bf16
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * (NT * 8);
-    const int slices = K >> 5;
+    // ksplit > 1: a cluster of ksplit CTAs shares the weight rows of one block, CTA r of it takes the r-th part of K
+    const int krank = blockIdx.x % ksplit;
+    const int n0 = (blockIdx.x / ksplit) * (NT * 8);
+    const int all_slices = K >> 5, per_cta = (all_slices + ksplit - 1) / ksplit;
+    const int s_lo = krank * per_cta, slices = min(all_slices, s_lo + per_cta);
     pdl_release();
 
     const __nv_bfloat16* wrow[NT];
@@ -86,7 +91,7 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
             for (int j = 0; j < NT; j++) wv[u][j] = s < slices ? ld_stream(wrow[j] + 32 * s) : make_uint4(0, 0, 0, 0);
         }
     };
-    load_weights(warp);              // the weights do not depend on the kernel before this one
+    load_weights(s_lo + warp);       // the weights do not depend on the kernel before this one
     // the output elements this thread finishes at the end: their bias and residual are requested now, not after the reduction
     constexpr int EI = (MT * 16 * NT * 8 + kWarps * 32 - 1) / (kWarps * 32);
     float bpre[EI], rpre[EI];
@@ -99,7 +104,7 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
 #pragma unroll
     for (int it = 0; it < EI; it++) {
         const int e = tid + it * kWarps * 32, m = e / (NT * 8), n = n0 + e % (NT * 8);
-        rpre[it] = (R && m < M && n < N) ? __bfloat162float(R[(long long)m * ldc + n]) : 0.0f;
+        rpre[it] = (R && krank == 0 && m < M && n < N) ? __bfloat162float(R[(long long)m * ldc + n]) : 0.0f;
     }
 
     const long long a_ld = NORM ? (long long)(K + 8) : lda;
@@ -189,8 +194,8 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
         __syncthreads();
     }
 
-    for (int s0 = warp; s0 < slices; s0 += kWarps * S) {
-        if (s0 != warp) load_weights(s0);
+    for (int s0 = s_lo + warp; s0 < slices; s0 += kWarps * S) {
+        if (s0 != s_lo + warp) load_weights(s0);
 #pragma unroll
         for (int u = 0; u < S; u++) {
             const int s = s0 + u * kWarps;
@@ -220,15 +225,49 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
             red[warp][16 * i + g + 8][8 * j + 2 * t + 1] = acc[i][j][3];
         }
     __syncthreads();
+    float tot[EI];
+#pragma unroll
+    for (int it = 0; it < EI; it++) {
+        const int e = tid + it * kWarps * 32;
+        const int m = e / (NT * 8), nn = e % (NT * 8);
+        tot[it] = 0.0f;
+        if (m < MT * 16) {
+            float sum = red[0][m][nn];
+#pragma unroll
+            for (int w = 1; w < kWarps; w++) sum += red[w][m][nn];
+            tot[it] = sum;
+        }
+    }
+    if (ksplit > 1) {
+        // the CTAs' sums meet in the cluster's first CTA, read through distributed shared memory and added in rank order
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        __syncthreads();                                  // every thread has read red[*] before red[0] is reused
+#pragma unroll
+        for (int it = 0; it < EI; it++) {
+            const int e = tid + it * kWarps * 32;
+            if (e < MT * 16 * NT * 8) red[0][e / (NT * 8)][e % (NT * 8)] = tot[it];
+        }
+        cluster.sync();
+        if (krank == 0) {
+            for (int r = 1; r < ksplit; r++) {
+                const float* other = cluster.map_shared_rank(&red[0][0][0], r);
+#pragma unroll
+                for (int it = 0; it < EI; it++) {
+                    const int e = tid + it * kWarps * 32;
+                    if (e < MT * 16 * NT * 8) tot[it] += other[(e / (NT * 8)) * (NT * 8 + 1) + e % (NT * 8)];
+                }
+            }
+        }
+        cluster.sync();                                   // no CTA leaves while its shared memory may still be read
+        if (krank != 0) return;
+    }
 #pragma unroll
     for (int it = 0; it < EI; it++) {
         const int e = tid + it * kWarps * 32;
         const int m = e / (NT * 8), nn = e % (NT * 8), n = n0 + nn;
         if (m >= M || n >= N || m >= MT * 16) continue;
-        float sum = red[0][m][nn];
-#pragma unroll
-        for (int w = 1; w < kWarps; w++) sum += red[w][m][nn];
-        float v = fmaf(sum, alpha, bpre[it]);
+        float v = fmaf(tot[it], alpha, bpre[it]);
         if (epilogue == EPI_GELU) v = gelu_fast2(make_float2(v, 0.0f)).x;
         else if (epilogue == EPI_SWIGLU) v = silu_fast(v);
         if (R) v = epilogue == EPI_SWIGLU ? v * rpre[it] : v + rpre[it];
@@ -241,6 +280,13 @@ size_t norm_smem(const GemmDesc& d) { return (size_t)d.M * (d.K + 8) * 2; }
 
 template <int MT, int NT, bool NORM>
 int launch(const GemmDesc& d, const RowNorm& nrm, bool dependent) {
+    // Few weight rows and a long K (the projections back to the model width): clusters of 2 or 4 CTAs split K, so that the launch
+    // still covers the SMs and a warp's share of K is one round of loads.
+    int ksplit = 1;
+    if constexpr (!NORM) {
+        const long long blocks = ceil_div(d.N, NT * 8);
+        while (ksplit < 4 && blocks * ksplit * 2 <= 3ll * rt().sm_count && d.K / (ksplit * 2) >= 32 * kWarps) ksplit *= 2;
+    }
     constexpr int S = NT == 1 ? 8 : NT == 2 ? 4 : 2;
     auto kern = linear_few_rows_kernel<MT, NT, S, NORM>;
     const size_t smem = NORM ? norm_smem(d) : 0;
@@ -248,10 +294,10 @@ int launch(const GemmDesc& d, const RowNorm& nrm, bool dependent) {
         static bool granted = false;                                   // per instantiation
         if (!granted) { SPT_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNormSmemLimit)); granted = true; }
     }
-    const int grid = ceil_div(d.N, NT * 8);
-    SPT_CUDA(launch_dependent(kern, dim3(grid), dim3(kWarps * 32), smem, dependent, 1,
+    const int grid = ceil_div(d.N, NT * 8) * ksplit;
+    SPT_CUDA(launch_dependent(kern, dim3(grid), dim3(kWarps * 32), smem, dependent, ksplit,
                               static_cast<const __nv_bfloat16*>(d.A), d.lda, static_cast<const __nv_bfloat16*>(d.B), d.ldb, static_cast<__nv_bfloat16*>(d.C), d.ldc,
-                              d.bias, static_cast<const __nv_bfloat16*>(d.R), d.M, d.N, d.K, d.alpha, d.epilogue, nrm));
+                              d.bias, static_cast<const __nv_bfloat16*>(d.R), d.M, d.N, d.K, d.alpha, d.epilogue, nrm, ksplit));
     note_submit();
     return 0;
 }

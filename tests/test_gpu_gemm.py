@@ -93,9 +93,9 @@ def test_linear_with_few_rows_vs_oracle(backend, oracle, M, K, N):
     assert np.array_equal(backend.linear(onehot, wi, mode=MM_BF16), wi[:, ks].T)
 
 
-def test_linear_with_few_rows_kernel_up_to_64_rows():
-    """Row counts 33 .. 64 take the tcgen05 tiles by default; SPTORCH_B200_FEW_ROWS=64 (read once per process, hence the child
-    process) sends them through the weight-streaming kernel's four-row-group variants, which must agree with the oracle too."""
+def test_linear_with_few_rows_on_tcgen05_tiles():
+    """Row counts up to 64 take the weight-streaming kernel by default; SPTORCH_B200_FEW_ROWS=0 (read once per process, hence the
+    child process) sends them through the 128-row tcgen05 tiles instead, which must agree with the oracle too."""
     import os, subprocess, sys, textwrap
     code = textwrap.dedent("""
         import numpy as np
@@ -122,7 +122,7 @@ def test_linear_with_few_rows_kernel_up_to_64_rows():
         print("ok")
     """)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, SPTORCH_B200_FEW_ROWS="64", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    env = dict(os.environ, SPTORCH_B200_FEW_ROWS="0", PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
     out = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "ok" in out.stdout, out.stdout + out.stderr
 
