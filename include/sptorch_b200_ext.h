@@ -124,6 +124,10 @@ int sptorch_ext_set_gemm_pair(int mode);
  * threads issue at the same time (their transpose and product kernels can interleave on the stream), race. */
 int sptorch_ext_matmul_f32_static(const void* a, const void* b, void* out, size_t m, size_t k, size_t n);
 
+/* bf16 problems of at most 64 rows run a weight-streaming kernel (the projections of a decode step) whose sums are taken in
+ * another order than the 128-row tensor-core tiles': the same row may differ in its last bit between a call with 64 rows and
+ * one with more.  The model forward (sptorch_ext_gpt_forward*) never takes that kernel: a row of its output does not depend
+ * on the batch. */
 int sptorch_ext_linear(const void* x, const void* w, const void* bias_f32, const void* residual, void* out,
                        size_t M, size_t K, size_t N, size_t ldo, float alpha, int epilogue, int mode, int out_dtype);
 

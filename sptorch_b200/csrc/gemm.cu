@@ -672,7 +672,7 @@ static std::atomic<int> g_pair_mode{[] { const char* e = getenv("SPTORCH_B200_GE
 
 int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     const char* why = nullptr;
-    if (linear_few_rows_supported(d)) {
+    if (d.few_rows_ok && linear_few_rows_supported(d)) {
         plan->d = d;
         plan->few_rows = true;
         plan->valid = true;
@@ -1005,6 +1005,7 @@ int sptorch_ext_linear(const void* x, const void* w, const void* bias, const voi
     d.M = (int)M; d.N = (int)N; d.K = (int)K;
     d.lda = (long long)K; d.ldb = (long long)K; d.ldc = (long long)ldo;
     d.alpha = alpha; d.epilogue = epilogue; d.mode = mode; d.out_dtype = out_dtype;
+    d.few_rows_ok = 1;
     if (mode == SPT_MM_TF32 && !gemm_supported(d, nullptr) && out_dtype == SPT_F32 && ldo == N)
         return simt_matmul_f32((const float*)x, (const float*)w, (float*)out, 1, (int)M, (int)N, (int)K, false, (const float*)bias,
                                (const float*)residual, alpha, epilogue);

@@ -25,6 +25,10 @@ struct GemmDesc {
     int out_dtype = BF16;    // C and R element type
     int causal_lower = 0;    // 1: square per-batch output, tiles entirely above the diagonal are skipped (never written)
     int b_broadcast = 0;     // 1: B has no batch dims (one weight matrix for every batch entry)
+    // 1: a problem of at most 64 rows may run the weight-streaming kernel (linear_few_rows.cu) instead of 128-row tiles.  Its sums
+    // are taken in another order, so the caller must not need a row's bits to be the same whatever the number of rows
+    // (the model forward does: it leaves this 0; the decode step and the stand-alone Linear set it).
+    int few_rows_ok = 0;
     int causal_k = 0;        // 1: A is lower triangular per batch (A[m,k] = 0 for k > m): k-blocks past the tile's last row are skipped
     // LayerNorm folded into the product.  With W' = W * gamma (per input feature), s[n] = sum_k W'[n,k], c[n] = sum_k beta[k] W[n,k] + bias[n]:
     //   LN(x) W^T + bias = inv[m] * (x W'^T)[m,n] - (mean[m] inv[m]) * s[n] + c[n]
