@@ -345,7 +345,7 @@ def run_ours(args):
             "e2e": e2e,
             "e2e_loss": e2e_loss,
             "gpu_launches": int(sum(prof_n)) if sum(prof_n) else model.launches(nseq, T) * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (Linear: QK, V^T, Wo, up, down, LM head)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16> (Linear: [Wq;Wk;Wv], Wo, up, down, LM head)",
                          "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tf_sustained"] if peaks["tf_sustained"] else None,
                          "peak_source": f"{peaks['source']} (sustained cuBLAS bf16, kernel timed inside a long step)",
