@@ -601,6 +601,19 @@ def sweep_decode(b, peaks, steps=32, emit=None, batches=(1, 8, 64)):
         out.append({"op": "decode_step", "batch": batch, "cached_positions": n_ctx, "ms_per_step": ms, "tokens_per_s": batch / (ms * 1e-3),
                     "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"],
                     "algorithmic_bytes": nbytes})
+        if batch == 1:
+            # the reference's generation loop (decode_next_token: decode step, sampling candidates on the device, the draw on the
+            # host) in its greedy configuration, host-driven, wall clock: the first call prefills the prompt and is not timed
+            import time
+            toks = [int(t) for t in ids[0]]
+            model._gen_ctx, model._prompt_len = None, len(toks)
+            model.decode_next_token(toks, top_k=1)
+            b.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(32):
+                model.decode_next_token(toks, top_k=1)
+            b.synchronize()
+            out[-1]["generate_greedy_tokens_per_s"] = 32 / (time.perf_counter() - t0)
         if emit:
             emit(out[-1])
         model.close()
@@ -623,8 +636,9 @@ def compact_sweeps(b, peaks, iters):
         "rowops": [{"op": e["op"], "dtype": e["dtype"], **({"dim": e["dim"]} if "dim" in e else {}), "ms": r3(e["ms"]), "gbs": r3(e["gbs"]), "frac": r3(e["frac"])} for e in row],
         "rowops_roof": f"{peaks['hbm']} GB/s ({peaks['source']} copy bandwidth)",
         "decode": [{"batch": e["batch"], "cached_positions": e["cached_positions"], "ms_per_step": r3(e["ms_per_step"]), "tokens_per_s": r3(e["tokens_per_s"]),
-                    "frac": r3(e["frac"])} for e in dec],
-        "decode_note": "one new token per sequence through the key/value cache of the GPT-2-small shape; frac = (weights + cached K/V bytes) per step over the copy bandwidth",
+                    "frac": r3(e["frac"]), **({"generate_greedy_tokens_per_s": r3(e["generate_greedy_tokens_per_s"])} if "generate_greedy_tokens_per_s" in e else {})}
+                   for e in dec],
+        "decode_note": "one new token per sequence through the key/value cache of the GPT-2-small shape; frac = (weights + cached K/V bytes) per step over the copy bandwidth; generate_greedy_tokens_per_s: the host-driven generation loop (decode step + device sampling candidates + host draw), wall clock",
     }
 
 

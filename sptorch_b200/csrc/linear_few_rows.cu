@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
             for (int o = 16; o > 0; o >>= 1) acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
             if (lane == 0) part[r][my_p] = acc1;
         }
-        __syncthreads();
+        if (P == 1) __syncwarp(); else __syncthreads();      // one warp per row: its sums never leave the warp
         if (ln) {
 #pragma unroll 1
             for (int r = my_r; r < M; r += RP) {
@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(kWarps * 32) linear_few_rows_kernel(const __nv
                 for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
                 if (lane == 0) part2[r][my_p] = var;
             }
-            __syncthreads();
+            if (P == 1) __syncwarp(); else __syncthreads();
         }
 #pragma unroll 1
         for (int r = my_r; r < M; r += RP) {
