@@ -249,6 +249,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint32_t tile_par = 0, tile_seq = 0;
         bool ok = true;
         const bool has_bias = p.bias != nullptr;
+        const bool plain_acc = !has_bias && p.alpha == 1.0f;
         if (!has_bias) {
             bias_s[eidx] = 0.0f; bias_s[256 + eidx] = 0.0f;
             mbar_arrive(bar_bias);
@@ -339,6 +340,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         float2 hi = __ffma2_rn(make_float2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), inv2, __ffma2_rn(nmi2, make_float2(s4.z, s4.w), make_float2(b4.z, b4.w)));
                         f[j] = lo.x; f[j + 1] = lo.y; f[j + 2] = hi.x; f[j + 3] = hi.y;
                     }
+                } else if (plain_acc) {
+                    // alpha 1, no bias: the accumulator is the value.  Every epilogue instruction shows up in the step time: without
+                    // these 16 FMAs and 8 shared-memory loads per chunk the 49 Linear launches of a GPT-2-small-shape forward (three
+                    // of five kinds have no bias) take 15.11 instead of 15.40 ms, measured twice in one call
+#pragma unroll
+                    for (int j = 0; j < 32; j++) f[j] = __uint_as_float(v[j]);
                 } else {
                 const float2 al2 = make_float2(p.alpha, p.alpha);
 #pragma unroll
