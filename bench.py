@@ -409,6 +409,19 @@ def _time_op(b, fn, iters, warmup=3):
     return statistics.median(ts), min(ts)
 
 
+def _time_stream(b, fns, launches=8):
+    """Device time per launch of `launches` launches issued back to back between one pair of events, alternating between the given
+    closures (each works on its own buffers; together they exceed L2, so no launch finds its input there).  What a kernel costs
+    inside a stream of launches, as in the forward; _time_op times one launch alone, launch latency included."""
+    for f in fns:
+        f()
+    b.flush_l2()
+    b.timer_begin()
+    for i in range(launches):
+        fns[i % len(fns)]()
+    return b.timer_end() / launches
+
+
 def sweep_abi(args, b):
     """The eleven ops of the reference's C-ABI through sptorch_*_f32 with HOST slices (upload, kernel, download: what the
     reference's FfiBackend wrapper does per op, crates/hal-ffi/src/lib.rs:337-446), device-resident, and the reference's own C
@@ -544,10 +557,15 @@ def sweep_rowops(b, peaks, iters, emit=None):
             _fill(b, x, rows * dim, es, 4, mean=0.5, std=3.0)
             fn = lambda: b._check(lib.sptorch_ext_layernorm(x.handle, g.handle, be.handle, y.handle, rows, dim, C.c_float(1e-5), dt), "layernorm")
             med, best = _time_op(b, fn, iters)
+            x2, y2 = b.alloc(rows * dim, es), b.alloc(rows * dim, es)
+            _fill(b, x2, rows * dim, es, 7, mean=0.5, std=3.0)
+            fn2 = lambda: b._check(lib.sptorch_ext_layernorm(x2.handle, g.handle, be.handle, y2.handle, rows, dim, C.c_float(1e-5), dt), "layernorm")
+            ms_s = _time_stream(b, [fn, fn2])
             nbytes = 2 * rows * dim * es + 2 * dim * 4
             rec({"op": "layernorm", "rows": rows, "dim": dim, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-                 "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
-            for buf in (x, y, g, be):
+                 "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes,
+                 "ms_back_to_back": ms_s, "frac_back_to_back": nbytes / (ms_s * 1e-3) / 1e9 / peaks["hbm"]})
+            for buf in (x, y, g, be, x2, y2):
                 buf.free()
     for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
         B_, H_, T_ = 16, 12, 1024
@@ -556,20 +574,32 @@ def sweep_rowops(b, peaks, iters, emit=None):
         _fill(b, x, n, es, 5, std=2.0)
         fn = lambda: b._check(lib.sptorch_ext_causal_softmax(x.handle, y.handle, B_ * H_, T_, C.c_float(1.0), dt), "causal_softmax")
         med, best = _time_op(b, fn, iters)
+        x2, y2 = b.alloc(n, es), b.alloc(n, es)
+        _fill(b, x2, n, es, 8, std=2.0)
+        fn2 = lambda: b._check(lib.sptorch_ext_causal_softmax(x2.handle, y2.handle, B_ * H_, T_, C.c_float(1.0), dt), "causal_softmax")
+        ms_s = _time_stream(b, [fn, fn2])
         nbytes = (T_ * (T_ + 1) // 2 + T_ * T_) * B_ * H_ * es
         rec({"op": "causal_softmax", "shape": [B_, H_, T_, T_], "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes, "full_read_bytes": 2 * n * es})
-        x.free(); y.free()
+             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes, "full_read_bytes": 2 * n * es,
+             "ms_back_to_back": ms_s, "frac_back_to_back": nbytes / (ms_s * 1e-3) / 1e9 / peaks["hbm"]})
+        for buf in (x, y, x2, y2):
+            buf.free()
     for dt, name, es in ((F32, "f32", 4), (BF16, "bf16", 2)):
         n = 64 << 20
         x, y = b.alloc(n, es), b.alloc(n, es)
         _fill(b, x, n, es, 6)
         fn = lambda: b._check(lib.sptorch_ext_gelu(x.handle, y.handle, n, dt), "gelu")
         med, best = _time_op(b, fn, iters)
+        x2, y2 = b.alloc(n, es), b.alloc(n, es)
+        _fill(b, x2, n, es, 9)
+        fn2 = lambda: b._check(lib.sptorch_ext_gelu(x2.handle, y2.handle, n, dt), "gelu")
+        ms_s = _time_stream(b, [fn, fn2])
         nbytes = 2 * n * es
         rec({"op": "gelu", "n": n, "dtype": name, "ms": med, "ms_best": best, "gbs": nbytes / (med * 1e-3) / 1e9,
-             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes})
-        x.free(); y.free()
+             "frac": nbytes / (med * 1e-3) / 1e9 / peaks["hbm"], "peak": peaks["hbm"], "algorithmic_bytes": nbytes,
+             "ms_back_to_back": ms_s, "frac_back_to_back": nbytes / (ms_s * 1e-3) / 1e9 / peaks["hbm"]})
+        for buf in (x, y, x2, y2):
+            buf.free()
     return out
 
 
@@ -634,8 +664,10 @@ def compact_sweeps(b, peaks, iters):
         "linear": [{"M": e["M"], "K": e["K"], "N": e["N"], "mode": e["mode"], "ms": r3(e["ms"]), "tflops": r3(e["tflops"]), "frac": r3(e["frac"])} for e in lin],
         "linear_roof": f"{peaks['tf']} TFLOP/s bf16 ({peaks['source']} burst), TF32 against half of it",
         "attention": [{"B": e["B"], "T": e["T"], "H": e["H"], "hd": e["hd"], "ms": r3(e["ms"]), "tflops": r3(e["tflops"]), "frac": r3(e["frac"])} for e in att],
-        "rowops": [{"op": e["op"], "dtype": e["dtype"], **({"dim": e["dim"]} if "dim" in e else {}), "ms": r3(e["ms"]), "gbs": r3(e["gbs"]), "frac": r3(e["frac"])} for e in row],
-        "rowops_roof": f"{peaks['hbm']} GB/s ({peaks['source']} copy bandwidth)",
+        "rowops": [{"op": e["op"], "dtype": e["dtype"], **({"dim": e["dim"]} if "dim" in e else {}), "ms": r3(e["ms"]), "gbs": r3(e["gbs"]), "frac": r3(e["frac"]),
+                    "ms_back_to_back": r3(e["ms_back_to_back"]), "frac_back_to_back": r3(e["frac_back_to_back"])} for e in row],
+        "rowops_roof": f"{peaks['hbm']} GB/s ({peaks['source']} copy bandwidth); frac: one launch timed alone (its launch latency included); "
+                       "frac_back_to_back: eight launches between one pair of events, alternating between two sets of buffers (together larger than L2)",
         "decode": [{"batch": e["batch"], "cached_positions": e["cached_positions"], "ms_per_step": r3(e["ms_per_step"]), "tokens_per_s": r3(e["tokens_per_s"]),
                     "frac": r3(e["frac"]), **({"generate_greedy_tokens_per_s": r3(e["generate_greedy_tokens_per_s"])} if "generate_greedy_tokens_per_s" in e else {})}
                    for e in dec],
