@@ -78,6 +78,9 @@ struct RowNorm { int kind = 0; const float* gamma = nullptr; const float* beta =
 bool linear_few_rows_supported(const GemmDesc& d);
 bool linear_few_rows_norm_supported(const GemmDesc& d, const RowNorm& nrm);
 int linear_few_rows(const GemmDesc& d, const RowNorm* nrm = nullptr, bool dependent = false);
+// the normalisation alone, for at most 64 bf16 rows (row counts the projection kernel does not normalise itself)
+bool norm_few_rows_supported(const void* x, const void* out, int rows, int K, const RowNorm& nrm);
+int norm_few_rows(const void* x, void* out, int rows, int K, const RowNorm& nrm, bool dependent);
 
 // CUDA-core f32 FMA matmul for shapes the TMA path cannot express and for MM_F32.
 // B is [K,N] row-major when b_is_kn, else [N,K].

@@ -935,9 +935,19 @@ static int decode_linear(Gpt* g, const void* x, const RowNorm* nrm, const void* 
     }
     const void* a = x;
     if (nrm) {
-        if (nrm->kind == 2 ? rms_launch(x, nrm->gamma, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)
-                           : ln(x, nrm->gamma, nrm->beta, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)) return 1;
+        if (c.dtype == SPT_BF16 && norm_few_rows_supported(x, g->h, B, K, *nrm)) {
+            ProfScope ps(PROF_LAYERNORM);
+            if (norm_few_rows(x, g->h, B, K, *nrm, true)) return 1;
+        } else if (nrm->kind == 2 ? rms_launch(x, nrm->gamma, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)
+                                  : ln(x, nrm->gamma, nrm->beta, g->h, (size_t)B, (size_t)K, nrm->eps, c.dtype)) return 1;
         a = g->h;
+    }
+    if (c.dtype == SPT_BF16) {
+        GemmDesc d;
+        d.A = a; d.B = w; d.C = out; d.bias = bias; d.R = res;
+        d.M = B; d.N = N; d.K = K; d.lda = K; d.ldb = K; d.ldc = ldo;
+        d.epilogue = epi; d.mode = MM_BF16; d.out_dtype = BF16;
+        if (linear_few_rows_supported(d)) { ProfScope ps(PROF_LINEAR); return linear_few_rows(d, nullptr, true); }
     }
     return linear(g, a, w, bias, res, out, B, K, N, ldo, epi);
 }

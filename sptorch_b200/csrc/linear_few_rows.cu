@@ -326,6 +326,83 @@ int dispatch(const GemmDesc& d, const RowNorm& nrm, bool dependent) {
     }
 }
 
+// LayerNorm / RMSNorm of a handful of rows as a launch of its own (17 .. 64 rows, where normalising inside every CTA of the
+// projection costs more than it saves): one warp per row, the row in registers, nothing else -- the pipelined kernel of
+// rowops.cu spends longer setting up its ring than these rows take.
+template <int VMAX>
+__global__ void __launch_bounds__(256) norm_few_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, int rows, int K, RowNorm nrm) {
+    pdl_release();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    pdl_acquire();
+    if (r >= rows) return;
+    const int nvec = K >> 3;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)r * K);
+    uint4 d[VMAX];
+    float sum = 0.0f, sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VMAX; i++) {
+        const int c = i * 32 + lane;
+        d[i] = c < nvec ? src[c] : make_uint4(0, 0, 0, 0);
+        const uint32_t wd[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float lo = __uint_as_float(wd[j] << 16), hi = __uint_as_float(wd[j] & 0xffff0000u);
+            sum += lo + hi; sq += lo * lo + hi * hi;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { sum += __shfl_xor_sync(0xffffffffu, sum, o); sq += __shfl_xor_sync(0xffffffffu, sq, o); }
+    const bool ln = nrm.kind == 1;
+    float mean = 0.0f, inv;
+    if (ln) {
+        mean = sum / (float)K;
+        float var = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VMAX; i++) {
+            if (i * 32 + lane < nvec) {
+                const uint32_t wd[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float lo = __uint_as_float(wd[j] << 16) - mean, hi = __uint_as_float(wd[j] & 0xffff0000u) - mean;
+                    var += lo * lo + hi * hi;
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+        inv = 1.0f / sqrtf(var / (float)K + nrm.eps);
+    } else {
+        inv = 1.0f / sqrtf(sq / (float)K + nrm.eps);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * K);
+#pragma unroll
+    for (int i = 0; i < VMAX; i++) {
+        const int c = i * 32 + lane;
+        if (c < nvec) {
+            const uint32_t wd[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(nrm.gamma + 8 * c)), g1 = __ldg(reinterpret_cast<const float4*>(nrm.gamma + 8 * c + 4));
+            const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float bb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (ln) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4*>(nrm.beta + 8 * c)), b1 = __ldg(reinterpret_cast<const float4*>(nrm.beta + 8 * c + 4));
+                bb[0] = b0.x; bb[1] = b0.y; bb[2] = b0.z; bb[3] = b0.w; bb[4] = b1.x; bb[5] = b1.y; bb[6] = b1.z; bb[7] = b1.w;
+            }
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float lo = __uint_as_float(wd[j] << 16), hi = __uint_as_float(wd[j] & 0xffff0000u);
+                float y0, y1;
+                if (ln) { y0 = fmaf(gg[2 * j], (lo - mean) * inv, bb[2 * j]); y1 = fmaf(gg[2 * j + 1], (hi - mean) * inv, bb[2 * j + 1]); }
+                else { y0 = lo * inv * gg[2 * j]; y1 = hi * inv * gg[2 * j + 1]; }
+                oh[j] = __floats2bfloat162_rn(y0, y1);
+            }
+            dst[c] = o;
+        }
+    }
+}
+
 }  // namespace
 
 bool linear_few_rows_supported(const GemmDesc& d) {
@@ -341,6 +418,25 @@ bool linear_few_rows_norm_supported(const GemmDesc& d, const RowNorm& nrm) {
     const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     return linear_few_rows_supported(d) && (nrm.kind == 1 || nrm.kind == 2) && nrm.gamma && al16(nrm.gamma) && (nrm.kind == 2 || (nrm.beta && al16(nrm.beta))) &&
            d.M <= kNormMaxRows && norm_smem(d) <= kNormSmemLimit;
+}
+
+bool norm_few_rows_supported(const void* x, const void* out, int rows, int K, const RowNorm& nrm) {
+    const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return rows >= 1 && rows <= 64 && K % 8 == 0 && K >= 8 && K <= 8 * 32 * 16 && (nrm.kind == 1 || nrm.kind == 2) && nrm.gamma && al16(nrm.gamma) &&
+           (nrm.kind == 2 || (nrm.beta && al16(nrm.beta))) && al16(x) && al16(out);
+}
+
+int norm_few_rows(const void* x, void* out, int rows, int K, const RowNorm& nrm, bool dependent) {
+    if (!norm_few_rows_supported(x, out, rows, K, nrm)) return fail("norm_few_rows: unsupported problem");
+    const int v = ceil_div(K / 8, 32);
+    const dim3 grid(ceil_div(rows, 8)), block(256);
+    const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* op = static_cast<__nv_bfloat16*>(out);
+    if (v <= 4) SPT_CUDA(launch_dependent(norm_few_rows_kernel<4>, grid, block, 0, dependent, 1, xp, op, rows, K, nrm));
+    else if (v <= 8) SPT_CUDA(launch_dependent(norm_few_rows_kernel<8>, grid, block, 0, dependent, 1, xp, op, rows, K, nrm));
+    else SPT_CUDA(launch_dependent(norm_few_rows_kernel<16>, grid, block, 0, dependent, 1, xp, op, rows, K, nrm));
+    note_submit();
+    return 0;
 }
 
 int linear_few_rows(const GemmDesc& d, const RowNorm* nrm, bool dependent) {
