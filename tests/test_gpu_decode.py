@@ -55,6 +55,24 @@ def test_decode_over_a_long_cache_matches_full_forward(backend, dtype, tol):
         assert np.abs(step - full[:, t]).max() <= tol * np.abs(full).max(), t
 
 
+@pytest.mark.parametrize("nseq", [20, 40, 64])
+def test_decode_with_many_sequences_matches_full_forward(backend, nseq):
+    """17 .. 64 sequences in bf16: the projections run the weight-streaming kernel with two or four 16-row groups behind a
+    normalisation launch of its own, the attention one CTA of four warps per (sequence, head).  Every appended token's logits
+    equal the row of the full forward at its position."""
+    cfg = dict(vocab=96, d_model=128, n_layer=2, n_head=2, d_ff=256, seq_len=48)
+    params, index = synth.gpt_params(cfg, 13, randomize_affine=True)
+    m = _model(backend, cfg, BF16, nseq, params, index)
+    m.enable_kv_cache(48)
+    ids = synth.randint(19, nseq * 40, 96).reshape(nseq, 40)
+    full = m.forward(ids)
+    m.prefill_kv_cache(ids[:, :32])
+    for t in range(32, 40):
+        step = m.append_and_decode(ids[:, t])
+        assert np.abs(step - full[:, t]).max() <= 3e-2 * np.abs(full).max(), t
+    m.close()
+
+
 # The reference asserts 1e-4 between its two exact-f32 paths.  Here the full forward contracts Q K^T and P V on the tensor
 # cores (TF32 / bf16) while the decode kernel works in f32, so the two differ by the contraction tolerance of the mode.
 @pytest.mark.parametrize("dtype,tol", [(F32, 2e-3), (BF16, 3e-2)])

@@ -111,16 +111,18 @@ def test_qwen_like_gpt2_small_shape_layer_slice(backend, oracle):
     m.close()
 
 
+# 2 sequences: the projections normalise their rows themselves; 20: a normalisation launch of its own in front of them (17 .. 64 rows)
+@pytest.mark.parametrize("nseq", [2, 20])
 @pytest.mark.parametrize("dtype,tol", [(F32, 2e-3), (BF16, 3e-2)])
-def test_qwen_like_incremental_decode_equals_full_forward(backend, dtype, tol):
+def test_qwen_like_incremental_decode_equals_full_forward(backend, dtype, tol, nseq):
     """The reference's self-consistency checks for the cache path (crates/nn/src/lib.rs:3749-3830) on the RoPE model: decoding from
     the cache equals the last row of the full forward, appending token by token equals the full forward's rows.  The cache
     holds rotated keys (project_kv_cache_with_offset, :672-683); the query is rotated to its absolute position (:718-721)."""
     cfg = dict(vocab=64, d_model=64, n_layer=2, n_head=2, d_ff=128, seq_len=32)
     params, index = synth.gpt_params(cfg, 9, arch="qwen", randomize_affine=True)
-    m = _qwen(backend, cfg, dtype, 2, params, index)
+    m = _qwen(backend, cfg, dtype, nseq, params, index)
     m.enable_kv_cache()
-    ids = synth.randint(4, 2 * 24, 64).reshape(2, 24)
+    ids = synth.randint(4, nseq * 24, 64).reshape(nseq, 24)
     full = m.forward(ids)
     scale = np.abs(full).max()
     pre = m.prefill_kv_cache(ids[:, :8])
