@@ -19,8 +19,10 @@
 //               because the 16-per-clock exponential unit would otherwise be the limit), and writes P as bf16
 //               back into the TMEM columns the scores came from
 // O accumulates in TMEM over the key tiles of an item and is rescaled in place only when a row maximum grows by
-// more than 2^8 (lazy rescaling).  TMEM: S/P of tile 0 at columns 0..127, of tile 1 at 128..255, O_0 at 256,
-// O_1 at 384 (512 columns, one CTA per SM).
+// more than 2^8 (lazy rescaling).  TMEM, head size 128: S/P of tile 0 at columns 0..127, of tile 1 at 128..255, O_0 at 256,
+// O_1 at 384 (512 columns, one CTA per SM).  Head size 64 (accumulators of 64 columns): THREE score buffers at 0 / 128 / 256
+// that the Q K^T products take in turn, O_0 at 384, O_1 at 448 -- a tile's next scores are ready before its softmax warps
+// have finished the current ones.
 // Algorithmic work per (sequence, head): 2 * T(T+1) * hd FLOP; HBM traffic: Q, K, V read once per query tile
 // (K/V re-reads hit L2 thanks to the work schedule below), O written once.
 #include "gemm.h"
@@ -158,13 +160,21 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t q_free = q_full + 8;             // 1
     const uint32_t kv_full = q_free + 8;            // NS
     const uint32_t kv_empty = kv_full + 8 * NS;     // NS
-    const uint32_t s_full = kv_empty + 8 * NS;      // 2 (per query tile)
-    const uint32_t p_full = s_full + 16;            // 2
-    const uint32_t pv_done = p_full + 16;           // 2
+    // Head size 64 leaves 128 TMEM columns free beside two score tiles and two 64-column accumulators: a THIRD score buffer.  The
+    // three buffers go round robin to the Q K^T products in issue order (tile 0 / tile 1 alternating), so a query tile's next
+    // scores are computed while its softmax warps are still on the current ones, and the softmax never waits for the tensor core
+    // (ROT).  Head size 128 fills the 512 columns with two score tiles and two accumulators: buffer = query tile, as before.
+    constexpr bool ROT = HD == 64;
+    constexpr int NSB = ROT ? 3 : 2;                // score buffers
+    constexpr uint32_t O_COL = ROT ? 384 : 256;     // first accumulator column
+    constexpr uint32_t O_STRIDE = ROT ? 64 : 128;
+    const uint32_t s_full = kv_empty + 8 * NS;      // NSB (per score buffer)
+    const uint32_t p_full = s_full + 8 * 3;         // NSB
+    const uint32_t pv_done = p_full + 8 * 3;        // 2 (per query tile)
     const uint32_t o_free = pv_done + 16;           // 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBars + 240);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBars + 244);
-    static_assert(8 * (2 + 2 * NS + 8) <= 240, "barrier block overflows");
+    static_assert(8 * (2 + 2 * NS + 10) <= 240, "barrier block overflows");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = p.B * p.H;
@@ -177,9 +187,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(q_free, 1);
         for (int s = 0; s < NS; s++) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_empty + 8 * s, 1); }
-        for (int g = 0; g < 2; g++) {
+        for (int g = 0; g < 3; g++) {
             mbar_init(s_full + 8 * g, 1);
             mbar_init(p_full + 8 * g, 4);           // one arrival per softmax warp of the tile
+        }
+        for (int g = 0; g < 2; g++) {
             mbar_init(pv_done + 8 * g, 1);
             mbar_init(o_free + 8 * g, 4);
         }
@@ -259,10 +271,82 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const uint64_t bdesc = make_mnmajor_sw128_desc(base + L::kKV + (gg % NS) * L::kStageBytes + L::kKBytes, kKvTile * 128);
 #pragma unroll
             for (int k = 0; k < kKvTile / 16; k++)
-                mma_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
+                mma_ts(tmem_base + O_COL + t * O_STRIDE, tmem_base + t * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
             mma_commit(pv_done + 8 * t);
         };
         auto kv_ready = [&](uint32_t gg) -> bool { return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait); };
+        if constexpr (ROT) {
+            // The products of an item in issue order ("entries"): key tile by key tile, query tile 0 before query tile 1 where both
+            // still have that key tile.  Scores run up to two entries ahead of the P V product that is issued next; score number n
+            // (counted over the whole kernel) lives in buffer n % 3, which P V number n - 3 -- issued earlier by this thread, and
+            // the tensor pipe runs one thread's MMAs in order -- has finished reading.
+            uint32_t G = 0;                     // scores issued in earlier items
+            auto issue_s3 = [&](int t, uint32_t gg, uint32_t n) {
+                const uint32_t buf = n % 3;
+                const uint32_t kaddr = base + L::kKV + (gg % NS) * L::kStageBytes;
+#pragma unroll
+                for (int kb = 0; kb < KB; kb++) {
+                    const uint64_t adesc = make_kmajor_sw128_desc(base + L::kQ + t * L::kQTileBytes + kb * (kQTile * 128));
+                    const uint64_t bdesc = make_kmajor_sw128_desc(kaddr + kb * (kKvTile * 128));
+#pragma unroll
+                    for (int k = 0; k < 4; k++) mma_ss<false>(tmem_base + buf * 128, adesc + 2 * k, bdesc + 2 * k, IDESC_S, (kb | k) != 0 ? 1u : 0u);
+                }
+                mma_commit(s_full + 8 * buf);
+            };
+            auto issue_pv3 = [&](int t, uint32_t gg, uint32_t n, bool accumulate) {
+                const uint32_t buf = n % 3;
+                const uint64_t bdesc = make_mnmajor_sw128_desc(base + L::kKV + (gg % NS) * L::kStageBytes + L::kKBytes, kKvTile * 128);
+#pragma unroll
+                for (int k = 0; k < kKvTile / 16; k++)
+                    mma_ts(tmem_base + O_COL + t * O_STRIDE, tmem_base + buf * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
+                mma_commit(pv_done + 8 * t);
+            };
+            for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
+                const int item_next = fetch(k + 1);
+                int q0, bb, hh, n0, n1;
+                decode(item, q0, bb, hh, n0, n1);
+                item = item_next;
+                const int E = n0 + n1, nmin = min(n0, n1), t_long = n1 > n0 ? 1 : 0;
+                auto entry = [&](int e, int& t, int& j) {
+                    if (e < 2 * nmin) { j = e >> 1; t = e & 1; } else { j = nmin + (e - 2 * nmin); t = t_long; }
+                };
+                ok = mbar_wait(q_full, it & 1, abort_flag, p.status, kErrMmaWait);
+                if (!ok) break;
+                int issued = 0, kv_seen = -1;
+                for (int e = 0; e < E && ok; e++) {
+                    while (issued < min(E, e + 3)) {
+                        int ts, js;
+                        entry(issued, ts, js);
+                        if (js > kv_seen) { ok = kv_ready(g + js); kv_seen = js; if (!ok) break; }
+                        tc_fence_after();
+                        if (elect_one_sync()) {
+                            issue_s3(ts, g + js, G + issued);
+                            if (issued == E - 1) mma_commit(q_free);            // the item's last read of Q
+                        }
+                        __syncwarp();
+                        issued++;
+                    }
+                    if (!ok) break;
+                    int t, j;
+                    entry(e, t, j);
+                    const uint32_t n = G + e, buf = n % 3;
+                    ok = mbar_wait(p_full + 8 * buf, (n / 3) & 1, abort_flag, p.status, kErrMmaWait);
+                    // the item's first product overwrites the accumulator: the previous item's output must have been read
+                    if (ok && j == 0) ok = mbar_wait(o_free + 8 * t, (it & 1) ^ 1, abort_flag, p.status, kErrMmaWait);
+                    if (!ok) break;
+                    tc_fence_after();
+                    int tn = 0, jn = -1;
+                    if (e + 1 < E) entry(e + 1, tn, jn);
+                    if (elect_one_sync()) {
+                        issue_pv3(t, g + j, n, j > 0);
+                        if (jn != j) mma_commit(kv_empty + 8 * ((g + j) % NS));     // every MMA that reads this stage has been issued
+                    }
+                    __syncwarp();
+                }
+                g += max(n0, n1);
+                G += E;
+            }
+        } else
         for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
             const int item_next = fetch(k + 1);
             int q0, bb, hh, n0, n1;
@@ -311,10 +395,10 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int quarter = warp & 3;                            // TMEM lane quarter a warp may access = warp index % 4
         const int r = quarter * 32 + lane;                       // row inside the tile = TMEM lane
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_off + t * 128;          // scores, and P over their first 64 columns
-        const uint32_t o_addr = tmem_base + lane_off + 256 + t * 128;
+        const uint32_t o_addr = tmem_base + lane_off + O_COL + t * O_STRIDE;
         bool ok = true;
         uint32_t step = 0, it = 0;                               // softmax steps of this tile so far; items so far
+        uint32_t G = 0;                                          // ROT: scores of earlier items (both tiles), as the MMA warp counts them
         for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
             const int item_next = fetch(k + 1);
             int q0, bb, hh, n0, n1;
@@ -324,7 +408,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const int qrow = q0 + t * kQTile + r;
             float m = -INFINITY, l = 0.0f;
             for (int j = 0; j < n_kv && ok; j++, step++) {
-                ok = mbar_wait(s_full + 8 * t, step & 1, abort_flag, p.status, kErrEpilogueWait);
+                // ROT: this step's scores are number G + (entries of the item before (t, j)) of the kernel, in buffer number % 3
+                const uint32_t sn = ROT ? G + (uint32_t)(min(j, n0) + min(j, n1) + ((t == 1 && j < n0) ? 1 : 0)) : step;
+                const uint32_t sbuf = ROT ? sn % 3 : (uint32_t)t;
+                const uint32_t s_addr = tmem_base + lane_off + sbuf * 128;          // scores, and P over their first 64 columns
+                ok = mbar_wait(s_full + 8 * sbuf, (ROT ? sn / 3 : sn) & 1, abort_flag, p.status, kErrEpilogueWait);
                 if (!ok) break;
                 tc_fence_after();
                 const bool diag = (j == n_kv - 1);               // the tile on the diagonal: keys q .. q+127 of rows q .. q+127
@@ -425,9 +513,10 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full + 8 * t);
+                if (lane == 0) mbar_arrive(p_full + 8 * sbuf);
                 l += (sum_a.x + sum_a.y) + (sum_b.x + sum_b.y);
             }
+            G += (uint32_t)(n0 + n1);
             if (!ok) break;
             if (n_kv > 0) {
                 const float inv = 1.0f / l;
