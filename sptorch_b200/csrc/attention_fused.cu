@@ -142,7 +142,7 @@ struct AttnSmem {
 // Persistent kernel: CTA c works through column c of a schedule built on the host (attention_schedule below), and all
 // roles run straight through item boundaries (barrier phases are driven by running counters), so the loads and the
 // first Q K^T of the next item are in flight while the current one drains.
-template <int HD, int NPOLY>
+template <int HD, int NPOLY, bool ROTP = true>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -164,17 +164,21 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     // three buffers go round robin to the Q K^T products in issue order (tile 0 / tile 1 alternating), so a query tile's next
     // scores are computed while its softmax warps are still on the current ones, and the softmax never waits for the tensor core
     // (ROT).  Head size 128 fills the 512 columns with two score tiles and two accumulators: buffer = query tile, as before.
-    constexpr bool ROT = HD == 64;
+    constexpr bool ROT = HD == 64 && ROTP;
     constexpr int NSB = ROT ? 3 : 2;                // score buffers
     constexpr uint32_t O_COL = ROT ? 384 : 256;     // first accumulator column
     constexpr uint32_t O_STRIDE = ROT ? 64 : 128;
     const uint32_t s_full = kv_empty + 8 * NS;      // NSB (per score buffer)
     const uint32_t p_full = s_full + 8 * 3;         // NSB
-    const uint32_t pv_done = p_full + 8 * 3;        // 2 (per query tile)
-    const uint32_t o_free = pv_done + 16;           // 2
+    // P V products done: two barriers per query tile, taken in turn by the tile's steps (index step & 1, phase step >> 1).  With
+    // rotating score buffers a tile's softmax can finish step j before P V of step j - 1 has completed, so its wait for the
+    // product of step j on a single barrier would be two phases ahead -- which a parity wait cannot tell from none; on the
+    // barrier of its own parity class it is never more than one phase ahead (the product of step j + 2 needs this thread's P).
+    const uint32_t pv_done = p_full + 8 * 3;        // 4: [query tile][step & 1]
+    const uint32_t o_free = pv_done + 32;           // 2
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::kBars + 240);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kBars + 244);
-    static_assert(8 * (2 + 2 * NS + 10) <= 240, "barrier block overflows");
+    static_assert(8 * (2 + 2 * NS + 12) <= 240, "barrier block overflows");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int BH = p.B * p.H;
@@ -191,10 +195,8 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(s_full + 8 * g, 1);
             mbar_init(p_full + 8 * g, 4);           // one arrival per softmax warp of the tile
         }
-        for (int g = 0; g < 2; g++) {
-            mbar_init(pv_done + 8 * g, 1);
-            mbar_init(o_free + 8 * g, 4);
-        }
+        for (int g = 0; g < 4; g++) mbar_init(pv_done + 8 * g, 1);
+        for (int g = 0; g < 2; g++) mbar_init(o_free + 8 * g, 4);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -267,12 +269,12 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mma_commit(s_full + 8 * t);
         };
         // O_t (+)= P_t V with the value tile of ring position gg; P is read from the TMEM columns of S_t
-        auto issue_pv = [&](int t, uint32_t gg, bool accumulate) {
+        auto issue_pv = [&](int t, uint32_t gg, bool accumulate, uint32_t pvidx) {      // pvidx: which product of this tile (over the whole kernel)
             const uint64_t bdesc = make_mnmajor_sw128_desc(base + L::kKV + (gg % NS) * L::kStageBytes + L::kKBytes, kKvTile * 128);
 #pragma unroll
             for (int k = 0; k < kKvTile / 16; k++)
                 mma_ts(tmem_base + O_COL + t * O_STRIDE, tmem_base + t * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
-            mma_commit(pv_done + 8 * t);
+            mma_commit(pv_done + 8 * (2 * t + (pvidx & 1)));
         };
         auto kv_ready = [&](uint32_t gg) -> bool { return mbar_wait(kv_full + 8 * (gg % NS), (gg / NS) & 1, abort_flag, p.status, kErrMmaWait); };
         if constexpr (ROT) {
@@ -293,13 +295,13 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 mma_commit(s_full + 8 * buf);
             };
-            auto issue_pv3 = [&](int t, uint32_t gg, uint32_t n, bool accumulate) {
+            auto issue_pv3 = [&](int t, uint32_t gg, uint32_t n, bool accumulate, uint32_t pvidx) {
                 const uint32_t buf = n % 3;
                 const uint64_t bdesc = make_mnmajor_sw128_desc(base + L::kKV + (gg % NS) * L::kStageBytes + L::kKBytes, kKvTile * 128);
 #pragma unroll
                 for (int k = 0; k < kKvTile / 16; k++)
                     mma_ts(tmem_base + O_COL + t * O_STRIDE, tmem_base + buf * 128 + 8 * k, bdesc + (uint64_t)(128 * k), IDESC_O, (accumulate || k != 0) ? 1u : 0u);
-                mma_commit(pv_done + 8 * t);
+                mma_commit(pv_done + 8 * (2 * t + (pvidx & 1)));
             };
             for (int k = 0, item = fetch(0); item >= 0 && ok; k++, it++) {
                 const int item_next = fetch(k + 1);
@@ -338,10 +340,11 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     int tn = 0, jn = -1;
                     if (e + 1 < E) entry(e + 1, tn, jn);
                     if (elect_one_sync()) {
-                        issue_pv3(t, g + j, n, j > 0);
+                        issue_pv3(t, g + j, n, j > 0, steps[t]);
                         if (jn != j) mma_commit(kv_empty + 8 * ((g + j) % NS));     // every MMA that reads this stage has been issued
                     }
                     __syncwarp();
+                    steps[t]++;
                 }
                 g += max(n0, n1);
                 G += E;
@@ -375,7 +378,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     steps[t]++;
                     tc_fence_after();
                     if (elect_one_sync()) {
-                        issue_pv(t, g, j > 0);
+                        issue_pv(t, g, j > 0, steps[t] - 1);
                         // the next scores of this tile go into the columns P was just read from: the tensor pipe runs the
                         // MMAs of one thread in order, so the product above has consumed P before these overwrite it
                         if (j + 1 < nt[t]) {
@@ -454,7 +457,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                         sum_a.x *= alpha; sum_a.y *= alpha; sum_b.x *= alpha; sum_b.y *= alpha;
                         if (j > 0) {
                             // every product accumulated so far is in place (the commit of step - 1; the next one needs this thread's P)
-                            if (!mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
+                            if (!mbar_wait(pv_done + 8 * (2 * t + ((step - 1) & 1)), ((step - 1) >> 1) & 1, abort_flag, p.status, kErrEpilogueWait)) return false;
                             tc_fence_after();
 #pragma unroll
                             for (int cc = 0; cc < HD / 32; cc++) {
@@ -520,7 +523,7 @@ attn_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (!ok) break;
             if (n_kv > 0) {
                 const float inv = 1.0f / l;
-                ok = mbar_wait(pv_done + 8 * t, (step - 1) & 1, abort_flag, p.status, kErrEpilogueWait);     // the item's last product
+                ok = mbar_wait(pv_done + 8 * (2 * t + ((step - 1) & 1)), ((step - 1) >> 1) & 1, abort_flag, p.status, kErrEpilogueWait);     // the item's last product
                 if (!ok) break;
                 tc_fence_after();
                 __nv_bfloat16* orow = p.out + ((long long)bb * p.T + qrow) * p.ld_out + (long long)hh * HD;
@@ -693,7 +696,9 @@ int attention_fused(const void* q, const void* k, const void* v, void* out, int 
     const int np = attn_npoly(hd);
     int lrc;
     if (hd == 64) {
-        if (np <= 0) lrc = launch(attn_fused_kernel<64, 0>, AttnSmem<64>::kTotal);
+        static const bool rot_off = getenv("SPTORCH_B200_ATTN_ROT") && atoi(getenv("SPTORCH_B200_ATTN_ROT")) == 0;
+        if (rot_off) lrc = launch(attn_fused_kernel<64, 0, false>, AttnSmem<64>::kTotal);
+        else if (np <= 0) lrc = launch(attn_fused_kernel<64, 0>, AttnSmem<64>::kTotal);
         else if (np <= 4) lrc = launch(attn_fused_kernel<64, 4>, AttnSmem<64>::kTotal);
         else if (np <= 5) lrc = launch(attn_fused_kernel<64, 5>, AttnSmem<64>::kTotal);
         else if (np <= 6) lrc = launch(attn_fused_kernel<64, 6>, AttnSmem<64>::kTotal);
