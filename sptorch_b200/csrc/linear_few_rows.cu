@@ -8,7 +8,10 @@
 // CTAs, every warp takes every eighth 32-element slice of K, issues its weight loads (16 bytes per lane, up to eight slices
 // in flight) before it touches the activations, and multiplies with mma.sync m16n8k16 -- the tensor unit is idle either way,
 // the warp-level instruction needs no allocation and no barrier.  The eight warps' partial sums meet in shared memory and are
-// added in warp order (the result does not depend on scheduling).
+// added in warp order (the result does not depend on scheduling).  Where the weight rows alone do not cover the SMs (the
+// projections back to the model width: N = d, K up to 4 d) a cluster of 2 or 4 CTAs splits K and the CTAs' sums meet in the
+// cluster's first CTA through distributed shared memory, again in a fixed order.  Up to 16 rows the LayerNorm / RMSNorm in front
+// of a projection is applied to the rows on the fly; 17 .. 64 rows take norm_few_rows_kernel below as a launch of its own.
 //
 // k order inside a 32-element slice: lane t of a quad loads the 8 consecutive elements 8t .. 8t+7 of a weight row and of an
 // activation row; the first mma takes elements 0..3 of every lane as its k = {2t, 2t+1, 2t+8, 2t+9}, the second elements 4..7.
