@@ -418,7 +418,6 @@ struct SmReserveScope {
     ~SmReserveScope() { rt().sm_reserve = saved; }
 };
 static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* logits, const HeadReduce* hr) {
-    SmReserveScope reserve;
     const sptorch_gpt_config& c = g->c;
     const int d = c.d_model, M = B * T, dl = g->d_loc, Fl = g->F_loc, dt = c.dtype;
     const bool lead = c.tp_rank == 0;
@@ -434,6 +433,8 @@ static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* log
     void* xb[2] = {rows(g->x, 0, d), rows(g->x, 1, d)};
     void* yb[2] = {rows(g->y, 0, d), rows(g->y, 1, d)};
     bool pending[2] = {false, false};             // a reduction of this half is in flight on the second stream
+    {
+    SmReserveScope reserve;                       // the blocks only: the final LayerNorm and the LM head run beside no collective
     auto reduce_async = [&](int ch) -> int {
         SPT_CUDA(cudaEventRecord(g->ev_partial[ch], cs));
         SPT_CUDA(cudaStreamWaitEvent(ms, g->ev_partial[ch], 0));
@@ -467,6 +468,7 @@ static int forward_tp_pipelined(Gpt* g, const void* ids, int B, int T, void* log
         }
     }
     if (wait_reduced(0) || wait_reduced(1)) return 1;
+    }
     // two swaps per layer and half: both halves are back in the same base buffer, contiguous
     void* x = xb[0];
     if (ln(x, g->lnfg, g->lnfb, g->h, (size_t)M, (size_t)d, c.eps, dt)) return 1;
