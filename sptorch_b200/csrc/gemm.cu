@@ -667,7 +667,8 @@ static int max_pairs() {
     return n;
 }
 
-// 3 (default): CTA pairs where they measured faster -- TF32 problems, and bf16 problems with K >= 1536 -- from 2048 rows up;
+// 3 (default): CTA pairs where they measured faster -- TF32 problems, bf16 problems with K >= 1536, and bf16 problems with a plain
+// epilogue -- from 2048 rows up;
 // 0: one-CTA tiles only; 1: CTA pairs wherever they apply; 2: CTA pairs for TF32 problems only.  Measured on B200 (median of 10,
 // L2 flushed, one CTA vs pairs): bf16 65536 x 3072 -> 768 0.223 vs 0.203 ms, 16384 x 4096 -> 4096 0.368 vs 0.343 ms (1603 TFLOP/s),
 // 16384 x 3072 -> 768 0.072 vs 0.064 ms, but 65536 x 768 -> 3072 0.244 vs 0.244 ms and 4096 x 768 -> 768 0.0164 vs 0.0174 ms (a
@@ -706,7 +707,12 @@ int gemm_plan(const GemmDesc& d, GemmPlan* plan) {
     // wide problems run on CTA pairs (each SM then loads half of the B tile); the triangular attention products do not
     int pairs = 0;
     const int pm = g_pair_mode.load();
-    const bool pair_auto = pm == 3 && d.M >= 2048 && d.nb1 * d.nb2 == 1 && (d.mode == MM_TF32 || d.K >= 1536);
+    // ... and bf16 problems whose epilogue has nothing to add (no bias, no residual, alpha 1): with the plain epilogue the pair kernel
+    // is ahead at K = 768 too (65536 x 768 -> 2304: 0.173 vs 0.156 ms; 32768 x 768 -> 50304: 1.778 vs 1.650 ms), while with a
+    // residual it is behind (65536 x 768 -> 768 + residual: 0.098 vs 0.102 ms).  SPTORCH_B200_GEMM_PAIR_PLAIN=0 drops this clause.
+    static const bool pair_plain = !(getenv("SPTORCH_B200_GEMM_PAIR_PLAIN") && atoi(getenv("SPTORCH_B200_GEMM_PAIR_PLAIN")) == 0);
+    const bool plain = pair_plain && !d.bias && !d.R && d.alpha == 1.0f && d.epilogue == EPI_NONE;
+    const bool pair_auto = pm == 3 && d.M >= 2048 && d.nb1 * d.nb2 == 1 && (d.mode == MM_TF32 || d.K >= 1536 || plain);
     if (!d.norm_axis && !d.reduce && (pm == 1 || (pm == 2 && d.mode == MM_TF32) || pair_auto) && bn == 256 && d.M > BM && !d.causal_lower && !d.causal_k) pairs = std::min(max_pairs(), compute_sms() / 2);
     plan->pair = pairs > 0;
     plan->tiles_m = ceil_div(d.M, plan->pair ? 2 * BM : BM);
