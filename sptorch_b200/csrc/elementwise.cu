@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kThreads) unary_bf16_vec(const uint4* __restri
             bf16x8 x = *reinterpret_cast<bf16x8*>(&v[u]);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                float2 f = __bfloat1622float2(x.v[j]);
+                float2 f = bf16x2_to_float2(x.v[j]);
                 x.v[j] = __floats2bfloat162_rn(op(f.x), op(f.y));
             }
             __stcs(out + i + u * stride, *reinterpret_cast<uint4*>(&x));
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads) unary_bf16_vec(const uint4* __restri
         bf16x8 x = *reinterpret_cast<bf16x8*>(&v);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            float2 f = __bfloat1622float2(x.v[j]);
+            float2 f = bf16x2_to_float2(x.v[j]);
             x.v[j] = __floats2bfloat162_rn(op(f.x), op(f.y));
         }
         __stcs(out + i, *reinterpret_cast<uint4*>(&x));
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kThreads) binary_bf16_vec(const uint4* __restr
         bf16x8 x = *reinterpret_cast<bf16x8*>(&va), y = *reinterpret_cast<bf16x8*>(&vb);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            float2 f = __bfloat1622float2(x.v[j]), g = __bfloat1622float2(y.v[j]);
+            float2 f = bf16x2_to_float2(x.v[j]), g = bf16x2_to_float2(y.v[j]);
             x.v[j] = __floats2bfloat162_rn(op(f.x, g.x), op(f.y, g.y));
         }
         __stcs(out + i, *reinterpret_cast<uint4*>(&x));

@@ -401,7 +401,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         for (int k = 0; k < NV; k++) {
                             const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rcur[k]);
 #pragma unroll
-                            for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[8 * k + 2 * q] *= g2.x; f[8 * k + 2 * q + 1] *= g2.y; }
+                            for (int q = 0; q < 4; q++) {
+                                const uint32_t rw = *reinterpret_cast<const uint32_t*>(&rh[q]);
+                                const float2 pr2 = __fmul2_rn(make_float2(f[8 * k + 2 * q], f[8 * k + 2 * q + 1]),
+                                                              make_float2(__uint_as_float(rw << 16), __uint_as_float(rw & 0xffff0000u)));
+                                f[8 * k + 2 * q] = pr2.x; f[8 * k + 2 * q + 1] = pr2.y;
+                            }
                         }
                     } else {
 #pragma unroll
@@ -416,13 +421,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                         for (int k = 0; k < NV; k++) {
                             const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rcur[k]);
 #pragma unroll
-                            for (int q = 0; q < 4; q++) { float2 g2 = __bfloat1622float2(rh[q]); f[8 * k + 2 * q] += g2.x; f[8 * k + 2 * q + 1] += g2.y; }
+                            for (int q = 0; q < 4; q++) {
+                                // bf16 pair -> f32 pair is a shift and a mask; one packed add per pair
+                                const uint32_t rw = *reinterpret_cast<const uint32_t*>(&rh[q]);
+                                const float2 sum2 = __fadd2_rn(make_float2(f[8 * k + 2 * q], f[8 * k + 2 * q + 1]),
+                                                               make_float2(__uint_as_float(rw << 16), __uint_as_float(rw & 0xffff0000u)));
+                                f[8 * k + 2 * q] = sum2.x; f[8 * k + 2 * q + 1] = sum2.y;
+                            }
                         }
                     } else {
 #pragma unroll
                         for (int k = 0; k < NV; k++) {
-                            f[4 * k] += __uint_as_float(rcur[k].x); f[4 * k + 1] += __uint_as_float(rcur[k].y);
-                            f[4 * k + 2] += __uint_as_float(rcur[k].z); f[4 * k + 3] += __uint_as_float(rcur[k].w);
+                            const float2 lo2 = __fadd2_rn(make_float2(f[4 * k], f[4 * k + 1]), make_float2(__uint_as_float(rcur[k].x), __uint_as_float(rcur[k].y)));
+                            const float2 hi2 = __fadd2_rn(make_float2(f[4 * k + 2], f[4 * k + 3]), make_float2(__uint_as_float(rcur[k].z), __uint_as_float(rcur[k].w)));
+                            f[4 * k] = lo2.x; f[4 * k + 1] = lo2.y; f[4 * k + 2] = hi2.x; f[4 * k + 3] = hi2.y;
                         }
                     }
                 }

@@ -40,7 +40,7 @@ template <> struct Vec<__nv_bfloat16> {
         Vec r;
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
 #pragma unroll
-        for (int j = 0; j < 4; j++) { float2 f = __bfloat1622float2(h[j]); r.v[2 * j] = f.x; r.v[2 * j + 1] = f.y; }
+        for (int j = 0; j < 4; j++) { float2 f = bf16x2_to_float2(h[j]); r.v[2 * j] = f.x; r.v[2 * j + 1] = f.y; }
         return r;
     }
     __device__ static Vec load(const __nv_bfloat16* p) { return unpack(__ldcs(reinterpret_cast<const uint4*>(p))); }
